@@ -1,0 +1,204 @@
+// Internal declarations shared by the translation units of libeb200.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <atomic>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/eb200.h"
+
+namespace eb200 {
+
+// ---- error reporting --------------------------------------------------------
+int set_error(int status, const char* fmt, ...);
+void clear_error();
+
+#define EB_CHECK_CUDA(expr)                                                        \
+    do {                                                                           \
+        cudaError_t _e = (expr);                                                   \
+        if (_e != cudaSuccess) {                                                   \
+            return ::eb200::set_error(                                             \
+                _e == cudaErrorMemoryAllocation ? EB200_ERR_OOM : EB200_ERR_CUDA,  \
+                "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__,  \
+                __LINE__);                                                         \
+        }                                                                          \
+    } while (0)
+
+#define EB_REQUIRE(cond, status, ...)                    \
+    do {                                                 \
+        if (!(cond)) return ::eb200::set_error(status, __VA_ARGS__); \
+    } while (0)
+
+extern std::atomic<int64_t> g_launch_count;
+inline void count_launch(int n = 1) { g_launch_count.fetch_add(n, std::memory_order_relaxed); }
+
+// ---- device-side parameter block ---------------------------------------------
+// What every generic kernel receives by value: the collapsed iteration space,
+// operand addressing, bound conditions and the map program.
+constexpr int KMAX_DIMS = EB200_MAX_DIMS;
+constexpr int KMAX_IN = EB200_MAX_INPUTS;
+constexpr int KMAX_BOUNDS = 8;   // total over all operands
+constexpr int KMAX_INSNS = EB200_MAX_INSNS;
+constexpr int KMAX_CONSTS = 32;
+constexpr int KSTACK = 16;       // evaluation stack depth of the interpreter
+
+struct KOperand {
+    char* ptr;                 // set at launch
+    long long offset;          // elements
+    long long strides[KMAX_DIMS];
+    int dtype;
+    int bound_begin;
+    int n_bounds;
+    float pad;
+};
+
+struct KBound {
+    long long coef[KMAX_DIMS];
+    long long c, lo, hi;
+};
+
+struct KInsn {
+    short op;
+    short arg;
+    float imm;
+};
+
+struct KParams {
+    int ndim;
+    int n_in;
+    int n_insns;
+    int n_consts;
+    long long shape[KMAX_DIMS];
+    long long total;           // product of shape
+    // reduce bookkeeping (collapsed coordinates)
+    int raxis;                 // reduce dim, -1 if none
+    int rop;
+    long long rlen;            // shape[raxis]
+    long long kept;            // total / rlen
+    int splits;                // partial reductions over the reduce dim
+    int vec;                   // 4 = 128-bit path legal, 1 = scalar
+    long long chunk;           // reduce-dim elements per split
+    KOperand in[KMAX_IN];
+    KOperand out;
+    KBound bounds[KMAX_BOUNDS];
+    KInsn prog[KMAX_INSNS];
+    float consts[KMAX_CONSTS];
+};
+
+// ---- host objects ------------------------------------------------------------
+struct Device {
+    int index = 0;
+    cudaStream_t stream = nullptr;
+    cudaMemPool_t pool = nullptr;
+    cudaEvent_t ev_begin = nullptr, ev_end = nullptr;
+    cudaDeviceProp prop{};
+    std::atomic<int64_t> in_use{0}, peak{0}, n_allocs{0};
+};
+
+// Reference-counted device storage; several buffer handles may share one
+// storage until one of them is written (copy-on-write clone).
+struct Storage {
+    Device* dev = nullptr;
+    void* ptr = nullptr;
+    size_t bytes = 0;
+    ~Storage();
+};
+
+int storage_alloc(Device* dev, size_t bytes, bool zero, std::shared_ptr<Storage>* out);
+
+}  // namespace eb200
+
+struct eb200_device : eb200::Device {};
+
+struct eb200_buffer {
+    std::atomic<int> refs{1};
+    eb200::Device* dev = nullptr;
+    size_t bytes = 0;
+    std::shared_ptr<eb200::Storage> storage;
+};
+
+namespace eb200 {
+
+// Makes `buf` the only owner of its storage.  `keep_contents` copies the old
+// bytes device-to-device; otherwise the new storage is left uninitialised.
+int buffer_unshare(eb200_buffer* buf, bool keep_contents);
+
+// ---- kernel plans -------------------------------------------------------------
+enum Impl {
+    IMPL_EW = 0,          // fused elementwise chain, 128-bit vectorised
+    IMPL_REDUCE_INNER,    // reduce over the contiguous innermost dim (row reduce)
+    IMPL_REDUCE_OUTER,    // reduce over a strided dim (column reduce) + generic fallback
+    IMPL_TRANSPOSE,       // batched 2-D transpose through shared memory
+    IMPL_SCATTER,         // zero fill + red.global.add
+    IMPL_SGD,             // p - lr*g
+    IMPL_GEMM_SIMT,       // dense contraction, fp32 FFMA tiles (exact-f32 fallback)
+    IMPL_GEMM_TC,         // dense contraction, tcgen05 TF32 / 3xTF32
+};
+
+struct GemmShape {
+    // C[b][m][n] = sum_k A[b][m][k] * B[b][k][n]; element strides
+    long long batch = 1, m = 0, n = 0, k = 0;
+    long long a_sb = 0, a_sm = 0, a_sk = 0, a_off = 0;
+    long long b_sb = 0, b_sk = 0, b_sn = 0, b_off = 0;
+    long long c_sb = 0, c_sm = 0, c_sn = 0, c_off = 0;
+    int a_input = 0, b_input = 1;  // which kernel input is A / B
+    int mode = EB200_GEMM_3XTF32;
+};
+
+struct TransposeShape {
+    // out[b][r][c] (contiguous) = in[b*sb + c*sc + r]  (input contiguous along r)
+    long long batch = 1, rows = 0, cols = 0;
+    long long in_sb = 0, in_sc = 0, in_off = 0;
+    long long out_sb = 0, out_off = 0;
+    int esize = 4;
+};
+
+struct Plan {
+    Impl impl = IMPL_EW;
+    KParams p{};
+    int chain = -1;           // index into the compiled-functor table, -1 = interpreter
+    int threads_per_row = 0;  // REDUCE_INNER: 1, 32 or 256
+    GemmShape gemm;
+    TransposeShape tr;
+    int64_t scratch_bytes = 0;
+    int64_t algo_bytes = 0, algo_flops = 0;
+    int launches = 1;
+    float scalar = 0.f;
+    int n_inputs = 0;
+    int in_dtype[KMAX_IN] = {0};
+    int64_t in_numel[KMAX_IN] = {0};
+    int out_dtype = 0;
+    int64_t out_numel = 0;
+    char name[64] = {0};
+};
+
+// plan.cpp: validate + normalise + classify.  Pure host logic, no CUDA calls.
+int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan);
+
+// chains: compiled functors for known map programs (chains.cu)
+int find_chain(const KInsn* prog, int n_insns, float* consts, int* n_consts);
+int chain_count();
+const char* chain_name(int chain);
+
+// launchers (one per .cu)
+int launch_ew(Device* dev, const Plan& plan, const KParams& p);
+int launch_reduce(Device* dev, const Plan& plan, const KParams& p, void* scratch);
+int launch_transpose(Device* dev, const Plan& plan, const void* in, void* out);
+int launch_scatter(Device* dev, const Plan& plan, const KParams& p);
+int launch_sgd(Device* dev, const Plan& plan, const float* p, const float* g, float* out, long long n);
+int launch_gemm_simt(Device* dev, const Plan& plan, const float* a, const float* b, float* c);
+
+}  // namespace eb200
+
+struct eb200_kernel {
+    std::atomic<int> refs{1};
+    eb200::Device* dev = nullptr;
+    eb200::Plan plan;
+    std::shared_ptr<eb200::Storage> scratch;
+};

@@ -1,0 +1,93 @@
+// gemm_simt: dense contraction on the FP32 pipes.
+//
+// The reference has no f32 matmul op: `C = A.B` is spelled
+// unsqueeze -> expand -> mul -> sum(axis=K) (crates/nn/src/functional/linear.rs:27-56,
+// examples/matmul_demo.rs:43-60) and lowers to an R_ kernel whose body is
+// `acc = acc + A[..] * B[..]` in a sequential triple loop.  The classifier
+// recognises that pattern from operand strides (plan.cpp) and hands it here or
+// to the tensor-core kernel.  This kernel keeps full f32 products and adds
+// each output's terms in increasing k, like the reference loop, so it is the
+// f32-faithful path for shapes or strides the tensor-core kernel does not take.
+// 64x64 output tile per CTA, 16-deep k slices through shared memory, 4x4
+// register micro-tile per thread; any A/B/C strides, batched over gridDim.z.
+#include "common.h"
+
+namespace eb200 {
+
+constexpr int GM = 64, GN = 64, GK = 16;
+
+__global__ void __launch_bounds__(256) gemm_simt_kernel(const __grid_constant__ GemmShape g,
+                                                        const float* __restrict__ A,
+                                                        const float* __restrict__ B,
+                                                        float* __restrict__ C) {
+    __shared__ float As[GK][GM + 4];
+    __shared__ float Bs[GK][GN + 4];
+    const int t = threadIdx.x;
+    const long long m0 = (long long)blockIdx.x * GM, n0 = (long long)blockIdx.y * GN;
+    const long long bz = blockIdx.z;
+    const float* Ab = A + g.a_off + bz * g.a_sb;
+    const float* Bb = B + g.b_off + bz * g.b_sb;
+    float* Cb = C + g.c_off + bz * g.c_sb;
+    const int ty = t >> 4, tx = t & 15;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    const bool a_kfast = g.a_sk == 1;
+    const bool b_nfast = g.b_sn == 1;
+    for (long long k0 = 0; k0 < g.k; k0 += GK) {
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) {
+            int m, k;
+            if (a_kfast) { m = (t >> 4) + pass * 16; k = t & 15; }
+            else { k = (t >> 6) + pass * 4; m = t & 63; }
+            const long long gm = m0 + m, gk = k0 + k;
+            As[k][m] = (gm < g.m && gk < g.k) ? __ldg(Ab + gm * g.a_sm + gk * g.a_sk) : 0.0f;
+            int n, kb;
+            if (b_nfast) { kb = (t >> 6) + pass * 4; n = t & 63; }
+            else { n = (t >> 4) + pass * 16; kb = t & 15; }
+            const long long gn = n0 + n, gkb = k0 + kb;
+            Bs[kb][n] = (gn < g.n && gkb < g.k) ? __ldg(Bb + gkb * g.b_sk + gn * g.b_sn) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < GK; ++kk) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const long long gm = m0 + ty * 4 + i;
+        if (gm >= g.m) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const long long gn = n0 + tx * 4 + j;
+            if (gn < g.n) Cb[gm * g.c_sm + gn * g.c_sn] = acc[i][j];
+        }
+    }
+}
+
+int launch_gemm_simt(Device* dev, const Plan& plan, const float* a, const float* b, float* c) {
+    const GemmShape& g = plan.gemm;
+    if (g.m <= 0 || g.n <= 0 || g.batch <= 0) return EB200_OK;
+    EB_REQUIRE(g.batch <= 65535, EB200_ERR_UNSUPPORTED, "batch %lld exceeds grid.z", g.batch);
+    const long long by = (g.n + GN - 1) / GN;
+    EB_REQUIRE(by <= 65535, EB200_ERR_UNSUPPORTED, "n = %lld exceeds grid.y tiles", g.n);
+    dim3 grid((unsigned)((g.m + GM - 1) / GM), (unsigned)by, (unsigned)g.batch);
+    gemm_simt_kernel<<<grid, 256, 0, dev->stream>>>(g, a, b, c);
+    count_launch();
+    EB_CHECK_CUDA(cudaGetLastError());
+    return EB200_OK;
+}
+
+}  // namespace eb200

@@ -1,0 +1,149 @@
+// Kernel objects of the C ABI: create (classify + select), launch, release.
+//
+// eb200_kernel_create stands where the reference's backends render source and
+// run a compiler (crates/backend-c/src/lib.rs:91-110 -> Pipeline::compile_ast,
+// src/backend/pipeline.rs:135-216); eb200_kernel_launch stands where they call
+// the loaded symbol (crates/backend-c/src/kernel.rs:114-168) or launch the PTX
+// (crates/backend-cuda/src/kernel.rs:148-233).  Launches are asynchronous on the
+// device stream; the reference synchronises after every launch.
+#include <string.h>
+
+#define EB_CHAIN_TABLE
+#include "expr.cuh"
+
+namespace eb200 {
+
+int chain_count() { return EB_CHAIN_COUNT; }
+const char* chain_name(int chain) { return chain >= 0 && chain < EB_CHAIN_COUNT ? chain_table[chain].name : "interpreter"; }
+
+int find_chain(const KInsn* prog, int n_insns, float* consts, int* n_consts) {
+    for (int c = 0; c < EB_CHAIN_COUNT; ++c) {
+        const ChainEntry& e = chain_table[c];
+        if (e.n != n_insns) continue;
+        bool same = true;
+        for (int i = 0; i < n_insns && same; ++i) {
+            if (e.prog[i].op != prog[i].op) same = false;
+            else if (prog[i].op != EB200_OP_CONST && e.prog[i].arg != prog[i].arg) same = false;
+        }
+        if (!same) continue;
+        int nc = 0;
+        for (int i = 0; i < n_insns; ++i)
+            if (prog[i].op == EB200_OP_CONST) {
+                if (nc >= KMAX_CONSTS) return -1;
+                consts[nc++] = prog[i].imm;
+            }
+        *n_consts = nc;
+        return c;
+    }
+    *n_consts = 0;
+    return -1;
+}
+
+static int dtype_bytes(int dt) { return dt == EB200_BOOL ? 1 : (dt == EB200_I64 ? 8 : 4); }
+
+}  // namespace eb200
+
+using namespace eb200;
+
+extern "C" {
+
+int eb200_kernel_create(eb200_device* dev, const eb200_kernel_desc* desc, eb200_kernel** out) {
+    EB_REQUIRE(dev && desc && out, EB200_ERR_INVALID, "null argument");
+    auto k = new eb200_kernel();
+    k->dev = dev;
+    int st = build_plan(desc, dev->prop.multiProcessorCount, &k->plan);
+    if (st) { delete k; return st; }
+    if (k->plan.scratch_bytes > 0) {
+        cudaSetDevice(dev->index);
+        st = storage_alloc(dev, (size_t)k->plan.scratch_bytes, false, &k->scratch);
+        if (st) { delete k; return st; }
+    }
+    *out = k;
+    return EB200_OK;
+}
+
+static void fill_info(const Plan& plan, eb200_kernel_info* info) {
+    memset(info, 0, sizeof(*info));
+    strncpy(info->impl, plan.name, sizeof(info->impl) - 1);
+    info->launches = plan.launches;
+    info->specialised = plan.chain >= 0 || plan.impl == IMPL_TRANSPOSE || plan.impl == IMPL_SCATTER ||
+                        plan.impl == IMPL_SGD || plan.impl == IMPL_GEMM_SIMT || plan.impl == IMPL_GEMM_TC;
+    info->scratch_bytes = plan.scratch_bytes;
+    info->algo_bytes = plan.algo_bytes;
+    info->algo_flops = plan.algo_flops;
+}
+
+int eb200_kernel_get_info(eb200_kernel* k, eb200_kernel_info* info) {
+    EB_REQUIRE(k && info, EB200_ERR_INVALID, "null argument");
+    fill_info(k->plan, info);
+    return EB200_OK;
+}
+
+int eb200_kernel_query(const eb200_kernel_desc* desc, int sm_count, eb200_kernel_info* info) {
+    EB_REQUIRE(desc && info, EB200_ERR_INVALID, "null argument");
+    Plan plan;
+    int st = build_plan(desc, sm_count > 0 ? sm_count : 148, &plan);
+    if (st) return st;
+    fill_info(plan, info);
+    return EB200_OK;
+}
+
+int eb200_kernel_launch(eb200_kernel* k, eb200_buffer* const* inputs, int n_inputs,
+                        eb200_buffer* const* outputs, int n_outputs) {
+    EB_REQUIRE(k && (inputs || !n_inputs) && outputs, EB200_ERR_INVALID, "null argument");
+    const Plan& plan = k->plan;
+    EB_REQUIRE(n_inputs == plan.n_inputs, EB200_ERR_INVALID, "kernel takes %d inputs, got %d", plan.n_inputs, n_inputs);
+    EB_REQUIRE(n_outputs == 1, EB200_ERR_INVALID, "kernel writes 1 output, got %d", n_outputs);
+    Device* dev = k->dev;
+    for (int i = 0; i < n_inputs; ++i) {
+        EB_REQUIRE(inputs[i] && inputs[i]->dev == dev, EB200_ERR_INVALID, "input %d is null or lives on another device", i);
+        size_t need = (size_t)plan.in_numel[i] * dtype_bytes(plan.in_dtype[i]);
+        EB_REQUIRE(inputs[i]->bytes >= need, EB200_ERR_BOUNDS, "input %d holds %zu bytes, kernel addresses %zu", i, inputs[i]->bytes, need);
+    }
+    eb200_buffer* ob = outputs[0];
+    EB_REQUIRE(ob && ob->dev == dev, EB200_ERR_INVALID, "output is null or lives on another device");
+    {
+        size_t need = (size_t)plan.out_numel * dtype_bytes(plan.out_dtype);
+        EB_REQUIRE(ob->bytes >= need, EB200_ERR_BOUNDS, "output holds %zu bytes, kernel addresses %zu", ob->bytes, need);
+    }
+    EB_CHECK_CUDA(cudaSetDevice(dev->index));
+    // the output may share storage with a clone: give it its own, keeping the
+    // bytes the kernel does not overwrite
+    int st = buffer_unshare(ob, true);
+    if (st) return st;
+    for (int i = 0; i < n_inputs; ++i)
+        EB_REQUIRE(inputs[i]->storage->ptr != ob->storage->ptr || plan.impl == IMPL_SGD, EB200_ERR_INVALID,
+                   "input %d aliases the output", i);
+
+    KParams p = plan.p;
+    for (int i = 0; i < n_inputs; ++i) p.in[i].ptr = reinterpret_cast<char*>(inputs[i]->storage->ptr);
+    p.out.ptr = reinterpret_cast<char*>(ob->storage->ptr);
+    void* scratch = k->scratch ? k->scratch->ptr : nullptr;
+    switch (plan.impl) {
+        case IMPL_EW: return launch_ew(dev, plan, p);
+        case IMPL_REDUCE_INNER:
+        case IMPL_REDUCE_OUTER: return launch_reduce(dev, plan, p, scratch);
+        case IMPL_TRANSPOSE: return launch_transpose(dev, plan, p.in[0].ptr, p.out.ptr);
+        case IMPL_SCATTER: return launch_scatter(dev, plan, p);
+        case IMPL_SGD:
+            return launch_sgd(dev, plan, reinterpret_cast<const float*>(p.in[0].ptr) + p.in[0].offset,
+                              reinterpret_cast<const float*>(p.in[1].ptr) + p.in[1].offset,
+                              reinterpret_cast<float*>(p.out.ptr) + p.out.offset, p.total);
+        case IMPL_GEMM_SIMT:
+            return launch_gemm_simt(dev, plan, reinterpret_cast<const float*>(p.in[plan.gemm.a_input].ptr),
+                                    reinterpret_cast<const float*>(p.in[plan.gemm.b_input].ptr),
+                                    reinterpret_cast<float*>(p.out.ptr));
+        default: return set_error(EB200_ERR_UNSUPPORTED, "kernel implementation %d is not built", (int)plan.impl);
+    }
+}
+
+int eb200_kernel_release(eb200_kernel* k) {
+    if (!k) return EB200_OK;
+    if (k->refs.fetch_sub(1) == 1) {
+        cudaSetDevice(k->dev->index);
+        delete k;
+    }
+    return EB200_OK;
+}
+
+}  // extern "C"

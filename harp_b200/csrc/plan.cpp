@@ -1,0 +1,424 @@
+// Kernel-class dispatch: descriptor -> plan.
+//
+// The reference decides the kernel class in Lowerer::lower_node
+// (src/lowerer/lower.rs:335-388) and then emits a loop nest for it.  Here the
+// loop nest arrives as an eb200_kernel_desc and this file decides which
+// hand-written kernel serves it:
+//
+//   E_ (elementwise)            -> ew (vectorised fused chain)
+//   E_/C_ identity over a view  -> transpose (shared-memory tiles) or ew gather
+//   R_ (reduce)                 -> gemm      if it is sum(mul(A,B)) over two broadcast views
+//                                  reduce_inner if the reduce dim is innermost
+//                                  reduce_outer otherwise (also the generic fallback)
+//   S_ (scatter-add / fold)     -> scatter
+//
+// Pure host logic: no CUDA calls, so it is unit-testable without a GPU.
+#include <string.h>
+
+#include <algorithm>
+
+#include "common.h"
+
+namespace eb200 {
+
+namespace {
+
+struct Op {
+    int dtype;
+    long long offset;
+    long long strides[KMAX_DIMS];
+    long long numel;
+    float pad;
+    std::vector<eb200_bound> bounds;
+};
+
+int dtype_size(int dt) {
+    switch (dt) {
+        case EB200_F32: return 4;
+        case EB200_BOOL: return 1;
+        case EB200_I32: return 4;
+        case EB200_I64: return 8;
+    }
+    return 0;
+}
+
+// min / max of c + sum coef[d]*idx[d] over the box 0 <= idx[d] < shape[d]
+template <class TC, class TS>
+void affine_range(const TC* coef, long long c, const TS* shape, int nd, int skip,
+                  long long* lo, long long* hi) {
+    long long mn = c, mx = c;
+    for (int d = 0; d < nd; ++d) {
+        if (d == skip || shape[d] <= 0) continue;
+        long long e = (long long)coef[d] * ((long long)shape[d] - 1);
+        if (e < 0) mn += e; else mx += e;
+    }
+    *lo = mn;
+    *hi = mx;
+}
+
+int check_program(const eb200_kernel_desc* d) {
+    int depth = 0, maxdepth = 0;
+    for (int i = 0; i < d->n_insns; ++i) {
+        const eb200_insn& in = d->prog[i];
+        int pop = 0;
+        switch (in.op) {
+            case EB200_OP_LOAD:
+                EB_REQUIRE(in.arg >= 0 && in.arg < d->n_inputs, EB200_ERR_INVALID,
+                           "map instruction %d loads input %d of %d", i, in.arg, d->n_inputs);
+                pop = 0; break;
+            case EB200_OP_CONST: pop = 0; break;
+            case EB200_OP_ADD: case EB200_OP_MUL: case EB200_OP_MAX: case EB200_OP_LT:
+            case EB200_OP_AND: case EB200_OP_REM: case EB200_OP_IDIV: pop = 2; break;
+            case EB200_OP_RECIP: case EB200_OP_SQRT: case EB200_OP_LOG2: case EB200_OP_EXP2:
+            case EB200_OP_SIN: case EB200_OP_FLOOR: case EB200_OP_NOT: pop = 1; break;
+            case EB200_OP_CAST:
+                EB_REQUIRE(dtype_size(in.arg) != 0, EB200_ERR_INVALID, "cast to unknown dtype %d", in.arg);
+                pop = 1; break;
+            case EB200_OP_SELECT: case EB200_OP_FMA: pop = 3; break;
+            default:
+                return set_error(EB200_ERR_INVALID, "unknown map opcode %d at %d", in.op, i);
+        }
+        EB_REQUIRE(depth >= pop, EB200_ERR_INVALID, "map program underflows its stack at %d", i);
+        depth = depth - pop + 1;
+        maxdepth = std::max(maxdepth, depth);
+    }
+    if (d->n_insns) {
+        EB_REQUIRE(depth == 1, EB200_ERR_INVALID, "map program leaves %d values on the stack", depth);
+        EB_REQUIRE(maxdepth <= KSTACK, EB200_ERR_UNSUPPORTED, "map program needs stack depth %d > %d", maxdepth, KSTACK);
+    }
+    return EB200_OK;
+}
+
+bool try_gemm(const KParams& p, Plan* plan, int mode) {
+    if (p.rop != EB200_R_SUM || p.raxis < 0) return false;
+    if (p.n_insns != 3) return false;
+    if (p.prog[0].op != EB200_OP_LOAD || p.prog[1].op != EB200_OP_LOAD || p.prog[2].op != EB200_OP_MUL) return false;
+    int ia = p.prog[0].arg, ib = p.prog[1].arg;
+    if (ia == ib) return false;
+    const KOperand* A = &p.in[ia];
+    const KOperand* B = &p.in[ib];
+    if (A->dtype != EB200_F32 || B->dtype != EB200_F32 || p.out.dtype != EB200_F32) return false;
+    if (A->n_bounds || B->n_bounds) return false;
+    if (A->strides[p.raxis] == 0 || B->strides[p.raxis] == 0) return false;
+    int dm = -1, dn = -1, db = -1;
+    for (int d = 0; d < p.ndim; ++d) {
+        if (d == p.raxis) continue;
+        bool a = A->strides[d] != 0, b = B->strides[d] != 0;
+        if (a && !b) { if (dm >= 0) return false; dm = d; }
+        else if (!a && b) { if (dn >= 0) return false; dn = d; }
+        else if (a && b) { if (db >= 0) return false; db = d; }
+        else return false;
+    }
+    if (dm < 0 || dn < 0) return false;
+    GemmShape g;
+    g.mode = mode == EB200_GEMM_DEFAULT ? EB200_GEMM_3XTF32 : mode;
+    g.a_input = ia; g.b_input = ib;
+    g.m = p.shape[dm]; g.n = p.shape[dn]; g.k = p.shape[p.raxis];
+    g.batch = db >= 0 ? p.shape[db] : 1;
+    g.a_sm = A->strides[dm]; g.a_sk = A->strides[p.raxis]; g.a_sb = db >= 0 ? A->strides[db] : 0; g.a_off = A->offset;
+    g.b_sn = B->strides[dn]; g.b_sk = B->strides[p.raxis]; g.b_sb = db >= 0 ? B->strides[db] : 0; g.b_off = B->offset;
+    g.c_sm = p.out.strides[dm]; g.c_sn = p.out.strides[dn]; g.c_sb = db >= 0 ? p.out.strides[db] : 0; g.c_off = p.out.offset;
+    if (g.c_sm == 0 || g.c_sn == 0) return false;
+    // Orient so that C is written along n (c_sn == 1) where possible:
+    // C^T = B^T A^T swaps the roles of the operands.
+    if (g.c_sn != 1 && g.c_sm == 1) {
+        GemmShape t = g;
+        t.a_input = g.b_input; t.b_input = g.a_input;
+        t.m = g.n; t.n = g.m;
+        t.a_sm = g.b_sn; t.a_sk = g.b_sk; t.a_sb = g.b_sb; t.a_off = g.b_off;
+        t.b_sn = g.a_sm; t.b_sk = g.a_sk; t.b_sb = g.a_sb; t.b_off = g.a_off;
+        t.c_sm = g.c_sn; t.c_sn = g.c_sm;
+        g = t;
+    }
+    plan->gemm = g;
+    return true;
+}
+
+}  // namespace
+
+int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
+    EB_REQUIRE(d && plan, EB200_ERR_INVALID, "null argument");
+    EB_REQUIRE(d->kclass >= EB200_K_ELEMENTWISE && d->kclass <= EB200_K_SGD, EB200_ERR_INVALID, "unknown kernel class %d", d->kclass);
+    EB_REQUIRE(d->ndim >= 0 && d->ndim <= EB200_MAX_DIMS, EB200_ERR_INVALID, "rank %d out of range", d->ndim);
+    EB_REQUIRE(d->n_inputs >= 1 && d->n_inputs <= EB200_MAX_INPUTS, EB200_ERR_INVALID, "%d inputs out of range", d->n_inputs);
+    EB_REQUIRE(d->n_insns >= 0 && d->n_insns <= EB200_MAX_INSNS, EB200_ERR_INVALID, "%d map instructions out of range", d->n_insns);
+    for (int i = 0; i < d->ndim; ++i)
+        EB_REQUIRE(d->shape[i] >= 0 && d->shape[i] < (1LL << 40), EB200_ERR_INVALID, "shape[%d] = %lld out of range", i, (long long)d->shape[i]);
+    for (int i = 0; i <= d->n_inputs; ++i) {
+        const eb200_operand& o = i < d->n_inputs ? d->inputs[i] : d->output;
+        EB_REQUIRE(dtype_size(o.dtype) != 0, EB200_ERR_INVALID, "operand %d has unknown dtype %d", i, o.dtype);
+        EB_REQUIRE(o.n_bounds >= 0 && o.n_bounds <= EB200_MAX_BOUNDS, EB200_ERR_INVALID, "operand %d has %d bounds", i, o.n_bounds);
+        EB_REQUIRE(o.numel >= 0, EB200_ERR_INVALID, "operand %d has negative numel", i);
+        EB_REQUIRE(o.dtype != EB200_I64, EB200_ERR_UNSUPPORTED, "i64 tensors are not served by any kernel class yet");
+    }
+    EB_REQUIRE(d->output.n_bounds == 0, EB200_ERR_INVALID, "the store operand cannot carry bounds");
+    int st = check_program(d);
+    if (st) return st;
+
+    const bool is_reduce = d->kclass == EB200_K_REDUCE;
+    if (is_reduce) {
+        EB_REQUIRE(d->reduce_op >= EB200_R_SUM && d->reduce_op <= EB200_R_PROD, EB200_ERR_INVALID, "reduce op %d", d->reduce_op);
+        EB_REQUIRE(d->reduce_axis >= 0 && d->reduce_axis < d->ndim, EB200_ERR_INVALID, "reduce axis %d of rank %d", d->reduce_axis, d->ndim);
+    } else {
+        EB_REQUIRE(d->reduce_op == EB200_R_NONE, EB200_ERR_INVALID, "reduce op on a non-reduce kernel");
+    }
+    if (d->n_insns == 0)
+        EB_REQUIRE(d->kclass != EB200_K_ELEMENTWISE || d->n_inputs == 1, EB200_ERR_INVALID, "empty map needs exactly one input");
+
+    // ---- address range validation: never let a kernel index outside a buffer
+    long long total = 1;
+    for (int i = 0; i < d->ndim; ++i) total *= d->shape[i];
+    if (total > 0) {
+        for (int i = 0; i <= d->n_inputs; ++i) {
+            const eb200_operand& o = i < d->n_inputs ? d->inputs[i] : d->output;
+            if (o.n_bounds) continue;  // masked loads are guarded element by element
+            long long lo, hi;
+            int skip = (i == d->n_inputs && is_reduce) ? d->reduce_axis : -1;
+            affine_range(o.strides, o.offset, d->shape, d->ndim, skip, &lo, &hi);
+            EB_REQUIRE(lo >= 0 && hi < o.numel, EB200_ERR_BOUNDS,
+                       "%s %d addresses elements [%lld, %lld] of a buffer of %lld",
+                       i < d->n_inputs ? "input" : "output", i < d->n_inputs ? i : 0, lo, hi, (long long)o.numel);
+        }
+    }
+
+    // ---- normalise: drop extent-1 dims and provably true bounds, collapse
+    int keep[KMAX_DIMS], nk = 0, raxis = -1;
+    for (int i = 0; i < d->ndim; ++i) {
+        bool is_r = is_reduce && i == d->reduce_axis;
+        if (d->shape[i] != 1 || is_r) {
+            if (is_r) raxis = nk;
+            keep[nk++] = i;
+        }
+    }
+    std::vector<Op> ops(d->n_inputs + 1);
+    long long shape[KMAX_DIMS];
+    for (int j = 0; j < nk; ++j) shape[j] = d->shape[keep[j]];
+    for (int i = 0; i <= d->n_inputs; ++i) {
+        const eb200_operand& o = i < d->n_inputs ? d->inputs[i] : d->output;
+        Op& q = ops[i];
+        q.dtype = o.dtype; q.offset = o.offset; q.numel = o.numel; q.pad = o.pad_value;
+        for (int j = 0; j < nk; ++j) q.strides[j] = o.strides[keep[j]];
+        if (i == d->n_inputs && raxis >= 0) q.strides[raxis] = 0;
+        for (int b = 0; b < o.n_bounds; ++b) {
+            eb200_bound nb{};
+            for (int j = 0; j < nk; ++j) nb.coef[j] = o.bounds[b].coef[keep[j]];
+            nb.c = o.bounds[b].c; nb.lo = o.bounds[b].lo; nb.hi = o.bounds[b].hi;
+            long long lo, hi;
+            affine_range(nb.coef, nb.c, shape, nk, -1, &lo, &hi);
+            if (lo >= nb.lo && hi < nb.hi) continue;  // always true
+            q.bounds.push_back(nb);
+        }
+    }
+    // collapse dim j (outer) into j+1 (inner) when every operand walks them as one
+    for (int j = nk - 2; j >= 0; --j) {
+        if (j == raxis || j + 1 == raxis) continue;
+        bool ok = true;
+        for (auto& q : ops) {
+            if (q.strides[j] != q.strides[j + 1] * shape[j + 1]) { ok = false; break; }
+            for (auto& b : q.bounds)
+                if (b.coef[j] != b.coef[j + 1] * shape[j + 1]) { ok = false; break; }
+            if (!ok) break;
+        }
+        if (!ok) continue;
+        // the merged dim keeps the inner strides and takes the product extent;
+        // it lands at position j once dim j is removed
+        shape[j + 1] *= shape[j];
+        for (int t = j; t < nk - 1; ++t) shape[t] = shape[t + 1];
+        for (auto& q : ops) {
+            for (int t = j; t < nk - 1; ++t) q.strides[t] = q.strides[t + 1];
+            for (auto& b : q.bounds)
+                for (int t = j; t < nk - 1; ++t) b.coef[t] = b.coef[t + 1];
+        }
+        if (raxis > j) --raxis;
+        --nk;
+    }
+
+    Plan& pl = *plan;
+    pl = Plan();
+    KParams& p = pl.p;
+    memset(&p, 0, sizeof(p));
+    p.ndim = nk;
+    p.n_in = d->n_inputs;
+    p.total = total;
+    for (int j = 0; j < nk; ++j) p.shape[j] = shape[j];
+    p.raxis = raxis;
+    p.rop = d->reduce_op;
+    p.rlen = raxis >= 0 ? shape[raxis] : 1;
+    p.kept = raxis >= 0 ? (p.rlen ? total / p.rlen : 0) : total;
+    if (raxis >= 0 && p.rlen == 0) {
+        long long k = 1;
+        for (int j = 0; j < nk; ++j) if (j != raxis) k *= shape[j];
+        p.kept = k;
+    }
+    p.splits = 1;
+    p.chunk = p.rlen;
+    int nb_total = 0;
+    for (int i = 0; i <= d->n_inputs; ++i) {
+        KOperand& ko = i < d->n_inputs ? p.in[i] : p.out;
+        const Op& q = ops[i];
+        ko.ptr = nullptr; ko.offset = q.offset; ko.dtype = q.dtype; ko.pad = q.pad;
+        for (int j = 0; j < nk; ++j) ko.strides[j] = q.strides[j];
+        ko.bound_begin = nb_total; ko.n_bounds = (int)q.bounds.size();
+        EB_REQUIRE(nb_total + ko.n_bounds <= KMAX_BOUNDS, EB200_ERR_UNSUPPORTED, "more than %d live bound conditions in one kernel", KMAX_BOUNDS);
+        for (auto& b : q.bounds) {
+            KBound& kb = p.bounds[nb_total++];
+            for (int j = 0; j < nk; ++j) kb.coef[j] = b.coef[j];
+            kb.c = b.c; kb.lo = b.lo; kb.hi = b.hi;
+        }
+    }
+    if (d->n_insns == 0) {
+        p.n_insns = 1;
+        p.prog[0].op = EB200_OP_LOAD; p.prog[0].arg = 0; p.prog[0].imm = 0.f;
+    } else {
+        p.n_insns = d->n_insns;
+        for (int i = 0; i < d->n_insns; ++i) {
+            p.prog[i].op = (short)d->prog[i].op; p.prog[i].arg = (short)d->prog[i].arg; p.prog[i].imm = d->prog[i].imm;
+        }
+    }
+    pl.n_inputs = d->n_inputs;
+    for (int i = 0; i < d->n_inputs; ++i) { pl.in_dtype[i] = d->inputs[i].dtype; pl.in_numel[i] = d->inputs[i].numel; }
+    pl.out_dtype = d->output.dtype;
+    pl.out_numel = d->output.numel;
+    pl.scalar = d->scalar;
+
+    // ---- algorithmic traffic: every operand element that is addressed, once
+    {
+        int64_t bytes = 0;
+        for (int i = 0; i <= d->n_inputs; ++i) {
+            const KOperand& ko = i < d->n_inputs ? p.in[i] : p.out;
+            int64_t n = 1;
+            for (int j = 0; j < nk; ++j) if (ko.strides[j] != 0) n *= shape[j];
+            if (i == d->n_inputs && raxis < 0 && d->kclass != EB200_K_SCATTER) n = total;
+            if (d->kclass == EB200_K_SCATTER && i == d->n_inputs) n = d->output.numel;
+            if (total == 0) n = 0;
+            bytes += n * dtype_size(ko.dtype);
+        }
+        pl.algo_bytes = bytes;
+    }
+
+    // ---- 128-bit legality along the innermost collapsed dim
+    auto vec_ok = [&](const KOperand& ko, int inner, bool is_store) -> bool {
+        if (ko.dtype != EB200_F32 || ko.n_bounds) return false;
+        long long s = ko.strides[inner];
+        if (s == 0) return !is_store;
+        if (s != 1) return false;
+        if (ko.offset % 4) return false;
+        for (int j = 0; j < nk; ++j) if (j != inner && ko.strides[j] % 4) return false;
+        return true;
+    };
+
+    // ---- classify
+    const bool identity = p.n_insns == 1 && p.prog[0].op == EB200_OP_LOAD;
+    switch (d->kclass) {
+        case EB200_K_SGD: {
+            EB_REQUIRE(d->n_inputs == 2 && nk <= 1, EB200_ERR_UNSUPPORTED, "sgd kernel wants two flat f32 inputs");
+            for (int i = 0; i < 2; ++i)
+                EB_REQUIRE(p.in[i].dtype == EB200_F32 && (nk == 0 || p.in[i].strides[0] == 1), EB200_ERR_UNSUPPORTED, "sgd operands must be flat f32");
+            EB_REQUIRE(p.out.dtype == EB200_F32 && (nk == 0 || p.out.strides[0] == 1), EB200_ERR_UNSUPPORTED, "sgd output must be flat f32");
+            pl.impl = IMPL_SGD;
+            snprintf(pl.name, sizeof(pl.name), "sgd_update");
+            break;
+        }
+        case EB200_K_SCATTER: {
+            EB_REQUIRE(d->n_inputs == 1 && identity, EB200_ERR_UNSUPPORTED, "scatter takes one input and no map");
+            EB_REQUIRE(p.in[0].dtype == EB200_F32 && p.out.dtype == EB200_F32, EB200_ERR_UNSUPPORTED, "scatter-add is f32 only");
+            pl.impl = IMPL_SCATTER;
+            pl.launches = 2;
+            snprintf(pl.name, sizeof(pl.name), "scatter_add");
+            break;
+        }
+        case EB200_K_COPY:
+            EB_REQUIRE(d->n_inputs == 1 && identity, EB200_ERR_INVALID, "copy takes one input and no map");
+            EB_REQUIRE(p.in[0].dtype == p.out.dtype, EB200_ERR_UNSUPPORTED, "copy cannot change dtype");
+            /* fallthrough */
+        case EB200_K_ELEMENTWISE: {
+            pl.impl = IMPL_EW;
+            // batched 2-D transpose: output contiguous, input unit-stride on a
+            // dim that is not the innermost one
+            bool tr = identity && p.in[0].dtype == p.out.dtype && !p.in[0].n_bounds && nk >= 2 &&
+                      dtype_size(p.out.dtype) == 4 && p.in[0].strides[nk - 1] != 1;
+            if (tr) {
+                long long acc = 1;
+                for (int j = nk - 1; j >= 0; --j) { if (p.out.strides[j] != acc) tr = false; acc *= shape[j]; }
+            }
+            int rdim = -1;
+            if (tr) {
+                for (int j = 0; j < nk - 1; ++j) if (p.in[0].strides[j] == 1) { rdim = j; break; }
+                if (rdim < 0 || shape[rdim] < 16 || shape[nk - 1] < 16) tr = false;
+            }
+            if (tr) {
+                pl.impl = IMPL_TRANSPOSE;
+                p.raxis = rdim;  // the dim the input is contiguous along
+                snprintf(pl.name, sizeof(pl.name), "transpose_copy");
+            } else {
+                int inner = nk - 1;
+                bool v = nk >= 1 && shape[inner] % 4 == 0 && vec_ok(p.out, inner, true);
+                for (int i = 0; v && i < d->n_inputs; ++i) v = vec_ok(p.in[i], inner, false);
+                p.vec = v ? 4 : 1;
+                snprintf(pl.name, sizeof(pl.name), "ew_chain_v%d", p.vec);
+            }
+            break;
+        }
+        case EB200_K_REDUCE: {
+            if (try_gemm(p, &pl, d->gemm_mode)) {
+                pl.impl = IMPL_GEMM_SIMT;
+                pl.algo_flops = 2 * pl.gemm.batch * pl.gemm.m * pl.gemm.n * pl.gemm.k;
+                snprintf(pl.name, sizeof(pl.name), "gemm_simt_f32");
+                break;
+            }
+            if (raxis == nk - 1) {
+                pl.impl = IMPL_REDUCE_INNER;
+                bool v = p.rlen % 4 == 0 && p.rlen >= 4;
+                for (int i = 0; v && i < d->n_inputs; ++i) v = vec_ok(p.in[i], raxis, false);
+                p.vec = v ? 4 : 1;
+                pl.threads_per_row = p.rlen <= 64 ? 1 : (p.rlen <= 4096 ? 32 : 256);
+                // few long rows: split each row over several CTAs, finish in a second pass
+                long long ctas = pl.threads_per_row == 256 ? p.kept : 0;
+                if (pl.threads_per_row == 256 && ctas < 2LL * sm_count && p.rlen >= 65536) {
+                    long long want = (4LL * sm_count + ctas - 1) / std::max(1LL, ctas);
+                    long long maxs = p.rlen / 16384;
+                    int s = (int)std::max(1LL, std::min(want, std::min(maxs, 1024LL)));
+                    if (s > 1) {
+                        long long chunk = (p.rlen + s - 1) / s;
+                        chunk = (chunk + 3) / 4 * 4;
+                        s = (int)((p.rlen + chunk - 1) / chunk);
+                        p.splits = s;
+                        p.chunk = chunk;
+                        pl.scratch_bytes = (int64_t)s * p.kept * 4;
+                        pl.launches = 2;
+                    }
+                }
+                snprintf(pl.name, sizeof(pl.name), "reduce_inner_t%d_v%d%s", pl.threads_per_row, p.vec, p.splits > 1 ? "_split" : "");
+            } else {
+                pl.impl = IMPL_REDUCE_OUTER;
+                int inner = nk - 1;
+                bool v = shape[inner] % 4 == 0 && vec_ok(p.out, inner, true);
+                for (int i = 0; v && i < d->n_inputs; ++i) v = vec_ok(p.in[i], inner, false);
+                p.vec = v ? 4 : 1;
+                // enough thread blocks to fill the machine: split the reduce dim
+                long long threads = p.kept / p.vec;
+                long long blocks = (threads + 255) / 256;
+                if (blocks < 4LL * sm_count && p.rlen >= 64) {
+                    long long want = (8LL * sm_count + blocks - 1) / std::max(1LL, blocks);
+                    int s = (int)std::max(1LL, std::min(want, std::min(p.rlen / 16, 1024LL)));
+                    if (s > 1) {
+                        long long chunk = (p.rlen + s - 1) / s;
+                        s = (int)((p.rlen + chunk - 1) / chunk);
+                        p.splits = s;
+                        p.chunk = chunk;
+                        pl.scratch_bytes = (int64_t)s * p.kept * 4;
+                        pl.launches = 2;
+                    }
+                }
+                snprintf(pl.name, sizeof(pl.name), "reduce_outer_v%d%s", p.vec, p.splits > 1 ? "_split" : "");
+            }
+            break;
+        }
+    }
+    if (pl.impl == IMPL_EW || pl.impl == IMPL_REDUCE_INNER || pl.impl == IMPL_REDUCE_OUTER) {
+        pl.chain = find_chain(p.prog, p.n_insns, p.consts, &p.n_consts);
+    }
+    return EB200_OK;
+}
+
+}  // namespace eb200

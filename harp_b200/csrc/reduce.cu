@@ -1,0 +1,282 @@
+// Axis reductions with a fused pre-map (kernel class R_,
+// src/lowerer/lower.rs:525-571; loop shape src/lowerer/loop_gen.rs:87-151;
+// identities and combiners src/graph/node.rs:29-77).
+//
+// The reference runs `acc = op(acc, map(loads))` sequentially, reduce loop
+// innermost.  Two kernels replace it:
+//
+//  reduce_inner  the reduce dim is the innermost collapsed dim (contiguous
+//                rows).  A group of T threads (1, a warp, or a 256-thread CTA)
+//                walks one row with 128-bit loads, evaluates the map, and
+//                combines through warp shuffles and a shared-memory tree.
+//                Few very long rows are split over several CTAs into scratch
+//                partials and finished by reduce_finish.
+//  reduce_outer  the reduce dim is strided (e.g. max over axis 0): each thread
+//                owns 4 adjacent kept elements, so a warp reads 512 contiguous
+//                bytes per reduce step; the reduce dim is split over
+//                gridDim.y into scratch partials [split][kept] which
+//                reduce_finish folds.  With one split it is also the generic
+//                fallback for any reduce the other paths do not take.
+//
+// Both are HBM-bound: algorithmic bytes = 4 B x (input elements + outputs).
+#include "expr.cuh"
+#include "index.cuh"
+
+namespace eb200 {
+
+// idx[d] = v without dynamic register indexing
+__device__ __forceinline__ void set_idx(long long* idx, int d, long long v) {
+#pragma unroll
+    for (int i = 0; i < KMAX_DIMS; ++i)
+        if (i == d) idx[i] = v;
+}
+
+template <int T>
+__device__ __forceinline__ float group_reduce(float v, int rop, float* smem) {
+    if (T == 1) return v;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = red_combine(rop, v, __shfl_xor_sync(0xffffffffu, v, o));
+    if (T == 32) return v;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) smem[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        v = lane < (T >> 5) ? smem[lane] : red_identity(rop);
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) v = red_combine(rop, v, __shfl_xor_sync(0xffffffffu, v, o));
+    }
+    __syncthreads();
+    return v;
+}
+
+// One input vector of 4 consecutive reduce-dim elements starting at element
+// address `a`, or a broadcast scalar when the operand does not move along it.
+__device__ __forceinline__ void load4(const KOperand& o, long long a, long long rstride, float* dst) {
+    const float* src = reinterpret_cast<const float*>(o.ptr) + a;
+    if (rstride == 1) {
+        float4 t = __ldg(reinterpret_cast<const float4*>(src));
+        dst[0] = t.x; dst[1] = t.y; dst[2] = t.z; dst[3] = t.w;
+    } else {
+        float t = __ldg(src);
+        dst[0] = t; dst[1] = t; dst[2] = t; dst[3] = t;
+    }
+}
+
+template <class F, int T>
+__global__ void __launch_bounds__(256) reduce_inner_kernel(const __grid_constant__ KParams p, float* __restrict__ scratch) {
+    __shared__ float smem[8];
+    constexpr int ROWS = 256 / T;
+    const int lane = threadIdx.x % T;
+    const int sub = threadIdx.x / T;
+    const int ra = p.raxis;
+    const int n = F::nin(p);
+    const long long work = p.kept * p.splits;  // (row, split) pairs
+    const long long nblk = (work + ROWS - 1) / ROWS;
+    for (long long blk = blockIdx.x; blk < nblk; blk += gridDim.x) {
+        const long long item = blk * ROWS + sub;
+        const bool live = item < work;
+        const long long row = live ? item / p.splits : 0;
+        const int split = live ? (int)(item - row * p.splits) : 0;
+        long long idx[KMAX_DIMS];
+        decompose(p, row, idx, ra);
+        const long long r0 = (long long)split * p.chunk;
+        long long r1 = r0 + p.chunk;
+        if (r1 > p.rlen) r1 = p.rlen;
+        float acc = red_identity(p.rop);
+        if (live) {
+            if (p.vec == 4) {
+                long long base[KMAX_IN];
+#pragma unroll
+                for (int i = 0; i < (F::kCompiled ? n : KMAX_IN); ++i) {
+                    if (i >= n) break;
+                    base[i] = operand_index(p, p.in[i], idx);
+                }
+                float a4[4];
+#pragma unroll
+                for (int v = 0; v < 4; ++v) a4[v] = acc;
+                const long long step = (long long)T * 4;
+                for (long long c0 = r0 + lane * 4; c0 < r1; c0 += 2 * step) {
+                    const long long c1 = c0 + step;
+                    const bool has1 = c1 < r1;
+                    float in0[KMAX_IN][4], in1[KMAX_IN][4], v0[4], v1[4];
+#pragma unroll
+                    for (int i = 0; i < (F::kCompiled ? n : KMAX_IN); ++i) {
+                        if (i >= n) break;
+                        const long long rs = p.in[i].strides[ra];
+                        load4(p.in[i], base[i] + c0 * rs, rs, in0[i]);
+                        if (has1) load4(p.in[i], base[i] + c1 * rs, rs, in1[i]);
+                    }
+                    F::template eval<4>(p, in0, v0);
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) a4[v] = red_combine(p.rop, a4[v], v0[v]);
+                    if (has1) {
+                        F::template eval<4>(p, in1, v1);
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) a4[v] = red_combine(p.rop, a4[v], v1[v]);
+                    }
+                }
+                acc = red_combine(p.rop, red_combine(p.rop, a4[0], a4[1]), red_combine(p.rop, a4[2], a4[3]));
+            } else {
+                for (long long c = r0 + lane; c < r1; c += T) {
+                    set_idx(idx, ra, c);
+                    float in[KMAX_IN][1], v[1];
+#pragma unroll
+                    for (int i = 0; i < (F::kCompiled ? n : KMAX_IN); ++i) {
+                        if (i >= n) break;
+                        const KOperand& o = p.in[i];
+                        if (o.n_bounds && !bounds_ok(p, o, idx)) in[i][0] = o.pad;
+                        else in[i][0] = load_elem(o, operand_index(p, o, idx));
+                    }
+                    F::template eval<1>(p, in, v);
+                    acc = red_combine(p.rop, acc, v[0]);
+                }
+                set_idx(idx, ra, 0);
+            }
+        }
+        acc = group_reduce<T>(acc, p.rop, smem);
+        if (live && lane == 0) {
+            if (p.splits > 1) scratch[(long long)split * p.kept + row] = acc;
+            else store_elem(p.out, operand_index(p, p.out, idx), acc);
+        }
+    }
+}
+
+template <class F>
+__global__ void __launch_bounds__(256) reduce_outer_kernel(const __grid_constant__ KParams p, float* __restrict__ scratch) {
+    const int ra = p.raxis;
+    const int n = F::nin(p);
+    const int split = blockIdx.y;
+    const long long r0 = (long long)split * p.chunk;
+    long long r1 = r0 + p.chunk;
+    if (r1 > p.rlen) r1 = p.rlen;
+    const long long nwork = p.vec == 4 ? (p.kept >> 2) : p.kept;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long wv = (long long)blockIdx.x * blockDim.x + threadIdx.x; wv < nwork; wv += stride) {
+        const long long k = p.vec == 4 ? (wv << 2) : wv;
+        long long idx[KMAX_DIMS];
+        decompose(p, k, idx, ra);
+        if (p.vec == 4) {
+            long long base[KMAX_IN];
+#pragma unroll
+            for (int i = 0; i < (F::kCompiled ? n : KMAX_IN); ++i) {
+                if (i >= n) break;
+                base[i] = operand_index(p, p.in[i], idx);
+            }
+            const int inner = p.ndim - 1;
+            float a4[4];
+#pragma unroll
+            for (int v = 0; v < 4; ++v) a4[v] = red_identity(p.rop);
+            long long r = r0;
+            for (; r + 4 <= r1; r += 4) {
+                float in[4][KMAX_IN][4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+#pragma unroll
+                    for (int i = 0; i < (F::kCompiled ? n : KMAX_IN); ++i) {
+                        if (i >= n) break;
+                        load4(p.in[i], base[i] + (r + u) * p.in[i].strides[ra], p.in[i].strides[inner], in[u][i]);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    float v4[4];
+                    F::template eval<4>(p, in[u], v4);
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) a4[v] = red_combine(p.rop, a4[v], v4[v]);
+                }
+            }
+            for (; r < r1; ++r) {
+                float in[KMAX_IN][4], v4[4];
+#pragma unroll
+                for (int i = 0; i < (F::kCompiled ? n : KMAX_IN); ++i) {
+                    if (i >= n) break;
+                    load4(p.in[i], base[i] + r * p.in[i].strides[ra], p.in[i].strides[inner], in[i]);
+                }
+                F::template eval<4>(p, in, v4);
+#pragma unroll
+                for (int v = 0; v < 4; ++v) a4[v] = red_combine(p.rop, a4[v], v4[v]);
+            }
+            float4 res = make_float4(a4[0], a4[1], a4[2], a4[3]);
+            if (p.splits > 1) *reinterpret_cast<float4*>(scratch + (long long)split * p.kept + k) = res;
+            else *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out.ptr) + operand_index(p, p.out, idx)) = res;
+        } else {
+            float acc = red_identity(p.rop);
+            for (long long r = r0; r < r1; ++r) {
+                set_idx(idx, ra, r);
+                float in[KMAX_IN][1], v[1];
+#pragma unroll
+                for (int i = 0; i < (F::kCompiled ? n : KMAX_IN); ++i) {
+                    if (i >= n) break;
+                    const KOperand& o = p.in[i];
+                    if (o.n_bounds && !bounds_ok(p, o, idx)) in[i][0] = o.pad;
+                    else in[i][0] = load_elem(o, operand_index(p, o, idx));
+                }
+                F::template eval<1>(p, in, v);
+                acc = red_combine(p.rop, acc, v[0]);
+            }
+            set_idx(idx, ra, 0);
+            if (p.splits > 1) scratch[(long long)split * p.kept + k] = acc;
+            else store_elem(p.out, operand_index(p, p.out, idx), acc);
+        }
+    }
+}
+
+// Folds scratch partials [splits][kept] into the output operand.
+__global__ void __launch_bounds__(256) reduce_finish_kernel(const __grid_constant__ KParams p, const float* __restrict__ scratch) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long k = (long long)blockIdx.x * blockDim.x + threadIdx.x; k < p.kept; k += stride) {
+        float acc = red_identity(p.rop);
+        for (int s = 0; s < p.splits; ++s) acc = red_combine(p.rop, acc, scratch[(long long)s * p.kept + k]);
+        long long idx[KMAX_DIMS];
+        decompose(p, k, idx, p.raxis);
+        store_elem(p.out, operand_index(p, p.out, idx), acc);
+    }
+}
+
+template <class F>
+static int launch_one(Device* dev, const Plan& plan, const KParams& p, float* scratch) {
+    const int sms = dev->prop.multiProcessorCount;
+    if (p.kept <= 0) return EB200_OK;
+    if (plan.impl == IMPL_REDUCE_INNER) {
+        const int T = plan.threads_per_row;
+        const long long work = p.kept * p.splits;
+        const long long rows = 256 / T;
+        long long blocks = (work + rows - 1) / rows;
+        long long cap = (long long)sms * 32;
+        if (blocks > cap) blocks = cap;
+        if (T == 1) reduce_inner_kernel<F, 1><<<(unsigned)blocks, 256, 0, dev->stream>>>(p, scratch);
+        else if (T == 32) reduce_inner_kernel<F, 32><<<(unsigned)blocks, 256, 0, dev->stream>>>(p, scratch);
+        else reduce_inner_kernel<F, 256><<<(unsigned)blocks, 256, 0, dev->stream>>>(p, scratch);
+    } else {
+        const long long nwork = p.vec == 4 ? (p.kept >> 2) : p.kept;
+        long long bx = (nwork + 255) / 256;
+        long long cap = (long long)sms * 32;
+        if (bx > cap) bx = cap;
+        dim3 grid((unsigned)bx, (unsigned)p.splits);
+        reduce_outer_kernel<F><<<grid, 256, 0, dev->stream>>>(p, scratch);
+    }
+    count_launch();
+    EB_CHECK_CUDA(cudaGetLastError());
+    if (p.splits > 1) {
+        long long blocks = (p.kept + 255) / 256;
+        long long cap = (long long)sms * 8;
+        if (blocks > cap) blocks = cap;
+        reduce_finish_kernel<<<(unsigned)blocks, 256, 0, dev->stream>>>(p, scratch);
+        count_launch();
+        EB_CHECK_CUDA(cudaGetLastError());
+    }
+    return EB200_OK;
+}
+
+int launch_reduce(Device* dev, const Plan& plan, const KParams& p, void* scratch) {
+    float* s = reinterpret_cast<float*>(scratch);
+    EB_REQUIRE(p.splits == 1 || s, EB200_ERR_INVALID, "split reduction launched without scratch");
+    switch (plan.chain) {
+#define X(i) case i: return launch_one<Compiled<Chain##i>>(dev, plan, p, s);
+        EB_FOR_EACH_CHAIN(X)
+#undef X
+        default: return launch_one<Interp>(dev, plan, p, s);
+    }
+}
+
+}  // namespace eb200

@@ -1,0 +1,75 @@
+"""Kernel descriptors and seeded inputs of the benchmark configurations.
+
+Each function returns what eclat's lowerer would hand the backend for that
+configuration (with this backend's elementwise-chain fusion applied), plus the
+synthetic inputs: numpy ``default_rng(seed)`` tensors with the shapes and value
+distributions the configuration names.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from . import desc as D
+from .desc import Ast
+
+w = Ast.w
+
+
+# ---- config 2: fused elementwise + reduce, column max, transposing copy --------
+
+def cfg2_input(rows: int = 8192, cols: int = 8192, seed: int = 2) -> np.ndarray:
+    return np.random.default_rng(seed).standard_normal((rows, cols), dtype=np.float32)
+
+
+def cfg2_y(rows: int = 8192, cols: int = 8192) -> D.KernelDesc:
+    """y = sum(exp(c0*x + c1) * x, axis=1).  The constants are D0 tensors
+    broadcast with stride 0 (the Tensor API has no scalar literal:
+    src/tensor/ops.rs:699-707).  The reference would run mul, add, exp as three
+    E_ kernels and fuse only the last mul into the R_ kernel
+    (src/lowerer/fusion.rs:28-56); here the whole chain is one map."""
+    scalar = D.Operand([0, 0], 0, D.F32, 1)
+    expr = ((w(0) * w(1)) + w(2)).exp() * w(1)
+    return D.reduce([rows, cols], [scalar, D.contiguous([rows, cols]), scalar], expr, D.R_SUM, 1)
+
+
+def cfg2_z(rows: int = 8192, cols: int = 8192) -> D.KernelDesc:
+    """z = max(x, axis=0): kept axis outside, reduce axis innermost in the
+    reference's loop nest (src/lowerer/loop_gen.rs:87-151)."""
+    return D.reduce([rows, cols], [D.contiguous([rows, cols])], w(0), D.R_MAX, 0)
+
+
+def cfg2_t(rows: int = 8192, cols: int = 8192) -> D.KernelDesc:
+    """t = x.permute(1,0).contiguous(): identity-map E_ kernel over the permuted
+    view (src/graph/node.rs:431-445); out[c][r] = x[r][c]."""
+    src = D.Operand([1, cols], 0, D.F32, rows * cols)
+    return D.elementwise([cols, rows], [src], w(0))
+
+
+def cfg2_consts():
+    return np.array([0.5], np.float32), np.array([1.0], np.float32)
+
+
+# ---- configs 1 and 5: dense contraction spelled as broadcast-mul + sum ----------
+
+def matmul_desc(m: int, k: int, n: int, batch: int = 0, mode: int = D.GEMM_DEFAULT) -> D.KernelDesc:
+    """C = A.B as examples/matmul_demo.rs:43-60 builds it: A [M,K] -> [M,K,1],
+    B [K,N] -> [1,K,N], expand to [M,K,N], multiply, sum over axis 1."""
+    if batch:
+        a = D.Operand([m * k, k, 1, 0], 0, D.F32, batch * m * k)
+        b = D.Operand([k * n, 0, n, 1], 0, D.F32, batch * k * n)
+        return D.reduce([batch, m, k, n], [a, b], w(0) * w(1), D.R_SUM, 2, gemm_mode=mode)
+    a = D.Operand([k, 1, 0], 0, D.F32, m * k)
+    b = D.Operand([0, n, 1], 0, D.F32, k * n)
+    return D.reduce([m, k, n], [a, b], w(0) * w(1), D.R_SUM, 1, gemm_mode=mode)
+
+
+def linear_desc(batch: int, in_f: int, out_f: int, mode: int = D.GEMM_DEFAULT) -> D.KernelDesc:
+    """x [B,I] . W[O,I]^T as functional::linear builds it
+    (crates/nn/src/functional/linear.rs:27-56): [B,1,I] * [1,O,I] summed over axis 2."""
+    x = D.Operand([in_f, 0, 1], 0, D.F32, batch * in_f)
+    wt = D.Operand([0, in_f, 1], 0, D.F32, out_f * in_f)
+    return D.reduce([batch, out_f, in_f], [x, wt], w(0) * w(1), D.R_SUM, 2, gemm_mode=mode)
+
+
+def uniform_pm1(shape, seed: int) -> np.ndarray:
+    return np.random.default_rng(seed).uniform(-1.0, 1.0, shape).astype(np.float32)

@@ -1,0 +1,357 @@
+"""CPU oracle: the C the reference's C backend would emit for a lowered kernel.
+
+TEST INFRASTRUCTURE ONLY.  Nothing on the product path may import this module;
+it is the checker for the parity tests, for ``__graft_entry__.smoke()`` and for
+the CPU-baseline legs of ``bench.py``.
+
+The reference (eclat, 100 % Rust) has no native sources and cannot be built
+without a Rust toolchain, but the arithmetic of its CPU backend is C text that
+it generates at run time and hands to the system ``gcc``.  This module restates
+that generator for the kernel classes on the hot path, so the oracle is real
+compiled C built with the reference's own flags:
+
+* loop nests: ``for (long long ridxN = 0; ridxN < S; ridxN += 1)`` in axis order,
+  reduce axis innermost (src/lowerer/loop_gen.rs:51-151, range rendering
+  src/backend/renderer.rs:638-648);
+* addressing: ``offset + sum ridx_d * stride_d`` (src/lowerer/index_gen.rs:45-63),
+  reduce output index with the reduce axis forced to 0 (index_gen.rs:107-112);
+* padded loads ``(cond ? buf[idx] : pad)`` (src/lowerer/lower.rs:1145-1157) with
+  ``cond`` built from ``<``, ``&&``, ``!`` (src/graph/shape/view.rs:997-1011);
+* expressions: every binary op parenthesised, ``fmaxf/sqrtf/log2f/exp2f/sinf/
+  floorf``, ``(1.0f / x)`` (src/backend/renderer.rs:268-441,
+  crates/backend-c/src/renderer.rs:181-206), f32 literal formatting
+  (src/backend/renderer.rs:196-215);
+* reduce: block-scope ``float acc;``, identity store, sequential combine
+  (src/lowerer/lower.rs:525-571, src/graph/node.rs:29-77);
+* scatter: zero-fill nest then ``out[dst] += in[src]`` nest
+  (src/lowerer/lower.rs:580-683, crates/backend-c/src/renderer.rs:208-214);
+* header and signature (crates/backend-c/src/renderer.rs:153-174): pointers
+  without ``const``, inputs first then the output;
+* flags ``gcc -O3 -ffast-math -shared -fPIC -o lib.so kernel.c -lm``
+  (crates/backend-c/src/compiler.rs:153-165); the OpenMP variant adds
+  ``#include <omp.h>``, ``#pragma omp parallel for`` on the outermost loop
+  (crates/backend-openmp/src/renderer.rs:217-259) and ``-fopenmp``
+  (crates/backend-openmp/src/compiler.rs:161).
+
+Parity pinning: the known-answer vectors of the reference's backend tests
+(crates/backend-c/src/lib.rs:164-339, crates/backend-openmp/src/lib.rs:167-231)
+are replayed against this oracle in tests/test_oracle.py.  Transcendentals come
+from glibc libm under ``-ffast-math``; no reference test pins their values:
+PARITY UNPINNED at that boundary (the 1e-5 relative tolerance is the contract).
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import math
+import os
+import subprocess
+import tempfile
+from typing import List, Sequence
+
+import numpy as np
+
+from harp_b200 import desc as D
+
+_CACHE_DIR = os.environ.get(
+    "EB200_ORACLE_CACHE", os.path.join(tempfile.gettempdir(), "eb200_oracle_cache"))
+
+C_TYPE = {D.F32: "float", D.BOOL: "unsigned char", D.I32: "int", D.I64: "long long"}
+
+HEADER = """/* Generated C code by Harp */
+/* This code is pure C99 without parallelization */
+
+#include <math.h>
+#include <stdlib.h>
+#include <stdint.h>
+
+"""
+
+
+def f32_literal(v: float) -> str:
+    """Literal::F32 rendering (src/backend/renderer.rs:196-215): Rust's shortest
+    round-trip ``{}`` formatting, ``.0`` appended when no point/exponent."""
+    f = np.float32(v)
+    if np.isnan(f):
+        return "NAN"
+    if np.isinf(f):
+        return "INFINITY" if f > 0 else "(-INFINITY)"
+    s = np.format_float_positional(f, unique=True, trim="-")  # Rust prints no exponent for f32 Display
+    if "." not in s:
+        s += ".0"
+    return s + "f"
+
+
+def _affine(offset: int, strides: Sequence[int], skip_axis: int = -1) -> str:
+    """Index expression after Expr::simplify: zero terms dropped, ``*1`` folded."""
+    terms: List[str] = []
+    if offset:
+        terms.append(str(int(offset)))
+    for d, s in enumerate(strides):
+        if s == 0 or d == skip_axis:
+            continue
+        terms.append(f"ridx{d}" if s == 1 else f"(ridx{d} * {int(s)})")
+    if not terms:
+        return "0"
+    out = terms[0]
+    for t in terms[1:]:
+        out = f"({out} + {t})"
+    return out
+
+
+def _cond(b: D.Bound) -> str:
+    e = _affine(b.c, b.coef)
+    return f"((!({e} < {int(b.lo)})) && ({e} < {int(b.hi)}))"
+
+
+def _load(name: str, op: D.Operand) -> str:
+    ld = f"{name}[{_affine(op.offset, op.strides)}]"
+    if op.bounds:
+        cond = _cond(op.bounds[0])
+        for b in op.bounds[1:]:
+            cond = f"({cond} && {_cond(b)})"
+        return f"({cond} ? {ld} : {f32_literal(op.pad_value)})"
+    return ld
+
+
+def render_expr(n: D.Ast, loads: List[str], fma: bool = False) -> str:
+    r = lambda a: render_expr(a, loads, fma)
+    a = n.args
+    if n.op == "w":
+        return loads[n.value]
+    if n.op == "const":
+        return f32_literal(n.value)
+    if n.op == "add":
+        if fma and a[0].op == "mul":
+            return f"fma({r(a[0].args[0])}, {r(a[0].args[1])}, {r(a[1])})"
+        return f"({r(a[0])} + {r(a[1])})"
+    if n.op == "mul":
+        return f"({r(a[0])} * {r(a[1])})"
+    if n.op == "max":
+        return f"fmaxf({r(a[0])}, {r(a[1])})"
+    if n.op == "recip":
+        return f"(1.0f / {r(a[0])})"
+    if n.op in ("sqrt", "log2", "exp2", "sin", "floor"):
+        return f"{n.op}f({r(a[0])})"
+    if n.op == "lt":
+        return f"({r(a[0])} < {r(a[1])})"
+    if n.op == "and":
+        return f"({r(a[0])} && {r(a[1])})"
+    if n.op == "not":
+        return f"(!{r(a[0])})"
+    if n.op == "select":
+        return f"({r(a[0])} ? {r(a[1])} : {r(a[2])})"
+    if n.op == "rem":
+        return f"({r(a[0])} % {r(a[1])})"
+    if n.op == "idiv":
+        return f"({r(a[0])} / {r(a[1])})"
+    if n.op == "cast":
+        return f"({C_TYPE[n.value]})({r(a[0])})"
+    if n.op == "fma":
+        return f"fma({r(a[0])}, {r(a[1])}, {r(a[2])})"
+    raise ValueError(n.op)
+
+
+_IDENTITY = {D.R_SUM: 0.0, D.R_MAX: -math.inf, D.R_MIN: math.inf, D.R_PROD: 1.0}
+
+
+def _combine(op: int, acc: str, val: str, fma: bool, val_ast) -> str:
+    if op == D.R_SUM:
+        if fma and val_ast is not None and val_ast.op == "mul":
+            return None  # handled by caller
+        return f"({acc} + {val})"
+    if op == D.R_MAX:
+        return f"fmaxf({acc}, {val})"
+    if op == D.R_MIN:
+        # ReduceOp::Min combines with Select(Lt) (src/graph/node.rs:67-74)
+        return f"(({acc} < {val}) ? {acc} : {val})"
+    if op == D.R_PROD:
+        return f"({acc} * {val})"
+    raise ValueError(op)
+
+
+def emit_kernel_c(k: D.KernelDesc, fn_name: str = "kernel", openmp: bool = False,
+                  fma: bool = False) -> str:
+    """C source for one kernel.  ``fma=True`` gives the form the backend-side
+    AST rule ``a*b+c -> fma(a,b,c)`` produces (src/opt/ast/rules/mod.rs:115-143),
+    rendered as the double-precision ``fma()`` (src/backend/renderer.rs:107-109)."""
+    nd = k.ndim
+    names = [f"buf{i}" for i in range(len(k.inputs))]
+    params = [f"{C_TYPE[o.dtype]}* {n}" for o, n in zip(k.inputs, names)]
+    params.append(f"{C_TYPE[k.output.dtype]}* out")
+    src = HEADER
+    if openmp:
+        src = src.replace("#include <math.h>", "#include <omp.h>\n#include <math.h>")
+    src += "// === Kernel Functions ===\n"
+    src += f"void {fn_name}({', '.join(params)}) {{\n"
+    ind = 1
+    pragma_done = [not openmp]
+
+    def open_loop(d: int, extent: int):
+        nonlocal src, ind
+        if not pragma_done[0]:
+            src += " " * (4 * ind) + "#pragma omp parallel for\n"
+            pragma_done[0] = True
+        src += " " * (4 * ind) + f"for (long long ridx{d} = 0; ridx{d} < {extent}; ridx{d} += 1) {{\n"
+        ind += 1
+
+    def close_loop():
+        nonlocal src, ind
+        ind -= 1
+        src += " " * (4 * ind) + "}\n"
+
+    def line(s: str):
+        nonlocal src
+        src += " " * (4 * ind) + s + "\n"
+
+    loads = [_load(n, o) for n, o in zip(names, k.inputs)]
+
+    if k.kclass in (D.K_ELEMENTWISE, D.K_COPY):
+        value = render_expr(k.map, loads, fma) if k.map is not None else loads[0]
+        for d in range(nd):
+            open_loop(d, k.shape[d])
+        line(f"out[{_affine(k.output.offset, k.output.strides)}] = {value};")
+        for _ in range(nd):
+            close_loop()
+    elif k.kclass == D.K_REDUCE:
+        ax = k.reduce_axis
+        order = [d for d in range(nd) if d != ax]
+        for d in order:
+            open_loop(d, k.shape[d])
+        line("float acc;")
+        line(f"acc = {f32_literal(_IDENTITY[k.reduce_op])};")
+        pragma_done[0] = True  # never parallelise the sequential reduce loop
+        open_loop(ax, k.shape[ax])
+        if fma and k.reduce_op == D.R_SUM and k.map is not None and k.map.op == "mul":
+            a, b = k.map.args
+            line(f"acc = fma({render_expr(a, loads, fma)}, {render_expr(b, loads, fma)}, acc);")
+        else:
+            val = render_expr(k.map, loads, fma) if k.map is not None else loads[0]
+            line(f"acc = {_combine(k.reduce_op, 'acc', val, False, None)};")
+        close_loop()
+        line(f"out[{_affine(k.output.offset, k.output.strides, skip_axis=ax)}] = acc;")
+        for _ in order:
+            close_loop()
+    elif k.kclass == D.K_SCATTER:
+        # zero-fill over the (contiguous) output, then accumulate in loop order
+        line(f"for (long long ridx0 = 0; ridx0 < {int(k.output.numel)}; ridx0 += 1) {{")
+        line("    out[ridx0] = 0.0f;")
+        line("}")
+        pragma_done[0] = True  # `+=` is not atomic in the C backend: keep sequential
+        for d in range(nd):
+            open_loop(d, k.shape[d])
+        line(f"/* atomic_add (sequential) */ (out[{_affine(k.output.offset, k.output.strides)}] += {loads[0]});")
+        for _ in range(nd):
+            close_loop()
+    elif k.kclass == D.K_SGD:
+        # host loop of SGD::step (crates/nn/src/optim/sgd.rs:73-103): p - lr*g
+        open_loop(0, k.shape[0])
+        line(f"out[ridx0] = (buf0[ridx0] - ({f32_literal(k.scalar)} * buf1[ridx0]));")
+        close_loop()
+    else:
+        raise ValueError(f"kernel class {k.kclass}")
+    src += "}\n"
+    return src
+
+
+def gcc_flags(openmp: bool) -> List[str]:
+    flags = ["-O3", "-ffast-math", "-shared", "-fPIC"]
+    if openmp:
+        flags.insert(2, "-fopenmp")
+    return flags
+
+
+def compile_c(source: str, openmp: bool = False) -> str:
+    """Compile with the reference's flags; returns the path of the .so (cached)."""
+    os.makedirs(_CACHE_DIR, exist_ok=True)
+    h = hashlib.sha256((source + str(openmp)).encode()).hexdigest()[:24]
+    so = os.path.join(_CACHE_DIR, f"lib{h}.so")
+    if not os.path.exists(so):
+        cfile = os.path.join(_CACHE_DIR, f"k{h}.c")
+        with open(cfile, "w") as f:
+            f.write(source)
+        tmp = so + f".{os.getpid()}.tmp"
+        cmd = ["gcc"] + gcc_flags(openmp) + ["-o", tmp, cfile, "-lm"]
+        subprocess.run(cmd, check=True, capture_output=True)
+        os.replace(tmp, so)
+    return so
+
+
+class OracleKernel:
+    """A compiled oracle kernel; call with numpy inputs in parameter order."""
+
+    def __init__(self, k: D.KernelDesc, openmp: bool = False, fma: bool = False):
+        self.desc = k
+        self.source = emit_kernel_c(k, "kernel", openmp, fma)
+        self.lib = ctypes.CDLL(compile_c(self.source, openmp))
+        self.fn = self.lib.kernel
+        self.fn.restype = None
+
+    def __call__(self, inputs: Sequence[np.ndarray], out: np.ndarray = None) -> np.ndarray:
+        k = self.desc
+        assert len(inputs) == len(k.inputs)
+        args = []
+        keep = []
+        for a, o in zip(inputs, k.inputs):
+            a = np.ascontiguousarray(a, dtype=D.DTYPE_NP[o.dtype])
+            keep.append(a)
+            args.append(a.ctypes.data_as(ctypes.c_void_p))
+        if out is None:
+            # zero-initialised like CBuffer (crates/backend-c/src/buffer.rs:84-93)
+            out = np.zeros(int(k.output.numel), dtype=D.DTYPE_NP[k.output.dtype])
+        args.append(out.ctypes.data_as(ctypes.c_void_p))
+        self.fn(*args)
+        return out
+
+
+def run(k: D.KernelDesc, inputs: Sequence[np.ndarray], openmp: bool = False,
+        fma: bool = False) -> np.ndarray:
+    return OracleKernel(k, openmp, fma)(inputs)
+
+
+# ---- float64 evaluation (cross-check for cancellation-prone sums) ----------
+
+def eval_f64(k: D.KernelDesc, inputs: Sequence[np.ndarray]) -> np.ndarray:
+    """Evaluate an ELEMENTWISE / REDUCE / COPY descriptor in float64 with numpy.
+    Only for unmasked operands; used to show that CPU and GPU both sit within
+    rounding of the exact result where sums cancel."""
+    shape = tuple(k.shape)
+
+    def view(a, op):
+        a = np.asarray(a).reshape(-1)
+        idx = np.full(shape, op.offset, dtype=np.int64)
+        for d, s in enumerate(op.strides):
+            if s:
+                sh = [1] * len(shape)
+                sh[d] = shape[d]
+                idx = idx + (np.arange(shape[d], dtype=np.int64) * s).reshape(sh)
+        return a[idx].astype(np.float64)
+
+    loads = [view(a, o) for a, o in zip(inputs, k.inputs)]
+
+    def ev(n):
+        a = n.args
+        if n.op == "w": return loads[n.value]
+        if n.op == "const": return np.float64(np.float32(n.value))
+        if n.op == "add": return ev(a[0]) + ev(a[1])
+        if n.op == "mul": return ev(a[0]) * ev(a[1])
+        if n.op == "max": return np.maximum(ev(a[0]), ev(a[1]))
+        if n.op == "recip": return 1.0 / ev(a[0])
+        if n.op == "sqrt": return np.sqrt(ev(a[0]))
+        if n.op == "log2": return np.log2(ev(a[0]))
+        if n.op == "exp2": return np.exp2(ev(a[0]))
+        if n.op == "sin": return np.sin(ev(a[0]))
+        if n.op == "floor": return np.floor(ev(a[0]))
+        if n.op == "lt": return (ev(a[0]) < ev(a[1])).astype(np.float64)
+        if n.op == "and": return ((ev(a[0]) != 0) & (ev(a[1]) != 0)).astype(np.float64)
+        if n.op == "not": return (ev(a[0]) == 0).astype(np.float64)
+        if n.op == "select": return np.where(ev(a[0]) != 0, ev(a[1]), ev(a[2]))
+        if n.op == "fma": return ev(a[0]) * ev(a[1]) + ev(a[2])
+        raise ValueError(n.op)
+
+    val = ev(k.map) if k.map is not None else loads[0]
+    val = np.broadcast_to(val, shape)
+    if k.kclass == D.K_REDUCE:
+        f = {D.R_SUM: np.sum, D.R_MAX: np.max, D.R_MIN: np.min, D.R_PROD: np.prod}[k.reduce_op]
+        return f(val, axis=k.reduce_axis).reshape(-1)
+    return np.ascontiguousarray(val).reshape(-1)

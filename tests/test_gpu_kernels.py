@@ -1,0 +1,376 @@
+"""Parity of the CUDA kernels with the CPU oracle, through the C ABI.
+
+Bit-exact for copies/permutes/gathers and exact ops (add, mul, max, compare);
+1e-5 relative for f32 maps with transcendentals; sums are compared with the
+cancellation-safe bound |gpu - cpu| <= 1e-5 * sum|terms| (any order of adding the
+same f32 terms stays inside it) and against a float64 evaluation.
+"""
+import numpy as np
+import pytest
+
+from harp_b200 import capi
+from harp_b200 import desc as D
+from harp_b200 import workloads as W
+from harp_b200.chains import CHAINS
+from harp_b200.desc import Ast
+from oracle import c_emit as O
+
+from util import assert_close, run_gpu, sum_tolerance
+
+pytestmark = pytest.mark.gpu
+w = Ast.w
+
+
+def rnd(shape, seed, lo=-1.0, hi=1.0):
+    return np.random.default_rng(seed).uniform(lo, hi, shape).astype(np.float32)
+
+
+# ---- the reference's own known-answer vectors, through the GPU path ------------------
+
+def test_ref_vectors_add_mul(dev):
+    k = D.elementwise([4], [D.contiguous([4])] * 2, w(0) + w(1))
+    out, kern = run_gpu(dev, k, [np.array([1, 2, 3, 4.]), np.array([5, 6, 7, 8.])])
+    assert out.tolist() == [6.0, 8.0, 10.0, 12.0]
+    k = D.elementwise([4], [D.contiguous([4])] * 2, w(0) * w(1))
+    out, _ = run_gpu(dev, k, [np.array([1, 2, 3, 4.]), np.array([2, 3, 4, 5.])])
+    assert out.tolist() == [2.0, 6.0, 12.0, 20.0]
+    k = D.elementwise([2, 3], [D.contiguous([2, 3])] * 2, w(0) + w(1))
+    out, _ = run_gpu(dev, k, [np.arange(1, 7.), np.arange(6, 0, -1.)])
+    assert out.tolist() == [7.0] * 6
+    k = D.elementwise([10000], [D.contiguous([10000])] * 2, w(0) + w(1))
+    i = np.arange(10000, dtype=np.float32)
+    out, _ = run_gpu(dev, k, [i, 10000 - i])
+    assert (out == 10000.0).all()
+
+
+def test_ref_vector_unfold_fold(dev):
+    src = D.Operand([8, 2, 4, 1], 0, D.F32, 16)
+    unfold = D.copy([2, 2, 2, 2], src)
+    fold = D.KernelDesc(D.K_SCATTER, [2, 2, 2, 2], [D.contiguous([2, 2, 2, 2])],
+                        D.Operand([8, 2, 4, 1], 0, D.F32, 16))
+    x = np.arange(16, dtype=np.float32)
+    u, _ = run_gpu(dev, unfold, [x])
+    assert (u == O.run(unfold, [x])).all()
+    f, _ = run_gpu(dev, fold, [u], out_init=np.full(16, 7.0, np.float32))  # scatter zero-fills first
+    assert f.sum() == 120.0 and (f == x).all()
+
+
+# ---- buffers ----------------------------------------------------------------------------
+
+def test_buffer_semantics(dev, registry):
+    b = registry.allocate_buffer(dev, [5, 3])
+    assert b.shape() == [5, 3] and b.byte_len() == 60
+    assert (b.read_vec() == 0).all()                      # zero-initialised like CBuffer
+    with pytest.raises(capi.Eb200Error) as e:             # size mismatch is an error
+        b.write_from_host(b"\0" * 59)
+    assert e.value.status == capi.ERR_INVALID and "mismatch" in e.value.message
+    data = np.arange(15, dtype=np.float32)
+    b.write_vec(data)
+    assert b.read_to_host() == data.tobytes()
+    c = b.clone_buffer()                                   # value copy (copy-on-write)
+    b.write_vec(data * 2)
+    assert (c.read_vec() == data).all() and (b.read_vec() == data * 2).all()
+    # a kernel writing into a clone must not disturb the original
+    d = b.clone_buffer()
+    k = registry.compile_ast(dev, D.elementwise([15], [D.contiguous([15])], w(0) * Ast.const(3.0)))
+    k.execute([c], [d])
+    assert (d.read_vec() == data * 3).all() and (b.read_vec() == data * 2).all()
+    with pytest.raises(TypeError):
+        k.execute([np.zeros(15)], [d])
+    st = dev.mem_stats()
+    assert st["in_use"] > 0 and st["peak"] >= st["in_use"]
+
+
+def test_launch_rejects_short_buffers(dev, registry):
+    k = registry.compile_ast(dev, D.elementwise([16], [D.contiguous([16])], w(0)))
+    a = registry.allocate_buffer(dev, [8])
+    o = registry.allocate_buffer(dev, [16])
+    with pytest.raises(capi.Eb200Error) as e:
+        k.execute([a], [o])
+    assert e.value.status == capi.ERR_BOUNDS
+
+
+# ---- elementwise -------------------------------------------------------------------------
+
+@pytest.mark.parametrize("name,expr", CHAINS, ids=[n for n, _ in CHAINS])
+def test_every_compiled_chain_matches_oracle(dev, name, expr):
+    nin = max(expr.wildcards()) + 1
+    shape = [37, 20]
+    positive = any(t in expr.key() for t in ("log2", "sqrt", "recip"))
+    ins = [rnd(shape, 100 + i, 0.5 if positive else -2.0, 2.0) for i in range(nin)]
+    k = D.elementwise(shape, [D.contiguous(shape)] * nin, expr)
+    got, kern = run_gpu(dev, k, ins)
+    assert kern.specialised, name
+    ref = O.run(k, ins)
+    assert_close(got, ref, rel=1e-5, abs_tol=2e-6, what=name)
+
+
+def test_interpreter_matches_oracle_and_compiled(dev):
+    shape = [33, 7]
+    a, b = rnd(shape, 1, 0.1, 3.0), rnd(shape, 2, 0.1, 3.0)
+    e = Ast.select((w(0).sin() * w(1).sqrt() + w(0)).floor().lt(w(1)), w(0).log2(), w(1).exp2().recip())
+    k = D.elementwise(shape, [D.contiguous(shape)] * 2, e)
+    got, kern = run_gpu(dev, k, [a, b])
+    assert not kern.specialised
+    assert_close(got, O.run(k, [a, b]), rel=1e-5, abs_tol=2e-6)
+    # a chain that has a compiled functor, forced through the interpreter by
+    # adding a no-op: both evaluators must agree
+    chain = ((w(0) * Ast.const(0.5)) + Ast.const(1.0)).exp() * w(0)
+    slow = chain + Ast.const(0.0) * w(0)
+    k1 = D.elementwise(shape, [D.contiguous(shape)], chain)
+    k2 = D.elementwise(shape, [D.contiguous(shape)], slow)
+    g1, kn1 = run_gpu(dev, k1, [a])
+    g2, kn2 = run_gpu(dev, k2, [a])
+    assert kn1.specialised and not kn2.specialised
+    assert_close(g2, g1, rel=1e-6)
+
+
+@pytest.mark.parametrize("shape", [[1], [3], [4], [5, 1, 7], [128, 32], [2, 3, 4, 5, 6], [1, 1, 1024], [257, 129]])
+def test_elementwise_shapes_and_broadcasts(dev, shape):
+    nd = len(shape)
+    a = rnd(shape, 3)
+    # operand 1 broadcasts along every other axis (stride 0), like an expanded bias
+    bshape = [s if d % 2 == nd % 2 else 1 for d, s in enumerate(shape)]
+    b = rnd(bshape, 4)
+    bst = [st if bshape[d] != 1 else 0 for d, st in enumerate(D.contiguous_strides(bshape))]
+    opb = D.Operand(bst, 0, D.F32, b.size)
+    k = D.elementwise(shape, [D.contiguous(shape), opb], (w(0) + w(1)).maximum(Ast.const(0.0)))
+    got, _ = run_gpu(dev, k, [a, b])
+    assert (got == O.run(k, [a, b])).all()     # add + max are exact
+
+
+def test_bool_output_and_input(dev):
+    shape = [19, 5]
+    a, b = rnd(shape, 5), rnd(shape, 6)
+    k = D.elementwise(shape, [D.contiguous(shape)] * 2, w(0).lt(w(1)), out_dtype=D.BOOL)
+    mask, _ = run_gpu(dev, k, [a, b])
+    assert mask.dtype == np.uint8 and (mask == (a < b).reshape(-1)).all()
+    k2 = D.elementwise(shape, [D.contiguous(shape, D.BOOL), D.contiguous(shape), D.contiguous(shape)],
+                       Ast.select(w(0), w(1), w(2)))
+    got, _ = run_gpu(dev, k2, [mask, a, b])
+    assert (got == np.where(a < b, a, b).reshape(-1)).all()
+
+
+def test_padded_view_loads(dev):
+    # 2-D pad (1,2)x(2,1) of a 5x6 tensor: View::padded (src/graph/shape/view.rs:980-1054)
+    x = rnd([5, 6], 7)
+    op = D.Operand([6, 1], -1 * 6 - 2, D.F32, 30,
+                   [D.Bound([1, 0], 0, 1, 6), D.Bound([0, 1], 0, 2, 8)], -3.0)
+    k = D.elementwise([8, 9], [op], w(0) * Ast.const(2.0))
+    got, _ = run_gpu(dev, k, [x])
+    assert (got == O.run(k, [x])).all()
+    ref = np.full((8, 9), -3.0, np.float32)
+    ref[1:6, 2:8] = x
+    assert (got.reshape(8, 9) == ref * 2).all()
+
+
+def test_gather_copy_unfold_windows(dev):
+    # im2col of a [2,3,8,8] tensor with 3x3 windows, stride 1: C_ kernel (lower.rs:355-359)
+    x = rnd([2, 3, 8, 8], 8)
+    src = D.Operand([192, 64, 8, 1, 8, 1], 0, D.F32, x.size)
+    k = D.copy([2, 3, 6, 6, 3, 3], src)
+    got, _ = run_gpu(dev, k, [x])
+    assert got.tobytes() == O.run(k, [x]).tobytes()
+
+
+# ---- reductions -----------------------------------------------------------------------------
+
+@pytest.mark.parametrize("rows,cols", [(1, 1), (7, 10), (50, 4), (9, 64), (33, 100), (5, 1024), (3, 4100), (2, 8192), (300, 17)])
+@pytest.mark.parametrize("op", [D.R_SUM, D.R_MAX, D.R_MIN, D.R_PROD])
+def test_reduce_inner_axis(dev, rows, cols, op):
+    lo, hi = (0.9, 1.1) if op == D.R_PROD else (-1.0, 1.0)
+    x = rnd([rows, cols], rows * 1000 + cols, lo, hi)
+    k = D.reduce([rows, cols], [D.contiguous([rows, cols])], w(0), op, 1)
+    got, _ = run_gpu(dev, k, [x])
+    ref = O.run(k, [x])
+    if op in (D.R_MAX, D.R_MIN):
+        assert (got == ref).all()
+    elif op == D.R_SUM:
+        assert (np.abs(got.astype(np.float64) - ref) <= sum_tolerance(k, [x]) + 1e-30).all()
+    else:
+        assert_close(got, ref, rel=1e-4)
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 1), (10, 7), (64, 4), (1000, 12), (4096, 64), (513, 130), (70, 1024)])
+@pytest.mark.parametrize("op", [D.R_SUM, D.R_MAX])
+def test_reduce_outer_axis(dev, rows, cols, op):
+    x = rnd([rows, cols], rows * 7 + cols)
+    k = D.reduce([rows, cols], [D.contiguous([rows, cols])], w(0), op, 0)
+    got, _ = run_gpu(dev, k, [x])
+    ref = O.run(k, [x])
+    if op == D.R_MAX:
+        assert (got == ref).all()
+    else:
+        assert (np.abs(got.astype(np.float64) - ref) <= sum_tolerance(k, [x]) + 1e-30).all()
+
+
+def test_reduce_middle_axis_with_map_and_broadcast(dev):
+    shape = [6, 50, 20]
+    a = rnd(shape, 11)
+    b = rnd([6, 1, 20], 12)
+    opb = D.Operand([20, 0, 1], 0, D.F32, 120)
+    k = D.reduce(shape, [D.contiguous(shape), opb], (w(0) - w(1)) * (w(0) - w(1)), D.R_SUM, 1)
+    got, _ = run_gpu(dev, k, [a, b])
+    assert (np.abs(got.astype(np.float64) - O.run(k, [a, b])) <= sum_tolerance(k, [a, b])).all()
+
+
+def test_long_single_row_split_sum(dev):
+    n = 1 << 22
+    x = rnd([1, n], 13)
+    k = D.reduce([1, n], [D.contiguous([1, n])], w(0) * w(0), D.R_SUM, 1)
+    got, kern = run_gpu(dev, k, [x])
+    assert kern.launches == 2 and kern.scratch_bytes > 0
+    exact = float((x.astype(np.float64) ** 2).sum())
+    assert abs(got[0] - exact) <= 1e-5 * exact
+    assert abs(O.run(k, [x])[0] - exact) <= 1e-3 * exact   # the sequential f32 loop drifts more
+
+
+def test_reduce_with_padded_input(dev):
+    x = rnd([6, 10], 14)
+    op = D.Operand([10, 1], -2, D.F32, 60, [D.Bound([0, 1], 0, 2, 12)], 0.0)
+    k = D.reduce([6, 14], [op], w(0), D.R_SUM, 1)
+    got, _ = run_gpu(dev, k, [x])
+    assert_close(got, O.run(k, [x]), rel=1e-5, abs_tol=1e-5)
+
+
+def test_softmax_pieces_over_ten_classes(dev):
+    # log_softmax (crates/nn/src/functional/activation.rs:174-187): max, sub+exp+sum
+    logits = rnd([512, 10], 15, -4, 4)
+    kmax = D.reduce([512, 10], [D.contiguous([512, 10])], w(0), D.R_MAX, 1)
+    m, _ = run_gpu(dev, kmax, [logits])
+    assert (m == logits.max(1)).all()
+    mb = D.Operand([1, 0], 0, D.F32, 512)
+    ksum = D.reduce([512, 10], [D.contiguous([512, 10]), mb], (w(0) - w(1)).exp(), D.R_SUM, 1)
+    s, _ = run_gpu(dev, ksum, [logits, m])
+    assert_close(s, O.run(ksum, [logits, m]), rel=1e-5)
+
+
+# ---- transposes -----------------------------------------------------------------------------
+
+@pytest.mark.parametrize("rows,cols", [(16, 16), (64, 64), (65, 63), (17, 300), (1000, 33), (512, 2048)])
+def test_transpose_bit_exact(dev, rows, cols):
+    x = rnd([rows, cols], rows + cols)
+    x.reshape(-1)[::97] = np.nan        # payload bits must survive too
+    k = W.cfg2_t(rows, cols)
+    got, kern = run_gpu(dev, k, [x])
+    assert kern.impl == "transpose_copy"
+    assert got.tobytes() == np.ascontiguousarray(x.T).tobytes()
+    assert got.tobytes() == O.run(k, [x]).tobytes()
+
+
+def test_batched_and_inner_permutes_bit_exact(dev):
+    x = rnd([3, 40, 5, 48], 16)
+    for perm in [(0, 3, 2, 1), (3, 0, 1, 2), (1, 0, 3, 2), (2, 3, 0, 1), (0, 2, 1, 3)]:
+        st = D.contiguous_strides(x.shape)
+        shape = [x.shape[p] for p in perm]
+        src = D.Operand([st[p] for p in perm], 0, D.F32, x.size)
+        k = D.elementwise(shape, [src], w(0))
+        got, _ = run_gpu(dev, k, [x])
+        assert got.tobytes() == np.ascontiguousarray(x.transpose(perm)).tobytes(), perm
+
+
+def test_conv_patch_permute_bit_exact(dev):
+    # [N,C,Ho,Wo,kh,kw] -> [N,Ho,Wo,C,kh,kw] (crates/nn/src/functional/conv.rs:150-158)
+    x = rnd([4, 8, 11, 11, 3, 3], 17)
+    perm = (0, 2, 3, 1, 4, 5)
+    st = D.contiguous_strides(x.shape)
+    shape = [x.shape[p] for p in perm]
+    k = D.elementwise(shape, [D.Operand([st[p] for p in perm], 0, D.F32, x.size)], w(0))
+    got, _ = run_gpu(dev, k, [x])
+    assert got.tobytes() == np.ascontiguousarray(x.transpose(perm)).tobytes()
+
+
+# ---- dense contraction ------------------------------------------------------------------------
+
+def gemm_check(dev, k, a, b, ref64, rel):
+    got, kern = run_gpu(dev, k, [a, b])
+    assert kern.impl.startswith("gemm")
+    scale = np.abs(a.astype(np.float64)).max() * np.abs(b.astype(np.float64)).max() * k.shape[k.reduce_axis]
+    err = np.abs(got.astype(np.float64) - ref64.reshape(-1)).max()
+    assert err <= rel * scale, (err, scale)
+    return got, kern
+
+
+def test_cfg1_matmul_512(dev):
+    """BASELINE config 1: A, B uniform[-1,1] from seed 0 (A first), 512^3."""
+    rng = np.random.default_rng(0)
+    a = rng.uniform(-1, 1, (512, 512)).astype(np.float32)
+    b = rng.uniform(-1, 1, (512, 512)).astype(np.float32)
+    k = W.matmul_desc(512, 512, 512)
+    got, _ = gemm_check(dev, k, a, b, a.astype(np.float64) @ b.astype(np.float64), 1e-6)
+    for fma in (False, True):           # both forms the reference's C backend can take
+        ref = O.run(k, [a, b], fma=fma)
+        assert_close(got, ref, rel=1e-5, abs_tol=1e-5 * np.sqrt(512) * 0.34)
+
+
+@pytest.mark.parametrize("m,k_,n", [(1, 1, 1), (5, 7, 3), (64, 16, 64), (65, 17, 66), (200, 300, 10), (1000, 9, 32)])
+def test_gemm_odd_shapes_all_forms(dev, m, k_, n):
+    a, b = rnd([m, k_], 20), rnd([k_, n], 21)
+    ref = a.astype(np.float64) @ b.astype(np.float64)
+    gemm_check(dev, W.matmul_desc(m, k_, n), a, b, ref, 1e-6)
+    # linear form: x[M,K] . W[N,K]^T
+    wt = np.ascontiguousarray(b.T)
+    gemm_check(dev, W.linear_desc(m, k_, n), a, wt, ref, 1e-6)
+
+
+def test_gemm_batched(dev):
+    a, b = rnd([6, 33, 20], 22), rnd([6, 20, 41], 23)
+    ref = np.einsum("bmk,bkn->bmn", a.astype(np.float64), b.astype(np.float64))
+    gemm_check(dev, W.matmul_desc(33, 20, 41, batch=6), a, b, ref, 1e-6)
+
+
+def test_gemm_weight_gradient_form(dev):
+    # dW[o,i] = sum_b dy[b,o] * x[b,i]  (VJP of linear: src/grad/rules.rs:196-222): reduce over axis 0
+    dy, x = rnd([50, 12], 24), rnd([50, 30], 25)
+    a = D.Operand([12, 1, 0], 0, D.F32, dy.size)
+    b = D.Operand([30, 0, 1], 0, D.F32, x.size)
+    k = D.reduce([50, 12, 30], [a, b], w(0) * w(1), D.R_SUM, 0)
+    gemm_check(dev, k, dy, x, dy.astype(np.float64).T @ x.astype(np.float64), 1e-6)
+
+
+# ---- scatter / sgd ---------------------------------------------------------------------------------
+
+def test_scatter_add_overlapping_windows(dev):
+    # fold of 3x3 stride-1 windows over [2,4,9,9] -> overlapping accumulation
+    n, c, h = 2, 4, 9
+    oh = h - 2
+    cols = rnd([n, c, oh, oh, 3, 3], 26)
+    out = D.Operand([c * h * h, h * h, h, 1, h, 1], 0, D.F32, n * c * h * h)
+    k = D.KernelDesc(D.K_SCATTER, list(cols.shape), [D.contiguous(cols.shape)], out)
+    got, _ = run_gpu(dev, k, [cols])
+    assert_close(got, O.run(k, [cols]), rel=1e-5, abs_tol=1e-5)
+
+
+@pytest.mark.parametrize("n", [1, 5, 4096, 225034])
+def test_sgd_update_bit_exact(dev, n):
+    p, g = rnd([n], 27), rnd([n], 28)
+    k = D.KernelDesc(D.K_SGD, [n], [D.contiguous([n]), D.contiguous([n])], D.contiguous([n]), scalar=1e-2)
+    got, _ = run_gpu(dev, k, [p, g])
+    lr = np.float32(1e-2)
+    assert got.tobytes() == (p - lr * g).astype(np.float32).tobytes()
+
+
+# ---- BASELINE config 2 at full size -------------------------------------------------------------------
+
+def test_cfg2_full_size(dev, registry):
+    x = W.cfg2_input()
+    c0, c1 = W.cfg2_consts()
+    ky, kz, kt = W.cfg2_y(), W.cfg2_z(), W.cfg2_t()
+    y, kern_y = run_gpu(dev, ky, [c0, x, c1])
+    z, kern_z = run_gpu(dev, kz, [x])
+    t, kern_t = run_gpu(dev, kt, [x])
+    assert kern_y.impl == "reduce_inner_t256_v4" and kern_y.specialised
+    assert kern_z.impl == "reduce_outer_v4_split" and kern_t.impl == "transpose_copy"
+    # oracle at full size (OpenMP form, same arithmetic per row)
+    y_ref = O.run(ky, [c0, x, c1], openmp=True)
+    tol = sum_tolerance(ky, [c0, x, c1])
+    assert (np.abs(y.astype(np.float64) - y_ref) <= tol).all()
+    y64 = O.eval_f64(ky, [c0, x, c1])
+    assert (np.abs(y - y64) <= tol).all() and (np.abs(y_ref - y64) <= tol).all()
+    assert (z == x.max(axis=0)).all()
+    assert t.tobytes() == np.ascontiguousarray(x.T).tobytes()
+    # size-independent properties: transposing twice is the identity; the max of
+    # the column maxima is the global max
+    tt, _ = run_gpu(dev, kt, [t])
+    assert tt.tobytes() == x.tobytes()
+    assert z.max() == x.max()

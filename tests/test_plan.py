@@ -1,0 +1,123 @@
+"""Kernel-class dispatch (descriptor -> hand-written kernel) checked on the CPU
+through eb200_kernel_query: classification, validation errors, collapsing."""
+import ctypes as C
+
+import pytest
+
+from harp_b200 import capi
+from harp_b200 import desc as D
+from harp_b200 import workloads as W
+from harp_b200.desc import Ast
+
+w = Ast.w
+
+
+def query(k: D.KernelDesc, sms: int = 148):
+    info = D.CKernelInfo()
+    cd = k.to_c()
+    capi.call("eb200_kernel_query", C.byref(cd), sms, C.byref(info))
+    return info
+
+
+def test_cfg2_row_sum_is_vectorised_cta_per_row_and_compiled():
+    i = query(W.cfg2_y())
+    assert i.impl.decode() == "reduce_inner_t256_v4"
+    assert i.specialised == 1 and i.launches == 1 and i.scratch_bytes == 0
+    assert i.algo_bytes == 4 * 8192 * 8192 + 4 * 8192 + 8   # x once, y once, two scalars
+
+
+def test_cfg2_col_max_splits_rows_into_scratch():
+    i = query(W.cfg2_z())
+    assert i.impl.decode() == "reduce_outer_v4_split"
+    assert i.launches == 2 and i.scratch_bytes > 0 and i.scratch_bytes % (8192 * 4) == 0
+    assert i.algo_bytes == 4 * 8192 * 8192 + 4 * 8192
+
+
+def test_cfg2_permute_is_a_transpose():
+    i = query(W.cfg2_t())
+    assert i.impl.decode() == "transpose_copy"
+    assert i.algo_bytes == 8 * 8192 * 8192
+
+
+def test_contiguous_elementwise_collapses_to_one_vector_dim():
+    k = D.elementwise([8, 16, 32], [D.contiguous([8, 16, 32])] * 2, w(0) + w(1))
+    assert query(k).impl.decode() == "ew_chain_v4"
+    k = D.elementwise([7, 3], [D.contiguous([7, 3])] * 2, w(0) + w(1))
+    assert query(k).impl.decode() == "ew_chain_v1"   # 21 elements: not a multiple of 4
+
+
+def test_unknown_expression_runs_on_the_interpreter():
+    e = (w(0).sin() * w(1).sqrt() + w(0)).floor()
+    k = D.elementwise([64], [D.contiguous([64])] * 2, e)
+    i = query(k)
+    assert i.impl.decode() == "ew_chain_v4" and i.specialised == 0
+
+
+def test_matmul_spelled_as_broadcast_mul_sum_is_a_gemm():
+    for k in (W.matmul_desc(512, 512, 512), W.linear_desc(64, 32, 16), W.matmul_desc(64, 32, 48, batch=4)):
+        i = query(k)
+        assert i.impl.decode().startswith("gemm"), i.impl
+    i = query(W.matmul_desc(512, 512, 512))
+    assert i.algo_flops == 2 * 512 ** 3
+
+
+def test_small_rows_use_thread_or_warp_per_row():
+    k = D.reduce([1000, 10], [D.contiguous([1000, 10])], w(0), D.R_MAX, 1)
+    assert query(k).impl.decode() == "reduce_inner_t1_v1"
+    k = D.reduce([1000, 1024], [D.contiguous([1000, 1024])], w(0), D.R_SUM, 1)
+    assert query(k).impl.decode() == "reduce_inner_t32_v4"
+
+
+def test_long_single_row_is_split():
+    n = 1 << 24
+    k = D.reduce([1, n], [D.contiguous([1, n])], w(0), D.R_SUM, 1)
+    i = query(k)
+    assert i.impl.decode() == "reduce_inner_t256_v4_split" and i.launches == 2 and i.scratch_bytes > 0
+
+
+def test_out_of_range_store_is_rejected_not_faulted():
+    # a sliced/offset store view that would index past the allocation
+    out = D.Operand([1], 8, D.F32, 16)
+    k = D.elementwise([16], [D.contiguous([16])], w(0), out=out)
+    with pytest.raises(capi.Eb200Error) as e:
+        query(k)
+    assert e.value.status == capi.ERR_BOUNDS
+
+
+def test_out_of_range_load_is_rejected():
+    src = D.Operand([2], 0, D.F32, 16)
+    k = D.elementwise([16], [src], w(0))
+    with pytest.raises(capi.Eb200Error) as e:
+        query(k)
+    assert e.value.status == capi.ERR_BOUNDS
+
+
+def test_malformed_program_is_invalid():
+    k = D.elementwise([16], [D.contiguous([16])], w(0) + w(1))   # loads input 1 of 1
+    with pytest.raises(capi.Eb200Error) as e:
+        query(k)
+    assert e.value.status == capi.ERR_INVALID
+
+
+def test_trivially_true_bounds_are_dropped():
+    # conv2d always pads, even with padding 0 (crates/nn/src/functional/conv.rs:142):
+    # the mask is kept by View::padded but can never fail
+    op = D.Operand([1], 0, D.F32, 64, [D.Bound([1], 0, 0, 64)], 0.0)
+    k = D.elementwise([64], [op], w(0) * D.Ast.const(2.0))
+    assert query(k).impl.decode() == "ew_chain_v4"
+    op = D.Operand([1], -1, D.F32, 64, [D.Bound([1], 0, 1, 65)], 0.0)
+    k = D.elementwise([66], [op], w(0) * D.Ast.const(2.0))
+    assert query(k).impl.decode() == "ew_chain_v1"
+
+
+def test_broadcast_operand_keeps_vector_path():
+    bias = D.Operand([0, 1], 0, D.F32, 32)
+    k = D.elementwise([128, 32], [D.contiguous([128, 32]), bias], w(0) + w(1))
+    assert query(k).impl.decode() == "ew_chain_v4"
+
+
+def test_i64_is_unsupported_not_miscomputed():
+    k = D.elementwise([16], [D.contiguous([16], D.I64)], w(0), out_dtype=D.I64)
+    with pytest.raises(capi.Eb200Error) as e:
+        query(k)
+    assert e.value.status == capi.ERR_UNSUPPORTED
