@@ -89,6 +89,7 @@ struct KParams {
     KBound bounds[KMAX_BOUNDS];
     KInsn prog[KMAX_INSNS];
     float consts[KMAX_CONSTS];
+    const float* cptr[KMAX_CONSTS];  // non-null: constant slot is read from a one-element tensor
 };
 
 // ---- host objects ------------------------------------------------------------
@@ -170,7 +171,10 @@ struct Plan {
     int64_t algo_bytes = 0, algo_flops = 0;
     int launches = 1;
     float scalar = 0.f;
-    int n_inputs = 0;
+    int n_inputs = 0;         // inputs of the descriptor
+    int perm[KMAX_IN] = {0};  // kernel operand c is descriptor input perm[c]
+    int dyn_input[KMAX_CONSTS];   // constant slot j is read from descriptor input dyn_input[j] (-1: literal)
+    long long dyn_offset[KMAX_CONSTS] = {0};
     int in_dtype[KMAX_IN] = {0};
     int64_t in_numel[KMAX_IN] = {0};
     int out_dtype = 0;
@@ -182,7 +186,7 @@ struct Plan {
 int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan);
 
 // chains: compiled functors for known map programs (chains.cu)
-int find_chain(const KInsn* prog, int n_insns, float* consts, int* n_consts);
+int find_chain(const KInsn* prog, int n_insns);
 int chain_count();
 const char* chain_name(int chain);
 

@@ -116,7 +116,7 @@ int launch_transpose(Device* dev, const Plan& plan, const void* in, void* out) {
     q.tiles = batch * q.tiles_r * q.tiles_c;
     if (q.tiles <= 0) return EB200_OK;
     long long blocks = q.tiles;
-    const long long cap = (long long)dev->prop.multiProcessorCount * 64;
+    const long long cap = (1LL << 31) - 1;
     if (blocks > cap) blocks = cap;
     transpose_kernel<<<(unsigned)blocks, 256, 0, dev->stream>>>(q, reinterpret_cast<const uint32_t*>(in),
                                                                reinterpret_cast<uint32_t*>(out));

@@ -4,78 +4,95 @@
 // The reference renders a scalar nested loop per arithmetic node.  Here one
 // launch evaluates a whole composed chain: each thread owns 4 consecutive
 // elements along the innermost collapsed dim and moves them with 128-bit
-// loads/stores; broadcast operands (stride 0) are read once per vector.
+// loads/stores, four such vectors in flight per thread; broadcast operands
+// (stride 0) are read once per vector and one-element operands once per thread.
+// The kernel is instantiated per collapsed rank (1, 2, 3, any) so the common
+// cases carry no index arithmetic beyond what their rank needs.
 // HBM-bound: algorithmic bytes = 4 B x (elements read + elements written).
 #include "expr.cuh"
 #include "index.cuh"
 
 namespace eb200 {
 
-template <class F>
+constexpr int EW_U = 4;  // independent 128-bit vectors in flight per thread
+
+template <class F, int ND>
 __device__ __forceinline__ void load_vec4(const KParams& p, long long e, float (*in)[4]) {
     long long idx[KMAX_DIMS];
-    decompose(p, e, idx);
-    const int inner = p.ndim - 1;
+    if (ND != 1) decompose<ND>(p, e, idx);
+    const int inner = ND > 0 ? ND - 1 : p.ndim - 1;
     const int n = F::nin(p);
 #pragma unroll
     for (int i = 0; i < (F::kCompiled ? n : KMAX_IN); ++i) {
         if (i >= n) break;
         const KOperand& o = p.in[i];
-        long long a = operand_index(p, o, idx);
+        const long long a = ND == 1 ? o.offset + e * o.strides[0] : operand_index<ND>(p, o, idx);
         const float* src = reinterpret_cast<const float*>(o.ptr) + a;
         if (o.strides[inner] == 1) {
-            float4 t = __ldg(reinterpret_cast<const float4*>(src));
+            const float4 t = __ldg(reinterpret_cast<const float4*>(src));
             in[i][0] = t.x; in[i][1] = t.y; in[i][2] = t.z; in[i][3] = t.w;
         } else {
-            float t = __ldg(src);
+            const float t = __ldg(src);
             in[i][0] = t; in[i][1] = t; in[i][2] = t; in[i][3] = t;
         }
     }
 }
 
+template <int ND>
 __device__ __forceinline__ void store_vec4(const KParams& p, long long e, const float* v) {
-    long long idx[KMAX_DIMS];
-    decompose(p, e, idx);
-    long long a = operand_index(p, p.out, idx);
+    long long a;
+    if (ND == 1) {
+        a = p.out.offset + e;
+    } else {
+        long long idx[KMAX_DIMS];
+        decompose<ND>(p, e, idx);
+        a = operand_index<ND>(p, p.out, idx);
+    }
     *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out.ptr) + a) = make_float4(v[0], v[1], v[2], v[3]);
 }
 
-template <class F>
+template <class F, int ND>
 __global__ void __launch_bounds__(256) ew_kernel(const __grid_constant__ KParams p) {
-    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long stride = (long long)gridDim.x * blockDim.x;
+    const int n = F::nin(p);
+    float cl[F::kNconst];
+    load_consts<F>(p, cl);
     if (p.vec == 4) {
         const long long nvec = p.total >> 2;
-        for (long long v0 = tid; v0 < nvec; v0 += 2 * stride) {
-            const long long v1 = v0 + stride;
-            const bool has1 = v1 < nvec;
-            float in0[KMAX_IN][4], in1[KMAX_IN][4];
-            float r0[4], r1[4];
-            load_vec4<F>(p, v0 << 2, in0);
-            if (has1) load_vec4<F>(p, v1 << 2, in1);
-            F::template eval<4>(p, in0, r0);
-            store_vec4(p, v0 << 2, r0);
-            if (has1) {
-                F::template eval<4>(p, in1, r1);
-                store_vec4(p, v1 << 2, r1);
+        // a CTA owns EW_U consecutive 4 KB segments per iteration
+        for (long long v0 = ((long long)blockIdx.x * EW_U) * blockDim.x + threadIdx.x; v0 < nvec; v0 += EW_U * stride) {
+            float in[EW_U][KMAX_IN][4];
+#pragma unroll
+            for (int u = 0; u < EW_U; ++u) {
+                const long long v = v0 + (long long)u * blockDim.x;
+                if (v < nvec) load_vec4<F, ND>(p, v << 2, in[u]);
+            }
+#pragma unroll
+            for (int u = 0; u < EW_U; ++u) {
+                const long long v = v0 + (long long)u * blockDim.x;
+                if (v < nvec) {
+                    float r[4];
+                    F::template eval<4>(p, in[u], r, cl);
+                    store_vec4<ND>(p, v << 2, r);
+                }
             }
         }
     } else {
-        const int n = F::nin(p);
+        const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
         for (long long e = tid; e < p.total; e += stride) {
             long long idx[KMAX_DIMS];
-            decompose(p, e, idx);
+            decompose<ND>(p, e, idx);
             float in[KMAX_IN][1];
 #pragma unroll
             for (int i = 0; i < (F::kCompiled ? n : KMAX_IN); ++i) {
                 if (i >= n) break;
                 const KOperand& o = p.in[i];
                 if (o.n_bounds && !bounds_ok(p, o, idx)) in[i][0] = o.pad;
-                else in[i][0] = load_elem(o, operand_index(p, o, idx));
+                else in[i][0] = load_elem(o, operand_index<ND>(p, o, idx));
             }
             float r[1];
-            F::template eval<1>(p, in, r);
-            store_elem(p.out, operand_index(p, p.out, idx), r[0]);
+            F::template eval<1>(p, in, r, cl);
+            store_elem(p.out, operand_index<ND>(p, p.out, idx), r[0]);
         }
     }
 }
@@ -84,11 +101,18 @@ template <class F>
 static int launch_one(Device* dev, const KParams& p) {
     long long work = p.vec == 4 ? (p.total >> 2) : p.total;
     if (work <= 0) return EB200_OK;
-    long long per_block = 256LL * (p.vec == 4 ? 2 : 1);
+    long long per_block = 256LL * (p.vec == 4 ? EW_U : 1);
     long long blocks = (work + per_block - 1) / per_block;
-    long long cap = (long long)dev->prop.multiProcessorCount * 16;
+    long long cap = (long long)dev->prop.multiProcessorCount * 32;
     if (blocks > cap) blocks = cap;
-    ew_kernel<F><<<(unsigned)blocks, 256, 0, dev->stream>>>(p);
+    const int nd = (p.total < (1LL << 31) && p.ndim <= 3) ? p.ndim : 0;
+    const unsigned g = (unsigned)blocks;
+    switch (nd) {
+        case 1: ew_kernel<F, 1><<<g, 256, 0, dev->stream>>>(p); break;
+        case 2: ew_kernel<F, 2><<<g, 256, 0, dev->stream>>>(p); break;
+        case 3: ew_kernel<F, 3><<<g, 256, 0, dev->stream>>>(p); break;
+        default: ew_kernel<F, 0><<<g, 256, 0, dev->stream>>>(p); break;
+    }
     count_launch();
     EB_CHECK_CUDA(cudaGetLastError());
     return EB200_OK;

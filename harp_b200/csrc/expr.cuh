@@ -72,10 +72,12 @@ __device__ __forceinline__ bool bounds_ok(const KParams& p, const KOperand& o, c
 // ---- bytecode interpreter ---------------------------------------------------------
 struct Interp {
     static constexpr bool kCompiled = false;
+    static constexpr int kNin = KMAX_IN;
+    static constexpr int kNconst = KMAX_CONSTS;
     __device__ __forceinline__ static int nin(const KParams& p) { return p.n_in; }
 
     template <int V>
-    __device__ static void eval(const KParams& p, const float (*in)[V], float* out) {
+    __device__ static void eval(const KParams& p, const float (*in)[V], float* out, const float* cl) {
         float st[KSTACK][V];
         int sp = 0;
         for (int pc = 0; pc < p.n_insns; ++pc) {
@@ -87,7 +89,7 @@ struct Interp {
                     ++sp; break;
                 case EB200_OP_CONST:
 #pragma unroll
-                    for (int v = 0; v < V; ++v) st[sp][v] = ins.imm;
+                    for (int v = 0; v < V; ++v) st[sp][v] = cl[ins.arg];
                     ++sp; break;
 #define EB_BIN(OPC, EXPR)                                                       \
     case OPC:                                                                   \
@@ -145,21 +147,34 @@ struct Interp {
 template <class C>
 struct Compiled {
     static constexpr bool kCompiled = true;
+    static constexpr int kNin = C::NIN > 0 ? C::NIN : 1;
+    static constexpr int kNconst = C::NCONST > 0 ? C::NCONST : 1;
     __device__ __forceinline__ static int nin(const KParams&) { return C::NIN; }
 
     template <int V>
-    __device__ __forceinline__ static void eval(const KParams& p, const float (*in)[V], float* out) {
+    __device__ __forceinline__ static void eval(const KParams& p, const float (*in)[V], float* out, const float* cl) {
 #pragma unroll
         for (int v = 0; v < V; ++v) {
             float w[C::NIN > 0 ? C::NIN : 1];
 #pragma unroll
             for (int i = 0; i < C::NIN; ++i) w[i] = in[i][v];
-            out[v] = C::f(w, p.consts);
+            out[v] = C::f(w, cl);
         }
     }
 };
 
 #include "chains_gen.inc"
+
+// Constant table of a launch: literal constants of the map, and one-element
+// tensor operands, which the plan turns into constants read once per thread.
+template <class F>
+__device__ __forceinline__ void load_consts(const KParams& p, float* cl) {
+#pragma unroll
+    for (int j = 0; j < F::kNconst; ++j) {
+        cl[j] = 0.0f;
+        if (j < p.n_consts) cl[j] = p.cptr[j] ? __ldg(p.cptr[j]) : p.consts[j];
+    }
+}
 
 // Reduce combiners (src/graph/node.rs:29-77).
 template <int ROP> struct Red;

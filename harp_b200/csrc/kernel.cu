@@ -16,7 +16,7 @@ namespace eb200 {
 int chain_count() { return EB_CHAIN_COUNT; }
 const char* chain_name(int chain) { return chain >= 0 && chain < EB_CHAIN_COUNT ? chain_table[chain].name : "interpreter"; }
 
-int find_chain(const KInsn* prog, int n_insns, float* consts, int* n_consts) {
+int find_chain(const KInsn* prog, int n_insns) {
     for (int c = 0; c < EB_CHAIN_COUNT; ++c) {
         const ChainEntry& e = chain_table[c];
         if (e.n != n_insns) continue;
@@ -25,17 +25,8 @@ int find_chain(const KInsn* prog, int n_insns, float* consts, int* n_consts) {
             if (e.prog[i].op != prog[i].op) same = false;
             else if (prog[i].op != EB200_OP_CONST && e.prog[i].arg != prog[i].arg) same = false;
         }
-        if (!same) continue;
-        int nc = 0;
-        for (int i = 0; i < n_insns; ++i)
-            if (prog[i].op == EB200_OP_CONST) {
-                if (nc >= KMAX_CONSTS) return -1;
-                consts[nc++] = prog[i].imm;
-            }
-        *n_consts = nc;
-        return c;
+        if (same) return c;
     }
-    *n_consts = 0;
     return -1;
 }
 
@@ -116,7 +107,11 @@ int eb200_kernel_launch(eb200_kernel* k, eb200_buffer* const* inputs, int n_inpu
                    "input %d aliases the output", i);
 
     KParams p = plan.p;
-    for (int i = 0; i < n_inputs; ++i) p.in[i].ptr = reinterpret_cast<char*>(inputs[i]->storage->ptr);
+    for (int c = 0; c < p.n_in; ++c) p.in[c].ptr = reinterpret_cast<char*>(inputs[plan.perm[c]]->storage->ptr);
+    for (int j = 0; j < p.n_consts; ++j)
+        p.cptr[j] = plan.dyn_input[j] >= 0
+                        ? reinterpret_cast<const float*>(inputs[plan.dyn_input[j]]->storage->ptr) + plan.dyn_offset[j]
+                        : nullptr;
     p.out.ptr = reinterpret_cast<char*>(ob->storage->ptr);
     void* scratch = k->scratch ? k->scratch->ptr : nullptr;
     switch (plan.impl) {

@@ -209,6 +209,14 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
             q.bounds.push_back(nb);
         }
     }
+    if (nk == 0) {  // a single element: keep one extent-1 dim so kernels always have a rank
+        nk = 1;
+        shape[0] = 1;
+        for (auto& q : ops) {
+            q.strides[0] = 0;
+            for (auto& b : q.bounds) b.coef[0] = 0;
+        }
+    }
     // collapse dim j (outer) into j+1 (inner) when every operand walks them as one
     for (int j = nk - 2; j >= 0; --j) {
         if (j == raxis || j + 1 == raxis) continue;
@@ -307,14 +315,92 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
         return true;
     };
 
+    // ---- one-element f32 operands become launch-time constants (read once per
+    //      thread instead of once per element); the remaining operands are
+    //      renumbered by first use in the map, so equal expressions meet the
+    //      same compiled functor whatever order their inputs were declared in
+    for (int j = 0; j < KMAX_CONSTS; ++j) pl.dyn_input[j] = -1;
+    for (int i = 0; i < KMAX_IN; ++i) pl.perm[i] = i;
+    if (d->kclass == EB200_K_ELEMENTWISE || d->kclass == EB200_K_REDUCE) {
+        KOperand old_in[KMAX_IN];
+        for (int i = 0; i < KMAX_IN; ++i) old_in[i] = p.in[i];
+        // (1) expression tree from the postfix program; one-element loads marked constant
+        struct Node { short op, arg; float imm; int kid[3]; int nk; int dyn; };
+        std::vector<Node> nodes;
+        std::vector<int> stack;
+        for (int pc = 0; pc < p.n_insns; ++pc) {
+            const KInsn& ins = p.prog[pc];
+            Node nd{ins.op, ins.arg, ins.imm, {-1, -1, -1}, 0, -1};
+            int pop = 0;
+            switch (ins.op) {
+                case EB200_OP_LOAD: {
+                    const KOperand& ko = old_in[ins.arg];
+                    bool one = ko.dtype == EB200_F32 && ko.n_bounds == 0;
+                    for (int j = 0; j < nk && one; ++j) one = ko.strides[j] == 0;
+                    if (one) { nd.op = EB200_OP_CONST; nd.dyn = ins.arg; }
+                    break;
+                }
+                case EB200_OP_CONST: break;
+                case EB200_OP_SELECT: case EB200_OP_FMA: pop = 3; break;
+                case EB200_OP_RECIP: case EB200_OP_SQRT: case EB200_OP_LOG2: case EB200_OP_EXP2:
+                case EB200_OP_SIN: case EB200_OP_FLOOR: case EB200_OP_NOT: case EB200_OP_CAST: pop = 1; break;
+                default: pop = 2; break;
+            }
+            nd.nk = pop;
+            for (int c = pop - 1; c >= 0; --c) { nd.kid[c] = stack.back(); stack.pop_back(); }
+            // (2) commutative ops: constant operand last
+            if (pop == 2 && (nd.op == EB200_OP_ADD || nd.op == EB200_OP_MUL || nd.op == EB200_OP_MAX) &&
+                nodes[nd.kid[0]].op == EB200_OP_CONST && nodes[nd.kid[1]].op != EB200_OP_CONST)
+                std::swap(nd.kid[0], nd.kid[1]);
+            nodes.push_back(nd);
+            stack.push_back((int)nodes.size() - 1);
+        }
+        // (3) re-emit: inputs renumbered by first use, constants given slots in order
+        int canon[KMAX_IN];
+        for (int i = 0; i < KMAX_IN; ++i) canon[i] = -1;
+        int n_kin = 0, nc = 0, n_out = 0;
+        bool too_many = false;
+        std::vector<int> order;   // iterative post-order
+        {
+            std::vector<std::pair<int, int>> st;
+            st.push_back({stack.back(), 0});
+            while (!st.empty()) {
+                auto& top = st.back();
+                const Node& nd = nodes[top.first];
+                if (top.second < nd.nk) { int k = nd.kid[top.second++]; st.push_back({k, 0}); }
+                else { order.push_back(top.first); st.pop_back(); }
+            }
+        }
+        for (int id : order) {
+            const Node& nd = nodes[id];
+            KInsn ins{nd.op, nd.arg, nd.imm};
+            if (nd.op == EB200_OP_LOAD) {
+                const int i = nd.arg;
+                if (canon[i] < 0) { canon[i] = n_kin; pl.perm[n_kin] = i; p.in[n_kin] = old_in[i]; ++n_kin; }
+                ins.arg = (short)canon[i];
+            } else if (nd.op == EB200_OP_CONST) {
+                if (nc >= KMAX_CONSTS) { too_many = true; break; }
+                ins.arg = (short)nc;
+                if (nd.dyn >= 0) { pl.dyn_input[nc] = nd.dyn; pl.dyn_offset[nc] = old_in[nd.dyn].offset; p.consts[nc] = 0.0f; ins.imm = 0.0f; }
+                else p.consts[nc] = nd.imm;
+                ++nc;
+            }
+            p.prog[n_out++] = ins;
+        }
+        EB_REQUIRE(!too_many, EB200_ERR_UNSUPPORTED, "map uses more than %d constants", KMAX_CONSTS);
+        p.n_insns = n_out;
+        p.n_in = n_kin;
+        p.n_consts = nc;
+    }
+
     // ---- classify
-    const bool identity = p.n_insns == 1 && p.prog[0].op == EB200_OP_LOAD;
+    const bool identity = p.n_insns == 1 && p.prog[0].op == EB200_OP_LOAD && p.n_in == 1;
     switch (d->kclass) {
         case EB200_K_SGD: {
             EB_REQUIRE(d->n_inputs == 2 && nk <= 1, EB200_ERR_UNSUPPORTED, "sgd kernel wants two flat f32 inputs");
             for (int i = 0; i < 2; ++i)
-                EB_REQUIRE(p.in[i].dtype == EB200_F32 && (nk == 0 || p.in[i].strides[0] == 1), EB200_ERR_UNSUPPORTED, "sgd operands must be flat f32");
-            EB_REQUIRE(p.out.dtype == EB200_F32 && (nk == 0 || p.out.strides[0] == 1), EB200_ERR_UNSUPPORTED, "sgd output must be flat f32");
+                EB_REQUIRE(p.in[i].dtype == EB200_F32 && (total <= 1 || p.in[i].strides[0] == 1), EB200_ERR_UNSUPPORTED, "sgd operands must be flat f32");
+            EB_REQUIRE(p.out.dtype == EB200_F32 && (total <= 1 || p.out.strides[0] == 1), EB200_ERR_UNSUPPORTED, "sgd output must be flat f32");
             pl.impl = IMPL_SGD;
             snprintf(pl.name, sizeof(pl.name), "sgd_update");
             break;
@@ -353,7 +439,7 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
             } else {
                 int inner = nk - 1;
                 bool v = nk >= 1 && shape[inner] % 4 == 0 && vec_ok(p.out, inner, true);
-                for (int i = 0; v && i < d->n_inputs; ++i) v = vec_ok(p.in[i], inner, false);
+                for (int i = 0; v && i < p.n_in; ++i) v = vec_ok(p.in[i], inner, false);
                 p.vec = v ? 4 : 1;
                 snprintf(pl.name, sizeof(pl.name), "ew_chain_v%d", p.vec);
             }
@@ -369,9 +455,13 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
             if (raxis == nk - 1) {
                 pl.impl = IMPL_REDUCE_INNER;
                 bool v = p.rlen % 4 == 0 && p.rlen >= 4;
-                for (int i = 0; v && i < d->n_inputs; ++i) v = vec_ok(p.in[i], raxis, false);
+                for (int i = 0; v && i < p.n_in; ++i) v = vec_ok(p.in[i], raxis, false);
                 p.vec = v ? 4 : 1;
-                pl.threads_per_row = p.rlen <= 64 ? 1 : (p.rlen <= 4096 ? 32 : 256);
+                pl.threads_per_row = p.rlen <= 64 ? 1 : (p.rlen <= 16384 ? 32 : 256);
+                // tuning override (desc.flags bits 0-1): 1 -> thread, 2 -> warp, 3 -> CTA per row
+                if ((d->flags & 3) == 1) pl.threads_per_row = 1;
+                if ((d->flags & 3) == 2) pl.threads_per_row = 32;
+                if ((d->flags & 3) == 3) pl.threads_per_row = 256;
                 // few long rows: split each row over several CTAs, finish in a second pass
                 long long ctas = pl.threads_per_row == 256 ? p.kept : 0;
                 if (pl.threads_per_row == 256 && ctas < 2LL * sm_count && p.rlen >= 65536) {
@@ -393,13 +483,14 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
                 pl.impl = IMPL_REDUCE_OUTER;
                 int inner = nk - 1;
                 bool v = shape[inner] % 4 == 0 && vec_ok(p.out, inner, true);
-                for (int i = 0; v && i < d->n_inputs; ++i) v = vec_ok(p.in[i], inner, false);
+                for (int i = 0; v && i < p.n_in; ++i) v = vec_ok(p.in[i], inner, false);
                 p.vec = v ? 4 : 1;
                 // enough thread blocks to fill the machine: split the reduce dim
                 long long threads = p.kept / p.vec;
                 long long blocks = (threads + 255) / 256;
                 if (blocks < 4LL * sm_count && p.rlen >= 64) {
-                    long long want = (8LL * sm_count + blocks - 1) / std::max(1LL, blocks);
+                    // one full wave: 4 resident CTAs per SM, all with equal work
+                    long long want = (4LL * sm_count) / std::max(1LL, blocks);
                     int s = (int)std::max(1LL, std::min(want, std::min(p.rlen / 16, 1024LL)));
                     if (s > 1) {
                         long long chunk = (p.rlen + s - 1) / s;
@@ -416,7 +507,7 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
         }
     }
     if (pl.impl == IMPL_EW || pl.impl == IMPL_REDUCE_INNER || pl.impl == IMPL_REDUCE_OUTER) {
-        pl.chain = find_chain(p.prog, p.n_insns, p.consts, &p.n_consts);
+        pl.chain = find_chain(p.prog, p.n_insns);
     }
     return EB200_OK;
 }

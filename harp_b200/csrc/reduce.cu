@@ -7,10 +7,12 @@
 //
 //  reduce_inner  the reduce dim is the innermost collapsed dim (contiguous
 //                rows).  A group of T threads (1, a warp, or a 256-thread CTA)
-//                walks one row with 128-bit loads, evaluates the map, and
-//                combines through warp shuffles and a shared-memory tree.
-//                Few very long rows are split over several CTAs into scratch
-//                partials and finished by reduce_finish.
+//                walks one row with 128-bit loads, four in flight per thread,
+//                evaluates the map, and combines through warp shuffles and a
+//                shared-memory tree.  Operands that do not move along the row
+//                (stride 0) are read once per row.  Few very long rows are
+//                split over several CTAs into scratch partials and finished by
+//                reduce_finish.
 //  reduce_outer  the reduce dim is strided (e.g. max over axis 0): each thread
 //                owns 4 adjacent kept elements, so a warp reads 512 contiguous
 //                bytes per reduce step; the reduce dim is split over
@@ -49,27 +51,26 @@ __device__ __forceinline__ float group_reduce(float v, int rop, float* smem) {
     return v;
 }
 
-// One input vector of 4 consecutive reduce-dim elements starting at element
-// address `a`, or a broadcast scalar when the operand does not move along it.
-__device__ __forceinline__ void load4(const KOperand& o, long long a, long long rstride, float* dst) {
-    const float* src = reinterpret_cast<const float*>(o.ptr) + a;
-    if (rstride == 1) {
-        float4 t = __ldg(reinterpret_cast<const float4*>(src));
-        dst[0] = t.x; dst[1] = t.y; dst[2] = t.z; dst[3] = t.w;
-    } else {
-        float t = __ldg(src);
-        dst[0] = t; dst[1] = t; dst[2] = t; dst[3] = t;
-    }
+__device__ __forceinline__ void ldg4(const float* src, float* dst) {
+    const float4 t = __ldg(reinterpret_cast<const float4*>(src));
+    dst[0] = t.x; dst[1] = t.y; dst[2] = t.z; dst[3] = t.w;
 }
+
+__device__ __forceinline__ void splat4(float v, float* dst) { dst[0] = v; dst[1] = v; dst[2] = v; dst[3] = v; }
+
+constexpr int RI_U = 4;  // independent 128-bit loads in flight per thread and operand
 
 template <class F, int T>
 __global__ void __launch_bounds__(256) reduce_inner_kernel(const __grid_constant__ KParams p, float* __restrict__ scratch) {
     __shared__ float smem[8];
     constexpr int ROWS = 256 / T;
+    constexpr int NI = F::kCompiled ? F::kNin : KMAX_IN;
     const int lane = threadIdx.x % T;
     const int sub = threadIdx.x / T;
     const int ra = p.raxis;
     const int n = F::nin(p);
+    float cl[F::kNconst];
+    load_consts<F>(p, cl);
     const long long work = p.kept * p.splits;  // (row, split) pairs
     const long long nblk = (work + ROWS - 1) / ROWS;
     for (long long blk = blockIdx.x; blk < nblk; blk += gridDim.x) {
@@ -85,49 +86,67 @@ __global__ void __launch_bounds__(256) reduce_inner_kernel(const __grid_constant
         float acc = red_identity(p.rop);
         if (live) {
             if (p.vec == 4) {
-                long long base[KMAX_IN];
+                // per row: a pointer for operands that walk the row, a value for those that do not
+                const float* rp[NI];
+                float rc[NI];
+                bool moves[NI];
 #pragma unroll
-                for (int i = 0; i < (F::kCompiled ? n : KMAX_IN); ++i) {
+                for (int i = 0; i < NI; ++i) {
                     if (i >= n) break;
-                    base[i] = operand_index(p, p.in[i], idx);
+                    const float* b = reinterpret_cast<const float*>(p.in[i].ptr) + operand_index(p, p.in[i], idx);
+                    moves[i] = p.in[i].strides[ra] == 1;
+                    rp[i] = b;
+                    rc[i] = moves[i] ? 0.0f : __ldg(b);
                 }
                 float a4[4];
 #pragma unroll
                 for (int v = 0; v < 4; ++v) a4[v] = acc;
                 const long long step = (long long)T * 4;
-                for (long long c0 = r0 + lane * 4; c0 < r1; c0 += 2 * step) {
-                    const long long c1 = c0 + step;
-                    const bool has1 = c1 < r1;
-                    float in0[KMAX_IN][4], in1[KMAX_IN][4], v0[4], v1[4];
+                long long c = r0 + lane * 4;
+                for (; c + (RI_U - 1) * step < r1; c += RI_U * step) {
+                    float in[RI_U][NI][4];
 #pragma unroll
-                    for (int i = 0; i < (F::kCompiled ? n : KMAX_IN); ++i) {
+                    for (int u = 0; u < RI_U; ++u) {
+#pragma unroll
+                        for (int i = 0; i < NI; ++i) {
+                            if (i >= n) break;
+                            if (moves[i]) ldg4(rp[i] + c + u * step, in[u][i]);
+                            else splat4(rc[i], in[u][i]);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < RI_U; ++u) {
+                        float v4[4];
+                        F::template eval<4>(p, in[u], v4, cl);
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) a4[v] = red_combine(p.rop, a4[v], v4[v]);
+                    }
+                }
+                for (; c < r1; c += step) {
+                    float in[NI][4], v4[4];
+#pragma unroll
+                    for (int i = 0; i < NI; ++i) {
                         if (i >= n) break;
-                        const long long rs = p.in[i].strides[ra];
-                        load4(p.in[i], base[i] + c0 * rs, rs, in0[i]);
-                        if (has1) load4(p.in[i], base[i] + c1 * rs, rs, in1[i]);
+                        if (moves[i]) ldg4(rp[i] + c, in[i]);
+                        else splat4(rc[i], in[i]);
                     }
-                    F::template eval<4>(p, in0, v0);
+                    F::template eval<4>(p, in, v4, cl);
 #pragma unroll
-                    for (int v = 0; v < 4; ++v) a4[v] = red_combine(p.rop, a4[v], v0[v]);
-                    if (has1) {
-                        F::template eval<4>(p, in1, v1);
-#pragma unroll
-                        for (int v = 0; v < 4; ++v) a4[v] = red_combine(p.rop, a4[v], v1[v]);
-                    }
+                    for (int v = 0; v < 4; ++v) a4[v] = red_combine(p.rop, a4[v], v4[v]);
                 }
                 acc = red_combine(p.rop, red_combine(p.rop, a4[0], a4[1]), red_combine(p.rop, a4[2], a4[3]));
             } else {
                 for (long long c = r0 + lane; c < r1; c += T) {
                     set_idx(idx, ra, c);
-                    float in[KMAX_IN][1], v[1];
+                    float in[NI][1], v[1];
 #pragma unroll
-                    for (int i = 0; i < (F::kCompiled ? n : KMAX_IN); ++i) {
+                    for (int i = 0; i < NI; ++i) {
                         if (i >= n) break;
                         const KOperand& o = p.in[i];
                         if (o.n_bounds && !bounds_ok(p, o, idx)) in[i][0] = o.pad;
                         else in[i][0] = load_elem(o, operand_index(p, o, idx));
                     }
-                    F::template eval<1>(p, in, v);
+                    F::template eval<1>(p, in, v, cl);
                     acc = red_combine(p.rop, acc, v[0]);
                 }
                 set_idx(idx, ra, 0);
@@ -141,10 +160,15 @@ __global__ void __launch_bounds__(256) reduce_inner_kernel(const __grid_constant
     }
 }
 
+constexpr int RO_U = 4;  // reduce steps in flight per thread
+
 template <class F>
 __global__ void __launch_bounds__(256) reduce_outer_kernel(const __grid_constant__ KParams p, float* __restrict__ scratch) {
+    constexpr int NI = F::kCompiled ? F::kNin : KMAX_IN;
     const int ra = p.raxis;
     const int n = F::nin(p);
+    float cl[F::kNconst];
+    load_consts<F>(p, cl);
     const int split = blockIdx.y;
     const long long r0 = (long long)split * p.chunk;
     long long r1 = r0 + p.chunk;
@@ -156,62 +180,72 @@ __global__ void __launch_bounds__(256) reduce_outer_kernel(const __grid_constant
         long long idx[KMAX_DIMS];
         decompose(p, k, idx, ra);
         if (p.vec == 4) {
-            long long base[KMAX_IN];
-#pragma unroll
-            for (int i = 0; i < (F::kCompiled ? n : KMAX_IN); ++i) {
-                if (i >= n) break;
-                base[i] = operand_index(p, p.in[i], idx);
-            }
             const int inner = p.ndim - 1;
+            // per thread: operands are a vector along the kept dim, or one value
+            // broadcast over it; each may or may not move with the reduce index
+            const float* bp[NI];
+            long long rs[NI];
+            bool isvec[NI];
+#pragma unroll
+            for (int i = 0; i < NI; ++i) {
+                if (i >= n) break;
+                bp[i] = reinterpret_cast<const float*>(p.in[i].ptr) + operand_index(p, p.in[i], idx) + r0 * p.in[i].strides[ra];
+                rs[i] = p.in[i].strides[ra];
+                isvec[i] = p.in[i].strides[inner] == 1;
+            }
             float a4[4];
 #pragma unroll
             for (int v = 0; v < 4; ++v) a4[v] = red_identity(p.rop);
             long long r = r0;
-            for (; r + 4 <= r1; r += 4) {
-                float in[4][KMAX_IN][4];
+            for (; r + RO_U <= r1; r += RO_U) {
+                float in[RO_U][NI][4];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < RO_U; ++u) {
 #pragma unroll
-                    for (int i = 0; i < (F::kCompiled ? n : KMAX_IN); ++i) {
+                    for (int i = 0; i < NI; ++i) {
                         if (i >= n) break;
-                        load4(p.in[i], base[i] + (r + u) * p.in[i].strides[ra], p.in[i].strides[inner], in[u][i]);
+                        if (isvec[i]) ldg4(bp[i], in[u][i]);
+                        else splat4(__ldg(bp[i]), in[u][i]);
+                        bp[i] += rs[i];
                     }
                 }
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < RO_U; ++u) {
                     float v4[4];
-                    F::template eval<4>(p, in[u], v4);
+                    F::template eval<4>(p, in[u], v4, cl);
 #pragma unroll
                     for (int v = 0; v < 4; ++v) a4[v] = red_combine(p.rop, a4[v], v4[v]);
                 }
             }
             for (; r < r1; ++r) {
-                float in[KMAX_IN][4], v4[4];
+                float in[NI][4], v4[4];
 #pragma unroll
-                for (int i = 0; i < (F::kCompiled ? n : KMAX_IN); ++i) {
+                for (int i = 0; i < NI; ++i) {
                     if (i >= n) break;
-                    load4(p.in[i], base[i] + r * p.in[i].strides[ra], p.in[i].strides[inner], in[i]);
+                    if (isvec[i]) ldg4(bp[i], in[i]);
+                    else splat4(__ldg(bp[i]), in[i]);
+                    bp[i] += rs[i];
                 }
-                F::template eval<4>(p, in, v4);
+                F::template eval<4>(p, in, v4, cl);
 #pragma unroll
                 for (int v = 0; v < 4; ++v) a4[v] = red_combine(p.rop, a4[v], v4[v]);
             }
-            float4 res = make_float4(a4[0], a4[1], a4[2], a4[3]);
+            const float4 res = make_float4(a4[0], a4[1], a4[2], a4[3]);
             if (p.splits > 1) *reinterpret_cast<float4*>(scratch + (long long)split * p.kept + k) = res;
             else *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out.ptr) + operand_index(p, p.out, idx)) = res;
         } else {
             float acc = red_identity(p.rop);
             for (long long r = r0; r < r1; ++r) {
                 set_idx(idx, ra, r);
-                float in[KMAX_IN][1], v[1];
+                float in[NI][1], v[1];
 #pragma unroll
-                for (int i = 0; i < (F::kCompiled ? n : KMAX_IN); ++i) {
+                for (int i = 0; i < NI; ++i) {
                     if (i >= n) break;
                     const KOperand& o = p.in[i];
                     if (o.n_bounds && !bounds_ok(p, o, idx)) in[i][0] = o.pad;
                     else in[i][0] = load_elem(o, operand_index(p, o, idx));
                 }
-                F::template eval<1>(p, in, v);
+                F::template eval<1>(p, in, v, cl);
                 acc = red_combine(p.rop, acc, v[0]);
             }
             set_idx(idx, ra, 0);

@@ -211,6 +211,7 @@ class KernelDesc:
     gemm_mode: int = GEMM_DEFAULT
     scalar: float = 0.0
     name: str = ""
+    flags: int = 0
 
     def __post_init__(self):
         self.shape = [int(s) for s in self.shape]
@@ -249,6 +250,7 @@ class KernelDesc:
         d.reduce_axis = self.reduce_axis
         d.gemm_mode = self.gemm_mode
         d.scalar = self.scalar
+        d.flags = self.flags
         prog = self.program()
         if len(prog) > MAX_INSNS:
             raise ValueError(f"map program of {len(prog)} instructions exceeds {MAX_INSNS}")

@@ -46,7 +46,6 @@ import hashlib
 import math
 import os
 import subprocess
-import tempfile
 from typing import List, Sequence
 
 import numpy as np
@@ -54,7 +53,7 @@ import numpy as np
 from harp_b200 import desc as D
 
 _CACHE_DIR = os.environ.get(
-    "EB200_ORACLE_CACHE", os.path.join(tempfile.gettempdir(), "eb200_oracle_cache"))
+    "EB200_ORACLE_CACHE", os.path.join(os.path.dirname(os.path.abspath(__file__)), "_build"))
 
 C_TYPE = {D.F32: "float", D.BOOL: "unsigned char", D.I32: "int", D.I64: "long long"}
 

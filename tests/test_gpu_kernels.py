@@ -284,7 +284,8 @@ def test_conv_patch_permute_bit_exact(dev):
 
 def gemm_check(dev, k, a, b, ref64, rel):
     got, kern = run_gpu(dev, k, [a, b])
-    assert kern.impl.startswith("gemm")
+    if min(k.shape) > 1:    # degenerate extents collapse into plain reduces
+        assert kern.impl.startswith("gemm")
     scale = np.abs(a.astype(np.float64)).max() * np.abs(b.astype(np.float64)).max() * k.shape[k.reduce_axis]
     err = np.abs(got.astype(np.float64) - ref64.reshape(-1)).max()
     assert err <= rel * scale, (err, scale)
@@ -359,7 +360,7 @@ def test_cfg2_full_size(dev, registry):
     y, kern_y = run_gpu(dev, ky, [c0, x, c1])
     z, kern_z = run_gpu(dev, kz, [x])
     t, kern_t = run_gpu(dev, kt, [x])
-    assert kern_y.impl == "reduce_inner_t256_v4" and kern_y.specialised
+    assert kern_y.impl.startswith("reduce_inner") and kern_y.specialised
     assert kern_z.impl == "reduce_outer_v4_split" and kern_t.impl == "transpose_copy"
     # oracle at full size (OpenMP form, same arithmetic per row)
     y_ref = O.run(ky, [c0, x, c1], openmp=True)
