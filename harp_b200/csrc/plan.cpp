@@ -459,9 +459,10 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
                 p.vec = v ? 4 : 1;
                 pl.threads_per_row = p.rlen <= 64 ? 1 : (p.rlen <= 16384 ? 32 : 256);
                 // tuning override (desc.flags bits 0-1): 1 -> thread, 2 -> warp, 3 -> CTA per row
-                if ((d->flags & 3) == 1) pl.threads_per_row = 1;
-                if ((d->flags & 3) == 2) pl.threads_per_row = 32;
-                if ((d->flags & 3) == 3) pl.threads_per_row = 256;
+                if ((d->flags & 7) == 1) pl.threads_per_row = 1;
+                if ((d->flags & 7) == 2) pl.threads_per_row = 32;
+                if ((d->flags & 7) == 3) pl.threads_per_row = 256;
+                if ((d->flags & 7) == 4) pl.threads_per_row = 128;
                 // few long rows: split each row over several CTAs, finish in a second pass
                 long long ctas = pl.threads_per_row == 256 ? p.kept : 0;
                 if (pl.threads_per_row == 256 && ctas < 2LL * sm_count && p.rlen >= 65536) {

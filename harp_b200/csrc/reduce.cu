@@ -26,6 +26,10 @@
 
 namespace eb200 {
 
+#ifndef EB_RI_U1
+#define EB_RI_U1 4
+#endif
+
 // idx[d] = v without dynamic register indexing
 __device__ __forceinline__ void set_idx(long long* idx, int d, long long v) {
 #pragma unroll
@@ -39,16 +43,17 @@ __device__ __forceinline__ float group_reduce(float v, int rop, float* smem) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = red_combine(rop, v, __shfl_xor_sync(0xffffffffu, v, o));
     if (T == 32) return v;
+    // T is 128 or 256: the 256-thread CTA holds 256/T row groups of T/32 warps
+    constexpr int WPG = T >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (lane == 0) smem[warp] = v;
     __syncthreads();
-    if (warp == 0) {
-        v = lane < (T >> 5) ? smem[lane] : red_identity(rop);
+    const int g0 = (warp / WPG) * WPG;   // first warp of this thread's group
+    float r = red_identity(rop);
 #pragma unroll
-        for (int o = 4; o > 0; o >>= 1) v = red_combine(rop, v, __shfl_xor_sync(0xffffffffu, v, o));
-    }
+    for (int w = 0; w < WPG; ++w) r = red_combine(rop, r, smem[g0 + w]);
     __syncthreads();
-    return v;
+    return r;
 }
 
 __device__ __forceinline__ void ldg4(const float* src, float* dst) {
@@ -58,13 +63,14 @@ __device__ __forceinline__ void ldg4(const float* src, float* dst) {
 
 __device__ __forceinline__ void splat4(float v, float* dst) { dst[0] = v; dst[1] = v; dst[2] = v; dst[3] = v; }
 
-constexpr int RI_U = 4;  // independent 128-bit loads in flight per thread and operand
 
 template <class F, int T>
 __global__ void __launch_bounds__(256) reduce_inner_kernel(const __grid_constant__ KParams p, float* __restrict__ scratch) {
     __shared__ float smem[8];
     constexpr int ROWS = 256 / T;
     constexpr int NI = F::kCompiled ? F::kNin : KMAX_IN;
+    // independent 128-bit loads in flight per thread and operand
+    constexpr int RI_U = (F::kCompiled && NI == 1) ? EB_RI_U1 : 4;
     const int lane = threadIdx.x % T;
     const int sub = threadIdx.x / T;
     const int ra = p.raxis;
@@ -276,10 +282,11 @@ static int launch_one(Device* dev, const Plan& plan, const KParams& p, float* sc
         const long long work = p.kept * p.splits;
         const long long rows = 256 / T;
         long long blocks = (work + rows - 1) / rows;
-        long long cap = (long long)sms * 32;
+        long long cap = (long long)sms * 64;
         if (blocks > cap) blocks = cap;
         if (T == 1) reduce_inner_kernel<F, 1><<<(unsigned)blocks, 256, 0, dev->stream>>>(p, scratch);
         else if (T == 32) reduce_inner_kernel<F, 32><<<(unsigned)blocks, 256, 0, dev->stream>>>(p, scratch);
+        else if (T == 128) reduce_inner_kernel<F, 128><<<(unsigned)blocks, 256, 0, dev->stream>>>(p, scratch);
         else reduce_inner_kernel<F, 256><<<(unsigned)blocks, 256, 0, dev->stream>>>(p, scratch);
     } else {
         const long long nwork = p.vec == 4 ? (p.kept >> 2) : p.kept;
