@@ -68,6 +68,7 @@ SIGNATURES = {
     "eb200_abi_sizes": [C.POINTER(C.c_size_t)] * 4,
     "eb200_kernel_launch": [_p, _pp, C.c_int, _pp, C.c_int],
     "eb200_kernel_release": [_p],
+    "eb200_reduce_cols_static": [_p, C.c_int64, C.c_int64, C.c_int, _p, _p],
     "eb200_launch_count": [C.POINTER(C.c_int64)],
 }
 

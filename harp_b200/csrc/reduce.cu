@@ -21,6 +21,8 @@
 //                fallback for any reduce the other paths do not take.
 //
 // Both are HBM-bound: algorithmic bytes = 4 B x (input elements + outputs).
+#include <string.h>
+
 #include "expr.cuh"
 #include "index.cuh"
 
@@ -321,3 +323,87 @@ int launch_reduce(Device* dev, const Plan& plan, const KParams& p, void* scratch
 }
 
 }  // namespace eb200
+
+// ---- column reduce without any allocation ------------------------------------------------
+//
+// eb200_reduce_cols_static serves callers that hold device memory but must not
+// allocate any: code running where cudaMalloc is off limits because it
+// synchronises the whole device (a latency-critical serving loop, a callback
+// between captured graphs) or because all device memory already belongs to the
+// caller's own arena.  Such callers cannot use eb200_kernel_create, whose split
+// reductions take their partial-result scratch from the device pool.  Here the
+// scratch is a fixed array inside the library image instead.
+namespace eb200 {
+
+constexpr long long kStaticScratchFloats = 1LL << 19;  // 2 MiB, resident on every device that loads the library
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+
+struct StaticDevice {
+    bool ready = false;
+    float* scratch = nullptr;   // device address of g_static_scratch on this device
+    int sms = 0;
+};
+static StaticDevice g_static_dev[64];
+static std::mutex g_static_mutex;
+
+}  // namespace eb200
+
+extern "C" int eb200_reduce_cols_static(const float* x, int64_t rows, int64_t cols, int reduce_op,
+                                        float* out, void* stream) {
+    using namespace eb200;
+    EB_REQUIRE(x && out, EB200_ERR_INVALID, "null argument");
+    EB_REQUIRE(rows >= 1 && cols >= 1, EB200_ERR_INVALID, "rows and cols must be positive");
+    EB_REQUIRE(reduce_op >= EB200_R_SUM && reduce_op <= EB200_R_PROD, EB200_ERR_INVALID, "reduce op %d", reduce_op);
+    int devid = -1;
+    EB_CHECK_CUDA(cudaGetDevice(&devid));
+    EB_REQUIRE(devid >= 0 && devid < 64, EB200_ERR_UNSUPPORTED, "device ordinal %d out of range", devid);
+    StaticDevice& sd = g_static_dev[devid];
+    {
+        // One-time set-up per device, with that device current.  The array's name
+        // is only a host-side stand-in: kernels need the address the runtime
+        // reports for this device.
+        std::lock_guard<std::mutex> lock(g_static_mutex);
+        if (!sd.ready) {
+            float* ptr = nullptr;
+            EB_CHECK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_scratch));
+            EB_REQUIRE(ptr != nullptr, EB200_ERR_CUDA, "no device address for the static scratch array");
+            int sms = 0;
+            EB_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, devid));
+            sd.scratch = ptr;
+            sd.sms = sms;
+            sd.ready = true;
+        }
+    }
+    // the same descriptor eb200_kernel_create would get for max/sum over axis 0 of [rows, cols]
+    eb200_kernel_desc d;
+    memset(&d, 0, sizeof(d));
+    d.kclass = EB200_K_REDUCE;
+    d.ndim = 2;
+    d.shape[0] = rows; d.shape[1] = cols;
+    d.n_inputs = 1;
+    d.reduce_op = reduce_op;
+    d.reduce_axis = 0;
+    d.inputs[0].dtype = EB200_F32; d.inputs[0].strides[0] = cols; d.inputs[0].strides[1] = 1; d.inputs[0].numel = rows * cols;
+    d.output.dtype = EB200_F32; d.output.strides[0] = 0; d.output.strides[1] = 1; d.output.numel = cols;
+    Plan plan;
+    int st = build_plan(&d, sd.sms, &plan);
+    if (st) return st;
+    EB_REQUIRE(plan.impl == IMPL_REDUCE_INNER || plan.impl == IMPL_REDUCE_OUTER, EB200_ERR_UNSUPPORTED,
+               "shape [%lld, %lld] is not served by a reduce kernel", (long long)rows, (long long)cols);
+    EB_REQUIRE(plan.scratch_bytes <= kStaticScratchFloats * (long long)sizeof(float), EB200_ERR_UNSUPPORTED,
+               "reduce of [%lld, %lld] needs %lld bytes of scratch; the static scratch holds %lld",
+               (long long)rows, (long long)cols, (long long)plan.scratch_bytes,
+               (long long)(kStaticScratchFloats * sizeof(float)));
+    EB_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0,
+               EB200_ERR_INVALID, "x and out must be 16-byte aligned");
+    Device dev;
+    dev.index = devid;
+    dev.stream = reinterpret_cast<cudaStream_t>(stream);
+    dev.prop.multiProcessorCount = sd.sms;
+    KParams p = plan.p;
+    p.in[0].ptr = reinterpret_cast<char*>(const_cast<float*>(x));
+    p.out.ptr = reinterpret_cast<char*>(out);
+    // every partial [split][column] is written by the first kernel before the
+    // second reads it, so nothing in the scratch has to start at zero
+    return launch_reduce(&dev, plan, p, sd.scratch);
+}

@@ -250,6 +250,22 @@ int eb200_kernel_query(const eb200_kernel_desc* desc, int sm_count, eb200_kernel
 int eb200_kernel_launch(eb200_kernel* k, eb200_buffer* const* inputs, int n_inputs,
                         eb200_buffer* const* outputs, int n_outputs);
 int eb200_kernel_release(eb200_kernel* k);
+/* Column reduce that allocates nothing (no counterpart in the reference; added
+ * for callers that own device memory but may not allocate: cudaMalloc
+ * synchronises the device, which a latency-critical loop cannot afford, and a
+ * caller whose arena already holds all device memory has nothing left to ask
+ * for).  out[c] = reduce over r of x[r*cols + c] for contiguous f32 x
+ * [rows, cols]; `reduce_op` is an eb200_reduce_op, `stream` the cudaStream_t
+ * to launch on (NULL = default stream); x and out are device pointers the
+ * caller owns, 16-byte aligned.  Partial results go through a 2 MiB array
+ * compiled into the library (every GPU that loads the library holds it until
+ * exit): row-splits x cols may not exceed 524 288 partials, and a shape whose
+ * split needs more fails with EB200_ERR_UNSUPPORTED before anything launches.
+ * The first call on a device looks up that array's device address; make that
+ * first call outside any stream capture.  All calls share the array: two calls
+ * whose kernels overlap on the GPU (different streams) race on it. */
+int eb200_reduce_cols_static(const float* x, int64_t rows, int64_t cols, int reduce_op,
+                             float* out, void* stream);
 /* Number of device kernel launches issued through this library so far. */
 int eb200_launch_count(int64_t* count);
 
