@@ -67,6 +67,14 @@ int buffer_unshare(eb200_buffer* buf, bool keep_contents) {
     return EB200_OK;
 }
 
+int check_device_flag(Device* dev) {
+    if (dev->error_flag_host && *reinterpret_cast<volatile int*>(dev->error_flag_host) != 0) {
+        *reinterpret_cast<volatile int*>(dev->error_flag_host) = 0;
+        return set_error(EB200_ERR_TIMEOUT, "a kernel gave up a bounded device-side wait; its output is not valid");
+    }
+    return EB200_OK;
+}
+
 }  // namespace eb200
 
 using namespace eb200;
@@ -125,6 +133,9 @@ int eb200_device_open(int index, eb200_device** out) {
     OPEN_CHECK(cudaMemPoolSetAttribute(dev->pool, cudaMemPoolAttrReleaseThreshold, &threshold));
     OPEN_CHECK(cudaEventCreate(&dev->ev_begin));
     OPEN_CHECK(cudaEventCreate(&dev->ev_end));
+    OPEN_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&dev->error_flag_host), sizeof(int), cudaHostAllocMapped));
+    *dev->error_flag_host = 0;
+    OPEN_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&dev->error_flag_dev), dev->error_flag_host, 0));
 #undef OPEN_CHECK
     *out = dev;
     return EB200_OK;
@@ -136,6 +147,7 @@ int eb200_device_close(eb200_device* dev) {
     cudaStreamSynchronize(dev->stream);
     if (dev->ev_begin) cudaEventDestroy(dev->ev_begin);
     if (dev->ev_end) cudaEventDestroy(dev->ev_end);
+    if (dev->error_flag_host) cudaFreeHost(dev->error_flag_host);
     if (dev->pool) cudaMemPoolDestroy(dev->pool);
     if (dev->stream) cudaStreamDestroy(dev->stream);
     delete dev;
@@ -145,7 +157,7 @@ int eb200_device_close(eb200_device* dev) {
 int eb200_device_sync(eb200_device* dev) {
     EB_REQUIRE(dev, EB200_ERR_INVALID, "dev is null");
     EB_CHECK_CUDA(cudaStreamSynchronize(dev->stream));
-    return EB200_OK;
+    return check_device_flag(dev);
 }
 
 int eb200_device_get_props(eb200_device* dev, eb200_device_props* props) {
@@ -275,7 +287,10 @@ static int buffer_read(eb200_buffer* buf, void* host, size_t bytes, bool sync) {
     EB_REQUIRE(bytes == buf->bytes, EB200_ERR_INVALID, "Buffer size mismatch: expected %zu, got %zu", buf->bytes, bytes);
     EB_CHECK_CUDA(cudaSetDevice(buf->dev->index));
     if (bytes) EB_CHECK_CUDA(cudaMemcpyAsync(host, buf->storage->ptr, bytes, cudaMemcpyDeviceToHost, buf->dev->stream));
-    if (sync) EB_CHECK_CUDA(cudaStreamSynchronize(buf->dev->stream));
+    if (sync) {
+        EB_CHECK_CUDA(cudaStreamSynchronize(buf->dev->stream));
+        return check_device_flag(buf->dev);
+    }
     return EB200_OK;
 }
 

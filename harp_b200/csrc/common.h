@@ -100,6 +100,10 @@ struct Device {
     cudaEvent_t ev_begin = nullptr, ev_end = nullptr;
     cudaDeviceProp prop{};
     std::atomic<int64_t> in_use{0}, peak{0}, n_allocs{0};
+    // raised by a kernel whose bounded device-side wait ran out (host-mapped, pinned)
+    int* error_flag_host = nullptr;
+    int* error_flag_dev = nullptr;
+    bool tc_configured = false;
 };
 
 // Reference-counted device storage; several buffer handles may share one
@@ -197,6 +201,11 @@ int launch_transpose(Device* dev, const Plan& plan, const void* in, void* out);
 int launch_scatter(Device* dev, const Plan& plan, const KParams& p);
 int launch_sgd(Device* dev, const Plan& plan, const float* p, const float* g, float* out, long long n);
 int launch_gemm_simt(Device* dev, const Plan& plan, const float* a, const float* b, float* c);
+bool gemm_tc_supported(const GemmShape& g);
+void gemm_tc_scratch(const GemmShape& g, long long* a_span, long long* b_span);
+int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b, float* c, void* scratch);
+// EB200_ERR_TIMEOUT if a kernel on this device reported a timed-out wait (clears the flag)
+int check_device_flag(Device* dev);
 
 }  // namespace eb200
 

@@ -1,0 +1,423 @@
+// gemm_tc: dense contraction on the 5th-generation tensor cores (sm_100a).
+//
+// The reference has no f32 matmul op; `C = A.B` is an R_ kernel over a
+// broadcast product (crates/nn/src/functional/linear.rs:27-56,
+// examples/matmul_demo.rs:43-60) that its backends run as a scalar triple loop.
+// The classifier (plan.cpp) recognises the pattern and this file serves it:
+//
+//   * operands stay f32 in HBM; TMA (cp.async.bulk.tensor, 128-byte swizzle)
+//     stages 128 x 32 / 32 x 128 tiles into a shared-memory ring, completion on
+//     mbarriers;
+//   * one elected thread issues tcgen05.mma kind::tf32 (M=128, N=128, K=8) with
+//     the accumulator in tensor memory (128 lanes x 128 columns of f32);
+//   * tcgen05.commit hands ring slots back to the TMA warp and, after the last
+//     k block, the accumulator to four epilogue warps, which read it with
+//     tcgen05.ld and store C.
+//
+// Modes: TF32 feeds the raw f32 bits (the tensor core ignores the low 13
+// mantissa bits); 3xTF32 first splits every operand into hi (exactly
+// representable in tf32) and lo = x - hi and accumulates hi.hi + lo.hi + hi.lo,
+// which restores f32-level accuracy at three times the MMA work.
+//
+// B may be K-major ([N][K], the `linear` form) or N-major ([K][N], the
+// matmul_demo form); A must be K-major.  Anything else (odd strides, unaligned
+// offsets, M-major A) stays on the f32 SIMT kernel.
+//
+// Every wait on an mbarrier is bounded: when the bound is hit the kernel raises
+// a flag in global memory, leaves its loops, frees its tensor memory and
+// returns; eb200_device_sync reports the flag as EB200_ERR_TIMEOUT.
+#include <cuda.h>
+
+#include <algorithm>
+
+#include "common.h"
+
+namespace eb200 {
+
+constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 32;   // tile; BK floats = one 128-byte swizzle row
+constexpr int TC_UK = 8;                               // K of one tf32 MMA
+constexpr int TC_TILE_BYTES = TC_BM * TC_BK * 4;       // 16 KB per operand tile
+constexpr int TC_THREADS = 192;                        // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+constexpr unsigned TC_SPIN_LIMIT = 1u << 24;
+
+struct TcParams {
+    long long m, n, k;
+    long long c_sm, c_sn, c_sb, c_off;
+    int b_nmajor;      // 1: B tiles are [k][n] with n contiguous
+    int three_pass;    // 1: 3xTF32
+    int stages;
+    int* error_flag;
+};
+
+// ---- PTX wrappers -----------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait; false when the bound was hit (the caller must bail out).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, int* error_flag) {
+    for (unsigned i = 0; i < TC_SPIN_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i > 4096) __nanosleep(64);
+    }
+    atomicExch(error_flag, 1);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, unsigned cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, unsigned cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem desc] * B[smem desc], kind::tf32, issued by one thread.
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// mbarrier arrives once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// 32 lanes x 32 columns of f32 from tensor memory: thread t of the warp gets lane t.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor (sm_100 format): start address, leading and
+// stride byte offsets in 16-byte units, version 1, 128-byte swizzle.
+// layout 2 = 128-byte swizzle of 16-byte chunks; layout 1 = 128-byte swizzle of
+// 32-byte chunks, the only layout the tensor core accepts for MN-major tf32.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout = 2) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;   // descriptor version
+    d |= (uint64_t)layout << 61;
+    return d;
+}
+
+// Instruction descriptor for kind::tf32: f32 accumulate, tf32 A and B, M x N tile.
+__host__ __device__ constexpr uint32_t umma_idesc_tf32(int M, int N, int b_nmajor) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(b_nmajor ? 1 : 0) << 16) |
+           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// ---- the kernel -------------------------------------------------------------------------
+// Shared memory: [stages][A hi | (A lo) | B hi | (B lo)] tiles, 1024-byte aligned,
+// then the mbarriers and the tensor-memory address slot.
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_alo,
+               const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_blo,
+               const __grid_constant__ TcParams q, float* __restrict__ C, int a_zmul, int b_zmul) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int tiles_per_stage = q.three_pass ? 4 : 2;
+    const int stage_bytes = tiles_per_stage * TC_TILE_BYTES;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)q.stages * stage_bytes);
+    uint64_t* empty_bar = full_bar + q.stages;
+    uint64_t* acc_bar = empty_bar + q.stages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long n0 = (long long)blockIdx.x * TC_BN, m0 = (long long)blockIdx.y * TC_BM;
+    const int bz = blockIdx.z;
+    const int num_kb = (int)((q.k + TC_BK - 1) / TC_BK);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < q.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(acc_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, TC_BN);   // 128 columns of f32 accumulators
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---- TMA producer (one thread) ----
+        if (lane == 0) {
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % q.stages;
+                const unsigned phase = (unsigned)(kb / q.stages) & 1u;
+                if (!mbar_wait(&empty_bar[s], phase ^ 1u, q.error_flag)) break;
+                unsigned char* st = smem + (size_t)s * stage_bytes;
+                mbar_expect_tx(&full_bar[s], (unsigned)stage_bytes);
+                const int kx = kb * TC_BK;
+                unsigned char* a_hi = st;
+                unsigned char* b_hi = st + (q.three_pass ? 2 : 1) * TC_TILE_BYTES;
+                tma_load_3d(a_hi, &map_a, &full_bar[s], kx, (int)m0, bz * a_zmul);
+                if (q.three_pass) tma_load_3d(st + TC_TILE_BYTES, &map_alo, &full_bar[s], kx, (int)m0, bz * a_zmul);
+                if (q.b_nmajor) {
+                    // four [32 k][32 n] boxes side by side along n
+#pragma unroll
+                    for (int j = 0; j < TC_BN / 32; ++j) {
+                        tma_load_3d(b_hi + j * 4096, &map_b, &full_bar[s], (int)n0 + j * 32, kx, bz * b_zmul);
+                        if (q.three_pass) tma_load_3d(b_hi + TC_TILE_BYTES + j * 4096, &map_blo, &full_bar[s], (int)n0 + j * 32, kx, bz * b_zmul);
+                    }
+                } else {
+                    tma_load_3d(b_hi, &map_b, &full_bar[s], kx, (int)n0, bz * b_zmul);
+                    if (q.three_pass) tma_load_3d(b_hi + TC_TILE_BYTES, &map_blo, &full_bar[s], kx, (int)n0, bz * b_zmul);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer (one thread) ----
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_tf32(TC_BM, TC_BN, q.b_nmajor);
+            bool ok = true;
+            for (int kb = 0; kb < num_kb && ok; ++kb) {
+                const int s = kb % q.stages;
+                const unsigned phase = (unsigned)(kb / q.stages) & 1u;
+                ok = mbar_wait(&full_bar[s], phase, q.error_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t st = smem_u32(smem + (size_t)s * stage_bytes);
+                const uint32_t a_hi = st, a_lo = st + TC_TILE_BYTES;
+                const uint32_t b_hi = st + (q.three_pass ? 2 : 1) * TC_TILE_BYTES, b_lo = b_hi + TC_TILE_BYTES;
+#pragma unroll
+                for (int j = 0; j < TC_BK / TC_UK; ++j) {
+                    // K-major: step 32 bytes inside the 128-byte swizzled row.
+                    // N-major B: step one 8-row group (1024 bytes); n atoms are 4096 bytes apart.
+                    const uint32_t a_step = j * TC_UK * 4;
+                    const uint32_t b_step = q.b_nmajor ? j * 1024 : j * TC_UK * 4;
+                    // (swizzle atom = 4 k rows = 512 bytes, so one K=8 MMA spans two atoms)
+                    const uint32_t b_lbo = q.b_nmajor ? 4096 : 16;
+                    const uint32_t b_sbo = q.b_nmajor ? 512 : 1024;
+                    const uint32_t b_layout = q.b_nmajor ? 1 : 2;
+                    const uint64_t da = umma_desc(a_hi + a_step, 16, 1024);
+                    const uint64_t db = umma_desc(b_hi + b_step, b_lbo, b_sbo, b_layout);
+                    umma_tf32(tmem_base, da, db, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                    if (q.three_pass) {
+                        const uint64_t dal = umma_desc(a_lo + a_step, 16, 1024);
+                        const uint64_t dbl = umma_desc(b_lo + b_step, b_lbo, b_sbo, b_layout);
+                        umma_tf32(tmem_base, dal, db, idesc, 1u);
+                        umma_tf32(tmem_base, da, dbl, idesc, 1u);
+                    }
+                }
+                umma_commit(&empty_bar[s]);   // slot is free once these MMAs have read it
+            }
+            umma_commit(acc_bar);             // accumulator complete
+        }
+    } else {
+        // ---- epilogue: warps 2..5 own tensor-memory lanes 32*(warp%4) .. +31 ----
+        const int quarter = warp & 3;
+        const bool ok = mbar_wait(acc_bar, 0, q.error_flag);
+        tc_fence_after();
+        const long long row = m0 + quarter * 32 + lane;
+        float* crow = C + q.c_off + (long long)bz * q.c_sb + row * q.c_sm;
+#pragma unroll 1
+        for (int c = 0; c < TC_BN / 32; ++c) {
+            float v[32];
+            tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), v);
+            const long long col0 = n0 + c * 32;
+            if (!ok || row >= q.m || col0 >= q.n) continue;
+            float* dst = crow + col0 * q.c_sn;
+            if (q.c_sn == 1 && col0 + 32 <= q.n && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 4)
+                    *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (col0 + i < q.n) dst[i * q.c_sn] = v[i];
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TC_BN);
+}
+
+// hi = x rounded to tf32 (low 13 mantissa bits zero), lo = x - hi (exact in f32).
+__global__ void __launch_bounds__(256) split_tf32_kernel(const float* __restrict__ src, float* __restrict__ hi,
+                                                         float* __restrict__ lo, long long n) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long nvec = n >> 2;
+    for (long long v = tid; v < nvec; v += stride) {
+        const float4 x = __ldg(reinterpret_cast<const float4*>(src) + v);
+        float4 h, l;
+        h.x = __uint_as_float((__float_as_uint(x.x) + 0x1000u) & 0xffffe000u); l.x = x.x - h.x;
+        h.y = __uint_as_float((__float_as_uint(x.y) + 0x1000u) & 0xffffe000u); l.y = x.y - h.y;
+        h.z = __uint_as_float((__float_as_uint(x.z) + 0x1000u) & 0xffffe000u); l.z = x.z - h.z;
+        h.w = __uint_as_float((__float_as_uint(x.w) + 0x1000u) & 0xffffe000u); l.w = x.w - h.w;
+        reinterpret_cast<float4*>(hi)[v] = h;
+        reinterpret_cast<float4*>(lo)[v] = l;
+    }
+    for (long long i = (nvec << 2) + tid; i < n; i += stride) {
+        const float x = src[i];
+        const float h = __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u);
+        hi[i] = h;
+        lo[i] = x - h;
+    }
+}
+
+// ---- host side --------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// 3-D f32 tensor map: dims {inner, rows, batch}, byte strides of dims 1 and 2, box {32, box_rows, 1}.
+static int make_map(CUtensorMap* map, const float* base, long long inner, long long rows, long long batch,
+                    long long row_stride, long long batch_stride, int box_rows,
+                    CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+    EncodeTiledFn fn = encode_fn();
+    EB_REQUIRE(fn, EB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)(batch > 0 ? batch : 1)};
+    cuuint64_t strides[2] = {(cuuint64_t)row_stride * 4, (cuuint64_t)(batch_stride > 0 ? batch_stride : row_stride * rows) * 4};
+    cuuint32_t box[3] = {32, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    EB_REQUIRE(r == CUDA_SUCCESS, EB200_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (inner %lld rows %lld stride %lld)",
+               (int)r, inner, rows, row_stride);
+    return EB200_OK;
+}
+
+// Whether the tensor-core kernel can take this contraction (plan.cpp asks).
+bool gemm_tc_supported(const GemmShape& g) {
+    if (g.a_sk != 1) return false;                       // A must be K-major
+    const bool b_kmajor = g.b_sk == 1, b_nmajor = g.b_sn == 1;
+    if (!b_kmajor && !b_nmajor) return false;
+    if (g.k == 1 && b_kmajor && b_nmajor) {}             // either reading works
+    auto mult4 = [](long long v) { return (v & 3) == 0; };
+    if (!mult4(g.a_sm) || !mult4(g.a_sb) || !mult4(g.a_off)) return false;
+    if (!mult4(b_kmajor ? g.b_sn : g.b_sk) || !mult4(g.b_sb) || !mult4(g.b_off)) return false;
+    if (g.a_sm < g.k) return false;
+    if (g.batch < 1 || g.batch > 65535) return false;
+    if (g.m < 1 || g.n < 1 || g.k < 1) return false;
+    if (g.m >= (1LL << 31) || g.n >= (1LL << 31) || g.k >= (1LL << 31)) return false;
+    if ((g.m + TC_BM - 1) / TC_BM > 65535) return false;
+    if (g.batch > 1 && (g.a_sb < 0 || g.b_sb < 0)) return false;
+    return true;
+}
+
+// Elements of the memory span an operand covers (hi/lo copies mirror the span).
+static long long span_of(long long batch, long long sb, long long rows, long long srow, long long inner) {
+    return (batch - 1) * sb + (rows - 1) * srow + inner;
+}
+
+void gemm_tc_scratch(const GemmShape& g, long long* a_span, long long* b_span) {
+    const bool b_kmajor = g.b_sk == 1;
+    long long a = span_of(g.batch, g.a_sb, g.m, g.a_sm, g.k);
+    long long b = b_kmajor ? span_of(g.batch, g.b_sb, g.n, g.b_sn, g.k) : span_of(g.batch, g.b_sb, g.k, g.b_sk, g.n);
+    *a_span = (a + 63) / 64 * 64;
+    *b_span = (b + 63) / 64 * 64;
+}
+
+int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b, float* c, void* scratch) {
+    const GemmShape& g = plan.gemm;
+    const bool three = g.mode == EB200_GEMM_3XTF32;
+    const bool b_nmajor = !(g.b_sk == 1);
+    const float* a_src = a + g.a_off;
+    const float* b_src = b + g.b_off;
+    EB_REQUIRE((reinterpret_cast<uintptr_t>(a_src) & 15) == 0 && (reinterpret_cast<uintptr_t>(b_src) & 15) == 0,
+               EB200_ERR_INVALID, "GEMM operands must be 16-byte aligned");
+    const float *a_hi = a_src, *a_lo = a_src, *b_hi = b_src, *b_lo = b_src;
+    if (three) {
+        EB_REQUIRE(scratch, EB200_ERR_INVALID, "3xTF32 launched without scratch");
+        long long a_span, b_span;
+        gemm_tc_scratch(g, &a_span, &b_span);
+        float* s = reinterpret_cast<float*>(scratch);
+        float *ah = s, *al = s + a_span, *bh = s + 2 * a_span, *bl = s + 2 * a_span + b_span;
+        const long long cap = (long long)dev->prop.multiProcessorCount * 16;
+        long long blocks = std::min(cap, (a_span / 4 + 255) / 256 + 1);
+        split_tf32_kernel<<<(unsigned)blocks, 256, 0, dev->stream>>>(a_src, ah, al, span_of(g.batch, g.a_sb, g.m, g.a_sm, g.k));
+        count_launch();
+        blocks = std::min(cap, (b_span / 4 + 255) / 256 + 1);
+        const long long bs = b_nmajor ? span_of(g.batch, g.b_sb, g.k, g.b_sk, g.n) : span_of(g.batch, g.b_sb, g.n, g.b_sn, g.k);
+        split_tf32_kernel<<<(unsigned)blocks, 256, 0, dev->stream>>>(b_src, bh, bl, bs);
+        count_launch();
+        EB_CHECK_CUDA(cudaGetLastError());
+        a_hi = ah; a_lo = al; b_hi = bh; b_lo = bl;
+    }
+    CUtensorMap ma, mal, mb, mbl;
+    const long long a_b = g.a_sb > 0 ? g.batch : 1, b_b = g.b_sb > 0 ? g.batch : 1;
+    int st;
+    if ((st = make_map(&ma, a_hi, g.k, g.m, a_b, g.a_sm, g.a_sb, TC_BM))) return st;
+    if ((st = make_map(&mal, a_lo, g.k, g.m, a_b, g.a_sm, g.a_sb, TC_BM))) return st;
+    if (b_nmajor) {
+        if ((st = make_map(&mb, b_hi, g.n, g.k, b_b, g.b_sk, g.b_sb, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))) return st;
+        if ((st = make_map(&mbl, b_lo, g.n, g.k, b_b, g.b_sk, g.b_sb, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))) return st;
+    } else {
+        if ((st = make_map(&mb, b_hi, g.k, g.n, b_b, g.b_sn, g.b_sb, TC_BN))) return st;
+        if ((st = make_map(&mbl, b_lo, g.k, g.n, b_b, g.b_sn, g.b_sb, TC_BN))) return st;
+    }
+    TcParams q{};
+    q.m = g.m; q.n = g.n; q.k = g.k;
+    q.c_sm = g.c_sm; q.c_sn = g.c_sn; q.c_sb = g.c_sb; q.c_off = g.c_off;
+    q.b_nmajor = b_nmajor ? 1 : 0;
+    q.three_pass = three ? 1 : 0;
+    q.stages = three ? 3 : 6;
+    q.error_flag = dev->error_flag_dev;
+    const int stage_bytes = (three ? 4 : 2) * TC_TILE_BYTES;
+    const size_t smem = (size_t)q.stages * stage_bytes + 1024 /* alignment */ + 256 /* barriers */;
+    if (!dev->tc_configured) {
+        EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        dev->tc_configured = true;
+    }
+    dim3 grid((unsigned)((g.n + TC_BN - 1) / TC_BN), (unsigned)((g.m + TC_BM - 1) / TC_BM), (unsigned)g.batch);
+    gemm_tc_kernel<<<grid, TC_THREADS, smem, dev->stream>>>(ma, mal, mb, mbl, q, c, g.a_sb > 0 ? 1 : 0, g.b_sb > 0 ? 1 : 0);
+    count_launch();
+    EB_CHECK_CUDA(cudaGetLastError());
+    return EB200_OK;
+}
+
+}  // namespace eb200

@@ -128,6 +128,10 @@ int eb200_kernel_launch(eb200_kernel* k, eb200_buffer* const* inputs, int n_inpu
             return launch_gemm_simt(dev, plan, reinterpret_cast<const float*>(p.in[plan.gemm.a_input].ptr),
                                     reinterpret_cast<const float*>(p.in[plan.gemm.b_input].ptr),
                                     reinterpret_cast<float*>(p.out.ptr));
+        case IMPL_GEMM_TC:
+            return launch_gemm_tc(dev, plan, reinterpret_cast<const float*>(p.in[plan.gemm.a_input].ptr),
+                                  reinterpret_cast<const float*>(p.in[plan.gemm.b_input].ptr),
+                                  reinterpret_cast<float*>(p.out.ptr), scratch);
         default: return set_error(EB200_ERR_UNSUPPORTED, "kernel implementation %d is not built", (int)plan.impl);
     }
 }

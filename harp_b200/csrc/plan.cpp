@@ -447,9 +447,25 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
         }
         case EB200_K_REDUCE: {
             if (try_gemm(p, &pl, d->gemm_mode)) {
-                pl.impl = IMPL_GEMM_SIMT;
                 pl.algo_flops = 2 * pl.gemm.batch * pl.gemm.m * pl.gemm.n * pl.gemm.k;
-                snprintf(pl.name, sizeof(pl.name), "gemm_simt_f32");
+                // tensor cores when the operand layout allows it and the problem
+                // is more than a few tiles of work; f32 FFMA tiles otherwise
+                const bool force_simt = (d->flags & 8) != 0;
+                if (!force_simt && gemm_tc_supported(pl.gemm) && pl.algo_flops >= (1LL << 22)) {
+                    pl.impl = IMPL_GEMM_TC;
+                    const bool three = pl.gemm.mode == EB200_GEMM_3XTF32;
+                    if (three) {
+                        long long a_span, b_span;
+                        gemm_tc_scratch(pl.gemm, &a_span, &b_span);
+                        pl.scratch_bytes = (2 * a_span + 2 * b_span) * 4;
+                        pl.launches = 3;
+                    }
+                    snprintf(pl.name, sizeof(pl.name), "gemm_tcgen05_%s_%s", three ? "3xtf32" : "tf32",
+                             pl.gemm.b_sk == 1 ? "tn" : "nn");
+                } else {
+                    pl.impl = IMPL_GEMM_SIMT;
+                    snprintf(pl.name, sizeof(pl.name), "gemm_simt_f32");
+                }
                 break;
             }
             if (raxis == nk - 1) {

@@ -298,10 +298,17 @@ def test_cfg1_matmul_512(dev):
     a = rng.uniform(-1, 1, (512, 512)).astype(np.float32)
     b = rng.uniform(-1, 1, (512, 512)).astype(np.float32)
     k = W.matmul_desc(512, 512, 512)
-    got, _ = gemm_check(dev, k, a, b, a.astype(np.float64) @ b.astype(np.float64), 1e-6)
+    got, kern = gemm_check(dev, k, a, b, a.astype(np.float64) @ b.astype(np.float64), 1e-6)
+    assert kern.impl == "gemm_tcgen05_3xtf32_nn"
+    bound = 1e-5 * (np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)).reshape(-1)
     for fma in (False, True):           # both forms the reference's C backend can take
         ref = O.run(k, [a, b], fma=fma)
-        assert_close(got, ref, rel=1e-5, abs_tol=1e-5 * np.sqrt(512) * 0.34)
+        assert (np.abs(got.astype(np.float64) - ref) <= bound).all()
+    # the f32 FFMA kernel on the same contraction agrees with the C loop much more tightly
+    k2 = W.matmul_desc(512, 512, 512); k2.flags = 8
+    got2, kern2 = run_gpu(dev, k2, [a, b])
+    assert kern2.impl == "gemm_simt_f32"
+    assert_close(got2, O.run(k2, [a, b]), rel=1e-5, abs_tol=1e-5 * np.sqrt(512) * 0.34)
 
 
 @pytest.mark.parametrize("m,k_,n", [(1, 1, 1), (5, 7, 3), (64, 16, 64), (65, 17, 66), (200, 300, 10), (1000, 9, 32)])
@@ -327,6 +334,55 @@ def test_gemm_weight_gradient_form(dev):
     b = D.Operand([30, 0, 1], 0, D.F32, x.size)
     k = D.reduce([50, 12, 30], [a, b], w(0) * w(1), D.R_SUM, 0)
     gemm_check(dev, k, dy, x, dy.astype(np.float64).T @ x.astype(np.float64), 1e-6)
+
+
+@pytest.mark.parametrize("mode,tol", [(D.GEMM_TF32, 1e-2), (D.GEMM_3XTF32, 1e-5)])
+@pytest.mark.parametrize("m,k_,n", [(128, 128, 128), (256, 96, 384), (300, 1000, 200), (129, 68, 260), (1024, 512, 64)])
+def test_gemm_tensor_core_modes_and_layouts(dev, mode, tol, m, k_, n):
+    """tcgen05 path: TF32 within 1e-2, 3xTF32 within 1e-5 of the float64 product,
+    relative to sum_k |a_ik b_kj| (the bound that holds for any summation order;
+    elementwise-relative is meaningless where a dot product cancels), for N-major B
+    (matmul_demo form) and K-major B (linear form), including ragged M/N/K tails."""
+    a, b = rnd([m, k_], 30), rnd([k_, n], 31)
+    ref = a.astype(np.float64) @ b.astype(np.float64)
+    scale = np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)
+    for form in ("nn", "tn"):
+        if form == "nn":
+            kd = W.matmul_desc(m, k_, n, mode=mode); got, kern = run_gpu(dev, kd, [a, b])
+        else:
+            kd = W.linear_desc(m, k_, n, mode=mode); got, kern = run_gpu(dev, kd, [a, np.ascontiguousarray(b.T)])
+        assert kern.impl.startswith("gemm_tcgen05"), kern.impl
+        err = np.abs(got.reshape(m, n) - ref)
+        assert (err <= tol * scale).all(), (form, err.max(), float((err / scale).max()))
+    dev.synchronize()     # would raise TIMEOUT had any bounded wait in the kernel run out
+
+
+def test_gemm_tensor_core_batched_and_strided_views(dev):
+    # batch of 5; A rows are a window [.., 0:64] of a wider [96, 80] matrix (lda = 80)
+    a_full, b = rnd([5, 96, 80], 32), rnd([5, 64, 160], 33)
+    a_op = D.Operand([96 * 80, 80, 1, 0], 0, D.F32, a_full.size)
+    b_op = D.Operand([64 * 160, 0, 160, 1], 0, D.F32, b.size)
+    kd = D.reduce([5, 96, 64, 160], [a_op, b_op], w(0) * w(1), D.R_SUM, 2)
+    got, kern = run_gpu(dev, kd, [a_full, b])
+    assert kern.impl.startswith("gemm_tcgen05")
+    ref = np.einsum("bmk,bkn->bmn", a_full[:, :, :64].astype(np.float64), b.astype(np.float64))
+    assert np.abs(got.reshape(ref.shape) - ref).max() <= 1e-5 * np.abs(ref).max()
+    # B shared across the batch (stride 0 on the batch dim)
+    b1 = rnd([64, 160], 34)
+    b_op = D.Operand([0, 0, 160, 1], 0, D.F32, b1.size)
+    kd = D.reduce([5, 96, 64, 160], [a_op, b_op], w(0) * w(1), D.R_SUM, 2)
+    got, kern = run_gpu(dev, kd, [a_full, b1])
+    ref = np.einsum("bmk,kn->bmn", a_full[:, :, :64].astype(np.float64), b1.astype(np.float64))
+    assert np.abs(got.reshape(ref.shape) - ref).max() <= 1e-5 * np.abs(ref).max()
+
+
+def test_gemm_misaligned_layout_stays_on_f32_kernel(dev):
+    # lda = 30 floats is not a multiple of 16 bytes: TMA cannot address it
+    a, b = rnd([64, 30], 35), rnd([30, 64], 36)
+    kd = W.matmul_desc(64, 30, 64)
+    got, kern = run_gpu(dev, kd, [a, b])
+    assert kern.impl == "gemm_simt_f32"
+    assert np.abs(got.reshape(64, 64) - a.astype(np.float64) @ b.astype(np.float64)).max() <= 1e-5
 
 
 # ---- scatter / sgd ---------------------------------------------------------------------------------

@@ -59,6 +59,12 @@ def test_matmul_spelled_as_broadcast_mul_sum_is_a_gemm():
         assert i.impl.decode().startswith("gemm"), i.impl
     i = query(W.matmul_desc(512, 512, 512))
     assert i.algo_flops == 2 * 512 ** 3
+    assert i.impl.decode() == "gemm_tcgen05_3xtf32_nn" and i.scratch_bytes == 4 * 4 * 512 * 512
+    assert query(W.matmul_desc(512, 512, 512, mode=D.GEMM_TF32)).impl.decode() == "gemm_tcgen05_tf32_nn"
+    assert query(W.linear_desc(4096, 256, 256)).impl.decode() == "gemm_tcgen05_3xtf32_tn"
+    assert query(W.matmul_desc(64, 30, 64)).impl.decode() == "gemm_simt_f32"     # lda not 16-byte aligned
+    k = W.matmul_desc(512, 512, 512); k.flags = 8
+    assert query(k).impl.decode() == "gemm_simt_f32"
 
 
 def test_small_rows_use_thread_or_warp_per_row():
