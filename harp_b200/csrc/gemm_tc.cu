@@ -28,13 +28,15 @@
 // returns; eb200_device_sync reports the flag as EB200_ERR_TIMEOUT.
 #include <cuda.h>
 
+#include <stdlib.h>
+
 #include <algorithm>
 
 #include "common.h"
 
 namespace eb200 {
 
-constexpr int TC_BM = 128, TC_BN = 128, TC_BK = 32;   // tile; BK floats = one 128-byte swizzle row
+constexpr int TC_BM = 128, TC_BK = 32;   // tile rows; BK floats = one 128-byte swizzle row (tile columns BN = 128 or 256)
 constexpr int TC_UK = 8;                               // K of one tf32 MMA
 constexpr int TC_TILE_BYTES = TC_BM * TC_BK * 4;       // 16 KB per operand tile
 constexpr int TC_THREADS = 192;                        // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
@@ -46,6 +48,8 @@ struct TcParams {
     int b_nmajor;      // 1: B tiles are [k][n] with n contiguous
     int three_pass;    // 1: 3xTF32
     int stages;
+    int raster;        // tile rows per band
+    int tiles_n;
     int* error_flag;
 };
 
@@ -146,22 +150,32 @@ __host__ __device__ constexpr uint32_t umma_idesc_tf32(int M, int N, int b_nmajo
 // ---- the kernel -------------------------------------------------------------------------
 // Shared memory: [stages][A hi | (A lo) | B hi | (B lo)] tiles, 1024-byte aligned,
 // then the mbarriers and the tensor-memory address slot.
+template <int TC_BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_alo,
                const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_blo,
                const __grid_constant__ TcParams q, float* __restrict__ C, int a_zmul, int b_zmul) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    const int tiles_per_stage = q.three_pass ? 4 : 2;
-    const int stage_bytes = tiles_per_stage * TC_TILE_BYTES;
+    constexpr int B_TILE_BYTES = TC_BN * TC_BK * 4;
+    const int stage_bytes = (q.three_pass ? 2 : 1) * (TC_TILE_BYTES + B_TILE_BYTES);
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)q.stages * stage_bytes);
     uint64_t* empty_bar = full_bar + q.stages;
     uint64_t* acc_bar = empty_bar + q.stages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long n0 = (long long)blockIdx.x * TC_BN, m0 = (long long)blockIdx.y * TC_BM;
+    // Tile order: bands of `raster` tile rows, walked column by column, so the
+    // CTAs in flight share a squarish set of A and B panels that stays in L2.
+    const int tiles_m = (int)((q.m + TC_BM - 1) / TC_BM);
+    const int per_band = q.raster * q.tiles_n;
+    const int band = (int)blockIdx.x / per_band, within = (int)blockIdx.x % per_band;
+    const int band_rows = min(q.raster, tiles_m - band * q.raster);
+    const int tile_m = band * q.raster + within % band_rows;
+    const int tile_n = within / band_rows;
+    const long long n0 = (long long)tile_n * TC_BN, m0 = (long long)tile_m * TC_BM;
     const int bz = blockIdx.z;
+    if (tile_n >= q.tiles_n) return;   // padding of the last, shorter band
     const int num_kb = (int)((q.k + TC_BK - 1) / TC_BK);
 
     if (threadIdx.x == 0) {
@@ -169,7 +183,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         mbar_init(acc_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) tmem_alloc(tmem_slot, TC_BN);   // 128 columns of f32 accumulators
+    if (warp == 1) tmem_alloc(tmem_slot, TC_BN);   // BN columns of f32 accumulators
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -186,7 +200,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 mbar_expect_tx(&full_bar[s], (unsigned)stage_bytes);
                 const int kx = kb * TC_BK;
                 unsigned char* a_hi = st;
-                unsigned char* b_hi = st + (q.three_pass ? 2 : 1) * TC_TILE_BYTES;
+                unsigned char* b_hi = st + (q.three_pass ? 2 : 1) * TC_TILE_BYTES;   // [A hi | A lo | B hi | B lo]
                 tma_load_3d(a_hi, &map_a, &full_bar[s], kx, (int)m0, bz * a_zmul);
                 if (q.three_pass) tma_load_3d(st + TC_TILE_BYTES, &map_alo, &full_bar[s], kx, (int)m0, bz * a_zmul);
                 if (q.b_nmajor) {
@@ -194,11 +208,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                     for (int j = 0; j < TC_BN / 32; ++j) {
                         tma_load_3d(b_hi + j * 4096, &map_b, &full_bar[s], (int)n0 + j * 32, kx, bz * b_zmul);
-                        if (q.three_pass) tma_load_3d(b_hi + TC_TILE_BYTES + j * 4096, &map_blo, &full_bar[s], (int)n0 + j * 32, kx, bz * b_zmul);
+                        if (q.three_pass) tma_load_3d(b_hi + B_TILE_BYTES + j * 4096, &map_blo, &full_bar[s], (int)n0 + j * 32, kx, bz * b_zmul);
                     }
                 } else {
                     tma_load_3d(b_hi, &map_b, &full_bar[s], kx, (int)n0, bz * b_zmul);
-                    if (q.three_pass) tma_load_3d(b_hi + TC_TILE_BYTES, &map_blo, &full_bar[s], kx, (int)n0, bz * b_zmul);
+                    if (q.three_pass) tma_load_3d(b_hi + B_TILE_BYTES, &map_blo, &full_bar[s], kx, (int)n0, bz * b_zmul);
                 }
             }
         }
@@ -215,7 +229,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 tc_fence_after();
                 const uint32_t st = smem_u32(smem + (size_t)s * stage_bytes);
                 const uint32_t a_hi = st, a_lo = st + TC_TILE_BYTES;
-                const uint32_t b_hi = st + (q.three_pass ? 2 : 1) * TC_TILE_BYTES, b_lo = b_hi + TC_TILE_BYTES;
+                const uint32_t b_hi = st + (q.three_pass ? 2 : 1) * TC_TILE_BYTES, b_lo = b_hi + B_TILE_BYTES;
 #pragma unroll
                 for (int j = 0; j < TC_BK / TC_UK; ++j) {
                     // K-major: step 32 bytes inside the 128-byte swizzled row.
@@ -393,28 +407,42 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
     int st;
     if ((st = make_map(&ma, a_hi, g.k, g.m, a_b, g.a_sm, g.a_sb, TC_BM))) return st;
     if ((st = make_map(&mal, a_lo, g.k, g.m, a_b, g.a_sm, g.a_sb, TC_BM))) return st;
+    // 256-wide tiles halve the L2 traffic per flop; keep 128 when that would
+    // leave SMs idle
+    const long long tiles_m = (g.m + TC_BM - 1) / TC_BM;
+    int bn = (tiles_m * ((g.n + 255) / 256) * g.batch >= 2LL * dev->prop.multiProcessorCount) ? 256 : 128;
+    if (const char* e = getenv("EB200_TC_BN")) bn = atoi(e) == 256 ? 256 : 128;
     if (b_nmajor) {
         if ((st = make_map(&mb, b_hi, g.n, g.k, b_b, g.b_sk, g.b_sb, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))) return st;
         if ((st = make_map(&mbl, b_lo, g.n, g.k, b_b, g.b_sk, g.b_sb, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))) return st;
     } else {
-        if ((st = make_map(&mb, b_hi, g.k, g.n, b_b, g.b_sn, g.b_sb, TC_BN))) return st;
-        if ((st = make_map(&mbl, b_lo, g.k, g.n, b_b, g.b_sn, g.b_sb, TC_BN))) return st;
+        if ((st = make_map(&mb, b_hi, g.k, g.n, b_b, g.b_sn, g.b_sb, bn))) return st;
+        if ((st = make_map(&mbl, b_lo, g.k, g.n, b_b, g.b_sn, g.b_sb, bn))) return st;
     }
     TcParams q{};
     q.m = g.m; q.n = g.n; q.k = g.k;
     q.c_sm = g.c_sm; q.c_sn = g.c_sn; q.c_sb = g.c_sb; q.c_off = g.c_off;
     q.b_nmajor = b_nmajor ? 1 : 0;
     q.three_pass = three ? 1 : 0;
-    q.stages = three ? 3 : 6;
+    const int stage_bytes = (three ? 2 : 1) * (TC_TILE_BYTES + bn * TC_BK * 4);
+    q.stages = std::min(8, (196 * 1024) / stage_bytes);
     q.error_flag = dev->error_flag_dev;
-    const int stage_bytes = (three ? 4 : 2) * TC_TILE_BYTES;
     const size_t smem = (size_t)q.stages * stage_bytes + 1024 /* alignment */ + 256 /* barriers */;
     if (!dev->tc_configured) {
-        EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         dev->tc_configured = true;
     }
-    dim3 grid((unsigned)((g.n + TC_BN - 1) / TC_BN), (unsigned)((g.m + TC_BM - 1) / TC_BM), (unsigned)g.batch);
-    gemm_tc_kernel<<<grid, TC_THREADS, smem, dev->stream>>>(ma, mal, mb, mbl, q, c, g.a_sb > 0 ? 1 : 0, g.b_sb > 0 ? 1 : 0);
+    const long long tiles_n = (g.n + bn - 1) / bn;
+    q.raster = 8;
+    if (const char* e = getenv("EB200_TC_RASTER")) q.raster = std::max(1, atoi(e));
+    const long long bands = (tiles_m + q.raster - 1) / q.raster;
+    q.tiles_n = (int)tiles_n;
+    // grid.x walks bands x (raster x tiles_n) slots; the last band may be padded
+    dim3 grid((unsigned)(bands * q.raster * tiles_n), 1, (unsigned)g.batch);
+    const int az = g.a_sb > 0 ? 1 : 0, bzm = g.b_sb > 0 ? 1 : 0;
+    if (bn == 256) gemm_tc_kernel<256><<<grid, TC_THREADS, smem, dev->stream>>>(ma, mal, mb, mbl, q, c, az, bzm);
+    else gemm_tc_kernel<128><<<grid, TC_THREADS, smem, dev->stream>>>(ma, mal, mb, mbl, q, c, az, bzm);
     count_launch();
     EB_CHECK_CUDA(cudaGetLastError());
     return EB200_OK;
