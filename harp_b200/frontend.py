@@ -91,6 +91,7 @@ class View:
         return View(sh, st, self.offset, self._remap_bounds(lambda c: c[:dim] + c[dim + 1:]), self.pad_value)
 
     def expand(self, shape) -> "View":
+        assert len(shape) == self.ndim, f"expand keeps the rank: {self.shape} -> {tuple(shape)}"
         st = list(self.strides)
         for d, (old, new) in enumerate(zip(self.shape, shape)):
             if old != new:
@@ -182,3 +183,599 @@ class Node:
         if self.kind == "fold":
             return self._fold_numel
         return math.prod(self.out_shape) if self.out_shape else 1
+
+
+# ---------------------------------------------------------------------------------------
+# tensors
+# ---------------------------------------------------------------------------------------
+w = Ast.w
+
+
+def _broadcast_shapes(a, b):
+    n = max(len(a), len(b))
+    a = (1,) * (n - len(a)) + tuple(a)
+    b = (1,) * (n - len(b)) + tuple(b)
+    out = []
+    for x, y in zip(a, b):
+        assert x == y or x == 1 or y == 1, f"shapes {a} and {b} do not broadcast"
+        out.append(max(x, y))
+    return tuple(out)
+
+
+class Tensor:
+    """Lazy tensor = (node, view).  Ops build graph nodes; ``realize`` runs them."""
+
+    def __init__(self, node: Node, view: Optional[View] = None, requires_grad=False):
+        self.node = node
+        self.view = view if view is not None else View.contiguous(node.out_shape)
+        self.requires_grad = requires_grad
+        self.grad: Optional["Tensor"] = None
+        self._parents: List[Tuple["Tensor", Callable[["Tensor"], "Tensor"]]] = []
+
+    # ---- construction ----
+    @staticmethod
+    def input(data, requires_grad=False, name="") -> "Tensor":
+        data = np.array(data, dtype=np.float32, order="C")      # keeps rank 0 for D0 tensors
+        return Tensor(Node("input", data.shape if data.ndim else (1,), data=data, name=name),
+                      View.contiguous(data.shape), requires_grad)
+
+    @staticmethod
+    def full(shape, value: float) -> "Tensor":
+        """A constant: one stored element broadcast with stride 0 (the reference
+        uploads full-size ones/zeros tensors, src/tensor/realize.rs:391-502)."""
+        node = Node("input", (1,), data=np.array([value], np.float32), name="scalar")
+        return Tensor(node, View(tuple(shape), (0,) * len(shape)))
+
+    @property
+    def shape(self):
+        return self.view.shape
+
+    @property
+    def ndim(self):
+        return self.view.ndim
+
+    def _track(self, out: "Tensor", *parents):
+        """Record (parent, grad_fn) pairs on `out` for parents that need gradients."""
+        for p, fn in parents:
+            if p.requires_grad:
+                out.requires_grad = True
+                out._parents.append((p, fn))
+        return out
+
+    # ---- views ----
+    def _view_op(self, view: View, back) -> "Tensor":
+        return self._track(Tensor(self.node, view), (self, back))
+
+    def permute(self, *axes) -> "Tensor":
+        axes = list(axes[0]) if len(axes) == 1 and isinstance(axes[0], (list, tuple)) else list(axes)
+        inv = [axes.index(i) for i in range(len(axes))]
+        return self._view_op(self.view.permute(axes), lambda g: g.permute(inv))
+
+    def unsqueeze(self, dim) -> "Tensor":
+        return self._view_op(self.view.unsqueeze(dim), lambda g: g.sum(dim))
+
+    def squeeze(self, dim) -> "Tensor":
+        return self._view_op(self.view.squeeze(dim), lambda g: g.unsqueeze(dim))
+
+    def expand(self, *shape) -> "Tensor":
+        shape = tuple(shape[0]) if len(shape) == 1 and isinstance(shape[0], (list, tuple)) else tuple(shape)
+        dims = [d for d, (o, n) in enumerate(zip(self.shape, shape)) if o != n]
+
+        def back(g):
+            for d in dims:
+                g = g.sum(d, keepdim=True)
+            return g
+        return self._view_op(self.view.expand(shape), back)
+
+    def reshape(self, *shape) -> "Tensor":
+        shape = tuple(shape[0]) if len(shape) == 1 and isinstance(shape[0], (list, tuple)) else tuple(shape)
+        src = self
+        v = self.view.reshape(shape)
+        if v is None:
+            src = self.contiguous()
+            v = src.view.reshape(shape)
+        old = self.shape
+        return src._track(Tensor(src.node, v), (src, lambda g: g.reshape(old)))
+
+    def pad(self, pads, value=0.0) -> "Tensor":
+        sl = [(b, b + s) for (b, _), s in zip(pads, self.shape)]
+        return self._view_op(self.view.pad(pads, value), lambda g: g._slice(sl))
+
+    def _slice(self, ranges) -> "Tensor":
+        v = self.view
+        off = v.offset + sum(lo * st for (lo, _), st in zip(ranges, v.strides))
+        bounds = tuple(Bound(list(b.coef), b.c + sum(k * lo for k, (lo, _) in zip(b.coef, ranges)), b.lo, b.hi) for b in v.bounds)
+        nv = View([hi - lo for lo, hi in ranges], v.strides, off, bounds, v.pad_value)
+        pads = [(lo, s - hi) for (lo, hi), s in zip(ranges, self.shape)]
+        return self._view_op(nv, lambda g: g.pad(pads))
+
+    def unfold(self, axes, sizes, strides, dilations) -> "Tensor":
+        """Materialised like the reference (every Unfold lowers to a C_ kernel,
+        src/lowerer/lower.rs:355-359); its gradient is fold, a scatter-add."""
+        uv = self.view.unfold(axes, sizes, strides, dilations)
+        node = Node("map", uv.shape, [(self.node, uv)], w(0), name="unfold")
+        in_shape = self.shape
+        out = Tensor(node)
+        return self._track(out, (self, lambda g: g.fold(in_shape, axes, sizes, strides, dilations)))
+
+    def fold(self, out_shape, axes, sizes, strides, dilations) -> "Tensor":
+        """Scatter-add windows back (S_ kernel, src/lowerer/lower.rs:580-683)."""
+        src = self.contiguous()
+        dst = View.contiguous(out_shape).unfold(axes, sizes, strides, dilations)
+        node = Node("fold", src.shape, [(src.node, src.view)], None, out_view=dst, name="fold")
+        node._fold_numel = math.prod(out_shape)
+        out = Tensor(node, View.contiguous(out_shape))
+        return src._track(out, (src, lambda g: g.unfold(axes, sizes, strides, dilations)))
+
+    def contiguous(self) -> "Tensor":
+        if self.view.is_contiguous() and self.view.numel() == self.node.out_numel:
+            return self
+        node = Node("map", self.shape, [(self.node, self.view)], w(0), name="contiguous")
+        return self._track(Tensor(node), (self, lambda g: g))
+
+    # ---- elementwise ----
+    @staticmethod
+    def _map(expr_fn, *ts: "Tensor", grads=None, name="") -> "Tensor":
+        shape = ()
+        for t in ts:
+            shape = _broadcast_shapes(shape, t.shape)
+        ops = []
+        for t in ts:
+            v = t.view
+            for _ in range(len(shape) - v.ndim):
+                v = v.unsqueeze(0)
+            ops.append((t.node, v.expand(shape)))
+        node = Node("map", shape, ops, expr_fn(*[w(i) for i in range(len(ts))]), name=name)
+        out = Tensor(node)
+        if grads:
+            for t, gfn in zip(ts, grads):
+                if t.requires_grad and gfn is not None:
+                    out.requires_grad = True
+                    out._parents.append((t, (lambda gfn, t: lambda g: _unbroadcast(gfn(g), t.shape))(gfn, t)))
+        return out
+
+    def __add__(self, o):
+        if not isinstance(o, Tensor):      # scalar literal: folded into the map
+            c = float(o)
+            return Tensor._map(lambda a: a + c, self, grads=[lambda g: g], name="add")
+        return Tensor._map(lambda a, b: a + b, self, o, grads=[lambda g: g, lambda g: g], name="add")
+
+    def __mul__(self, o):
+        if not isinstance(o, Tensor):
+            c = float(o)
+            return Tensor._map(lambda a: a * c, self, grads=[lambda g: g * c], name="mul")
+        return Tensor._map(lambda a, b: a * b, self, o, grads=[lambda g: g * o, lambda g: g * self], name="mul")
+
+    def __sub__(self, o):
+        if not isinstance(o, Tensor):
+            c = float(o)
+            return Tensor._map(lambda a: a - c, self, grads=[lambda g: g], name="sub")
+        return Tensor._map(lambda a, b: a - b, self, o, grads=[lambda g: g, lambda g: -g], name="sub")
+
+    def __truediv__(self, o):
+        if not isinstance(o, Tensor):
+            return self * (1.0 / float(o))
+        return Tensor._map(lambda a, b: a / b, self, o,
+                           grads=[lambda g: g / o, lambda g: -(g * self / (o * o))], name="div")
+
+    __radd__ = __add__
+    __rmul__ = __mul__
+
+    def __neg__(self):
+        return Tensor._map(lambda a: -a, self, grads=[lambda g: -g], name="neg")
+
+    def exp(self):
+        out = Tensor._map(lambda a: a.exp(), self, grads=[None], name="exp")
+        return self._track(out, (self, lambda g: g * out))
+
+    def ln(self):
+        return Tensor._map(lambda a: a.ln(), self, grads=[lambda g: g / self], name="ln")
+
+    def sqrt(self):
+        out = Tensor._map(lambda a: a.sqrt(), self, grads=[None], name="sqrt")
+        return self._track(out, (self, lambda g: g / (out * 2.0)))
+
+    def recip(self):
+        out = Tensor._map(lambda a: a.recip(), self, grads=[None], name="recip")
+        return self._track(out, (self, lambda g: -(g * out * out)))
+
+    def sin(self):
+        return Tensor._map(lambda a: a.sin(), self, grads=[lambda g: g * self.cos()], name="sin")
+
+    def cos(self):
+        return Tensor._map(lambda a: a.cos(), self, grads=[lambda g: -(g * self.sin())], name="cos")
+
+    def maximum(self, o):
+        if not isinstance(o, Tensor):
+            c = float(o)
+            return Tensor._map(lambda a: a.maximum(c), self,
+                               grads=[lambda g: Tensor._map(lambda g_, a: Ast.select(a.lt(c), 0.0, g_), g, self)], name="max")
+        # gradient goes to the larger operand (ties to the first), as a select on a < b
+        return Tensor._map(lambda a, b: a.maximum(b), self, o,
+                           grads=[lambda g: Tensor._map(lambda g_, a, b: Ast.select(a.lt(b), 0.0, g_), g, self, o),
+                                  lambda g: Tensor._map(lambda g_, a, b: Ast.select(a.lt(b), g_, 0.0), g, self, o)],
+                           name="max")
+
+    def relu(self):
+        # relu(x) = max(x, zeros) (crates/nn/src/functional/activation.rs:18-21)
+        # (the zeros tensor of the reference is a literal here)
+        return self.maximum(0.0)
+
+    def sigmoid(self):
+        # 1 / (1 + exp(-x))  (crates/nn/src/functional/activation.rs:50-58)
+        return ((-self).exp() + 1.0).recip()
+
+    def tanh(self):
+        # 2*sigmoid(2x) - 1, the mathematically intended form of
+        # crates/nn/src/functional/activation.rs:70-76 (whose scale() is a no-op)
+        return (self * 2.0).sigmoid() * 2.0 - 1.0
+
+    # ---- reductions ----
+    def _reduce(self, op, axis, keepdim) -> "Tensor":
+        axis = axis % self.ndim
+        if self.shape[axis] == 1 and op in (D.R_SUM, D.R_MAX, D.R_MIN, D.R_PROD):
+            return self if keepdim else self.squeeze(axis)     # nothing to fold
+        node = Node("reduce", self.shape, [(self.node, self.view)], w(0), reduce_op=op, axis=axis,
+                    name={D.R_SUM: "sum", D.R_MAX: "max"}.get(op, "reduce"))
+        out = Tensor(node)
+        if self.requires_grad:
+            full = self.shape
+            if op == D.R_SUM:
+                back = lambda g: g.expand(full)    # g has the kept-dim shape here
+            elif op == D.R_MAX:
+                kept = out
+                # mask of the positions equal to the maximum (all ties, unnormalised:
+                # src/grad/rules.rs:379-399)
+                back = lambda g: Tensor._map(lambda g_, x, m: Ast.select(x.lt(m), 0.0, g_),
+                                             g.expand(full), self, kept.expand(full))
+            else:
+                raise NotImplementedError("gradient of this reduce op")
+            out.requires_grad = True
+            out._parents.append((self, back))
+        if not keepdim:
+            res = Tensor(out.node, out.view.squeeze(axis), out.requires_grad)
+            if out.requires_grad:
+                res._parents.append((out, lambda g: g.unsqueeze(axis)))
+            return res
+        return out
+
+    def sum(self, axis=None, keepdim=False) -> "Tensor":
+        if axis is None:
+            t = self
+            for _ in range(self.ndim):
+                t = t.sum(0)
+            return t
+        return self._reduce(D.R_SUM, axis, keepdim)
+
+    def max(self, axis, keepdim=False) -> "Tensor":
+        return self._reduce(D.R_MAX, axis, keepdim)
+
+    # ---- compositions ----
+    def matmul(self, other: "Tensor") -> "Tensor":
+        """[.., M, K] @ [.., K, N] spelled as the reference spells it
+        (examples/matmul_demo.rs:43-60): unsqueeze, expand, multiply, sum over K."""
+        a = self.unsqueeze(self.ndim)                 # [.., M, K, 1]
+        b = other.unsqueeze(other.ndim - 2)           # [.., 1, K, N]
+        shape = _broadcast_shapes(a.shape, b.shape)
+        return (a.expand(shape) * b.expand(shape)).sum(len(shape) - 2)
+
+    def linear(self, weight: "Tensor", bias: Optional["Tensor"] = None) -> "Tensor":
+        """x [B, I], W [O, I] -> [B, O] (crates/nn/src/functional/linear.rs:27-56)."""
+        b_, i_ = self.shape
+        o_ = weight.shape[0]
+        y = (self.unsqueeze(1).expand(b_, o_, i_) * weight.unsqueeze(0).expand(b_, o_, i_)).sum(2)
+        if bias is not None:
+            y = y + bias.unsqueeze(0).expand(b_, o_)
+        return y
+
+    def conv2d(self, weight: "Tensor", bias: Optional["Tensor"] = None, stride=1, padding=0) -> "Tensor":
+        """crates/nn/src/functional/conv.rs:113-184: pad (always), unfold,
+        permute to [N,Ho,Wo,C,kh,kw], contiguous, GEMM over C*kh*kw, bias, permute back."""
+        n, c, h, wd = self.shape
+        co, _, kh, kw = weight.shape
+        x = self.pad([(0, 0), (0, 0), (padding, padding), (padding, padding)])
+        u = x.unfold([2, 3], [kh, kw], [stride, stride], [1, 1])       # [N, C, Ho, Wo, kh, kw]
+        ho, wo = u.shape[2], u.shape[3]
+        cols = u.permute(0, 2, 3, 1, 4, 5).contiguous().reshape(n * ho * wo, c * kh * kw)
+        y = cols.linear(weight.reshape(co, c * kh * kw))                  # [N*Ho*Wo, Co]
+        if bias is not None:
+            y = y + bias.unsqueeze(0).expand(n * ho * wo, co)
+        return y.reshape(n, ho, wo, co).permute(0, 3, 1, 2)
+
+    def max_pool2d(self, k: int) -> "Tensor":
+        """crates/nn/src/functional/pool.rs:117-160: unfold windows, max over them."""
+        n, c, h, wd = self.shape
+        u = self.unfold([2, 3], [k, k], [k, k], [1, 1])                 # [N, C, Ho, Wo, k, k]
+        return u.reshape(n, c, u.shape[2], u.shape[3], k * k).max(4)
+
+    def log_softmax(self, axis=-1) -> "Tensor":
+        """crates/nn/src/functional/activation.rs:174-187."""
+        axis = axis % self.ndim
+        m = self.max(axis, keepdim=True).expand(self.shape)
+        z = self - m
+        return z - z.exp().sum(axis, keepdim=True).expand(self.shape).ln()
+
+    # ---- autograd ----
+    def backward(self, params: Sequence["Tensor"]) -> List["Tensor"]:
+        """Reverse-mode sweep from this scalar (the role of grad::backward,
+        src/grad/backward.rs:41-87).  Returns one gradient tensor per parameter."""
+        order, seen = [], set()
+
+        def topo(t):
+            if id(t) in seen:
+                return
+            seen.add(id(t))
+            for p, _ in t._parents:
+                topo(p)
+            order.append(t)
+        topo(self)
+        grads: Dict[int, Tensor] = {id(self): Tensor.full(self.shape, 1.0)}
+        for t in reversed(order):
+            g = grads.get(id(t))
+            if g is None:
+                continue
+            for p, fn in t._parents:
+                gp = fn(g)
+                assert gp.shape == p.shape, (t.node.name, gp.shape, p.shape)
+                grads[id(p)] = gp if id(p) not in grads else grads[id(p)] + gp
+        out = []
+        for p in params:
+            g = grads.get(id(p))
+            p.grad = g if g is not None else Tensor.full(p.shape, 0.0)
+            out.append(p.grad)
+        return out
+
+
+def _as_tensor(x, like: Tensor) -> Tensor:
+    return x if isinstance(x, Tensor) else Tensor.full(like.shape, float(x))
+
+
+def _unbroadcast(g: Tensor, shape) -> Tensor:
+    """Sum a gradient over the dims an operand was broadcast along."""
+    while g.ndim > len(shape):
+        g = g.sum(0)
+    for d, (gs, s) in enumerate(zip(g.shape, shape)):
+        if gs != s:
+            g = g.sum(d, keepdim=True)
+    return g
+
+
+# ---------------------------------------------------------------------------------------
+# fusion + lowering
+# ---------------------------------------------------------------------------------------
+class _K:
+    """A kernel-to-be: mutable copy of a Node used by the fusion passes."""
+
+    def __init__(self, n: Node):
+        self.id, self.kind, self.shape, self.expr = n.id, n.kind, n.shape, n.expr
+        self.operands = [(src.id, v) for src, v in n.operands]
+        self.reduce_op, self.axis, self.dtype, self.name = n.reduce_op, n.axis, n.dtype, n.name
+        self.out_view, self.out_numel, self.out_shape = n.out_view, n.out_numel, n.out_shape
+        self.data = n.data
+
+
+def _dim_map(view: View, prod_shape) -> Optional[List[Optional[int]]]:
+    """How a consumer's view walks a producer's contiguous output: for every
+    consumer dim the producer dim it follows, or None for a broadcast.  None
+    overall when the view is not a pure permute/broadcast of the whole output."""
+    if view.bounds or view.offset != 0:
+        return None
+    cstr = D.contiguous_strides(prod_shape)
+    by_stride = {cstr[d]: d for d in range(len(prod_shape)) if prod_shape[d] > 1}
+    out, used = [], set()
+    for s, st in zip(view.shape, view.strides):
+        if s == 1 or st == 0:
+            out.append(None)
+            continue
+        pd = by_stride.get(st)
+        if pd is None or prod_shape[pd] != s or pd in used:
+            return None
+        used.add(pd)
+        out.append(pd)
+    if len(used) != len(by_stride):
+        return None
+    return out
+
+
+def _through(view: View, dmap, shape) -> View:
+    """A producer operand's view re-expressed over the consumer's dims."""
+    strides = [view.strides[pd] if pd is not None else 0 for pd in dmap]
+    bounds = tuple(Bound([b.coef[pd] if pd is not None else 0 for pd in dmap], b.c, b.lo, b.hi) for b in view.bounds)
+    return View(shape, strides, view.offset, bounds, view.pad_value)
+
+
+def _view_key(v: View):
+    return (v.shape, v.strides, v.offset, tuple((tuple(b.coef), b.c, b.lo, b.hi) for b in v.bounds), v.pad_value)
+
+
+def _fuse(ks: Dict[int, _K], order: List[int], roots: set, level: str):
+    if level == "none":
+        return
+    changed = True
+    while changed:
+        changed = False
+        consumers: Dict[int, int] = {}
+        for kid in order:
+            if kid in ks:
+                for src, _ in ks[kid].operands:
+                    consumers[src] = consumers.get(src, 0) + 1
+        for kid in order:
+            c = ks.get(kid)
+            if c is None or c.kind not in ("map", "reduce"):
+                continue
+            if level == "reference" and c.kind != "reduce":
+                continue       # eclat only folds an elementwise node into the reduce that consumes it
+            for j, (src, v) in enumerate(c.operands):
+                p = ks.get(src)
+                if p is None or p.kind != "map" or src in roots or consumers.get(src, 0) != 1:
+                    continue
+                if level == "reference" and getattr(c, "_absorbed", False):
+                    continue
+                dmap = _dim_map(v, p.shape)
+                if dmap is None:
+                    continue
+                # merged operand list (deduplicated), wildcard renumbering
+                new_ops = [o for i, o in enumerate(c.operands) if i != j]
+                remap_c = {}
+                for i in range(len(c.operands)):
+                    if i != j:
+                        remap_c[i] = w(i if i < j else i - 1)
+                sub = {}
+                for i, (ps, pv) in enumerate(p.operands):
+                    nv = _through(pv, dmap, c.shape)
+                    key = (ps, _view_key(nv))
+                    idx = next((t for t, (s2, v2) in enumerate(new_ops) if (s2, _view_key(v2)) == key), None)
+                    if idx is None:
+                        new_ops.append((ps, nv))
+                        idx = len(new_ops) - 1
+                    sub[i] = w(idx)
+                if len(new_ops) > D.MAX_INPUTS:
+                    continue
+                remap_c[j] = p.expr.substitute(sub)
+                new_expr = c.expr.substitute(remap_c)
+                if len(new_expr.postfix()) > D.MAX_INSNS:
+                    continue
+                c.operands, c.expr = new_ops, new_expr
+                c._absorbed = True
+                del ks[src]
+                changed = True
+                break
+            if changed:
+                break
+
+
+def _lower(k: _K, numel_of: Dict[int, int]) -> D.KernelDesc:
+    ins = [v.operand(numel_of[src], D.F32) for src, v in k.operands]
+    if k.kind == "map":
+        identity = k.expr.op == "w" and len(k.operands) == 1
+        if identity:
+            return D.KernelDesc(D.K_COPY, k.shape, ins, D.contiguous(k.shape), None, name=k.name)
+        return D.KernelDesc(D.K_ELEMENTWISE, k.shape, ins, D.contiguous(k.shape), k.expr, name=k.name)
+    if k.kind == "reduce":
+        return D.reduce(list(k.shape), ins, k.expr, k.reduce_op, k.axis)
+    if k.kind == "fold":
+        return D.KernelDesc(D.K_SCATTER, k.shape, ins, k.out_view.operand(k.out_numel, D.F32), None, name=k.name)
+    raise ValueError(k.kind)
+
+
+class Program:
+    """Compiled multi-root realize: every root (and every gradient) comes out of
+    one kernel list, parameters live in persistent buffers and are updated in
+    place.  (The reference re-runs the whole graph once per gradient and updates
+    on the host: crates/nn/src/optim/optimizer.rs:100-131, sgd.rs:73-103.)"""
+
+    def __init__(self, roots: Sequence[Tensor], executor, fuse: str = "chains",
+                 sgd: Sequence[Tuple[Tensor, Tensor]] = (), lr: float = 0.0):
+        self.ex = executor
+        self.roots = list(roots)
+        self.sgd = list(sgd)
+        all_roots = self.roots + [g for _, g in self.sgd] + [p for p, _ in self.sgd]
+        nodes: Dict[int, Node] = {}
+        order: List[int] = []
+
+        def visit(n: Node):
+            if n.id in nodes:
+                return
+            nodes[n.id] = n
+            for src, _ in n.operands:
+                visit(src)
+            order.append(n.id)
+        import sys
+        sys.setrecursionlimit(max(10000, sys.getrecursionlimit()))
+        for t in all_roots:
+            visit(t.node)
+        ks = {i: _K(nodes[i]) for i in order}
+        root_ids = {t.node.id for t in all_roots}
+        _fuse(ks, order, root_ids, fuse)
+        self.order = [i for i in order if i in ks]
+        self.ks = ks
+        self.numel = {i: ks[i].out_numel for i in self.order}
+        self.inputs = {i: ks[i] for i in self.order if ks[i].kind == "input"}
+        self.kernels = []          # (node id, desc, compiled kernel, [src ids])
+        for i in self.order:
+            k = ks[i]
+            if k.kind == "input":
+                continue
+            d = _lower(k, self.numel)
+            self.kernels.append((i, d, self.ex.compile(d), [s for s, _ in k.operands]))
+        # liveness: a buffer may go once its last consumer has run
+        last = {}
+        for pos, (i, _, _, srcs) in enumerate(self.kernels):
+            for s in srcs:
+                last[s] = pos
+        keep = set(root_ids) | set(self.inputs)
+        self.release_after = [[] for _ in self.kernels]
+        for s, pos in last.items():
+            if s not in keep:
+                self.release_after[pos].append(s)
+        self.sgd_kernels = []
+        for p, g in self.sgd:
+            n = p.node.out_numel
+            d = D.KernelDesc(D.K_SGD, [n], [D.contiguous([n]), D.contiguous([n])], D.contiguous([n]), scalar=lr)
+            self.sgd_kernels.append((p.node.id, g.node.id, self.ex.compile(d)))
+        self.buf: Dict[int, object] = {}
+        for i, k in self.inputs.items():
+            self.buf[i] = self.ex.alloc(self.numel[i])
+            self.ex.upload(self.buf[i], k.data.reshape(-1))
+
+    def set_input(self, t: Tensor, data: np.ndarray):
+        self.ex.upload(self.buf[t.node.id], np.ascontiguousarray(data, np.float32).reshape(-1))
+
+    def kernel_descs(self) -> List[D.KernelDesc]:
+        return [d for _, d, _, _ in self.kernels]
+
+    def run_forward(self):
+        """All kernels up to and including the gradients (no parameter update)."""
+        for pos, (i, d, kern, srcs) in enumerate(self.kernels):
+            if i not in self.buf:
+                self.buf[i] = self.ex.alloc(self.numel[i])
+            kern.execute([self.buf[s] for s in srcs], [self.buf[i]])
+            for s in self.release_after[pos]:
+                self.ex.free(self.buf.pop(s))
+
+    def run_update(self):
+        for pid, gid, kern in self.sgd_kernels:
+            kern.execute([self.buf[pid], self.buf[gid]], [self.buf[pid]])
+
+    def run(self):
+        self.run_forward()
+        self.run_update()
+
+    def buffer_of(self, t: Tensor):
+        return self.buf[t.node.id]
+
+    def fetch(self, t: Tensor) -> np.ndarray:
+        """Root value as a numpy array of the tensor's logical shape."""
+        flat = self.ex.download(self.buf[t.node.id], self.numel[t.node.id])
+        v = t.view
+        if v.is_contiguous() or not v.shape:
+            return flat[v.offset:v.offset + max(1, v.numel())].reshape(v.shape)
+        return np.lib.stride_tricks.as_strided(flat[v.offset:], v.shape, [s * 4 for s in v.strides]).copy()
+
+
+class B200Executor:
+    """Runs programs on the CUDA library."""
+
+    def __init__(self, device=None, registry=None):
+        from .backend import B200BackendRegistry
+        self.reg = registry or B200BackendRegistry()
+        self.dev = device or self.reg.create_device(0)
+
+    def alloc(self, numel):
+        from .backend import B200Buffer
+        return B200Buffer.allocate(self.dev, [numel], D.F32, zero=False)
+
+    def free(self, buf):
+        buf.release()
+
+    def upload(self, buf, data):
+        buf.write_vec(data)
+
+    def download(self, buf, numel):
+        return buf.read_vec()
+
+    def compile(self, d):
+        return self.reg.compile_ast(self.dev, d)
+
+    def synchronize(self):
+        self.dev.synchronize()
