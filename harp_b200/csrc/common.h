@@ -154,6 +154,9 @@ struct GemmShape {
     long long c_sb = 0, c_sm = 0, c_sn = 0, c_off = 0;
     int a_input = 0, b_input = 1;  // which kernel input is A / B
     int mode = EB200_GEMM_3XTF32;
+    int splits = 1;            // split-K: partial products go to scratch and are summed by a second kernel
+    long long k_chunk = 0;     // k extent per split (multiple of 32)
+    long long partial_off = 0; // float offset of the partials inside the kernel's scratch
 };
 
 struct TransposeShape {
@@ -200,7 +203,8 @@ int launch_reduce(Device* dev, const Plan& plan, const KParams& p, void* scratch
 int launch_transpose(Device* dev, const Plan& plan, const void* in, void* out);
 int launch_scatter(Device* dev, const Plan& plan, const KParams& p);
 int launch_sgd(Device* dev, const Plan& plan, const float* p, const float* g, float* out, long long n);
-int launch_gemm_simt(Device* dev, const Plan& plan, const float* a, const float* b, float* c);
+int launch_gemm_simt(Device* dev, const Plan& plan, const float* a, const float* b, float* c, void* scratch);
+int launch_splitk_reduce(Device* dev, const GemmShape& g, const float* partials, float* c);
 bool gemm_tc_supported(const GemmShape& g);
 void gemm_tc_scratch(const GemmShape& g, long long* a_span, long long* b_span);
 int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b, float* c, void* scratch);

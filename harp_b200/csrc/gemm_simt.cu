@@ -24,10 +24,15 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const __grid_constant__ 
     __shared__ float Bs[GK][GN + 4];
     const int t = threadIdx.x;
     const long long m0 = (long long)blockIdx.x * GM, n0 = (long long)blockIdx.y * GN;
-    const long long bz = blockIdx.z;
+    const long long bz = blockIdx.z / g.splits;
+    const long long split = blockIdx.z % g.splits;
+    const long long kbeg = split * g.k_chunk;
+    const long long kend = g.splits > 1 ? min(g.k, kbeg + g.k_chunk) : g.k;
     const float* Ab = A + g.a_off + bz * g.a_sb;
     const float* Bb = B + g.b_off + bz * g.b_sb;
-    float* Cb = C + g.c_off + bz * g.c_sb;
+    // with split-K the CTA writes a dense [m][n] partial; the caller passes the partial buffer as C
+    float* Cb = g.splits > 1 ? C + (long long)blockIdx.z * g.m * g.n : C + g.c_off + bz * g.c_sb;
+    const long long c_sm = g.splits > 1 ? g.n : g.c_sm, c_sn = g.splits > 1 ? 1 : g.c_sn;
     const int ty = t >> 4, tx = t & 15;
     float acc[4][4];
 #pragma unroll
@@ -36,19 +41,19 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const __grid_constant__ 
         for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
     const bool a_kfast = g.a_sk == 1;
     const bool b_nfast = g.b_sn == 1;
-    for (long long k0 = 0; k0 < g.k; k0 += GK) {
+    for (long long k0 = kbeg; k0 < kend; k0 += GK) {
 #pragma unroll
         for (int pass = 0; pass < 4; ++pass) {
             int m, k;
             if (a_kfast) { m = (t >> 4) + pass * 16; k = t & 15; }
             else { k = (t >> 6) + pass * 4; m = t & 63; }
             const long long gm = m0 + m, gk = k0 + k;
-            As[k][m] = (gm < g.m && gk < g.k) ? __ldg(Ab + gm * g.a_sm + gk * g.a_sk) : 0.0f;
+            As[k][m] = (gm < g.m && gk < kend) ? __ldg(Ab + gm * g.a_sm + gk * g.a_sk) : 0.0f;
             int n, kb;
             if (b_nfast) { kb = (t >> 6) + pass * 4; n = t & 63; }
             else { n = (t >> 4) + pass * 16; kb = t & 15; }
             const long long gn = n0 + n, gkb = k0 + kb;
-            Bs[kb][n] = (gn < g.n && gkb < g.k) ? __ldg(Bb + gkb * g.b_sk + gn * g.b_sn) : 0.0f;
+            Bs[kb][n] = (gn < g.n && gkb < kend) ? __ldg(Bb + gkb * g.b_sk + gn * g.b_sn) : 0.0f;
         }
         __syncthreads();
 #pragma unroll
@@ -72,21 +77,51 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const __grid_constant__ 
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const long long gn = n0 + tx * 4 + j;
-            if (gn < g.n) Cb[gm * g.c_sm + gn * g.c_sn] = acc[i][j];
+            if (gn < g.n) Cb[gm * c_sm + gn * c_sn] = acc[i][j];
         }
     }
 }
 
-int launch_gemm_simt(Device* dev, const Plan& plan, const float* a, const float* b, float* c) {
-    const GemmShape& g = plan.gemm;
-    if (g.m <= 0 || g.n <= 0 || g.batch <= 0) return EB200_OK;
-    EB_REQUIRE(g.batch <= 65535, EB200_ERR_UNSUPPORTED, "batch %lld exceeds grid.z", g.batch);
-    const long long by = (g.n + GN - 1) / GN;
-    EB_REQUIRE(by <= 65535, EB200_ERR_UNSUPPORTED, "n = %lld exceeds grid.y tiles", g.n);
-    dim3 grid((unsigned)((g.m + GM - 1) / GM), (unsigned)by, (unsigned)g.batch);
-    gemm_simt_kernel<<<grid, 256, 0, dev->stream>>>(g, a, b, c);
+// Sums split-K partials [batch][splits][m][n] into C through its strides, in
+// increasing split order (deterministic).
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const __grid_constant__ GemmShape g,
+                                                            const float* __restrict__ P, float* __restrict__ C) {
+    const long long mn = g.m * g.n, total = g.batch * mn;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += stride) {
+        const long long bz = e / mn, r = e - bz * mn;
+        const long long row = r / g.n, col = r - row * g.n;
+        const float* src = P + bz * g.splits * mn + r;
+        float acc = 0.0f;
+        for (int s = 0; s < g.splits; ++s) acc += src[(long long)s * mn];
+        C[g.c_off + bz * g.c_sb + row * g.c_sm + col * g.c_sn] = acc;
+    }
+}
+
+int launch_splitk_reduce(Device* dev, const GemmShape& g, const float* partials, float* c) {
+    const long long total = g.batch * g.m * g.n;
+    long long blocks = (total + 255) / 256;
+    const long long cap = (long long)dev->prop.multiProcessorCount * 16;
+    if (blocks > cap) blocks = cap;
+    splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, dev->stream>>>(g, partials, c);
     count_launch();
     EB_CHECK_CUDA(cudaGetLastError());
+    return EB200_OK;
+}
+
+int launch_gemm_simt(Device* dev, const Plan& plan, const float* a, const float* b, float* c, void* scratch) {
+    const GemmShape& g = plan.gemm;
+    if (g.m <= 0 || g.n <= 0 || g.batch <= 0) return EB200_OK;
+    EB_REQUIRE(g.batch * g.splits <= 65535, EB200_ERR_UNSUPPORTED, "batch %lld x splits %d exceeds grid.z", g.batch, g.splits);
+    const long long by = (g.n + GN - 1) / GN;
+    EB_REQUIRE(by <= 65535, EB200_ERR_UNSUPPORTED, "n = %lld exceeds grid.y tiles", g.n);
+    dim3 grid((unsigned)((g.m + GM - 1) / GM), (unsigned)by, (unsigned)(g.batch * g.splits));
+    float* partials = g.splits > 1 ? reinterpret_cast<float*>(scratch) + g.partial_off : nullptr;
+    EB_REQUIRE(g.splits == 1 || scratch, EB200_ERR_INVALID, "split-K launched without scratch");
+    gemm_simt_kernel<<<grid, 256, 0, dev->stream>>>(g, a, b, g.splits > 1 ? partials : c);
+    count_launch();
+    EB_CHECK_CUDA(cudaGetLastError());
+    if (g.splits > 1) return launch_splitk_reduce(dev, g, partials, c);
     return EB200_OK;
 }
 

@@ -46,6 +46,9 @@ struct TcParams {
     long long m, n, k;
     long long c_sm, c_sn, c_sb, c_off;
     int b_nmajor;      // 1: B tiles are [k][n] with n contiguous
+    int a_mmajor;      // 1: A tiles are [k][m] with m contiguous
+    int splits;        // split-K factor (blockIdx.z = batch * splits + split)
+    int kb_per_split;  // k blocks per split
     int three_pass;    // 1: 3xTF32
     int stages;
     int raster;        // tile rows per band
@@ -142,8 +145,8 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_b
 }
 
 // Instruction descriptor for kind::tf32: f32 accumulate, tf32 A and B, M x N tile.
-__host__ __device__ constexpr uint32_t umma_idesc_tf32(int M, int N, int b_nmajor) {
-    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(b_nmajor ? 1 : 0) << 16) |
+__host__ __device__ constexpr uint32_t umma_idesc_tf32(int M, int N, int a_mmajor, int b_nmajor) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(a_mmajor ? 1 : 0) << 15) | ((uint32_t)(b_nmajor ? 1 : 0) << 16) |
            ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
@@ -174,9 +177,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int tile_m = band * q.raster + within % band_rows;
     const int tile_n = within / band_rows;
     const long long n0 = (long long)tile_n * TC_BN, m0 = (long long)tile_m * TC_BM;
-    const int bz = blockIdx.z;
+    const int bz = (int)blockIdx.z / q.splits, split = (int)blockIdx.z % q.splits;
     if (tile_n >= q.tiles_n) return;   // padding of the last, shorter band
-    const int num_kb = (int)((q.k + TC_BK - 1) / TC_BK);
+    const int total_kb = (int)((q.k + TC_BK - 1) / TC_BK);
+    const int kb_begin = split * q.kb_per_split;
+    const int num_kb = min(total_kb - kb_begin, q.kb_per_split);   // k blocks of this CTA (>= 1 by construction)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < q.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -198,11 +203,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (!mbar_wait(&empty_bar[s], phase ^ 1u, q.error_flag)) break;
                 unsigned char* st = smem + (size_t)s * stage_bytes;
                 mbar_expect_tx(&full_bar[s], (unsigned)stage_bytes);
-                const int kx = kb * TC_BK;
+                const int kx = (kb_begin + kb) * TC_BK;
                 unsigned char* a_hi = st;
                 unsigned char* b_hi = st + (q.three_pass ? 2 : 1) * TC_TILE_BYTES;   // [A hi | A lo | B hi | B lo]
-                tma_load_3d(a_hi, &map_a, &full_bar[s], kx, (int)m0, bz * a_zmul);
-                if (q.three_pass) tma_load_3d(st + TC_TILE_BYTES, &map_alo, &full_bar[s], kx, (int)m0, bz * a_zmul);
+                if (q.a_mmajor) {
+                    // four [32 k][32 m] boxes side by side along m
+#pragma unroll
+                    for (int j = 0; j < TC_BM / 32; ++j) {
+                        tma_load_3d(a_hi + j * 4096, &map_a, &full_bar[s], (int)m0 + j * 32, kx, bz * a_zmul);
+                        if (q.three_pass) tma_load_3d(st + TC_TILE_BYTES + j * 4096, &map_alo, &full_bar[s], (int)m0 + j * 32, kx, bz * a_zmul);
+                    }
+                } else {
+                    tma_load_3d(a_hi, &map_a, &full_bar[s], kx, (int)m0, bz * a_zmul);
+                    if (q.three_pass) tma_load_3d(st + TC_TILE_BYTES, &map_alo, &full_bar[s], kx, (int)m0, bz * a_zmul);
+                }
                 if (q.b_nmajor) {
                     // four [32 k][32 n] boxes side by side along n
 #pragma unroll
@@ -219,7 +233,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else if (warp == 1) {
         // ---- MMA issuer (one thread) ----
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc_tf32(TC_BM, TC_BN, q.b_nmajor);
+            const uint32_t idesc = umma_idesc_tf32(TC_BM, TC_BN, q.a_mmajor, q.b_nmajor);
             bool ok = true;
             for (int kb = 0; kb < num_kb && ok; ++kb) {
                 const int s = kb % q.stages;
@@ -234,17 +248,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 for (int j = 0; j < TC_BK / TC_UK; ++j) {
                     // K-major: step 32 bytes inside the 128-byte swizzled row.
                     // N-major B: step one 8-row group (1024 bytes); n atoms are 4096 bytes apart.
-                    const uint32_t a_step = j * TC_UK * 4;
+                    const uint32_t a_step = q.a_mmajor ? j * 1024 : j * TC_UK * 4;
+                    const uint32_t a_lbo = q.a_mmajor ? 4096 : 16, a_sbo = q.a_mmajor ? 512 : 1024, a_layout = q.a_mmajor ? 1 : 2;
                     const uint32_t b_step = q.b_nmajor ? j * 1024 : j * TC_UK * 4;
                     // (swizzle atom = 4 k rows = 512 bytes, so one K=8 MMA spans two atoms)
                     const uint32_t b_lbo = q.b_nmajor ? 4096 : 16;
                     const uint32_t b_sbo = q.b_nmajor ? 512 : 1024;
                     const uint32_t b_layout = q.b_nmajor ? 1 : 2;
-                    const uint64_t da = umma_desc(a_hi + a_step, 16, 1024);
+                    const uint64_t da = umma_desc(a_hi + a_step, a_lbo, a_sbo, a_layout);
                     const uint64_t db = umma_desc(b_hi + b_step, b_lbo, b_sbo, b_layout);
                     umma_tf32(tmem_base, da, db, idesc, (kb > 0 || j > 0) ? 1u : 0u);
                     if (q.three_pass) {
-                        const uint64_t dal = umma_desc(a_lo + a_step, 16, 1024);
+                        const uint64_t dal = umma_desc(a_lo + a_step, a_lbo, a_sbo, a_layout);
                         const uint64_t dbl = umma_desc(b_lo + b_step, b_lbo, b_sbo, b_layout);
                         umma_tf32(tmem_base, dal, db, idesc, 1u);
                         umma_tf32(tmem_base, da, dbl, idesc, 1u);
@@ -260,7 +275,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const bool ok = mbar_wait(acc_bar, 0, q.error_flag);
         tc_fence_after();
         const long long row = m0 + quarter * 32 + lane;
-        float* crow = C + q.c_off + (long long)bz * q.c_sb + row * q.c_sm;
+        // split-K: C is the dense partial buffer [batch*splits][m][n] (strides set by the launcher)
+        float* crow = C + q.c_off + (long long)(q.splits > 1 ? (int)blockIdx.z : bz) * q.c_sb + row * q.c_sm;
 #pragma unroll 1
         for (int c = 0; c < TC_BN / 32; ++c) {
             float v[32];
@@ -347,14 +363,14 @@ static int make_map(CUtensorMap* map, const float* base, long long inner, long l
 
 // Whether the tensor-core kernel can take this contraction (plan.cpp asks).
 bool gemm_tc_supported(const GemmShape& g) {
-    if (g.a_sk != 1) return false;                       // A must be K-major
+    const bool a_kmajor = g.a_sk == 1, a_mmajor = g.a_sm == 1;
+    if (!a_kmajor && !a_mmajor) return false;
     const bool b_kmajor = g.b_sk == 1, b_nmajor = g.b_sn == 1;
     if (!b_kmajor && !b_nmajor) return false;
-    if (g.k == 1 && b_kmajor && b_nmajor) {}             // either reading works
     auto mult4 = [](long long v) { return (v & 3) == 0; };
-    if (!mult4(g.a_sm) || !mult4(g.a_sb) || !mult4(g.a_off)) return false;
+    if (!mult4(a_kmajor ? g.a_sm : g.a_sk) || !mult4(g.a_sb) || !mult4(g.a_off)) return false;
     if (!mult4(b_kmajor ? g.b_sn : g.b_sk) || !mult4(g.b_sb) || !mult4(g.b_off)) return false;
-    if (g.a_sm < g.k) return false;
+    if ((a_kmajor ? g.a_sm : g.a_sk) <= 0 || (b_kmajor ? g.b_sn : g.b_sk) <= 0) return false;
     if (g.batch < 1 || g.batch > 65535) return false;
     if (g.m < 1 || g.n < 1 || g.k < 1) return false;
     if (g.m >= (1LL << 31) || g.n >= (1LL << 31) || g.k >= (1LL << 31)) return false;
@@ -370,7 +386,7 @@ static long long span_of(long long batch, long long sb, long long rows, long lon
 
 void gemm_tc_scratch(const GemmShape& g, long long* a_span, long long* b_span) {
     const bool b_kmajor = g.b_sk == 1;
-    long long a = span_of(g.batch, g.a_sb, g.m, g.a_sm, g.k);
+    long long a = g.a_sk == 1 ? span_of(g.batch, g.a_sb, g.m, g.a_sm, g.k) : span_of(g.batch, g.a_sb, g.k, g.a_sk, g.m);
     long long b = b_kmajor ? span_of(g.batch, g.b_sb, g.n, g.b_sn, g.k) : span_of(g.batch, g.b_sb, g.k, g.b_sk, g.n);
     *a_span = (a + 63) / 64 * 64;
     *b_span = (b + 63) / 64 * 64;
@@ -380,6 +396,7 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
     const GemmShape& g = plan.gemm;
     const bool three = g.mode == EB200_GEMM_3XTF32;
     const bool b_nmajor = !(g.b_sk == 1);
+    const bool a_mmajor = !(g.a_sk == 1);
     const float* a_src = a + g.a_off;
     const float* b_src = b + g.b_off;
     EB_REQUIRE((reinterpret_cast<uintptr_t>(a_src) & 15) == 0 && (reinterpret_cast<uintptr_t>(b_src) & 15) == 0,
@@ -393,7 +410,8 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
         float *ah = s, *al = s + a_span, *bh = s + 2 * a_span, *bl = s + 2 * a_span + b_span;
         const long long cap = (long long)dev->prop.multiProcessorCount * 16;
         long long blocks = std::min(cap, (a_span / 4 + 255) / 256 + 1);
-        split_tf32_kernel<<<(unsigned)blocks, 256, 0, dev->stream>>>(a_src, ah, al, span_of(g.batch, g.a_sb, g.m, g.a_sm, g.k));
+        const long long as = a_mmajor ? span_of(g.batch, g.a_sb, g.k, g.a_sk, g.m) : span_of(g.batch, g.a_sb, g.m, g.a_sm, g.k);
+        split_tf32_kernel<<<(unsigned)blocks, 256, 0, dev->stream>>>(a_src, ah, al, as);
         count_launch();
         blocks = std::min(cap, (b_span / 4 + 255) / 256 + 1);
         const long long bs = b_nmajor ? span_of(g.batch, g.b_sb, g.k, g.b_sk, g.n) : span_of(g.batch, g.b_sb, g.n, g.b_sn, g.k);
@@ -405,12 +423,17 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
     CUtensorMap ma, mal, mb, mbl;
     const long long a_b = g.a_sb > 0 ? g.batch : 1, b_b = g.b_sb > 0 ? g.batch : 1;
     int st;
-    if ((st = make_map(&ma, a_hi, g.k, g.m, a_b, g.a_sm, g.a_sb, TC_BM))) return st;
-    if ((st = make_map(&mal, a_lo, g.k, g.m, a_b, g.a_sm, g.a_sb, TC_BM))) return st;
+    if (a_mmajor) {
+        if ((st = make_map(&ma, a_hi, g.m, g.k, a_b, g.a_sk, g.a_sb, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))) return st;
+        if ((st = make_map(&mal, a_lo, g.m, g.k, a_b, g.a_sk, g.a_sb, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))) return st;
+    } else {
+        if ((st = make_map(&ma, a_hi, g.k, g.m, a_b, g.a_sm, g.a_sb, TC_BM))) return st;
+        if ((st = make_map(&mal, a_lo, g.k, g.m, a_b, g.a_sm, g.a_sb, TC_BM))) return st;
+    }
     // 256-wide tiles halve the L2 traffic per flop; keep 128 when that would
     // leave SMs idle
     const long long tiles_m = (g.m + TC_BM - 1) / TC_BM;
-    int bn = (tiles_m * ((g.n + 255) / 256) * g.batch >= 2LL * dev->prop.multiProcessorCount) ? 256 : 128;
+    int bn = (tiles_m * ((g.n + 255) / 256) * g.batch * g.splits >= 2LL * dev->prop.multiProcessorCount) ? 256 : 128;
     if (const char* e = getenv("EB200_TC_BN")) bn = atoi(e) == 256 ? 256 : 128;
     if (b_nmajor) {
         if ((st = make_map(&mb, b_hi, g.n, g.k, b_b, g.b_sk, g.b_sb, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))) return st;
@@ -423,6 +446,15 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
     q.m = g.m; q.n = g.n; q.k = g.k;
     q.c_sm = g.c_sm; q.c_sn = g.c_sn; q.c_sb = g.c_sb; q.c_off = g.c_off;
     q.b_nmajor = b_nmajor ? 1 : 0;
+    q.a_mmajor = a_mmajor ? 1 : 0;
+    q.splits = g.splits;
+    q.kb_per_split = g.splits > 1 ? (int)(g.k_chunk / TC_BK) : (int)((g.k + TC_BK - 1) / TC_BK);
+    float* c_out = c;
+    if (g.splits > 1) {
+        EB_REQUIRE(scratch, EB200_ERR_INVALID, "split-K launched without scratch");
+        c_out = reinterpret_cast<float*>(scratch) + g.partial_off;     // dense [batch*splits][m][n]
+        q.c_off = 0; q.c_sm = g.n; q.c_sn = 1; q.c_sb = g.m * g.n;
+    }
     q.three_pass = three ? 1 : 0;
     const int stage_bytes = (three ? 2 : 1) * (TC_TILE_BYTES + bn * TC_BK * 4);
     q.stages = std::min(8, (196 * 1024) / stage_bytes);
@@ -439,12 +471,13 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
     const long long bands = (tiles_m + q.raster - 1) / q.raster;
     q.tiles_n = (int)tiles_n;
     // grid.x walks bands x (raster x tiles_n) slots; the last band may be padded
-    dim3 grid((unsigned)(bands * q.raster * tiles_n), 1, (unsigned)g.batch);
+    dim3 grid((unsigned)(bands * q.raster * tiles_n), 1, (unsigned)(g.batch * g.splits));
     const int az = g.a_sb > 0 ? 1 : 0, bzm = g.b_sb > 0 ? 1 : 0;
-    if (bn == 256) gemm_tc_kernel<256><<<grid, TC_THREADS, smem, dev->stream>>>(ma, mal, mb, mbl, q, c, az, bzm);
-    else gemm_tc_kernel<128><<<grid, TC_THREADS, smem, dev->stream>>>(ma, mal, mb, mbl, q, c, az, bzm);
+    if (bn == 256) gemm_tc_kernel<256><<<grid, TC_THREADS, smem, dev->stream>>>(ma, mal, mb, mbl, q, c_out, az, bzm);
+    else gemm_tc_kernel<128><<<grid, TC_THREADS, smem, dev->stream>>>(ma, mal, mb, mbl, q, c_out, az, bzm);
     count_launch();
     EB_CHECK_CUDA(cudaGetLastError());
+    if (g.splits > 1) return launch_splitk_reduce(dev, g, c_out, c);
     return EB200_OK;
 }
 

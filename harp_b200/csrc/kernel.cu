@@ -127,7 +127,7 @@ int eb200_kernel_launch(eb200_kernel* k, eb200_buffer* const* inputs, int n_inpu
         case IMPL_GEMM_SIMT:
             return launch_gemm_simt(dev, plan, reinterpret_cast<const float*>(p.in[plan.gemm.a_input].ptr),
                                     reinterpret_cast<const float*>(p.in[plan.gemm.b_input].ptr),
-                                    reinterpret_cast<float*>(p.out.ptr));
+                                    reinterpret_cast<float*>(p.out.ptr), scratch);
         case IMPL_GEMM_TC:
             return launch_gemm_tc(dev, plan, reinterpret_cast<const float*>(p.in[plan.gemm.a_input].ptr),
                                   reinterpret_cast<const float*>(p.in[plan.gemm.b_input].ptr),

@@ -451,21 +451,48 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
                 // tensor cores when the operand layout allows it and the problem
                 // is more than a few tiles of work; f32 FFMA tiles otherwise
                 const bool force_simt = (d->flags & 8) != 0;
-                if (!force_simt && gemm_tc_supported(pl.gemm) && pl.algo_flops >= (1LL << 22)) {
+                GemmShape& g = pl.gemm;
+                const bool tc = !force_simt && gemm_tc_supported(g) && pl.algo_flops >= (1LL << 22);
+                // split-K when the output has too few tiles to fill the machine
+                // (weight gradients: small M x N, K = batch)
+                {
+                    const long long tm = tc ? 128 : 64, tn = tc ? 128 : 64;
+                    const long long tiles = ((g.m + tm - 1) / tm) * ((g.n + tn - 1) / tn) * g.batch;
+                    const long long kblocks = (g.k + 31) / 32;
+                    if (tiles < sm_count && kblocks >= 16 && (d->flags & 16) == 0) {
+                        long long s = std::min<long long>((2LL * sm_count + tiles - 1) / tiles, kblocks / 8);
+                        s = std::min<long long>(s, 65535 / std::max<long long>(1, g.batch));
+                        if (s > 1) {
+                            long long per = (kblocks + s - 1) / s;
+                            s = (kblocks + per - 1) / per;
+                            g.splits = (int)s;
+                            g.k_chunk = per * 32;
+                        }
+                    }
+                }
+                long long scratch_floats = 0;
+                if (tc) {
                     pl.impl = IMPL_GEMM_TC;
-                    const bool three = pl.gemm.mode == EB200_GEMM_3XTF32;
+                    const bool three = g.mode == EB200_GEMM_3XTF32;
                     if (three) {
                         long long a_span, b_span;
-                        gemm_tc_scratch(pl.gemm, &a_span, &b_span);
-                        pl.scratch_bytes = (2 * a_span + 2 * b_span) * 4;
+                        gemm_tc_scratch(g, &a_span, &b_span);
+                        scratch_floats = 2 * a_span + 2 * b_span;
                         pl.launches = 3;
                     }
-                    snprintf(pl.name, sizeof(pl.name), "gemm_tcgen05_%s_%s", three ? "3xtf32" : "tf32",
-                             pl.gemm.b_sk == 1 ? "tn" : "nn");
+                    // name: arithmetic mode, then which dim of A and of B is contiguous (k, m / k, n)
+                    snprintf(pl.name, sizeof(pl.name), "gemm_tcgen05_%s_%c%c%s", three ? "3xtf32" : "tf32",
+                             g.a_sk == 1 ? 'k' : 'm', g.b_sk == 1 ? 'k' : 'n', g.splits > 1 ? "_splitk" : "");
                 } else {
                     pl.impl = IMPL_GEMM_SIMT;
-                    snprintf(pl.name, sizeof(pl.name), "gemm_simt_f32");
+                    snprintf(pl.name, sizeof(pl.name), "gemm_simt_f32%s", g.splits > 1 ? "_splitk" : "");
                 }
+                if (g.splits > 1) {
+                    g.partial_off = scratch_floats;
+                    scratch_floats += (long long)g.splits * g.batch * g.m * g.n;
+                    pl.launches += 1;
+                }
+                pl.scratch_bytes = scratch_floats * 4;
                 break;
             }
             if (raxis == nk - 1) {

@@ -299,7 +299,7 @@ def test_cfg1_matmul_512(dev):
     b = rng.uniform(-1, 1, (512, 512)).astype(np.float32)
     k = W.matmul_desc(512, 512, 512)
     got, kern = gemm_check(dev, k, a, b, a.astype(np.float64) @ b.astype(np.float64), 1e-6)
-    assert kern.impl == "gemm_tcgen05_3xtf32_nn"
+    assert kern.impl.startswith("gemm_tcgen05_3xtf32_kn")
     bound = 1e-5 * (np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)).reshape(-1)
     for fma in (False, True):           # both forms the reference's C backend can take
         ref = O.run(k, [a, b], fma=fma)
@@ -374,6 +374,21 @@ def test_gemm_tensor_core_batched_and_strided_views(dev):
     got, kern = run_gpu(dev, kd, [a_full, b1])
     ref = np.einsum("bmk,kn->bmn", a_full[:, :, :64].astype(np.float64), b1.astype(np.float64))
     assert np.abs(got.reshape(ref.shape) - ref).max() <= 1e-5 * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("b_,o_,i_", [(4096, 128, 256), (20000, 64, 288), (3000, 32, 9), (1000, 10, 128)])
+def test_gemm_weight_gradient_split_k(dev, b_, o_, i_):
+    """dW = dy^T x: M-major A, long K, split over CTAs with partials in scratch."""
+    dy, x = rnd([b_, o_], 37), rnd([b_, i_], 38)
+    a = D.Operand([o_, 1, 0], 0, D.F32, dy.size)
+    b = D.Operand([i_, 0, 1], 0, D.F32, x.size)
+    k = D.reduce([b_, o_, i_], [a, b], w(0) * w(1), D.R_SUM, 0)
+    got, kern = run_gpu(dev, k, [dy, x])
+    assert "splitk" in kern.impl and kern.scratch_bytes > 0
+    ref = dy.astype(np.float64).T @ x.astype(np.float64)
+    bound = 1e-5 * (np.abs(dy).astype(np.float64).T @ np.abs(x).astype(np.float64))
+    assert (np.abs(got.reshape(o_, i_) - ref) <= bound).all(), kern.impl
+    dev.synchronize()
 
 
 def test_gemm_misaligned_layout_stays_on_f32_kernel(dev):

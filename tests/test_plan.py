@@ -59,12 +59,27 @@ def test_matmul_spelled_as_broadcast_mul_sum_is_a_gemm():
         assert i.impl.decode().startswith("gemm"), i.impl
     i = query(W.matmul_desc(512, 512, 512))
     assert i.algo_flops == 2 * 512 ** 3
-    assert i.impl.decode() == "gemm_tcgen05_3xtf32_nn" and i.scratch_bytes == 4 * 4 * 512 * 512
-    assert query(W.matmul_desc(512, 512, 512, mode=D.GEMM_TF32)).impl.decode() == "gemm_tcgen05_tf32_nn"
-    assert query(W.linear_desc(4096, 256, 256)).impl.decode() == "gemm_tcgen05_3xtf32_tn"
+    assert i.impl.decode().startswith("gemm_tcgen05_3xtf32_kn") and i.scratch_bytes >= 4 * 4 * 512 * 512
+    assert query(W.matmul_desc(512, 512, 512, mode=D.GEMM_TF32)).impl.decode().startswith("gemm_tcgen05_tf32_kn")
+    assert query(W.matmul_desc(8192, 8192, 8192, mode=D.GEMM_TF32)).impl.decode() == "gemm_tcgen05_tf32_kn"
+    assert query(W.linear_desc(4096, 256, 256)).impl.decode() == "gemm_tcgen05_3xtf32_kk"
     assert query(W.matmul_desc(64, 30, 64)).impl.decode() == "gemm_simt_f32"     # lda not 16-byte aligned
     k = W.matmul_desc(512, 512, 512); k.flags = 8
     assert query(k).impl.decode() == "gemm_simt_f32"
+
+
+def test_weight_gradient_contractions_split_k():
+    # dW[o,i] = sum_b dy[b,o] x[b,i]: A is M-major, K = batch is long, M x N is small
+    a = D.Operand([256, 1, 0], 0, D.F32, 65536 * 256)
+    b = D.Operand([256, 0, 1], 0, D.F32, 65536 * 256)
+    k = D.reduce([65536, 256, 256], [a, b], w(0) * w(1), D.R_SUM, 0)
+    i = query(k)
+    assert i.impl.decode() == "gemm_tcgen05_3xtf32_mn_splitk" and i.launches == 4
+    # conv1 weight gradient: ldb = 9 floats cannot be a TMA stride -> f32 kernel, still split
+    a = D.Operand([32, 1, 0], 0, D.F32, 346112 * 32)
+    b = D.Operand([9, 0, 1], 0, D.F32, 346112 * 9)
+    i = query(D.reduce([346112, 32, 9], [a, b], w(0) * w(1), D.R_SUM, 0))
+    assert i.impl.decode() == "gemm_simt_f32_splitk" and i.scratch_bytes > 0
 
 
 def test_small_rows_use_thread_or_warp_per_row():
