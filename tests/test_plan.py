@@ -65,7 +65,7 @@ def test_matmul_spelled_as_broadcast_mul_sum_is_a_gemm():
     assert query(W.linear_desc(4096, 256, 256)).impl.decode() == "gemm_tcgen05_3xtf32_kk"
     assert query(W.matmul_desc(64, 30, 64)).impl.decode() == "gemm_simt_f32"     # lda not 16-byte aligned
     k = W.matmul_desc(512, 512, 512); k.flags = 8
-    assert query(k).impl.decode() == "gemm_simt_f32"
+    assert query(k).impl.decode().startswith("gemm_simt_f32")
 
 
 def test_weight_gradient_contractions_split_k():
