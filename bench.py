@@ -220,18 +220,8 @@ def run_b200(args):
 
     allreduce_z = None
     if world > 1:
-        import torch
-        import torch.distributed as dist
-
-        class _Alias:   # zero-copy view of the z buffer for the collective
-            def __init__(self, ptr, nelem):
-                self.__cuda_array_interface__ = {"shape": (nelem,), "typestr": "<f4", "data": (ptr, False), "version": 3}
-        z_t = torch.as_tensor(_Alias(bz.device_ptr(), COLS), device=torch.device("cuda", local_rank))
-        ext = torch.cuda.ExternalStream(dev.stream(), device=torch.device("cuda", local_rank))
-
-        def allreduce_z():
-            with torch.cuda.stream(ext):     # ordered on the backend's own stream
-                dist.all_reduce(z_t, op=dist.ReduceOp.MAX)
+        from harp_b200 import parallel
+        allreduce_z = parallel.make_allreduce([bz], "max", dev, local_rank)   # on the library's own stream
 
     def step():
         ky.execute([b0, bx, b1], [by])
@@ -298,6 +288,14 @@ def run_b200(args):
     e2e_ms = ea.elapsed_ms(eb)
     sampler.stop()
 
+    # release the config 2 buffers, then time the other configurations
+    extra = None
+    if not args.no_extra:
+        for b_ in (bx, by, bz, bt):
+            b_.release()
+        for h_ in (y_host, z_host, t_host):
+            h_.free()
+        extra = extra_measurements(reg, dev, rank, world, local_rank, quick=args.steps < 20)
     if world > 1:
         import torch
         import torch.distributed as dist
@@ -343,11 +341,98 @@ def run_b200(args):
     }
     if n == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(x_host.array)
+    if extra is not None:
+        line["extra"] = extra
     print(json.dumps(line))
     if world > 1:
         import torch.distributed as dist
         dist.barrier()
         dist.destroy_process_group()
+
+
+def time_kernel(dev, kern, ins, outs, reps=5, warm=2):
+    for _ in range(warm):
+        kern.execute(ins, outs)
+    dev.synchronize()
+    dev.timer_begin()
+    for _ in range(reps):
+        kern.execute(ins, outs)
+    return dev.timer_end() / reps
+
+
+def extra_measurements(reg, dev, rank, world, local_rank, quick=False):
+    """The other BASELINE configurations, timed with CUDA events on the library's
+    stream: dense contractions (configs 1 and 5, rank 0 only), the MLP step
+    (config 3, rank 0 only) and the data-parallel CNN step (config 4, all ranks)."""
+    from harp_b200 import desc as D
+    from harp_b200 import workloads as W
+    from harp_b200.frontend import B200Executor, Program
+    out = {}
+    rng = np.random.default_rng(5)
+    if rank == 0:
+        gemm = {}
+        shapes = [("cfg1_512", 512, 512, 512, 0), ("cfg5_8192", 8192, 8192, 8192, 0), ("cfg5_batched_64x1024", 1024, 1024, 1024, 64)]
+        for name, m, k_, n, batch in shapes:
+            bs = max(batch, 1)
+            ba = reg.allocate_buffer(dev, [bs * m * k_]); bb = reg.allocate_buffer(dev, [bs * k_ * n])
+            bo = reg.allocate_buffer(dev, [bs * m * n])
+            ba.write_vec(rng.uniform(-1, 1, bs * m * k_).astype(np.float32))
+            bb.write_vec(rng.uniform(-1, 1, bs * k_ * n).astype(np.float32))
+            for mode, mname in ((D.GEMM_TF32, "tf32"), (D.GEMM_3XTF32, "3xtf32")):
+                kern = reg.compile_ast(dev, W.matmul_desc(m, k_, n, batch=batch, mode=mode))
+                ms = time_kernel(dev, kern, [ba, bb], [bo], reps=3 if quick else 10)
+                gemm[f"{name}_{mname}"] = {"impl": kern.impl, "ms": ms, "tflops": 2.0 * bs * m * k_ * n / ms / 1e9}
+            for b_ in (ba, bb, bo):
+                b_.release()
+        out["matmul"] = gemm
+        # config 3: MLP training step, whole step as one CUDA graph
+        ex = B200Executor(dev, reg)
+        loss, ps, grads, _ = W.mlp_graph(65536, 256)
+        prog = Program([loss], ex, sgd=list(zip(ps, grads)), lr=1e-3, persistent=True)
+        prog.capture()
+        steps = 20 if quick else 100
+        for _ in range(3):
+            prog.run()
+        dev.synchronize(); dev.timer_begin()
+        for _ in range(steps):
+            prog.run()
+        ms = dev.timer_end() / steps
+        out["mlp_cfg3"] = {"ms_per_step": ms, "samples_per_s": 65536 / ms * 1e3, "kernels_per_step": len(prog.kernels) + len(prog.sgd_kernels),
+                           "derived_tflops": 2.597e10 / ms / 1e9, "loss_after": float(prog.fetch(loss)), "steps": steps + 3 + 1}
+        del prog
+    # config 4: CNN, global batch 4096 sharded over the ranks, gradient all-reduce
+    ex = B200Executor(dev, reg)
+    n_local = 4096 // world
+    loss, ps, grads, _ = W.cnn_graph(n_local, seed=4 + rank)
+    prog = Program([loss], ex, sgd=list(zip(ps, grads)), lr=1e-2 / world, persistent=True)
+    between = None
+    if world > 1:
+        from harp_b200 import parallel
+        prog.capture(include_update=False)
+        between = parallel.make_allreduce(prog.grad_buffers(), "sum", dev, local_rank)
+    else:
+        prog.capture()
+    steps = 5 if quick else 20
+    for _ in range(3):
+        prog.run(between)
+    dev.synchronize()
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    dev.timer_begin()
+    for _ in range(steps):
+        prog.run(between)
+    ms = dev.timer_end() / steps
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    out["cnn_cfg4"] = {"ms_per_step": ms, "img_per_s": 4096 / ms * 1e3, "global_batch": 4096, "per_gpu_batch": n_local,
+                       "kernels_per_step": len(prog.kernels) + len(prog.sgd_kernels),
+                       "allreduce_bytes_per_step": 225034 * 4 if world > 1 else 0, "loss_after": float(prog.fetch(loss))}
+    return out
 
 
 def main():
@@ -357,6 +442,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extra", action="store_true", help="only config 2 (skip matmul / MLP / CNN measurements)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -71,6 +71,15 @@ class B200Device:
     def event(self) -> "B200Event":
         return B200Event(self)
 
+    def graph_begin(self):
+        """Start recording launches on this device into a CUDA graph."""
+        capi.call("eb200_graph_begin", self._h)
+
+    def graph_end(self) -> "B200Graph":
+        h = C.c_void_p()
+        capi.call("eb200_graph_end", self._h, C.byref(h))
+        return B200Graph(h)
+
     def mem_stats(self) -> dict:
         a, b, c = C.c_int64(), C.c_int64(), C.c_int64()
         capi.call("eb200_device_mem_stats", self._h, C.byref(a), C.byref(b), C.byref(c))
@@ -80,6 +89,24 @@ class B200Device:
         if self._h:
             capi.call("eb200_device_close", self._h)
             self._h = None
+
+
+class B200Graph:
+    """A recorded step; ``launch`` replays it with one submission."""
+
+    def __init__(self, handle):
+        self._h = handle
+
+    def launch(self):
+        capi.call("eb200_graph_launch", self._h)
+
+    def __del__(self):
+        try:
+            if self._h:
+                capi.call("eb200_graph_release", self._h)
+                self._h = None
+        except Exception:
+            pass
 
 
 class B200Event:

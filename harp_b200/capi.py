@@ -48,6 +48,10 @@ SIGNATURES = {
     "eb200_event_record": [_p],
     "eb200_event_elapsed_ms": [_p, _p, C.POINTER(C.c_float)],
     "eb200_event_destroy": [_p],
+    "eb200_graph_begin": [_p],
+    "eb200_graph_end": [_p, _pp],
+    "eb200_graph_launch": [_p],
+    "eb200_graph_release": [_p],
     "eb200_device_mem_stats": [_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64)],
     "eb200_buffer_alloc": [_p, C.c_size_t, _pp],
     "eb200_buffer_alloc_uninit": [_p, C.c_size_t, _pp],

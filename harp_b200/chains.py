@@ -62,3 +62,34 @@ CHAINS = [
     ("sub_sub_ln", (w(0) - w(1)) - w(2).ln()),
     ("mul_neg", -(w(0) * w(1))),
 ]
+
+
+def _model_chains():
+    """Every elementwise / reduce map the fused training steps of configs 3 and 4
+    lower to, so those steps never fall back to the bytecode interpreter."""
+    from . import desc as D
+    from . import workloads as W
+    from .frontend import Program
+
+    class _Null:           # lowers without a device
+        def alloc(self, n): return None
+        def free(self, b): pass
+        def upload(self, b, d): pass
+        def compile(self, d): return None
+
+    out = []
+    for tag, (loss, ps, grads, _) in (("mlp", W.mlp_graph(8, 8)), ("cnn", W.cnn_graph(2))):
+        prog = Program([loss], _Null(), fuse="chains", sgd=list(zip(ps, grads)), lr=0.1)
+        for i, d in enumerate(prog.kernel_descs()):
+            if d.map is None or d.kclass not in (D.K_ELEMENTWISE, D.K_REDUCE):
+                continue
+            # one-element operands reach the kernels as launch-time constants
+            sub = {}
+            for j, op in enumerate(d.inputs):
+                if not op.bounds and all(st == 0 or ext == 1 for st, ext in zip(op.strides, d.shape)):
+                    sub[j] = Ast.const(1.0)
+            out.append((f"{tag}_{i}", d.map.substitute(sub)))
+    return out
+
+
+CHAINS = CHAINS + _model_chains()

@@ -193,6 +193,47 @@ int eb200_timer_end(eb200_device* dev, float* ms) {
     return EB200_OK;
 }
 
+struct eb200_graph {
+    eb200::Device* dev;
+    cudaGraph_t graph;
+    cudaGraphExec_t exec;
+};
+
+int eb200_graph_begin(eb200_device* dev) {
+    EB_REQUIRE(dev, EB200_ERR_INVALID, "dev is null");
+    EB_CHECK_CUDA(cudaSetDevice(dev->index));
+    EB_CHECK_CUDA(cudaStreamBeginCapture(dev->stream, cudaStreamCaptureModeThreadLocal));
+    return EB200_OK;
+}
+
+int eb200_graph_end(eb200_device* dev, eb200_graph** out) {
+    EB_REQUIRE(dev && out, EB200_ERR_INVALID, "null argument");
+    cudaGraph_t g = nullptr;
+    EB_CHECK_CUDA(cudaStreamEndCapture(dev->stream, &g));
+    cudaGraphExec_t exec = nullptr;
+    cudaError_t e = cudaGraphInstantiate(&exec, g, 0);
+    if (e != cudaSuccess) {
+        cudaGraphDestroy(g);
+        return set_error(EB200_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e));
+    }
+    *out = new eb200_graph{dev, g, exec};
+    return EB200_OK;
+}
+
+int eb200_graph_launch(eb200_graph* graph) {
+    EB_REQUIRE(graph, EB200_ERR_INVALID, "graph is null");
+    EB_CHECK_CUDA(cudaGraphLaunch(graph->exec, graph->dev->stream));
+    return EB200_OK;
+}
+
+int eb200_graph_release(eb200_graph* graph) {
+    if (!graph) return EB200_OK;
+    cudaGraphExecDestroy(graph->exec);
+    cudaGraphDestroy(graph->graph);
+    delete graph;
+    return EB200_OK;
+}
+
 struct eb200_event {
     eb200::Device* dev;
     cudaEvent_t ev;

@@ -665,8 +665,11 @@ class Program:
     on the host: crates/nn/src/optim/optimizer.rs:100-131, sgd.rs:73-103.)"""
 
     def __init__(self, roots: Sequence[Tensor], executor, fuse: str = "chains",
-                 sgd: Sequence[Tuple[Tensor, Tensor]] = (), lr: float = 0.0):
+                 sgd: Sequence[Tuple[Tensor, Tensor]] = (), lr: float = 0.0, persistent: bool = False):
         self.ex = executor
+        self.persistent = persistent      # keep every intermediate buffer between runs (no per-step allocation)
+        self.graph = None
+        self.graph_has_update = False
         self.roots = list(roots)
         self.sgd = list(sgd)
         all_roots = self.roots + [g for _, g in self.sgd] + [p for p, _ in self.sgd]
@@ -730,16 +733,46 @@ class Program:
             if i not in self.buf:
                 self.buf[i] = self.ex.alloc(self.numel[i])
             kern.execute([self.buf[s] for s in srcs], [self.buf[i]])
-            for s in self.release_after[pos]:
-                self.ex.free(self.buf.pop(s))
+            if not self.persistent:
+                for s in self.release_after[pos]:
+                    self.ex.free(self.buf.pop(s))
 
     def run_update(self):
         for pid, gid, kern in self.sgd_kernels:
             kern.execute([self.buf[pid], self.buf[gid]], [self.buf[pid]])
 
-    def run(self):
-        self.run_forward()
-        self.run_update()
+    def run(self, between=None):
+        """One step.  `between` (optional callable) runs after the gradients are
+        complete and before the parameter update -- where a data-parallel job
+        all-reduces its gradients."""
+        if self.graph is not None:
+            self.graph.launch()
+        else:
+            self.run_forward()
+        if between is not None:
+            between()
+        if self.graph is None or not self.graph_has_update:
+            self.run_update()
+
+    def capture(self, include_update: bool = True):
+        """Record one step as a CUDA graph; later ``run`` calls replay it.  With
+        ``include_update=False`` only forward+backward are recorded and the
+        parameter update stays a separate launch sequence (so a collective can sit
+        between them).  Needs ``persistent=True`` and the CUDA executor."""
+        assert self.persistent, "capture needs persistent buffers"
+        self.run_forward()                              # allocates every buffer, warms every kernel
+        self.ex.synchronize()
+        self.ex.dev.graph_begin()
+        try:
+            self.run_forward()
+            if include_update:
+                self.run_update()
+        finally:
+            self.graph = self.ex.dev.graph_end()
+        self.graph_has_update = include_update
+
+    def grad_buffers(self):
+        return [self.buf[g.node.id] for _, g in self.sgd]
 
     def buffer_of(self, t: Tensor):
         return self.buf[t.node.id]

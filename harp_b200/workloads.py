@@ -73,3 +73,54 @@ def linear_desc(batch: int, in_f: int, out_f: int, mode: int = D.GEMM_DEFAULT) -
 
 def uniform_pm1(shape, seed: int) -> np.ndarray:
     return np.random.default_rng(seed).uniform(-1.0, 1.0, shape).astype(np.float32)
+
+
+# ---- configs 3 and 4: training steps built through the graph front end ---------------
+
+def mlp_graph(batch: int = 65536, hidden: int = 256, seed: int = 3, weight_seed: int = 30):
+    """Config 3: 1 -> hidden -> hidden -> 1 with tanh, inputs uniform[-pi, pi],
+    target sin(x), Xavier-uniform weights, zero biases, MSE loss.  Returns
+    (loss, parameters, gradients, inputs) as lazy tensors."""
+    from .frontend import Tensor
+    rng = np.random.default_rng(seed)
+    X = rng.uniform(-np.pi, np.pi, (batch, 1)).astype(np.float32)
+    T = np.sin(X.astype(np.float64)).astype(np.float32)
+    prng = np.random.default_rng(weight_seed)
+
+    def xavier(o, i):
+        b = np.sqrt(6.0 / (i + o))
+        return prng.uniform(-b, b, (o, i)).astype(np.float32)
+    vals = [xavier(hidden, 1), np.zeros(hidden, np.float32), xavier(hidden, hidden), np.zeros(hidden, np.float32),
+            xavier(1, hidden), np.zeros(1, np.float32)]
+    ps = [Tensor.input(v, requires_grad=True) for v in vals]
+    x, t = Tensor.input(X), Tensor.input(T)
+    h = x.linear(ps[0], ps[1]).tanh().linear(ps[2], ps[3]).tanh().linear(ps[4], ps[5])
+    d = h - t
+    loss = (d * d).sum() * (1.0 / batch)
+    return loss, ps, loss.backward(ps), (x, t)
+
+
+def cnn_graph(n: int = 4096, seed: int = 4, label_seed: int = 40, weight_seed: int = 41):
+    """Config 4: MNIST-shaped CNN (conv 1->32 3x3, ReLU, maxpool 2, conv 32->64 3x3,
+    ReLU, maxpool 2, flatten 1600, linear 128, ReLU, linear 10, softmax
+    cross-entropy) on synthetic images uniform[0,1] and uniform labels; Kaiming
+    normal weights from `weight_seed` (the reference's deterministic sin() init is
+    not used), zero biases."""
+    from .frontend import Tensor
+    X = np.random.default_rng(seed).uniform(0, 1, (n, 1, 28, 28)).astype(np.float32)
+    lab = np.random.default_rng(label_seed).integers(0, 10, n)
+    prng = np.random.default_rng(weight_seed)
+
+    def kaiming(*shape):
+        fan_in = int(np.prod(shape[1:]))
+        return (prng.standard_normal(shape) * np.sqrt(2.0 / fan_in)).astype(np.float32)
+    vals = [kaiming(32, 1, 3, 3), np.zeros(32, np.float32), kaiming(64, 32, 3, 3), np.zeros(64, np.float32),
+            kaiming(128, 1600), np.zeros(128, np.float32), kaiming(10, 128), np.zeros(10, np.float32)]
+    ps = [Tensor.input(v, requires_grad=True) for v in vals]
+    x = Tensor.input(X)
+    onehot = Tensor.input(np.eye(10, dtype=np.float32)[lab])       # built on the host, as loss.rs:43-51 does
+    h = x.conv2d(ps[0], ps[1]).relu().max_pool2d(2)
+    h = h.conv2d(ps[2], ps[3]).relu().max_pool2d(2)
+    h = h.reshape(n, 1600).linear(ps[4], ps[5]).relu().linear(ps[6], ps[7])
+    loss = -(h.log_softmax(1) * onehot).sum() * (1.0 / n)
+    return loss, ps, loss.backward(ps), (x, onehot)

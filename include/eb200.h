@@ -207,6 +207,17 @@ int eb200_event_create(eb200_device* dev, eb200_event** ev);
 int eb200_event_record(eb200_event* ev);
 int eb200_event_elapsed_ms(eb200_event* a, eb200_event* b, float* ms);
 int eb200_event_destroy(eb200_event* ev);
+/* A whole step as one CUDA graph: launches issued on this thread between
+ * graph_begin and graph_end are recorded instead of run, then replayed by
+ * graph_launch with a single submission (the reference synchronises after every
+ * kernel, crates/backend-cuda/src/kernel.rs:213-225).  Allocate every buffer
+ * the step touches before graph_begin; buffer reads/writes and device_sync are
+ * not allowed while recording. */
+typedef struct eb200_graph eb200_graph;
+int eb200_graph_begin(eb200_device* dev);
+int eb200_graph_end(eb200_device* dev, eb200_graph** graph);
+int eb200_graph_launch(eb200_graph* graph);
+int eb200_graph_release(eb200_graph* graph);
 /* Pool statistics: bytes currently handed out, high-water mark, allocations. */
 int eb200_device_mem_stats(eb200_device* dev, int64_t* in_use, int64_t* peak, int64_t* n_allocs);
 

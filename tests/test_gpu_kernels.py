@@ -94,7 +94,7 @@ def test_launch_rejects_short_buffers(dev, registry):
 
 @pytest.mark.parametrize("name,expr", CHAINS, ids=[n for n, _ in CHAINS])
 def test_every_compiled_chain_matches_oracle(dev, name, expr):
-    nin = max(expr.wildcards()) + 1
+    nin = max(expr.wildcards()) + 1 if expr.wildcards() else 1
     shape = [37, 20]
     positive = any(t in expr.key() for t in ("log2", "sqrt", "recip"))
     ins = [rnd(shape, 100 + i, 0.5 if positive else -2.0, 2.0) for i in range(nin)]
@@ -307,7 +307,7 @@ def test_cfg1_matmul_512(dev):
     # the f32 FFMA kernel on the same contraction agrees with the C loop much more tightly
     k2 = W.matmul_desc(512, 512, 512); k2.flags = 8
     got2, kern2 = run_gpu(dev, k2, [a, b])
-    assert kern2.impl == "gemm_simt_f32"
+    assert kern2.impl.startswith("gemm_simt_f32")
     assert_close(got2, O.run(k2, [a, b]), rel=1e-5, abs_tol=1e-5 * np.sqrt(512) * 0.34)
 
 
