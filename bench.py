@@ -388,7 +388,7 @@ def extra_measurements(reg, dev, rank, world, local_rank, quick=False):
         # config 3: MLP training step, whole step as one CUDA graph
         ex = B200Executor(dev, reg)
         loss, ps, grads, _ = W.mlp_graph(65536, 256)
-        prog = Program([loss], ex, sgd=list(zip(ps, grads)), lr=1e-3, persistent=True)
+        prog = Program([loss], ex, sgd=list(zip(ps, grads)), lr=1e-3, persistent=True, flat=True)
         prog.capture()
         steps = 20 if quick else 100
         for _ in range(3):
@@ -404,7 +404,7 @@ def extra_measurements(reg, dev, rank, world, local_rank, quick=False):
     ex = B200Executor(dev, reg)
     n_local = 4096 // world
     loss, ps, grads, _ = W.cnn_graph(n_local, seed=4 + rank)
-    prog = Program([loss], ex, sgd=list(zip(ps, grads)), lr=1e-2 / world, persistent=True)
+    prog = Program([loss], ex, sgd=list(zip(ps, grads)), lr=1e-2 / world, persistent=True, flat=True)
     between = None
     if world > 1:
         from harp_b200 import parallel

@@ -300,7 +300,7 @@ class Tensor:
 
     def fold(self, out_shape, axes, sizes, strides, dilations) -> "Tensor":
         """Scatter-add windows back (S_ kernel, src/lowerer/lower.rs:580-683)."""
-        src = self.contiguous()
+        src = self          # the scatter kernel reads its input through any affine view
         dst = View.contiguous(out_shape).unfold(axes, sizes, strides, dilations)
         node = Node("fold", src.shape, [(src.node, src.view)], None, out_view=dst, name="fold")
         node._fold_numel = math.prod(out_shape)
@@ -644,18 +644,34 @@ def _fuse(ks: Dict[int, _K], order: List[int], roots: set, level: str):
                 break
 
 
-def _lower(k: _K, numel_of: Dict[int, int]) -> D.KernelDesc:
-    ins = [v.operand(numel_of[src], D.F32) for src, v in k.operands]
+def _lower(k: _K, loc) -> D.KernelDesc:
+    """`loc(node id) -> (offset, numel)` of the buffer that holds a node's value
+    (its own buffer, or a slice of a flat parameter / gradient buffer)."""
+    ins = []
+    for src, v in k.operands:
+        off, numel = loc(src)
+        op = v.operand(numel, D.F32)
+        op.offset += off
+        ins.append(op)
+    out_off, out_numel = loc(k.id)
     if k.kind == "map":
+        out = D.Operand(D.contiguous_strides(k.shape), out_off, D.F32, out_numel)
         identity = k.expr.op == "w" and len(k.operands) == 1
         if identity:
-            return D.KernelDesc(D.K_COPY, k.shape, ins, D.contiguous(k.shape), None, name=k.name)
-        return D.KernelDesc(D.K_ELEMENTWISE, k.shape, ins, D.contiguous(k.shape), k.expr, name=k.name)
+            return D.KernelDesc(D.K_COPY, k.shape, ins, out, None, name=k.name)
+        return D.KernelDesc(D.K_ELEMENTWISE, k.shape, ins, out, k.expr, name=k.name)
     if k.kind == "reduce":
-        return D.reduce(list(k.shape), ins, k.expr, k.reduce_op, k.axis)
+        kept = [1 if d == k.axis else e for d, e in enumerate(k.shape)]
+        st = D.contiguous_strides(kept)
+        st[k.axis] = 0
+        return D.reduce(list(k.shape), ins, k.expr, k.reduce_op, k.axis, out=D.Operand(st, out_off, D.F32, out_numel))
     if k.kind == "fold":
+        assert out_off == 0, "a scatter output owns its buffer (it is zero-filled as a whole)"
         return D.KernelDesc(D.K_SCATTER, k.shape, ins, k.out_view.operand(k.out_numel, D.F32), None, name=k.name)
     raise ValueError(k.kind)
+
+
+_FLAT_P, _FLAT_G = -1, -2       # container ids of the flat parameter / gradient buffers
 
 
 class Program:
@@ -665,13 +681,16 @@ class Program:
     on the host: crates/nn/src/optim/optimizer.rs:100-131, sgd.rs:73-103.)"""
 
     def __init__(self, roots: Sequence[Tensor], executor, fuse: str = "chains",
-                 sgd: Sequence[Tuple[Tensor, Tensor]] = (), lr: float = 0.0, persistent: bool = False):
+                 sgd: Sequence[Tuple[Tensor, Tensor]] = (), lr: float = 0.0, persistent: bool = False,
+                 flat: bool = False):
+        """`flat=True` lays all parameters out in one buffer and all gradients in
+        another (same offsets): one all-reduce and one update kernel per step."""
         self.ex = executor
         self.persistent = persistent      # keep every intermediate buffer between runs (no per-step allocation)
         self.graph = None
         self.graph_has_update = False
         self.roots = list(roots)
-        self.sgd = list(sgd)
+        self.sgd = [(p_, g_.contiguous()) for p_, g_ in sgd]     # gradient buffers share the parameter layout
         all_roots = self.roots + [g for _, g in self.sgd] + [p for p, _ in self.sgd]
         nodes: Dict[int, Node] = {}
         order: List[int] = []
@@ -694,12 +713,29 @@ class Program:
         self.ks = ks
         self.numel = {i: ks[i].out_numel for i in self.order}
         self.inputs = {i: ks[i] for i in self.order if ks[i].kind == "input"}
+        # where each node's value lives: (container id, offset); containers own the buffers
+        self.where: Dict[int, Tuple[int, int]] = {i: (i, 0) for i in self.order}
+        self.cnumel: Dict[int, int] = dict(self.numel)
+        pids, gids = [p_.node.id for p_, _ in self.sgd], [g_.node.id for _, g_ in self.sgd]
+        self.flat = bool(flat and self.sgd and len(set(pids)) == len(pids) and len(set(gids)) == len(gids)
+                         and all(ks[i].kind == "input" for i in pids)
+                         and all(ks[i].kind in ("map", "reduce") for i in gids))
+        if self.flat:
+            off = 0
+            for pid, gid in zip(pids, gids):
+                self.where[pid], self.where[gid] = (_FLAT_P, off), (_FLAT_G, off)
+                off += (self.numel[pid] + 63) // 64 * 64        # 256-byte aligned slices
+            self.cnumel[_FLAT_P] = self.cnumel[_FLAT_G] = off
+
+        def loc(i):
+            c, off = self.where[i]
+            return off, self.cnumel[c]
         self.kernels = []          # (node id, desc, compiled kernel, [src ids])
         for i in self.order:
             k = ks[i]
             if k.kind == "input":
                 continue
-            d = _lower(k, self.numel)
+            d = _lower(k, loc)
             self.kernels.append((i, d, self.ex.compile(d), [s for s, _ in k.operands]))
         # liveness: a buffer may go once its last consumer has run
         last = {}
@@ -709,20 +745,40 @@ class Program:
         keep = set(root_ids) | set(self.inputs)
         self.release_after = [[] for _ in self.kernels]
         for s, pos in last.items():
-            if s not in keep:
+            if s not in keep and self.where[s][0] == s:
                 self.release_after[pos].append(s)
         self.sgd_kernels = []
-        for p, g in self.sgd:
-            n = p.node.out_numel
+        if self.flat:
+            n = self.cnumel[_FLAT_P]
             d = D.KernelDesc(D.K_SGD, [n], [D.contiguous([n]), D.contiguous([n])], D.contiguous([n]), scalar=lr)
-            self.sgd_kernels.append((p.node.id, g.node.id, self.ex.compile(d)))
+            self.sgd_kernels.append((_FLAT_P, _FLAT_G, self.ex.compile(d)))
+        else:
+            for p, g in self.sgd:
+                n = p.node.out_numel
+                d = D.KernelDesc(D.K_SGD, [n], [D.contiguous([n]), D.contiguous([n])], D.contiguous([n]), scalar=lr)
+                self.sgd_kernels.append((p.node.id, g.node.id, self.ex.compile(d)))
         self.buf: Dict[int, object] = {}
+        if self.flat:
+            host = np.zeros(self.cnumel[_FLAT_P], np.float32)
+            for pid in pids:
+                o = self.where[pid][1]
+                host[o:o + self.numel[pid]] = ks[pid].data.reshape(-1)
+            self.buf[_FLAT_P] = self.ex.alloc(host.size)
+            self.ex.upload(self.buf[_FLAT_P], host)
+            self.buf[_FLAT_G] = self.ex.alloc(host.size)
+            self.ex.upload(self.buf[_FLAT_G], np.zeros_like(host))
         for i, k in self.inputs.items():
+            if self.where[i][0] != i:
+                continue
             self.buf[i] = self.ex.alloc(self.numel[i])
             self.ex.upload(self.buf[i], k.data.reshape(-1))
 
     def set_input(self, t: Tensor, data: np.ndarray):
+        assert self.where[t.node.id][0] == t.node.id, "parameters of a flat program are not re-uploaded one by one"
         self.ex.upload(self.buf[t.node.id], np.ascontiguousarray(data, np.float32).reshape(-1))
+
+    def _b(self, i):
+        return self.buf[self.where[i][0]]
 
     def kernel_descs(self) -> List[D.KernelDesc]:
         return [d for _, d, _, _ in self.kernels]
@@ -730,9 +786,10 @@ class Program:
     def run_forward(self):
         """All kernels up to and including the gradients (no parameter update)."""
         for pos, (i, d, kern, srcs) in enumerate(self.kernels):
-            if i not in self.buf:
-                self.buf[i] = self.ex.alloc(self.numel[i])
-            kern.execute([self.buf[s] for s in srcs], [self.buf[i]])
+            c = self.where[i][0]
+            if c not in self.buf:
+                self.buf[c] = self.ex.alloc(self.cnumel[c])
+            kern.execute([self._b(s) for s in srcs], [self.buf[c]])
             if not self.persistent:
                 for s in self.release_after[pos]:
                     self.ex.free(self.buf.pop(s))
@@ -772,14 +829,18 @@ class Program:
         self.graph_has_update = include_update
 
     def grad_buffers(self):
+        """The buffers a data-parallel job all-reduces (one when flat)."""
+        if self.flat:
+            return [self.buf[_FLAT_G]]
         return [self.buf[g.node.id] for _, g in self.sgd]
 
     def buffer_of(self, t: Tensor):
-        return self.buf[t.node.id]
+        return self._b(t.node.id)
 
     def fetch(self, t: Tensor) -> np.ndarray:
         """Root value as a numpy array of the tensor's logical shape."""
-        flat = self.ex.download(self.buf[t.node.id], self.numel[t.node.id])
+        c, off = self.where[t.node.id]
+        flat = self.ex.download(self.buf[c], self.cnumel[c])[off:off + self.numel[t.node.id]]
         v = t.view
         if v.is_contiguous() or not v.shape:
             return flat[v.offset:v.offset + max(1, v.numel())].reshape(v.shape)

@@ -178,3 +178,17 @@ def test_sgd_step_updates_parameters_in_place():
     assert np.allclose(p.ex.download(p.buffer_of(wt), 3), w0 - np.float32(0.1) * (2 * w0))
     p.run()
     assert np.allclose(p.ex.download(p.buffer_of(wt), 3), w0 * 0.8 * 0.8, rtol=1e-6)
+
+
+def test_flat_parameter_and_gradient_buffers_change_nothing():
+    from harp_b200 import workloads as W
+    res = []
+    for flat in (False, True):
+        loss, ps, grads, _ = W.cnn_graph(2)
+        p = Program([loss], OracleExecutor(), sgd=list(zip(ps, grads)), lr=0.05, persistent=True, flat=flat)
+        for _ in range(2):
+            p.run()
+        res.append((float(p.fetch(loss)), [p.fetch(q).copy() for q in ps], len(p.sgd_kernels), len(p.grad_buffers())))
+    assert res[0][0] == res[1][0] and res[0][2] == 8 and res[1][2] == 1 and res[1][3] == 1
+    for a, b in zip(res[0][1], res[1][1]):
+        assert (a == b).all()

@@ -42,12 +42,12 @@ def _worker(rank, world, port, q):
     from oracle.executor import OracleExecutor
     lo, hi = P.shard_range(32, rank, world)
     loss, ps, grads = _small_mlp(lo, hi)
-    prog = Program([loss], OracleExecutor(), sgd=list(zip(ps, grads)), lr=0.1 / world, persistent=True)
+    prog = Program([loss], OracleExecutor(), sgd=list(zip(ps, grads)), lr=0.1 / world, persistent=True, flat=True)
     prog.run_forward()
     allreduce = P.make_allreduce(prog.grad_buffers(), "sum")
     for _ in range(3):
         prog.run(allreduce)
-    params = [prog.ex.download(prog.buffer_of(p), 0).copy() for p in ps]
+    params = [prog.fetch(p).copy() for p in ps]
     # sharded column max: each rank reduces its row block, MAX all-reduce combines
     x = W.cfg2_input(64, 48)
     part = x[slice(*P.shard_range(64, rank, world))].max(axis=0).copy()
@@ -85,6 +85,6 @@ def test_two_gloo_ranks_match_one_rank():
     for _ in range(3):
         prog.run()
     for a, p in zip(params2, ps):
-        b = prog.ex.download(prog.buffer_of(p), 0)
+        b = prog.fetch(p)
         np.testing.assert_allclose(a, b, rtol=1e-4, atol=1e-6)
     assert (zmax == W.cfg2_input(64, 48).max(axis=0)).all()
