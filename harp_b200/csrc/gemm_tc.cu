@@ -300,6 +300,191 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 1) tmem_dealloc(tmem_base, TC_BN);
 }
 
+// ---- two-CTA form ---------------------------------------------------------------------------
+// A cluster of two CTAs computes a 256 x 256 tile with tcgen05.mma.cta_group::2:
+// CTA r stages rows [r*128, r*128+128) of A and columns [r*128, r*128+128) of B, the
+// tensor cores of both SMs read both halves of B, and each CTA's tensor memory holds
+// its 128 rows x 256 columns of the accumulator.  Per SM that is 32 KB of operands
+// per 128 x 256 x 32 block of MMA work, two thirds of the one-CTA kernel's traffic.
+// The MMA is issued by the even CTA only; both CTAs' TMA loads complete on its
+// mbarrier; tcgen05.commit multicasts slot-free and accumulator-ready to both.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `local` (a shared::cta address) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorMap* map, uint32_t leader_bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(leader_bar), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void umma_tf32_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives on the mbarrier at this offset in both CTAs of the pair once the MMAs so far are done
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"((unsigned short)3) : "memory");
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_alo,
+                const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_blo,
+                const __grid_constant__ TcParams q, float* __restrict__ C, int a_zmul, int b_zmul) {
+    constexpr int BN = 256, HALF = 128;                // pair tile columns; columns staged per CTA
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int stage_bytes = (q.three_pass ? 4 : 2) * TC_TILE_BYTES;   // A and B half tiles are both 128 x 32
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)q.stages * stage_bytes);
+    uint64_t* empty_bar = full_bar + q.stages;
+    uint64_t* acc_bar = empty_bar + q.stages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair = (int)blockIdx.x >> 1;
+    const int tiles_m = (int)((q.m + 255) / 256);
+    const int per_band = q.raster * q.tiles_n;
+    const int band = pair / per_band, within = pair % per_band;
+    const int band_rows = min(q.raster, tiles_m - band * q.raster);
+    const int tile_m = band * q.raster + within % band_rows;
+    const int tile_n = within / band_rows;
+    const bool idle = tile_n >= q.tiles_n;              // padding of the last band: same answer in both CTAs
+    const long long n0 = (long long)tile_n * BN, m0 = (long long)tile_m * 256 + rank * 128;
+    const int bz = (int)blockIdx.z / q.splits, split = (int)blockIdx.z % q.splits;
+    const int total_kb = (int)((q.k + TC_BK - 1) / TC_BK);
+    const int kb_begin = split * q.kb_per_split;
+    const int num_kb = min(total_kb - kb_begin, q.kb_per_split);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < q.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(acc_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // both CTAs' barriers exist before anything signals them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (!idle) {
+        if (warp == 0) {
+            if (lane == 0) {
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    const int s = kb % q.stages;
+                    const unsigned phase = (unsigned)(kb / q.stages) & 1u;
+                    if (!mbar_wait(&empty_bar[s], phase ^ 1u, q.error_flag)) break;
+                    unsigned char* st = smem + (size_t)s * stage_bytes;
+                    // every load of the pair completes on the even CTA's barrier
+                    const uint32_t lead = map_to_cta(smem_u32(&full_bar[s]), 0);
+                    if (rank == 0) mbar_expect_tx(&full_bar[s], 2u * (unsigned)stage_bytes);
+                    const int kx = (kb_begin + kb) * TC_BK;
+                    unsigned char* a_hi = st;
+                    unsigned char* b_hi = st + (q.three_pass ? 2 : 1) * TC_TILE_BYTES;
+                    const int nb = (int)n0 + (int)rank * HALF;    // this CTA's half of the columns
+                    if (q.a_mmajor) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            tma_load_3d_pair(a_hi + j * 4096, &map_a, lead, (int)m0 + j * 32, kx, bz * a_zmul);
+                            if (q.three_pass) tma_load_3d_pair(st + TC_TILE_BYTES + j * 4096, &map_alo, lead, (int)m0 + j * 32, kx, bz * a_zmul);
+                        }
+                    } else {
+                        tma_load_3d_pair(a_hi, &map_a, lead, kx, (int)m0, bz * a_zmul);
+                        if (q.three_pass) tma_load_3d_pair(st + TC_TILE_BYTES, &map_alo, lead, kx, (int)m0, bz * a_zmul);
+                    }
+                    if (q.b_nmajor) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            tma_load_3d_pair(b_hi + j * 4096, &map_b, lead, nb + j * 32, kx, bz * b_zmul);
+                            if (q.three_pass) tma_load_3d_pair(b_hi + TC_TILE_BYTES + j * 4096, &map_blo, lead, nb + j * 32, kx, bz * b_zmul);
+                        }
+                    } else {
+                        tma_load_3d_pair(b_hi, &map_b, lead, kx, nb, bz * b_zmul);
+                        if (q.three_pass) tma_load_3d_pair(b_hi + TC_TILE_BYTES, &map_blo, lead, kx, nb, bz * b_zmul);
+                    }
+                }
+            }
+        } else if (warp == 1) {
+            if (lane == 0 && rank == 0) {
+                const uint32_t idesc = umma_idesc_tf32(256, BN, q.a_mmajor, q.b_nmajor);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    const int s = kb % q.stages;
+                    const unsigned phase = (unsigned)(kb / q.stages) & 1u;
+                    if (!mbar_wait(&full_bar[s], phase, q.error_flag)) break;
+                    tc_fence_after();
+                    const uint32_t st = smem_u32(smem + (size_t)s * stage_bytes);
+                    const uint32_t a_hi = st, a_lo = st + TC_TILE_BYTES;
+                    const uint32_t b_hi = st + (q.three_pass ? 2 : 1) * TC_TILE_BYTES, b_lo = b_hi + TC_TILE_BYTES;
+#pragma unroll
+                    for (int j = 0; j < TC_BK / TC_UK; ++j) {
+                        const uint32_t a_step = q.a_mmajor ? j * 1024 : j * TC_UK * 4;
+                        const uint32_t a_lbo = q.a_mmajor ? 4096 : 16, a_sbo = q.a_mmajor ? 512 : 1024, a_layout = q.a_mmajor ? 1 : 2;
+                        const uint32_t b_step = q.b_nmajor ? j * 1024 : j * TC_UK * 4;
+                        const uint32_t b_lbo = q.b_nmajor ? 4096 : 16, b_sbo = q.b_nmajor ? 512 : 1024, b_layout = q.b_nmajor ? 1 : 2;
+                        const uint64_t da = umma_desc(a_hi + a_step, a_lbo, a_sbo, a_layout);
+                        const uint64_t db = umma_desc(b_hi + b_step, b_lbo, b_sbo, b_layout);
+                        umma_tf32_pair(tmem_base, da, db, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                        if (q.three_pass) {
+                            const uint64_t dal = umma_desc(a_lo + a_step, a_lbo, a_sbo, a_layout);
+                            const uint64_t dbl = umma_desc(b_lo + b_step, b_lbo, b_sbo, b_layout);
+                            umma_tf32_pair(tmem_base, dal, db, idesc, 1u);
+                            umma_tf32_pair(tmem_base, da, dbl, idesc, 1u);
+                        }
+                    }
+                    umma_commit_pair(&empty_bar[s]);
+                }
+                umma_commit_pair(acc_bar);
+            }
+        } else {
+            const int quarter = warp & 3;
+            const bool ok = mbar_wait(acc_bar, 0, q.error_flag);
+            tc_fence_after();
+            const long long row = m0 + quarter * 32 + lane;
+            float* crow = C + q.c_off + (long long)(q.splits > 1 ? (int)blockIdx.z : bz) * q.c_sb + row * q.c_sm;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                float v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), v);
+                const long long col0 = n0 + c * 32;
+                if (!ok || row >= q.m || col0 >= q.n) continue;
+                float* dst = crow + col0 * q.c_sn;
+                if (q.c_sn == 1 && col0 + 32 <= q.n && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (col0 + i < q.n) dst[i * q.c_sn] = v[i];
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // neither CTA leaves (or frees tensor memory) while the other still works
+    if (warp == 1)
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
+}
+
 // hi = x rounded to tf32 (low 13 mantissa bits zero), lo = x - hi (exact in f32).
 __global__ void __launch_bounds__(256) split_tf32_kernel(const float* __restrict__ src, float* __restrict__ hi,
                                                          float* __restrict__ lo, long long n) {
@@ -456,25 +641,55 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
         q.c_off = 0; q.c_sm = g.n; q.c_sn = 1; q.c_sb = g.m * g.n;
     }
     q.three_pass = three ? 1 : 0;
-    const int stage_bytes = (three ? 2 : 1) * (TC_TILE_BYTES + bn * TC_BK * 4);
-    q.stages = std::min(8, (196 * 1024) / stage_bytes);
+    // two-CTA pairs (256 x 256 per pair) when there are enough pair tiles to fill the machine
+    const long long pair_tiles = ((g.m + 255) / 256) * ((g.n + 255) / 256) * g.batch * g.splits;
+    bool two_cta = g.m > 128 && pair_tiles * 2 >= dev->prop.multiProcessorCount;
+    if (const char* e = getenv("EB200_TC_2CTA")) two_cta = atoi(e) != 0;
     q.error_flag = dev->error_flag_dev;
-    const size_t smem = (size_t)q.stages * stage_bytes + 1024 /* alignment */ + 256 /* barriers */;
+    q.raster = 8;
+    if (const char* e = getenv("EB200_TC_RASTER")) q.raster = std::max(1, atoi(e));
     if (!dev->tc_configured) {
         EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         dev->tc_configured = true;
     }
-    const long long tiles_n = (g.n + bn - 1) / bn;
-    q.raster = 8;
-    if (const char* e = getenv("EB200_TC_RASTER")) q.raster = std::max(1, atoi(e));
-    const long long bands = (tiles_m + q.raster - 1) / q.raster;
-    q.tiles_n = (int)tiles_n;
-    // grid.x walks bands x (raster x tiles_n) slots; the last band may be padded
-    dim3 grid((unsigned)(bands * q.raster * tiles_n), 1, (unsigned)(g.batch * g.splits));
     const int az = g.a_sb > 0 ? 1 : 0, bzm = g.b_sb > 0 ? 1 : 0;
-    if (bn == 256) gemm_tc_kernel<256><<<grid, TC_THREADS, smem, dev->stream>>>(ma, mal, mb, mbl, q, c_out, az, bzm);
-    else gemm_tc_kernel<128><<<grid, TC_THREADS, smem, dev->stream>>>(ma, mal, mb, mbl, q, c_out, az, bzm);
+    if (two_cta) {
+        // B maps were built for `bn`-row boxes when B is K-major; each CTA stages 128 columns
+        if (!b_nmajor && bn != 128) {
+            if ((st = make_map(&mb, b_hi, g.k, g.n, b_b, g.b_sn, g.b_sb, 128))) return st;
+            if ((st = make_map(&mbl, b_lo, g.k, g.n, b_b, g.b_sn, g.b_sb, 128))) return st;
+        }
+        const int stage_bytes = (three ? 4 : 2) * TC_TILE_BYTES;
+        q.stages = std::min(8, (196 * 1024) / stage_bytes);
+        const size_t smem = (size_t)q.stages * stage_bytes + 1024 + 256;
+        const long long tm2 = (g.m + 255) / 256, tn2 = (g.n + 255) / 256;
+        const long long bands = (tm2 + q.raster - 1) / q.raster;
+        q.tiles_n = (int)tn2;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(bands * q.raster * tn2 * 2), 1, (unsigned)(g.batch * g.splits));
+        cfg.blockDim = dim3(TC_THREADS, 1, 1);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = dev->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        EB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel, ma, mal, mb, mbl, q, c_out, az, bzm));
+    } else {
+        const int stage_bytes = (three ? 2 : 1) * (TC_TILE_BYTES + bn * TC_BK * 4);
+        q.stages = std::min(8, (196 * 1024) / stage_bytes);
+        const size_t smem = (size_t)q.stages * stage_bytes + 1024 /* alignment */ + 256 /* barriers */;
+        const long long tiles_n = (g.n + bn - 1) / bn;
+        const long long bands = (tiles_m + q.raster - 1) / q.raster;
+        q.tiles_n = (int)tiles_n;
+        // grid.x walks bands x (raster x tiles_n) slots; the last band may be padded
+        dim3 grid((unsigned)(bands * q.raster * tiles_n), 1, (unsigned)(g.batch * g.splits));
+        if (bn == 256) gemm_tc_kernel<256><<<grid, TC_THREADS, smem, dev->stream>>>(ma, mal, mb, mbl, q, c_out, az, bzm);
+        else gemm_tc_kernel<128><<<grid, TC_THREADS, smem, dev->stream>>>(ma, mal, mb, mbl, q, c_out, az, bzm);
+    }
     count_launch();
     EB_CHECK_CUDA(cudaGetLastError());
     if (g.splits > 1) return launch_splitk_reduce(dev, g, c_out, c);
