@@ -265,23 +265,54 @@ def run_b200(args):
     t_t = sum(e[2].elapsed_ms(e[3]) for e in evs) / K
 
     # ---- end-to-end: host buffers in, host buffers out, every step --------------------
+    # Double-buffered: the upload of batch i+1, the kernels of batch i and the
+    # download of batch i's results run concurrently (copies on two side streams,
+    # ordered against the compute stream by events).  Every step still moves its
+    # own x up and its own y, z, t down inside the timed region.
     y_host, z_host, t_host = PinnedArray((ROWS,)), PinnedArray((COLS,)), PinnedArray((COLS, ROWS))
-    KE = max(3, min(K, 10))
+    KE = max(4, min(K, 20))
+    up, down = dev.copy_stream(), dev.copy_stream()
+    xs = [bx, reg.allocate_buffer(dev, [ROWS, COLS])]
+    outs = [(by, bz, bt), (reg.allocate_buffer(dev, [ROWS]), reg.allocate_buffer(dev, [COLS]), reg.allocate_buffer(dev, [COLS, ROWS]))]
+    ev_up = [dev.event(), dev.event()]       # upload into xs[i] finished
+    ev_k = [dev.event(), dev.event()]        # kernels on slot i finished
+    ev_down = [dev.event(), dev.event()]     # download of outs[i] finished
 
-    def e2e_step():
-        bx.write_async(x_host.ptr, x_host.nbytes)
-        step()
-        by.read_async(y_host.ptr, y_host.nbytes)
-        bz.read_async(z_host.ptr, z_host.nbytes)
-        bt.read_async(t_host.ptr, t_host.nbytes)
-        dev.synchronize()                      # the caller holds the results
-    e2e_step()
+    def e2e_run(steps):
+        for i in range(steps + 1):
+            sl = i & 1
+            if i < steps:                      # upload batch i (needs the kernels that last read this slot)
+                if i >= 2:
+                    dev.wait_event(ev_k[sl], up)
+                xs[sl].write_on(up, x_host.ptr, x_host.nbytes)
+                ev_up[sl].record(up)
+                dev.wait_event(ev_up[sl])      # compute stream: kernels of batch i wait for its upload
+                if i >= 2:
+                    dev.wait_event(ev_down[sl])    # ... and for the previous results of this slot to have left
+                if allreduce_z and i >= 1:
+                    dev.wait_event(ev_down[1 - sl])   # both slots share the all-reduced z buffer
+                oy, oz, ot = outs[sl]
+                ky.execute([b0, xs[sl], b1], [oy])
+                kz.execute([xs[sl]], [oz])
+                if allreduce_z:
+                    allreduce_z()
+                kt.execute([xs[sl]], [ot])
+                ev_k[sl].record()
+                dev.wait_event(ev_k[sl], down)  # download batch i's results
+                oy.read_on(down, y_host.ptr, y_host.nbytes)
+                oz.read_on(down, z_host.ptr, z_host.nbytes)
+                ot.read_on(down, t_host.ptr, t_host.nbytes)
+                ev_down[sl].record(down)
+        down.synchronize()                     # the caller holds every result
+        dev.synchronize()
+    if allreduce_z:                            # the collective aliases bz only: keep slot outputs on bz
+        outs[1] = (outs[1][0], bz, outs[1][2])
+    e2e_run(2)
     barrier()
     ea, eb = dev.event(), dev.event()
     w2 = time.perf_counter()
     ea.record()
-    for _ in range(KE):
-        e2e_step()
+    e2e_run(KE)
     eb.record()
     barrier()
     w3 = time.perf_counter()
@@ -291,7 +322,7 @@ def run_b200(args):
     # release the config 2 buffers, then time the other configurations
     extra = None
     if not args.no_extra:
-        for b_ in (bx, by, bz, bt):
+        for b_ in (bx, by, bz, bt, xs[1], outs[1][0], outs[1][2]):
             b_.release()
         for h_ in (y_host, z_host, t_host):
             h_.free()

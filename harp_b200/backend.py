@@ -71,6 +71,14 @@ class B200Device:
     def event(self) -> "B200Event":
         return B200Event(self)
 
+    def copy_stream(self) -> "B200Stream":
+        """A side stream for host<->device copies that overlap compute."""
+        return B200Stream(self)
+
+    def wait_event(self, ev: "B200Event", stream: "B200Stream" = None):
+        """Make `stream` (default: this device's compute stream) wait for `ev`."""
+        capi.call("eb200_stream_wait", self._h, stream._h if stream else None, ev._h)
+
     def graph_begin(self):
         """Start recording launches on this device into a CUDA graph."""
         capi.call("eb200_graph_begin", self._h)
@@ -89,6 +97,24 @@ class B200Device:
         if self._h:
             capi.call("eb200_device_close", self._h)
             self._h = None
+
+
+class B200Stream:
+    def __init__(self, device: "B200Device"):
+        self.device = device
+        self._h = C.c_void_p()
+        capi.call("eb200_stream_create", device._h, C.byref(self._h))
+
+    def synchronize(self):
+        capi.call("eb200_stream_sync", self._h)
+
+    def __del__(self):
+        try:
+            if self._h:
+                capi.call("eb200_stream_destroy", self._h)
+                self._h = None
+        except Exception:
+            pass
 
 
 class B200Graph:
@@ -116,8 +142,11 @@ class B200Event:
         self._h = C.c_void_p()
         capi.call("eb200_event_create", device._h, C.byref(self._h))
 
-    def record(self):
-        capi.call("eb200_event_record", self._h)
+    def record(self, stream: "B200Stream" = None):
+        if stream is None:
+            capi.call("eb200_event_record", self._h)
+        else:
+            capi.call("eb200_event_record_on", self._h, stream._h)
 
     def elapsed_ms(self, later: "B200Event") -> float:
         ms = C.c_float()
@@ -190,6 +219,12 @@ class B200Buffer:
 
     def read_async(self, host_ptr: int, nbytes: int):
         capi.call("eb200_buffer_read_async", self._h, C.c_void_p(host_ptr), nbytes)
+
+    def write_on(self, stream: "B200Stream", host_ptr: int, nbytes: int):
+        capi.call("eb200_buffer_write_on", self._h, C.c_void_p(host_ptr), nbytes, stream._h)
+
+    def read_on(self, stream: "B200Stream", host_ptr: int, nbytes: int):
+        capi.call("eb200_buffer_read_on", self._h, C.c_void_p(host_ptr), nbytes, stream._h)
 
     def to_ndarray(self) -> np.ndarray:
         return self.read_vec().reshape(self._shape)

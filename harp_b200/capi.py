@@ -48,6 +48,13 @@ SIGNATURES = {
     "eb200_event_record": [_p],
     "eb200_event_elapsed_ms": [_p, _p, C.POINTER(C.c_float)],
     "eb200_event_destroy": [_p],
+    "eb200_stream_create": [_p, _pp],
+    "eb200_stream_destroy": [_p],
+    "eb200_stream_sync": [_p],
+    "eb200_stream_wait": [_p, _p, _p],
+    "eb200_event_record_on": [_p, _p],
+    "eb200_buffer_write_on": [_p, _p, C.c_size_t, _p],
+    "eb200_buffer_read_on": [_p, _p, C.c_size_t, _p],
     "eb200_graph_begin": [_p],
     "eb200_graph_end": [_p, _pp],
     "eb200_graph_launch": [_p],

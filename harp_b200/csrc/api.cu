@@ -268,6 +268,63 @@ int eb200_event_destroy(eb200_event* ev) {
     return EB200_OK;
 }
 
+struct eb200_stream {
+    eb200::Device* dev;
+    cudaStream_t s;
+};
+
+int eb200_stream_create(eb200_device* dev, eb200_stream** out) {
+    EB_REQUIRE(dev && out, EB200_ERR_INVALID, "null argument");
+    EB_CHECK_CUDA(cudaSetDevice(dev->index));
+    cudaStream_t s;
+    EB_CHECK_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    *out = new eb200_stream{dev, s};
+    return EB200_OK;
+}
+
+int eb200_stream_destroy(eb200_stream* s) {
+    if (!s) return EB200_OK;
+    cudaStreamSynchronize(s->s);
+    cudaStreamDestroy(s->s);
+    delete s;
+    return EB200_OK;
+}
+
+int eb200_stream_sync(eb200_stream* s) {
+    EB_REQUIRE(s, EB200_ERR_INVALID, "stream is null");
+    EB_CHECK_CUDA(cudaStreamSynchronize(s->s));
+    return EB200_OK;
+}
+
+int eb200_stream_wait(eb200_device* dev, eb200_stream* s, eb200_event* ev) {
+    EB_REQUIRE(dev && ev, EB200_ERR_INVALID, "null argument");
+    EB_CHECK_CUDA(cudaStreamWaitEvent(s ? s->s : dev->stream, ev->ev, 0));
+    return EB200_OK;
+}
+
+int eb200_event_record_on(eb200_event* ev, eb200_stream* s) {
+    EB_REQUIRE(ev, EB200_ERR_INVALID, "ev is null");
+    EB_CHECK_CUDA(cudaEventRecord(ev->ev, s ? s->s : ev->dev->stream));
+    return EB200_OK;
+}
+
+int eb200_buffer_write_on(eb200_buffer* buf, const void* host, size_t bytes, eb200_stream* s) {
+    EB_REQUIRE(buf && host && s, EB200_ERR_INVALID, "null argument");
+    EB_REQUIRE(bytes == buf->bytes, EB200_ERR_INVALID, "Buffer size mismatch: expected %zu, got %zu", buf->bytes, bytes);
+    EB_REQUIRE(buf->storage.use_count() <= 1, EB200_ERR_INVALID, "buffer shares storage with a clone; write it on the compute stream");
+    EB_CHECK_CUDA(cudaSetDevice(buf->dev->index));
+    EB_CHECK_CUDA(cudaMemcpyAsync(buf->storage->ptr, host, bytes, cudaMemcpyHostToDevice, s->s));
+    return EB200_OK;
+}
+
+int eb200_buffer_read_on(eb200_buffer* buf, void* host, size_t bytes, eb200_stream* s) {
+    EB_REQUIRE(buf && host && s, EB200_ERR_INVALID, "null argument");
+    EB_REQUIRE(bytes == buf->bytes, EB200_ERR_INVALID, "Buffer size mismatch: expected %zu, got %zu", buf->bytes, bytes);
+    EB_CHECK_CUDA(cudaSetDevice(buf->dev->index));
+    EB_CHECK_CUDA(cudaMemcpyAsync(host, buf->storage->ptr, bytes, cudaMemcpyDeviceToHost, s->s));
+    return EB200_OK;
+}
+
 int eb200_device_mem_stats(eb200_device* dev, int64_t* in_use, int64_t* peak, int64_t* n_allocs) {
     EB_REQUIRE(dev, EB200_ERR_INVALID, "dev is null");
     if (in_use) *in_use = dev->in_use.load();

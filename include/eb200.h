@@ -207,6 +207,20 @@ int eb200_event_create(eb200_device* dev, eb200_event** ev);
 int eb200_event_record(eb200_event* ev);
 int eb200_event_elapsed_ms(eb200_event* a, eb200_event* b, float* ms);
 int eb200_event_destroy(eb200_event* ev);
+/* Side streams for copies that overlap compute (PCIe is full duplex: the upload
+ * of the next batch, the kernels of this one and the download of the previous
+ * results can all be in flight).  A side stream only carries copies; ordering
+ * against the device's compute stream is explicit through events:
+ *   eb200_event_record_on(ev, s)   record on a side stream (NULL = compute stream)
+ *   eb200_stream_wait(dev, s, ev)  make `s` (NULL = compute stream) wait for ev */
+typedef struct eb200_stream eb200_stream;
+int eb200_stream_create(eb200_device* dev, eb200_stream** s);
+int eb200_stream_destroy(eb200_stream* s);
+int eb200_stream_sync(eb200_stream* s);
+int eb200_stream_wait(eb200_device* dev, eb200_stream* s, eb200_event* ev);
+int eb200_event_record_on(eb200_event* ev, eb200_stream* s);
+int eb200_buffer_write_on(eb200_buffer* buf, const void* pinned_host, size_t bytes, eb200_stream* s);
+int eb200_buffer_read_on(eb200_buffer* buf, void* pinned_host, size_t bytes, eb200_stream* s);
 /* A whole step as one CUDA graph: launches issued on this thread between
  * graph_begin and graph_end are recorded instead of run, then replayed by
  * graph_launch with a single submission (the reference synchronises after every

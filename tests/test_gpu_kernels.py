@@ -81,6 +81,32 @@ def test_buffer_semantics(dev, registry):
     assert st["in_use"] > 0 and st["peak"] >= st["in_use"]
 
 
+def test_side_stream_copies_ordered_by_events(dev, registry):
+    """Upload on one side stream, kernel on the compute stream, download on
+    another side stream, ordered only by events; two rounds reuse the buffers."""
+    from harp_b200.backend import PinnedArray
+    n = 1 << 20
+    src, dst = PinnedArray((n,)), PinnedArray((n,))
+    a, o = registry.allocate_buffer(dev, [n]), registry.allocate_buffer(dev, [n])
+    k = registry.compile_ast(dev, D.elementwise([n], [D.contiguous([n])], w(0) * Ast.const(2.0)))
+    up, down = dev.copy_stream(), dev.copy_stream()
+    e_up, e_k, e_down = dev.event(), dev.event(), dev.event()
+    for rnd_ in range(2):
+        src.array[...] = np.arange(n, dtype=np.float32) + rnd_
+        if rnd_:
+            dev.wait_event(e_k, up)            # the kernel that read `a` is done
+        a.write_on(up, src.ptr, src.nbytes); e_up.record(up)
+        dev.wait_event(e_up)
+        if rnd_:
+            dev.wait_event(e_down)             # the previous download of `o` is done
+        k.execute([a], [o]); e_k.record()
+        dev.wait_event(e_k, down)
+        o.read_on(down, dst.ptr, dst.nbytes); e_down.record(down)
+        down.synchronize()
+        assert (dst.array == 2 * (np.arange(n, dtype=np.float32) + rnd_)).all()
+    src.free(); dst.free()
+
+
 def test_launch_rejects_short_buffers(dev, registry):
     k = registry.compile_ast(dev, D.elementwise([16], [D.contiguous([16])], w(0)))
     a = registry.allocate_buffer(dev, [8])
