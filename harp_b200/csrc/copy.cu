@@ -16,6 +16,10 @@
 // sgd_update      p - lr*g, the host loop of SGD::step
 //                 (crates/nn/src/optim/sgd.rs:88-92) kept on the device; separate
 //                 multiply and subtract roundings, like the Rust loop.
+#include <stdlib.h>
+
+#include <algorithm>
+
 #include "expr.cuh"
 #include "index.cuh"
 
@@ -101,6 +105,83 @@ __global__ void __launch_bounds__(256) transpose_kernel(const __grid_constant__ 
     }
 }
 
+// Persistent form for extents that are multiples of 64 with 16-byte aligned lines:
+// a CTA walks tiles blockIdx.x, +gridDim.x, ...; while it writes tile i out of
+// shared memory, the four 128-bit loads of tile i+1 are already in flight in
+// registers, so the memory system never drains between a CTA's tiles.
+__global__ void __launch_bounds__(256) transpose_pipe_kernel(const __grid_constant__ TrParams q,
+                                                             const uint32_t* __restrict__ in,
+                                                             uint32_t* __restrict__ out) {
+    constexpr int TT = 64, P = TT + 1;
+    __shared__ uint32_t tile_mem[TT * P];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int tx = lane & 7, ty = lane >> 3;
+    const int seg = (warp & 1) * 32;
+    const int line0 = (warp >> 1) * 4 + ty;
+    auto bases = [&](long long t, long long& ib, long long& ob) {
+        long long rem = t;
+        const long long tc = rem % q.tiles_c; rem /= q.tiles_c;
+        const long long tr = rem % q.tiles_r; rem /= q.tiles_r;
+        long long ibase = q.in_off, obase = q.out_off;
+        for (int d = q.nbatch - 1; d >= 0; --d) {
+            const long long i = rem % q.bshape[d];
+            rem /= q.bshape[d];
+            ibase += i * q.bin[d];
+            obase += i * q.bout[d];
+        }
+        ib = ibase + tc * TT * q.in_sc + tr * TT;      // element (c0, r0) of the input
+        ob = obase + tr * TT * q.out_sr + tc * TT;     // element (r0, c0) of the output
+    };
+    // two tiles of loads in flight: slot 0 = the tile to store next, slot 1 = the one after
+    constexpr int DEPTH = 2;
+    uint4 nxt[DEPTH][4];
+    long long obq[DEPTH];
+    long long ib, ob;
+    const long long step = gridDim.x;
+#pragma unroll
+    for (int dpt = 0; dpt < DEPTH; ++dpt) {
+        const long long tt = (long long)blockIdx.x + dpt * step;
+        if (tt < q.tiles) {
+            bases(tt, ib, ob);
+            obq[dpt] = ob;
+#pragma unroll
+            for (int pass = 0; pass < 4; ++pass)
+                nxt[dpt][pass] = __ldg(reinterpret_cast<const uint4*>(in + ib + (long long)(pass * 16 + line0) * q.in_sc + seg + tx * 4));
+        }
+    }
+    for (long long t = blockIdx.x; t < q.tiles; t += step) {
+        const long long ob_cur = obq[0];
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) {
+            const int cl = pass * 16 + line0, rl = seg + tx * 4;
+            tile_mem[rl * P + cl] = nxt[0][pass].x; tile_mem[(rl + 1) * P + cl] = nxt[0][pass].y;
+            tile_mem[(rl + 2) * P + cl] = nxt[0][pass].z; tile_mem[(rl + 3) * P + cl] = nxt[0][pass].w;
+        }
+        __syncthreads();
+        // shift the queue and refill its tail
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) nxt[0][pass] = nxt[1][pass];
+        obq[0] = obq[1];
+        const long long tn = t + DEPTH * step;
+        if (tn < q.tiles) {
+            bases(tn, ib, ob);
+            obq[1] = ob;
+#pragma unroll
+            for (int pass = 0; pass < 4; ++pass)
+                nxt[1][pass] = __ldg(reinterpret_cast<const uint4*>(in + ib + (long long)(pass * 16 + line0) * q.in_sc + seg + tx * 4));
+        }
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) {
+            const int rl = pass * 16 + line0, cl = seg + tx * 4;
+            const uint32_t* src = tile_mem + rl * P + cl;
+            uint4 v;
+            v.x = src[0]; v.y = src[1]; v.z = src[2]; v.w = src[3];
+            *reinterpret_cast<uint4*>(out + ob_cur + (long long)rl * q.out_sr + cl) = v;
+        }
+        __syncthreads();
+    }
+}
+
 template <int TT>
 static int launch_tr(Device* dev, TrParams& q, const uint32_t* in, uint32_t* out) {
     q.tiles_r = (q.R + TT - 1) / TT;
@@ -147,6 +228,21 @@ int launch_transpose(Device* dev, const Plan& plan, const void* in, void* out) {
     uint32_t* dst = reinterpret_cast<uint32_t*>(out);
     // 64x64 tiles: 8 resident CTAs per SM; 128x128 tiles measured 30 % slower
     // (3 CTAs per SM leave too few loads in flight)
+    bool pipe = q.R % 64 == 0 && q.C % 64 == 0 && q.in_sc % 4 == 0 && q.out_sr % 4 == 0 &&
+                q.in_off % 4 == 0 && q.out_off % 4 == 0;
+    for (int d = 0; d < q.nbatch && pipe; ++d) pipe = q.bin[d] % 4 == 0 && q.bout[d] % 4 == 0;
+    if (pipe && (reinterpret_cast<uintptr_t>(in) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+        q.tiles_r = q.R / 64;
+        q.tiles_c = q.C / 64;
+        q.tiles *= q.tiles_r * q.tiles_c;
+        if (q.tiles <= 0) return EB200_OK;
+        const int per_sm = 8;
+        const long long blocks = std::min<long long>(q.tiles, (long long)dev->prop.multiProcessorCount * per_sm);
+        transpose_pipe_kernel<<<(unsigned)blocks, 256, 0, dev->stream>>>(q, src, dst);
+        count_launch();
+        EB_CHECK_CUDA(cudaGetLastError());
+        return EB200_OK;
+    }
     return launch_tr<64>(dev, q, src, dst);
 }
 
