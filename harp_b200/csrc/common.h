@@ -90,6 +90,9 @@ struct KParams {
     KInsn prog[KMAX_INSNS];
     float consts[KMAX_CONSTS];
     const float* cptr[KMAX_CONSTS];  // non-null: constant slot is read from a one-element tensor
+    int tuning;                      // copy of the descriptor's flags
+    int _pad1;
+    int* error_flag;                 // host-mapped word a kernel raises when a bounded wait runs out (may be null)
 };
 
 // ---- host objects ------------------------------------------------------------

@@ -113,6 +113,7 @@ int eb200_kernel_launch(eb200_kernel* k, eb200_buffer* const* inputs, int n_inpu
                         ? reinterpret_cast<const float*>(inputs[plan.dyn_input[j]]->storage->ptr) + plan.dyn_offset[j]
                         : nullptr;
     p.out.ptr = reinterpret_cast<char*>(ob->storage->ptr);
+    p.error_flag = dev->error_flag_dev;
     void* scratch = k->scratch ? k->scratch->ptr : nullptr;
     switch (plan.impl) {
         case IMPL_EW: return launch_ew(dev, plan, p);

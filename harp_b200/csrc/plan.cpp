@@ -260,6 +260,7 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
     }
     p.splits = 1;
     p.chunk = p.rlen;
+    p.tuning = d->flags;
     int nb_total = 0;
     for (int i = 0; i <= d->n_inputs; ++i) {
         KOperand& ko = i < d->n_inputs ? p.in[i] : p.out;

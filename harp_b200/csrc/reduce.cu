@@ -21,7 +21,10 @@
 //                fallback for any reduce the other paths do not take.
 //
 // Both are HBM-bound: algorithmic bytes = 4 B x (input elements + outputs).
+#include <stdlib.h>
 #include <string.h>
+
+#include <algorithm>
 
 #include "expr.cuh"
 #include "index.cuh"
@@ -168,6 +171,144 @@ __global__ void __launch_bounds__(256) reduce_inner_kernel(const __grid_constant
     }
 }
 
+// ---- row reduce with TMA staging -------------------------------------------------------
+// For long contiguous rows with one streaming operand: every warp owns rows and a
+// private 4-slot ring of 2 KB chunks in shared memory.  Lane 0 keeps the ring full
+// with bulk async copies (cp.async.bulk, completion on an mbarrier per slot); the
+// warp evaluates the map on a chunk as soon as it lands and refills the slot.
+// 16 warps x 8 KB = 128 KB in flight per SM with no registers tied up in loads
+// and no CTA-wide barrier anywhere.  Waits are bounded like the GEMM's.
+constexpr int RT_WARPS = 32, RT_CH = 512, RT_ST = 3;   // warps per CTA, floats per chunk, slots per warp
+constexpr unsigned RT_SPIN_LIMIT = 1u << 22;
+
+__device__ __forceinline__ uint32_t rt_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+template <class F>
+__global__ void __launch_bounds__(RT_WARPS * 32, 1) reduce_inner_tma_kernel(const __grid_constant__ KParams p) {
+    constexpr int NI = F::kCompiled ? F::kNin : KMAX_IN;
+    extern __shared__ __align__(128) unsigned char rt_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* ring = reinterpret_cast<float*>(rt_raw) + (size_t)warp * RT_ST * RT_CH;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(rt_raw + (size_t)RT_WARPS * RT_ST * RT_CH * 4) + warp * RT_ST;
+    const int ra = p.raxis;
+    const int n = F::nin(p);
+    float cl[F::kNconst];
+    load_consts<F>(p, cl);
+    int mov = 0;                                   // the one operand that walks the row
+#pragma unroll
+    for (int i = 0; i < NI; ++i)
+        if (i < n && p.in[i].strides[ra] == 1) mov = i;
+    if (lane == 0) {
+        for (int s = 0; s < RT_ST; ++s)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(rt_smem(&bars[s])));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    const long long wstride = (long long)gridDim.x * RT_WARPS;
+    const long long first = (long long)blockIdx.x * RT_WARPS + warp;
+    const int cpr = (int)((p.rlen + RT_CH - 1) / RT_CH);          // chunks per row
+    // producer cursor (lane 0): next chunk to request
+    long long prow = first;
+    int pchunk = 0;
+    const float* pbase = nullptr;
+    unsigned issued = 0, consumed = 0;
+    bool ok = true;
+    auto issue = [&]() {                            // lane 0 only
+        if (prow >= p.kept) return;
+        if (pchunk == 0) {
+            long long pidx[KMAX_DIMS];
+            decompose(p, prow, pidx, ra);
+            pbase = reinterpret_cast<const float*>(p.in[mov].ptr) + operand_index(p, p.in[mov], pidx);
+        }
+        const int s = issued % RT_ST;
+        const long long c0 = (long long)pchunk * RT_CH;
+        const unsigned bytes = (unsigned)(min((long long)RT_CH, p.rlen - c0) * 4);
+        const uint32_t bar = rt_smem(&bars[s]);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // our reads of this slot precede the copy
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(rt_smem(ring + (size_t)s * RT_CH)), "l"(pbase + c0), "r"(bytes), "r"(bar) : "memory");
+        ++issued;
+        if (++pchunk == cpr) { pchunk = 0; prow += wstride; }
+    };
+    if (lane == 0)
+        for (int s = 0; s < RT_ST; ++s) issue();
+    for (long long row = first; row < p.kept && ok; row += wstride) {
+        long long idx[KMAX_DIMS];
+        decompose(p, row, idx, ra);
+        float rc[NI];                               // operands that do not move along the row: one value per row
+#pragma unroll
+        for (int i = 0; i < NI; ++i) {
+            if (i >= n) break;
+            rc[i] = (i == mov) ? 0.0f : __ldg(reinterpret_cast<const float*>(p.in[i].ptr) + operand_index(p, p.in[i], idx));
+        }
+        float a4[4];
+#pragma unroll
+        for (int v = 0; v < 4; ++v) a4[v] = red_identity(p.rop);
+        for (int ch = 0; ch < cpr && ok; ++ch) {
+            const int s = consumed % RT_ST;
+            const unsigned parity = (consumed / RT_ST) & 1u;
+            const uint32_t bar = rt_smem(&bars[s]);
+            unsigned done = 0;
+            for (unsigned spin = 0; spin < RT_SPIN_LIMIT && !done; ++spin) {
+                asm volatile("{\n\t.reg .pred q;\n\tmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                             : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+            }
+            if (!done) {
+                if (p.error_flag) atomicExch(p.error_flag, 1);
+                ok = false;
+                break;
+            }
+            const long long c0 = (long long)ch * RT_CH;
+            const int len = (int)min((long long)RT_CH, p.rlen - c0);
+            const float* src = ring + (size_t)s * RT_CH;
+            // 512 floats = 4 vectors per lane, all evaluated together
+            float in[4][NI][4];
+            bool have[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int e = u * 128 + lane * 4;
+                have[u] = e < len;
+#pragma unroll
+                for (int i = 0; i < NI; ++i) {
+                    if (i >= n) break;
+                    if (i == mov) {
+                        const float4 t = have[u] ? *reinterpret_cast<const float4*>(src + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        in[u][i][0] = t.x; in[u][i][1] = t.y; in[u][i][2] = t.z; in[u][i][3] = t.w;
+                    } else {
+                        splat4(rc[i], in[u][i]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (!have[u]) continue;
+                float v4[4];
+                F::template eval<4>(p, in[u], v4, cl);
+#pragma unroll
+                for (int v = 0; v < 4; ++v) a4[v] = red_combine(p.rop, a4[v], v4[v]);
+            }
+            __syncwarp();                            // every lane has consumed its part of the slot
+            ++consumed;
+            if (lane == 0) issue();                  // refill it; three other slots are still in flight
+        }
+        float acc = red_combine(p.rop, red_combine(p.rop, a4[0], a4[1]), red_combine(p.rop, a4[2], a4[3]));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc = red_combine(p.rop, acc, __shfl_xor_sync(0xffffffffu, acc, o));
+        if (lane == 0 && ok) store_elem(p.out, operand_index(p, p.out, idx), acc);
+    }
+    // a warp that gave up still has copies in flight into its ring: wait for them (bounded)
+    if (!ok && lane == 0) {
+        for (unsigned c = consumed; c < issued; ++c) {
+            const uint32_t bar = rt_smem(&bars[c % RT_ST]);
+            unsigned done = 0;
+            for (unsigned spin = 0; spin < RT_SPIN_LIMIT && !done; ++spin)
+                asm volatile("{\n\t.reg .pred q;\n\tmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                             : "=r"(done) : "r"(bar), "r"((c / RT_ST) & 1u) : "memory");
+        }
+    }
+}
+
 constexpr int RO_U = 4;  // reduce steps in flight per thread
 
 template <class F>
@@ -286,6 +427,23 @@ static int launch_one(Device* dev, const Plan& plan, const KParams& p, float* sc
         long long blocks = (work + rows - 1) / rows;
         long long cap = (long long)sms * 64;
         if (blocks > cap) blocks = cap;
+        int moving = 0;
+        for (int i = 0; i < p.n_in; ++i) moving += p.in[i].strides[p.raxis] == 1;
+        // Staging rows through shared memory with bulk async copies is opt-in
+        // (descriptor flag 32): on B200 it measured 5.05 TB/s against 6.15 TB/s for
+        // the direct 128-bit loads on [8192, 8192] rows.
+        const bool tma = (p.tuning & 32) && T == 32 && p.vec == 4 && p.splits == 1 && moving == 1 && p.rlen >= 2048 &&
+                         p.error_flag != nullptr && p.kept >= sms;
+        if (tma) {
+            const size_t smem = (size_t)RT_WARPS * RT_ST * RT_CH * 4 + RT_WARPS * RT_ST * 8;
+            static bool configured = false;
+            if (!configured) {
+                EB_CHECK_CUDA(cudaFuncSetAttribute(reduce_inner_tma_kernel<F>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+                configured = true;
+            }
+            long long g = std::min<long long>(sms, (p.kept + RT_WARPS - 1) / RT_WARPS);
+            reduce_inner_tma_kernel<F><<<(unsigned)g, RT_WARPS * 32, smem, dev->stream>>>(p);
+        } else
         if (T == 1) reduce_inner_kernel<F, 1><<<(unsigned)blocks, 256, 0, dev->stream>>>(p, scratch);
         else if (T == 32) reduce_inner_kernel<F, 32><<<(unsigned)blocks, 256, 0, dev->stream>>>(p, scratch);
         else if (T == 128) reduce_inner_kernel<F, 128><<<(unsigned)blocks, 256, 0, dev->stream>>>(p, scratch);

@@ -230,6 +230,26 @@ def test_reduce_outer_axis(dev, rows, cols, op):
         assert (np.abs(got.astype(np.float64) - ref) <= sum_tolerance(k, [x]) + 1e-30).all()
 
 
+@pytest.mark.parametrize("rows,cols,op", [(300, 2048, D.R_SUM), (1000, 4100, D.R_SUM), (160, 8192, D.R_MAX), (500, 2052, D.R_SUM)])
+def test_reduce_inner_bulk_copy_staged_variant(dev, rows, cols, op):
+    """Descriptor flag 32: rows staged through shared memory by cp.async.bulk with
+    per-slot mbarriers; same results as the direct-load kernel."""
+    x = rnd([rows, cols], rows + cols)
+    m = rnd([rows], 7)
+    mb = D.Operand([1, 0], 0, D.F32, rows)
+    expr = (w(0) - w(1)).exp() if op == D.R_SUM else w(0) * w(1)
+    k = D.reduce([rows, cols], [D.contiguous([rows, cols]), mb], expr, op, 1)
+    base, _ = run_gpu(dev, k, [x, m])
+    k.flags = 32
+    got, kern = run_gpu(dev, k, [x, m])
+    dev.synchronize()
+    if op == D.R_MAX:
+        assert (got == base).all()
+    else:
+        assert_close(got, base, rel=2e-6)
+        assert (np.abs(got.astype(np.float64) - O.run(k, [x, m])) <= sum_tolerance(k, [x, m])).all()
+
+
 def test_reduce_middle_axis_with_map_and_broadcast(dev):
     shape = [6, 50, 20]
     a = rnd(shape, 11)
