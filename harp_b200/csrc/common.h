@@ -107,6 +107,7 @@ struct Device {
     int* error_flag_host = nullptr;
     int* error_flag_dev = nullptr;
     bool tc_configured = false;
+    bool conv_configured = false;
 };
 
 // Reference-counted device storage; several buffer handles may share one
@@ -147,6 +148,7 @@ enum Impl {
     IMPL_SGD,             // p - lr*g
     IMPL_GEMM_SIMT,       // dense contraction, fp32 FFMA tiles (exact-f32 fallback)
     IMPL_GEMM_TC,         // dense contraction, tcgen05 TF32 / 3xTF32
+    IMPL_CONV2D,          // convolution as implicit GEMM on the tensor cores
 };
 
 struct GemmShape {
@@ -160,6 +162,11 @@ struct GemmShape {
     int splits = 1;            // split-K: partial products go to scratch and are summed by a second kernel
     long long k_chunk = 0;     // k extent per split (multiple of 32)
     long long partial_off = 0; // float offset of the partials inside the kernel's scratch
+};
+
+struct ConvShape {
+    int N = 0, C = 0, H = 0, W = 0, Co = 0, KH = 0, KW = 0, pad = 0;
+    int relu = 0, mode = EB200_GEMM_3XTF32, has_bias = 0;
 };
 
 struct TransposeShape {
@@ -176,6 +183,7 @@ struct Plan {
     int chain = -1;           // index into the compiled-functor table, -1 = interpreter
     int threads_per_row = 0;  // REDUCE_INNER: 1, 32 or 256
     GemmShape gemm;
+    ConvShape conv;
     TransposeShape tr;
     int64_t scratch_bytes = 0;
     int64_t algo_bytes = 0, algo_flops = 0;
@@ -211,6 +219,9 @@ int launch_splitk_reduce(Device* dev, const GemmShape& g, const float* partials,
 bool gemm_tc_supported(const GemmShape& g);
 void gemm_tc_scratch(const GemmShape& g, long long* a_span, long long* b_span);
 int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b, float* c, void* scratch);
+bool conv2d_supported(const ConvShape& c);
+long long conv2d_scratch_floats(const ConvShape& c);
+int launch_conv2d(Device* dev, const Plan& plan, const float* x, const float* w, const float* bias, float* out, void* scratch);
 // EB200_ERR_TIMEOUT if a kernel on this device reported a timed-out wait (clears the flag)
 int check_device_flag(Device* dev);
 

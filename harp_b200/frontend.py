@@ -482,6 +482,25 @@ class Tensor:
             y = y + bias.unsqueeze(0).expand(n * ho * wo, co)
         return y.reshape(n, ho, wo, co).permute(0, 3, 1, 2)
 
+    def conv2d_fused(self, weight: "Tensor", bias: Optional["Tensor"] = None, padding=0, relu=False,
+                     mode: int = D.GEMM_DEFAULT) -> "Tensor":
+        """The same function as ``conv2d`` (stride 1) as ONE kernel: the window
+        tensor the reference materialises twice (conv.rs:150-166) is gathered on
+        the fly inside an implicit GEMM, bias and ReLU run in its epilogue.
+        Forward only: the training graphs keep the composed spelling, whose
+        backward the tape derives."""
+        assert not (self.requires_grad or weight.requires_grad or (bias is not None and bias.requires_grad)), \
+            "conv2d_fused is an inference kernel"
+        n, c, h, wd = self.shape
+        co, c2, kh, kw = weight.shape
+        assert c2 == c
+        ho, wo = h + 2 * padding - kh + 1, wd + 2 * padding - kw + 1
+        ops = [t if t.view.is_contiguous() and not t.view.bounds else t.contiguous()
+               for t in ([self, weight] + ([bias] if bias is not None else []))]
+        node = Node("conv", (n * ho * wo, co), [(t.node, t.view) for t in ops], name="conv2d")
+        node.conv = (n, c, h, wd, co, kh, kw, padding, bool(relu), mode)
+        return Tensor(node).reshape(n, ho, wo, co).permute(0, 3, 1, 2)
+
     def max_pool2d(self, k: int) -> "Tensor":
         """crates/nn/src/functional/pool.rs:117-160: unfold windows, max over them."""
         n, c, h, wd = self.shape
@@ -552,6 +571,7 @@ class _K:
         self.reduce_op, self.axis, self.dtype, self.name = n.reduce_op, n.axis, n.dtype, n.name
         self.out_view, self.out_numel, self.out_shape = n.out_view, n.out_numel, n.out_shape
         self.data = n.data
+        self.conv = getattr(n, "conv", None)
 
 
 def _dim_map(view: View, prod_shape) -> Optional[List[Optional[int]]]:
@@ -665,6 +685,13 @@ def _lower(k: _K, loc) -> D.KernelDesc:
         st = D.contiguous_strides(kept)
         st[k.axis] = 0
         return D.reduce(list(k.shape), ins, k.expr, k.reduce_op, k.axis, out=D.Operand(st, out_off, D.F32, out_numel))
+    if k.kind == "conv":
+        n, c, h, wd, co, kh, kw, pad, relu, mode = k.conv
+        z8 = [0] * 8
+        for op in ins:
+            op.strides = z8
+        return D.KernelDesc(D.K_CONV2D, [n, c, h, wd, co, kh, kw, pad], ins, D.Operand(z8, out_off, D.F32, out_numel),
+                            None, gemm_mode=mode, flags=D.FLAG_RELU if relu else 0, name=k.name)
     if k.kind == "fold":
         assert out_off == 0, "a scatter output owns its buffer (it is zero-filled as a whole)"
         return D.KernelDesc(D.K_SCATTER, k.shape, ins, k.out_view.operand(k.out_numel, D.F32), None, name=k.name)

@@ -61,7 +61,12 @@ typedef enum {
     EB200_K_REDUCE = 1,      /* R_: lower_reduce, lower.rs:525-571 */
     EB200_K_COPY = 2,        /* C_: lower_view, lower.rs:448-501 */
     EB200_K_SCATTER = 3,     /* S_: lower_scatter, lower.rs:580-683 */
-    EB200_K_SGD = 4          /* p <- p - lr*g (crates/nn/src/optim/sgd.rs:73-103), device resident */
+    EB200_K_SGD = 4,         /* p <- p - lr*g (crates/nn/src/optim/sgd.rs:73-103), device resident */
+    EB200_K_CONV2D = 5       /* functional::conv2d as one kernel (crates/nn/src/functional/conv.rs:113-184):
+                              * shape = {N, C, H, W, Co, KH, KW, pad}; inputs x [N,C,H,W], w [Co,C,KH,KW] and
+                              * optionally bias [Co], all contiguous; output [N*Ho*Wo, Co] row-major (the buffer
+                              * the reference's GEMM step writes before its final permute view); stride 1;
+                              * flags bit 6 = ReLU in the epilogue; gemm_mode picks TF32 / 3xTF32 */
 } eb200_kclass;
 
 /* ReduceOp (src/graph/node.rs:29-77). */

@@ -242,6 +242,34 @@ def emit_kernel_c(k: D.KernelDesc, fn_name: str = "kernel", openmp: bool = False
         line(f"/* atomic_add (sequential) */ (out[{_affine(k.output.offset, k.output.strides)}] += {loads[0]});")
         for _ in range(nd):
             close_loop()
+    elif k.kclass == D.K_CONV2D:
+        # What the reference's composition computes (crates/nn/src/functional/conv.rs:113-184):
+        # the R_ kernel over the unfolded-and-permuted windows adds, for every output
+        # position and channel, the products in (c, kh, kw) order; padding reads 0.0f.
+        n, c, h, w_, co, kh, kw, pad = k.shape
+        ho, wo = h + 2 * pad - kh + 1, w_ + 2 * pad - kw + 1
+        relu = bool(k.flags & D.FLAG_RELU)
+        for d, e in enumerate((n, ho, wo, co)):
+            open_loop(d, e)
+        line("float acc;")
+        line("acc = 0.0f;")
+        pragma_done[0] = True
+        for d, e in ((4, c), (5, kh), (6, kw)):
+            open_loop(d, e)
+        ih, iw = f"((ridx1 + ridx5) + {-pad})", f"((ridx2 + ridx6) + {-pad})"
+        o = [op.offset for op in k.inputs] + [0]
+        xv = f"buf0[{o[0]} + ((((ridx0 * {c}) + ridx4) * {h} + {ih}) * {w_} + {iw})]"
+        if pad:
+            xv = f"((((!({ih} < 0)) && ({ih} < {h})) && ((!({iw} < 0)) && ({iw} < {w_}))) ? {xv} : 0.0f)"
+        line(f"acc = (acc + ({xv} * buf1[{o[1]} + ((((ridx3 * {c}) + ridx4) * {kh} + ridx5) * {kw} + ridx6)]));")
+        for _ in range(3):
+            close_loop()
+        val = f"(acc + buf2[{o[2]} + ridx3])" if len(k.inputs) == 3 else "acc"
+        if relu:
+            val = f"fmaxf({val}, 0.0f)"
+        line(f"out[{k.output.offset} + ((((ridx0 * {ho}) + ridx1) * {wo} + ridx2) * {co} + ridx3)] = {val};")
+        for _ in range(4):
+            close_loop()
     elif k.kclass == D.K_SGD:
         # host loop of SGD::step (crates/nn/src/optim/sgd.rs:73-103): p - lr*g
         open_loop(0, k.shape[0])

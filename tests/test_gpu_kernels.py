@@ -492,3 +492,69 @@ def test_cfg2_full_size(dev, registry):
     tt, _ = run_gpu(dev, kt, [t])
     assert tt.tobytes() == x.tobytes()
     assert z.max() == x.max()
+
+
+# ---- conv2d as one implicit-GEMM kernel --------------------------------------------------------------
+
+def _conv_ref64(x, w_, b, pad, relu):
+    """float64 direct convolution in NHWC-flattened [M, Co] order, plus sum |terms|."""
+    n, c, h, wd = x.shape
+    co, _, kh, kw = w_.shape
+    xp = np.zeros((n, c, h + 2 * pad, wd + 2 * pad)); xp[:, :, pad:pad + h, pad:pad + wd] = x
+    ho, wo = h + 2 * pad - kh + 1, wd + 2 * pad - kw + 1
+    win = np.lib.stride_tricks.sliding_window_view(xp, (kh, kw), axis=(2, 3))       # [n, c, ho, wo, kh, kw]
+    cols = win.transpose(0, 2, 3, 1, 4, 5).reshape(n * ho * wo, c * kh * kw)
+    wm = w_.reshape(co, -1).astype(np.float64)
+    ref = cols @ wm.T
+    scale = np.abs(cols) @ np.abs(wm).T
+    if b is not None:
+        ref = ref + b.astype(np.float64)[None, :]
+        scale = scale + np.abs(b.astype(np.float64))[None, :]
+    if relu:
+        ref = np.maximum(ref, 0.0)
+    return ref, scale
+
+
+@pytest.mark.parametrize("mode,tol", [(D.GEMM_TF32, 1e-2), (D.GEMM_3XTF32, 1e-5)])
+@pytest.mark.parametrize("shape", [
+    (4, 1, 28, 28, 32, 3, 3, 0),       # first CNN layer: K = 9 padded to one 32-wide block
+    (3, 32, 13, 13, 64, 3, 3, 0),      # second CNN layer: K = 288, nine blocks
+    (2, 3, 17, 19, 20, 3, 3, 1),       # zero padding, ragged M (not a multiple of 128) and Co (not of 32)
+    (1, 8, 9, 9, 130, 5, 5, 2),        # Co spans two 128-wide column tiles, 5x5 window
+    (2, 5, 6, 7, 7, 1, 1, 0),          # 1x1 window
+])
+def test_conv2d_implicit_gemm_matches_direct_convolution(dev, mode, tol, shape):
+    n, c, h, wd, co, kh, kw, pad = shape
+    x, w_, b = rnd([n, c, h, wd], 60), rnd([co, c, kh, kw], 61), rnd([co], 62)
+    for bias, relu in ((True, True), (False, False)):
+        kd = D.conv2d(n, c, h, wd, co, kh, kw, pad=pad, bias=bias, relu=relu, mode=mode)
+        ins = [x, w_, b] if bias else [x, w_]
+        got, kern = run_gpu(dev, kd, ins)
+        assert kern.impl.startswith("conv2d_igemm"), kern.impl
+        ref, scale = _conv_ref64(x, w_, b if bias else None, pad, relu)
+        err = np.abs(got.reshape(ref.shape) - ref)
+        assert (err <= tol * scale + 1e-30).all(), (shape, bias, float((err / np.maximum(scale, 1e-30)).max()))
+        # and against the CPU oracle's loop nest (same bound: the summation orders differ)
+        cpu = O.run(kd, ins).reshape(ref.shape)
+        assert (np.abs(got.reshape(ref.shape) - cpu) <= 2 * tol * scale + 1e-30).all()
+    dev.synchronize()     # would raise TIMEOUT had a bounded wait in the kernel run out
+
+
+def test_conv2d_fused_front_end_equals_composed_spelling(dev):
+    """conv2d_fused (one kernel) against conv2d + relu spelled the reference's way
+    (pad, unfold, permute, contiguous, GEMM, bias), both on the GPU."""
+    from harp_b200 import frontend as F
+    x, w_, b = rnd([3, 4, 12, 12], 63), rnd([6, 4, 3, 3], 64), rnd([6], 65)
+    ex = F.B200Executor(dev)
+    outs = []
+    for fused in (True, False):
+        X, Wt, B = F.Tensor.input(x), F.Tensor.input(w_), F.Tensor.input(b)
+        y = X.conv2d_fused(Wt, B, padding=1, relu=True) if fused else X.conv2d(Wt, B, padding=1).relu()
+        y = y.contiguous()
+        p = F.Program([y], ex)
+        p.run()
+        outs.append(p.fetch(y))
+        if fused:
+            assert [d.kclass for d in p.kernel_descs()] == [D.K_CONV2D, D.K_COPY]
+    assert outs[0].shape == (3, 6, 12, 12)
+    assert np.abs(outs[0] - outs[1]).max() <= 1e-4

@@ -142,3 +142,26 @@ def test_i64_is_unsupported_not_miscomputed():
     with pytest.raises(capi.Eb200Error) as e:
         query(k)
     assert e.value.status == capi.ERR_UNSUPPORTED
+
+
+def test_conv2d_is_one_implicit_gemm_with_weight_scratch():
+    i = query(D.conv2d(64, 32, 28, 28, 64, 3, 3, pad=1, relu=True))
+    assert i.impl.decode() == "conv2d_igemm_3xtf32"
+    assert i.launches == 2                                   # weight split/pad + the implicit GEMM
+    assert i.scratch_bytes == 2 * 64 * 288 * 4               # hi and lo weights, K = 288 already a multiple of 32
+    assert i.algo_flops == 2 * 64 * 28 * 28 * 64 * 288
+    i = query(D.conv2d(8, 1, 28, 28, 32, 3, 3, pad=0, mode=D.GEMM_TF32))
+    assert i.impl.decode() == "conv2d_igemm_tf32" and i.scratch_bytes == 2 * 32 * 32 * 4     # K = 9 padded to 32
+
+
+def test_conv2d_rejects_what_the_kernel_does_not_serve():
+    with pytest.raises(capi.Eb200Error) as e:
+        query(D.conv2d(1, 256, 8, 8, 16, 3, 3))              # K = 2304 > 2048
+    assert e.value.status == capi.ERR_UNSUPPORTED
+    with pytest.raises(capi.Eb200Error):
+        query(D.conv2d(1, 1, 2, 2, 4, 3, 3))                 # window larger than the padded image
+    k = D.conv2d(2, 3, 8, 8, 4, 3, 3)
+    k.inputs[1].numel -= 1                                   # weight buffer one element short
+    with pytest.raises(capi.Eb200Error) as e:
+        query(k)
+    assert e.value.status == capi.ERR_BOUNDS
