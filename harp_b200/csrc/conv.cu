@@ -27,6 +27,7 @@ struct ConvParams {
     long long M;        // N * Ho * Wo
     int K, Kpad;        // C * KH * KW, rounded up to 32
     int relu, has_bias, three_pass, stages;
+    int tap_mask;       // KH * KW <= 32: the table carries one bit per window tap
     int* error_flag;
 };
 
@@ -36,7 +37,7 @@ constexpr int CV_MAX_K = 2048;
 __device__ __forceinline__ float tf32_hi(float x) { return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u); }
 
 template <int BN>
-__global__ void __launch_bounds__(CV_THREADS, 1)
+__global__ void __launch_bounds__(CV_THREADS, 3)
 conv2d_igemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_wlo,
                     const __grid_constant__ ConvParams q, const float* __restrict__ x,
                     const float* __restrict__ bias, float* __restrict__ out) {
@@ -48,7 +49,7 @@ conv2d_igemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     uint64_t* empty_bar = full_bar + q.stages;
     uint64_t* acc_bar = empty_bar + q.stages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
-    int2* ktab = reinterpret_cast<int2*>(tmem_slot + 2);     // per k: {offset into x, kh | kw << 16}
+    int2* ktab = reinterpret_cast<int2*>(tmem_slot + 2);     // per k: {offset into x, tap bit (or kh | kw << 16)}
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long m0 = (long long)blockIdx.x * TC_BM;
@@ -61,7 +62,7 @@ conv2d_igemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             const int c = k / (q.KH * q.KW), r = k - c * q.KH * q.KW;
             const int kh = r / q.KW, kw = r - kh * q.KW;
             e.x = (c * q.H + kh) * q.W + kw;
-            e.y = kh | (kw << 16);
+            e.y = q.tap_mask ? (int)(1u << (kh * q.KW + kw)) : (kh | (kw << 16));
         }
         ktab[k] = e;
     }
@@ -124,6 +125,16 @@ conv2d_igemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             oh = r / q.Wo; ow = r - oh * q.Wo;
         }
         const float* xrow = x + ((long long)n * q.C * q.H + (oh - q.pad)) * q.W + (ow - q.pad);
+        // Which taps of the window fall inside the image for this output position: one bit
+        // per (kh, kw) when the window has at most 32 taps, so that the per-element test
+        // in the gather is a single AND with the tap's bit from the table.
+        unsigned vm = 0;
+        if (q.tap_mask && live) {
+            for (int kh = 0; kh < q.KH; ++kh)
+                for (int kw = 0; kw < q.KW; ++kw)
+                    if ((unsigned)(oh + kh - q.pad) < (unsigned)q.H && (unsigned)(ow + kw - q.pad) < (unsigned)q.W)
+                        vm |= 1u << (kh * q.KW + kw);
+        }
         bool ok = true;
         for (int kb = 0; kb < num_kb && ok; ++kb) {
             const int s = kb % q.stages;
@@ -131,29 +142,34 @@ conv2d_igemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             if (!ok) break;
             unsigned char* a_hi = smem + (size_t)s * stage_bytes + (size_t)t * 128;
             unsigned char* a_lo = a_hi + TC_TILE_BYTES;
+            // all 32 loads of the row are issued before the first shared-memory store
+            float v[32];
+            const int2* kt = ktab + kb * TC_BK;
+            if (q.tap_mask) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                float v[4];
+                for (int i = 0; i < 32; ++i) {
+                    const int2 e = kt[i];
+                    v[i] = (vm & (unsigned)e.y) ? __ldg(xrow + e.x) : 0.0f;
+                }
+            } else {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int k = kb * TC_BK + j * 4 + i;
-                    const int2 e = ktab[k];
-                    bool in = live && k < q.K;
-                    if (q.pad) {
-                        const int ih = oh + (e.y & 0xffff) - q.pad, iw = ow + (e.y >> 16) - q.pad;
-                        in = in && ih >= 0 && ih < q.H && iw >= 0 && iw < q.W;
-                    }
+                for (int i = 0; i < 32; ++i) {
+                    const int2 e = kt[i];
+                    const int ih = oh + (e.y & 0xffff) - q.pad, iw = ow + (e.y >> 16) - q.pad;
+                    const bool in = live && kb * TC_BK + i < q.K && (unsigned)ih < (unsigned)q.H && (unsigned)iw < (unsigned)q.W;
                     v[i] = in ? __ldg(xrow + e.x) : 0.0f;
                 }
-                const int chunk = (j ^ (t & 7)) * 16;        // 128-byte swizzle: 16-byte chunk index XOR row % 8
-                if (q.three_pass) {
-                    float h[4];
+            }
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) h[i] = tf32_hi(v[i]);
-                    *reinterpret_cast<float4*>(a_hi + chunk) = make_float4(h[0], h[1], h[2], h[3]);
-                    *reinterpret_cast<float4*>(a_lo + chunk) = make_float4(v[0] - h[0], v[1] - h[1], v[2] - h[2], v[3] - h[3]);
+            for (int j = 0; j < 8; ++j) {
+                const int chunk = (j ^ (t & 7)) * 16;        // 128-byte swizzle: 16-byte chunk index XOR row % 8
+                const float v0 = v[4 * j], v1 = v[4 * j + 1], v2 = v[4 * j + 2], v3 = v[4 * j + 3];
+                if (q.three_pass) {
+                    const float h0 = tf32_hi(v0), h1 = tf32_hi(v1), h2 = tf32_hi(v2), h3 = tf32_hi(v3);
+                    *reinterpret_cast<float4*>(a_hi + chunk) = make_float4(h0, h1, h2, h3);
+                    *reinterpret_cast<float4*>(a_lo + chunk) = make_float4(v0 - h0, v1 - h1, v2 - h2, v3 - h3);
                 } else {
-                    *reinterpret_cast<float4*>(a_hi + chunk) = make_float4(v[0], v[1], v[2], v[3]);
+                    *reinterpret_cast<float4*>(a_hi + chunk) = make_float4(v0, v1, v2, v3);
                 }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // make the tile visible to the tensor core
@@ -252,8 +268,12 @@ int launch_conv2d(Device* dev, const Plan& plan, const float* x, const float* w,
     if ((st = make_map(&mw, whi, q.Kpad, c.Co, 1, q.Kpad, 0, bn))) return st;
     if ((st = make_map(&mwl, wlo, q.Kpad, c.Co, 1, q.Kpad, 0, bn))) return st;
     const int stage_bytes = (q.three_pass ? 2 : 1) * (TC_TILE_BYTES + bn * TC_BK * 4);
-    q.stages = std::max(2, std::min(6, (160 * 1024) / stage_bytes));
-    const size_t smem = (size_t)q.stages * stage_bytes + 1024 + 256 + (size_t)q.Kpad * sizeof(int2);
+    q.tap_mask = c.KH * c.KW <= 32;
+    // Three CTAs per SM (75 KB each) when two stages fit in that; the gather warps of one
+    // CTA then run under the tensor-core and epilogue phases of the others.
+    const size_t fixed = 1024 + 256 + (size_t)q.Kpad * sizeof(int2);
+    q.stages = std::max(2, std::min(4, (int)((75 * 1024 - fixed) / stage_bytes)));
+    const size_t smem = (size_t)q.stages * stage_bytes + fixed;
     if (!dev->conv_configured) {
         EB_CHECK_CUDA(cudaFuncSetAttribute(conv2d_igemm_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         EB_CHECK_CUDA(cudaFuncSetAttribute(conv2d_igemm_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
