@@ -67,7 +67,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     uint64_t* acc_bar = empty_bar + q.stages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = uniform_warp_idx(), lane = threadIdx.x & 31;
     // Tile order: bands of `raster` tile rows, walked column by column, so the
     // CTAs in flight share a squarish set of A and B panels that stays in L2.
     const int tiles_m = (int)((q.m + TC_BM - 1) / TC_BM);
@@ -94,13 +94,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    // The producer and the MMA warp run their loops as whole warps and elect one lane to
+    // issue: TMA and tcgen05.mma take their descriptors and coordinates from uniform
+    // registers, and only warp-uniform control flow lets the compiler keep them there
+    // (issued from a divergent lane-0 branch every tcgen05.mma cost ~200 cycles to issue).
     if (warp == 0) {
-        // ---- TMA producer (one thread) ----
-        if (lane == 0) {
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % q.stages;
-                const unsigned phase = (unsigned)(kb / q.stages) & 1u;
-                if (!mbar_wait(&empty_bar[s], phase ^ 1u, q.error_flag)) break;
+        // ---- TMA producer ----
+        int s = 0;
+        unsigned phase = 0;
+        for (int kb = 0; kb < num_kb; ++kb, s = (s + 1 == q.stages ? 0 : s + 1), phase ^= (s == 0)) {
+            if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], phase ^ 1u, q.error_flag))) break;
+            if (elect_one()) {
                 unsigned char* st = smem + (size_t)s * stage_bytes;
                 mbar_expect_tx(&full_bar[s], (unsigned)stage_bytes);
                 const int kx = (kb_begin + kb) * TC_BK;
@@ -129,46 +133,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (q.three_pass) tma_load_3d(b_hi + B_TILE_BYTES, &map_blo, &full_bar[s], kx, (int)n0, bz * b_zmul);
                 }
             }
+            __syncwarp();
         }
     } else if (warp == 1) {
-        // ---- MMA issuer (one thread) ----
-        if (lane == 0) {
-            const uint32_t idesc = umma_idesc_tf32(TC_BM, TC_BN, q.a_mmajor, q.b_nmajor);
-            bool ok = true;
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                const int s = kb % q.stages;
-                const unsigned phase = (unsigned)(kb / q.stages) & 1u;
-                ok = mbar_wait(&full_bar[s], phase, q.error_flag);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t st = smem_u32(smem + (size_t)s * stage_bytes);
-                const uint32_t a_hi = st, a_lo = st + TC_TILE_BYTES;
-                const uint32_t b_hi = st + (q.three_pass ? 2 : 1) * TC_TILE_BYTES, b_lo = b_hi + B_TILE_BYTES;
+        // ---- MMA issuer ----
+        const uint32_t idesc = umma_idesc_tf32(TC_BM, TC_BN, q.a_mmajor, q.b_nmajor);
+        // K-major: step 32 bytes inside the 128-byte swizzled row.
+        // M/N-major: step one 8-row group (1024 bytes); m/n atoms are 4096 bytes apart
+        // (swizzle atom = 4 k rows = 512 bytes, so one K=8 MMA spans two atoms).
+        const uint32_t a_lbo = q.a_mmajor ? 4096 : 16, a_sbo = q.a_mmajor ? 512 : 1024, a_layout = q.a_mmajor ? 1 : 2;
+        const uint32_t b_lbo = q.b_nmajor ? 4096 : 16, b_sbo = q.b_nmajor ? 512 : 1024, b_layout = q.b_nmajor ? 1 : 2;
+        const uint64_t a_jstep = (q.a_mmajor ? 1024u : (unsigned)(TC_UK * 4)) >> 4;    // descriptor address units of 16 bytes
+        const uint64_t b_jstep = (q.b_nmajor ? 1024u : (unsigned)(TC_UK * 4)) >> 4;
+        const uint32_t smem_base = smem_u32(smem);
+        const uint32_t b_off = (q.three_pass ? 2 : 1) * TC_TILE_BYTES;
+        int s = 0;
+        unsigned phase = 0;
+        for (int kb = 0; kb < num_kb; ++kb, s = (s + 1 == q.stages ? 0 : s + 1), phase ^= (s == 0)) {
+            if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[s], phase, q.error_flag))) break;
+            tc_fence_after();
+            const uint32_t st = smem_base + (uint32_t)s * (uint32_t)stage_bytes;
+            const uint64_t da0 = umma_desc(st, a_lbo, a_sbo, a_layout), dal0 = umma_desc(st + TC_TILE_BYTES, a_lbo, a_sbo, a_layout);
+            const uint64_t db0 = umma_desc(st + b_off, b_lbo, b_sbo, b_layout), dbl0 = umma_desc(st + b_off + B_TILE_BYTES, b_lbo, b_sbo, b_layout);
+            if (elect_one()) {
 #pragma unroll
                 for (int j = 0; j < TC_BK / TC_UK; ++j) {
-                    // K-major: step 32 bytes inside the 128-byte swizzled row.
-                    // N-major B: step one 8-row group (1024 bytes); n atoms are 4096 bytes apart.
-                    const uint32_t a_step = q.a_mmajor ? j * 1024 : j * TC_UK * 4;
-                    const uint32_t a_lbo = q.a_mmajor ? 4096 : 16, a_sbo = q.a_mmajor ? 512 : 1024, a_layout = q.a_mmajor ? 1 : 2;
-                    const uint32_t b_step = q.b_nmajor ? j * 1024 : j * TC_UK * 4;
-                    // (swizzle atom = 4 k rows = 512 bytes, so one K=8 MMA spans two atoms)
-                    const uint32_t b_lbo = q.b_nmajor ? 4096 : 16;
-                    const uint32_t b_sbo = q.b_nmajor ? 512 : 1024;
-                    const uint32_t b_layout = q.b_nmajor ? 1 : 2;
-                    const uint64_t da = umma_desc(a_hi + a_step, a_lbo, a_sbo, a_layout);
-                    const uint64_t db = umma_desc(b_hi + b_step, b_lbo, b_sbo, b_layout);
+                    const uint64_t da = da0 + j * a_jstep, db = db0 + j * b_jstep;
                     umma_tf32(tmem_base, da, db, idesc, (kb > 0 || j > 0) ? 1u : 0u);
                     if (q.three_pass) {
-                        const uint64_t dal = umma_desc(a_lo + a_step, a_lbo, a_sbo, a_layout);
-                        const uint64_t dbl = umma_desc(b_lo + b_step, b_lbo, b_sbo, b_layout);
-                        umma_tf32(tmem_base, dal, db, idesc, 1u);
-                        umma_tf32(tmem_base, da, dbl, idesc, 1u);
+                        umma_tf32(tmem_base, dal0 + j * a_jstep, db, idesc, 1u);
+                        umma_tf32(tmem_base, da, dbl0 + j * b_jstep, idesc, 1u);
                     }
                 }
                 umma_commit(&empty_bar[s]);   // slot is free once these MMAs have read it
             }
-            umma_commit(acc_bar);             // accumulator complete
+            __syncwarp();
         }
+        if (elect_one()) umma_commit(acc_bar);             // accumulator complete
+        __syncwarp();
     } else {
         // ---- epilogue: warps 2..5 own tensor-memory lanes 32*(warp%4) .. +31 ----
         const int quarter = warp & 3;
@@ -254,8 +256,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     uint64_t* acc_bar = empty_bar + q.stages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
 
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t rank = cluster_ctarank();
+    const int warp = uniform_warp_idx(), lane = threadIdx.x & 31;
+    const uint32_t rank = __shfl_sync(0xffffffffu, cluster_ctarank(), 0);     // provably warp-uniform
     const int pair = (int)blockIdx.x >> 1;
     const int tiles_m = (int)((q.m + 255) / 256);
     const int per_band = q.raster * q.tiles_n;
@@ -287,11 +289,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
     if (!idle) {
         if (warp == 0) {
-            if (lane == 0) {
-                for (int kb = 0; kb < num_kb; ++kb) {
-                    const int s = kb % q.stages;
-                    const unsigned phase = (unsigned)(kb / q.stages) & 1u;
-                    if (!mbar_wait(&empty_bar[s], phase ^ 1u, q.error_flag)) break;
+            int s = 0;
+            unsigned phase = 0;
+            for (int kb = 0; kb < num_kb; ++kb, s = (s + 1 == q.stages ? 0 : s + 1), phase ^= (s == 0)) {
+                if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], phase ^ 1u, q.error_flag))) break;
+                if (elect_one()) {
                     unsigned char* st = smem + (size_t)s * stage_bytes;
                     // every load of the pair completes on the even CTA's barrier
                     const uint32_t lead = map_to_cta(smem_u32(&full_bar[s]), 0);
@@ -321,37 +323,41 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         if (q.three_pass) tma_load_3d_pair(b_hi + TC_TILE_BYTES, &map_blo, lead, kx, nb, bz * b_zmul);
                     }
                 }
+                __syncwarp();
             }
         } else if (warp == 1) {
-            if (lane == 0 && rank == 0) {
+            if (rank == 0) {
                 const uint32_t idesc = umma_idesc_tf32(256, BN, q.a_mmajor, q.b_nmajor);
-                for (int kb = 0; kb < num_kb; ++kb) {
-                    const int s = kb % q.stages;
-                    const unsigned phase = (unsigned)(kb / q.stages) & 1u;
-                    if (!mbar_wait(&full_bar[s], phase, q.error_flag)) break;
+                const uint32_t a_lbo = q.a_mmajor ? 4096 : 16, a_sbo = q.a_mmajor ? 512 : 1024, a_layout = q.a_mmajor ? 1 : 2;
+                const uint32_t b_lbo = q.b_nmajor ? 4096 : 16, b_sbo = q.b_nmajor ? 512 : 1024, b_layout = q.b_nmajor ? 1 : 2;
+                const uint64_t a_jstep = (q.a_mmajor ? 1024u : (unsigned)(TC_UK * 4)) >> 4;
+                const uint64_t b_jstep = (q.b_nmajor ? 1024u : (unsigned)(TC_UK * 4)) >> 4;
+                const uint32_t smem_base = smem_u32(smem);
+                const uint32_t b_off = (q.three_pass ? 2 : 1) * TC_TILE_BYTES;
+                int s = 0;
+                unsigned phase = 0;
+                for (int kb = 0; kb < num_kb; ++kb, s = (s + 1 == q.stages ? 0 : s + 1), phase ^= (s == 0)) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[s], phase, q.error_flag))) break;
                     tc_fence_after();
-                    const uint32_t st = smem_u32(smem + (size_t)s * stage_bytes);
-                    const uint32_t a_hi = st, a_lo = st + TC_TILE_BYTES;
-                    const uint32_t b_hi = st + (q.three_pass ? 2 : 1) * TC_TILE_BYTES, b_lo = b_hi + TC_TILE_BYTES;
+                    const uint32_t st = smem_base + (uint32_t)s * (uint32_t)stage_bytes;
+                    const uint64_t da0 = umma_desc(st, a_lbo, a_sbo, a_layout), dal0 = umma_desc(st + TC_TILE_BYTES, a_lbo, a_sbo, a_layout);
+                    const uint64_t db0 = umma_desc(st + b_off, b_lbo, b_sbo, b_layout), dbl0 = umma_desc(st + b_off + TC_TILE_BYTES, b_lbo, b_sbo, b_layout);
+                    if (elect_one()) {
 #pragma unroll
-                    for (int j = 0; j < TC_BK / TC_UK; ++j) {
-                        const uint32_t a_step = q.a_mmajor ? j * 1024 : j * TC_UK * 4;
-                        const uint32_t a_lbo = q.a_mmajor ? 4096 : 16, a_sbo = q.a_mmajor ? 512 : 1024, a_layout = q.a_mmajor ? 1 : 2;
-                        const uint32_t b_step = q.b_nmajor ? j * 1024 : j * TC_UK * 4;
-                        const uint32_t b_lbo = q.b_nmajor ? 4096 : 16, b_sbo = q.b_nmajor ? 512 : 1024, b_layout = q.b_nmajor ? 1 : 2;
-                        const uint64_t da = umma_desc(a_hi + a_step, a_lbo, a_sbo, a_layout);
-                        const uint64_t db = umma_desc(b_hi + b_step, b_lbo, b_sbo, b_layout);
-                        umma_tf32_pair(tmem_base, da, db, idesc, (kb > 0 || j > 0) ? 1u : 0u);
-                        if (q.three_pass) {
-                            const uint64_t dal = umma_desc(a_lo + a_step, a_lbo, a_sbo, a_layout);
-                            const uint64_t dbl = umma_desc(b_lo + b_step, b_lbo, b_sbo, b_layout);
-                            umma_tf32_pair(tmem_base, dal, db, idesc, 1u);
-                            umma_tf32_pair(tmem_base, da, dbl, idesc, 1u);
+                        for (int j = 0; j < TC_BK / TC_UK; ++j) {
+                            const uint64_t da = da0 + j * a_jstep, db = db0 + j * b_jstep;
+                            umma_tf32_pair(tmem_base, da, db, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                            if (q.three_pass) {
+                                umma_tf32_pair(tmem_base, dal0 + j * a_jstep, db, idesc, 1u);
+                                umma_tf32_pair(tmem_base, da, dbl0 + j * b_jstep, idesc, 1u);
+                            }
                         }
+                        umma_commit_pair(&empty_bar[s]);
                     }
-                    umma_commit_pair(&empty_bar[s]);
+                    __syncwarp();
                 }
-                umma_commit_pair(acc_bar);
+                if (elect_one()) umma_commit_pair(acc_bar);
+                __syncwarp();
             }
         } else {
             const int quarter = warp & 3;

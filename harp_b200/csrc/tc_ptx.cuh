@@ -33,6 +33,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
+// One lane of a converged warp.  elect.sync (rather than lane == 0) lets the compiler keep
+// warp-uniform operands of what the elected lane issues in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+    unsigned pred = 0;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+// Warp index the compiler can prove warp-uniform.
+__device__ __forceinline__ int uniform_warp_idx() { return __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0); }
+
 // Bounded wait; false when the bound was hit (the caller must bail out).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, int* error_flag) {
     for (unsigned i = 0; i < TC_SPIN_LIMIT; ++i) {
@@ -43,10 +57,25 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, int* e
     return false;
 }
 
+// The same for a whole (converged) warp: lane 0 polls, the others wait at the warp
+// barrier, so that a barrier word is polled by one thread per warp instead of 32.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, unsigned parity, int* error_flag) {
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, error_flag) ? 1 : 0;
+    __syncwarp();
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}
+
+// Contiguous bulk copy global -> shared (16-byte aligned both sides, size a multiple of 16).
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, unsigned bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, unsigned cols) {
@@ -144,6 +173,20 @@ static inline int make_map(CUtensorMap* map, const float* base, long long inner,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     EB_REQUIRE(r == CUDA_SUCCESS, EB200_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (inner %lld rows %lld stride %lld)",
                (int)r, inner, rows, row_stride);
+    return EB200_OK;
+}
+
+// General 3-D f32 tensor map without swizzle: dims/box innermost first, byte strides of dims 1 and 2.
+static inline int make_map_plain(CUtensorMap* map, const float* base, const cuuint64_t dims[3], const cuuint64_t strides[2],
+                                 const cuuint32_t box[3]) {
+    EncodeTiledFn fn = encode_fn();
+    EB_REQUIRE(fn, EB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    EB_REQUIRE(r == CUDA_SUCCESS, EB200_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (dims %llu %llu %llu box %u %u %u)", (int)r,
+               (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2], box[0], box[1], box[2]);
     return EB200_OK;
 }
 

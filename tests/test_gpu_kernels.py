@@ -522,6 +522,10 @@ def _conv_ref64(x, w_, b, pad, relu):
     (2, 3, 17, 19, 20, 3, 3, 1),       # zero padding, ragged M (not a multiple of 128) and Co (not of 32)
     (1, 8, 9, 9, 130, 5, 5, 2),        # Co spans two 128-wide column tiles, 5x5 window
     (2, 5, 6, 7, 7, 1, 1, 0),          # 1x1 window
+    (2, 64, 10, 12, 48, 3, 3, 1),      # channel-blocked k order (C % 32 == 0) with padding
+    (300, 1, 28, 28, 32, 3, 3, 0),     # 1585 row tiles: every persistent CTA walks several tiles
+    (32, 32, 40, 40, 140, 3, 3, 1),    # 400 x 2 tiles, channel-blocked, two column tiles
+    (1, 32, 16, 16, 8, 7, 7, 3),       # 49 taps: the table without tap bits
 ])
 def test_conv2d_implicit_gemm_matches_direct_convolution(dev, mode, tol, shape):
     n, c, h, wd, co, kh, kw, pad = shape
