@@ -391,6 +391,43 @@ def time_kernel(dev, kern, ins, outs, reps=5, warm=2):
     return dev.timer_end() / reps
 
 
+CONV_SHAPES = [("cnn_conv1_1x28x28_to_32", (4096, 1, 28, 28, 32, 3, 3, 0)),
+               ("cnn_conv2_32x13x13_to_64", (4096, 32, 13, 13, 64, 3, 3, 0)),
+               ("conv_64x56x56_to_128_pad1", (256, 64, 56, 56, 128, 3, 3, 1))]
+
+
+def conv_measurements(reg, dev, rng, quick=False, shapes=None, reps=None):
+    """conv2d as one implicit-GEMM kernel (bias + ReLU in the epilogue): the two
+    layers of config 4 at batch 4096 and one padded 64->128 layer, TF32 and 3xTF32.
+    Inputs are larger than L2 except where `shapes` asks for a small profiling case."""
+    from harp_b200 import desc as D
+    res = {}
+    for name, (n, c, h, w_, co, kh, kw, pad) in (shapes or CONV_SHAPES):
+        ho, wo = h + 2 * pad - kh + 1, w_ + 2 * pad - kw + 1
+        bx = reg.allocate_buffer(dev, [n * c * h * w_]); bw = reg.allocate_buffer(dev, [co * c * kh * kw])
+        bb = reg.allocate_buffer(dev, [co]); bo = reg.allocate_buffer(dev, [n * ho * wo * co])
+        bx.write_vec(rng.uniform(-1, 1, n * c * h * w_).astype(np.float32))
+        bw.write_vec(rng.uniform(-1, 1, co * c * kh * kw).astype(np.float32))
+        bb.write_vec(rng.uniform(-1, 1, co).astype(np.float32))
+        for mode, mname in ((D.GEMM_TF32, "tf32"), (D.GEMM_3XTF32, "3xtf32")):
+            kern = reg.compile_ast(dev, D.conv2d(n, c, h, w_, co, kh, kw, pad=pad, relu=True, mode=mode))
+            ms = time_kernel(dev, kern, [bx, bw, bb], [bo], reps=reps or (3 if quick else 10))
+            res[f"{name}_{mname}"] = {"impl": kern.impl, "ms": ms, "tflops": 2.0 * n * ho * wo * co * c * kh * kw / ms / 1e9,
+                                      "gbs_x_plus_out": 4.0 * (n * c * h * w_ + n * ho * wo * co) / ms / 1e6}
+        for b_ in (bx, bw, bb, bo):
+            b_.release()
+    return res
+
+
+def run_only_conv(args):
+    """`--only conv2d`: a small case of the convolution kernel alone (for profiler captures)."""
+    from harp_b200.backend import B200BackendRegistry
+    reg = B200BackendRegistry()
+    dev = reg.create_device(0)
+    res = conv_measurements(reg, dev, np.random.default_rng(5), shapes=[("cnn_conv2_batch2048", (2048, 32, 13, 13, 64, 3, 3, 0))], reps=2)
+    print(json.dumps({"only": "conv2d", "conv2d": res}))
+
+
 def extra_measurements(reg, dev, rank, world, local_rank, quick=False):
     """The other BASELINE configurations, timed with CUDA events on the library's
     stream: dense contractions (configs 1 and 5, rank 0 only), the MLP step
@@ -416,6 +453,7 @@ def extra_measurements(reg, dev, rank, world, local_rank, quick=False):
             for b_ in (ba, bb, bo):
                 b_.release()
         out["matmul"] = gemm
+        out["conv2d"] = conv_measurements(reg, dev, rng, quick)
         # config 3: MLP training step, whole step as one CUDA graph
         ex = B200Executor(dev, reg)
         loss, ps, grads, _ = W.mlp_graph(65536, 256)
@@ -474,8 +512,11 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extra", action="store_true", help="only config 2 (skip matmul / MLP / CNN measurements)")
+    ap.add_argument("--only", default="", choices=["", "conv2d"], help="run one small kernel case alone (profiler captures); prints no bench line")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.only == "conv2d":
+        run_only_conv(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_b200(args)
