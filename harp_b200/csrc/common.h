@@ -166,7 +166,7 @@ struct GemmShape {
 
 struct ConvShape {
     int N = 0, C = 0, H = 0, W = 0, Co = 0, KH = 0, KW = 0, pad = 0;
-    int relu = 0, mode = EB200_GEMM_3XTF32, has_bias = 0;
+    int relu = 0, mode = EB200_GEMM_3XTF32, has_bias = 0, flip = 0;
 };
 
 struct TransposeShape {

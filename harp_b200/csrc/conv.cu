@@ -59,8 +59,9 @@ struct ConvParams {
 enum { CV_CBLOCK = 0, CV_TABLE = 1 };
 
 // How a patch reaches shared memory:
-//   CV_LOAD_BULK  the tile is a whole image without padding: the patch (CB channel planes) is one
-//                 contiguous run of the input, moved by a single bulk copy;
+//   CV_LOAD_BULK  small images: the patch is the CB whole channel planes of the tile's image exactly as
+//                 they lie in global memory, one contiguous run moved by a single bulk copy; padding is
+//                 not materialised, the gather tests one bit per window tap instead;
 //   CV_LOAD_TMA   W % 4 == 0: one tiled TMA load of a {PW, PR, CB} box; rows and columns outside the
 //                 image (zero padding, the bottom of the last tile) come back as zeros.  The box starts
 //                 at a multiple of 4 columns (TMA wants 16-byte aligned starts), pcol columns left of
@@ -137,7 +138,7 @@ conv2d_igemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 const int r = q.mode == CV_CBLOCK ? k : k - c * q.taps;
                 const int kh = r / q.KW, kw = r - kh * q.KW;
                 e.x = c * cs + kh * rs + kw;
-                e.y = q.staged ? 1 : (kh | (kw << 16));
+                e.y = q.staged ? (q.load_mode == CV_LOAD_BULK ? (int)(1u << r) : 1) : (kh | (kw << 16));
             }
             ktab[k] = e;
         }
@@ -228,7 +229,7 @@ conv2d_igemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         float* dst = patch0 + (size_t)p * q.patch_floats;
                         mbar_expect_tx(&pfull[p], bytes);
                         const long long plane = (long long)tc.n * q.C + (long long)pp * q.CB;
-                        if (q.load_mode == CV_LOAD_BULK) bulk_load(dst, x + plane * q.H * q.W, bytes, &pfull[p]);
+                        if (q.load_mode == CV_LOAD_BULK) bulk_load(dst, x + plane * q.H * q.W, bytes, &pfull[p]);     // CH == H * W
                         else tma_load_3d(dst, &map_x, &pfull[p], tc.ow0 - q.pad - q.pcol, tc.oh0 - q.pad, (int)plane);
                     }
                 }
@@ -290,7 +291,17 @@ conv2d_igemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             const int oh = tc.oh0 + r_oh, ow = tc.ow0 + r_ow;
             const bool live = r_oh < q.Rt && oh < q.Ho && ow < q.Wo;
             // staged: offset of this row's window origin inside the patch; direct: pointer into x
-            const int base_r = live ? r_oh * q.PW + r_ow + q.pcol : 0;
+            int base_r = live ? r_oh * q.PW + r_ow + q.pcol : 0;
+            unsigned vm = live ? 0xffffffffu : 0u;            // staged: which taps of this row's window to read
+            if (q.staged && q.load_mode == CV_LOAD_BULK && live) {
+                // the patch is the raw image: the window origin may lie outside it, one bit per tap inside
+                base_r = (oh - q.pad) * q.W + (ow - q.pad);
+                vm = 0;
+                for (int kh = 0; kh < q.KH; ++kh)
+                    for (int kw = 0; kw < q.KW; ++kw)
+                        if ((unsigned)(oh + kh - q.pad) < (unsigned)q.H && (unsigned)(ow + kw - q.pad) < (unsigned)q.W)
+                            vm |= 1u << (kh * q.KW + kw);
+            }
             const float* xrow = x + ((long long)tc.n * q.C * q.H + (oh - q.pad)) * q.W + (ow - q.pad);
             for (int pp = 0; pp < q.patches_per_tile && ok; ++pp, pst = (pst + 1 == q.pstages ? 0 : pst + 1), pph ^= (pst == 0)) {
                 if (q.staged) {
@@ -308,14 +319,15 @@ conv2d_igemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     if (q.staged) {
                         if (q.mode == CV_CBLOCK) {
                             const float* p0 = pb + ktab[kk].x;
+                            const bool in = (vm >> (q.load_mode == CV_LOAD_BULK ? kk : 0)) & 1u;
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] = p0[i * q.CH];
+                            for (int i = 0; i < 32; ++i) v[i] = in ? p0[i * q.CH] : 0.0f;
                         } else {
                             const int2* kt = ktab + (pp * q.kb_per_patch + kk) * TC_BK;
 #pragma unroll
                             for (int i = 0; i < 32; ++i) {
                                 const int2 e = kt[i];
-                                v[i] = e.y ? pb[e.x] : 0.0f;
+                                v[i] = (vm & (unsigned)e.y) ? pb[e.x] : 0.0f;
                             }
                         }
                     } else if (q.mode == CV_CBLOCK) {
@@ -406,7 +418,7 @@ conv2d_igemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 // Weights [Co][K] -> [Co][Kpad] zero padded, in the kernel's k order, as tf32 hi (and lo) parts.
 __global__ void __launch_bounds__(256) conv_prep_weights_kernel(const float* __restrict__ w, float* __restrict__ hi,
                                                                 float* __restrict__ lo, int Co, int K, int Kpad, int three,
-                                                                int cblock_taps) {
+                                                                int cblock_taps, int taps, int flip) {
     const int total = Co * Kpad;
     for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < total; e += gridDim.x * blockDim.x) {
         const int co = e / Kpad, k = e - co * Kpad;
@@ -415,7 +427,12 @@ __global__ void __launch_bounds__(256) conv_prep_weights_kernel(const float* __r
             const int ci = k & 31, r = k >> 5, cb = r / cblock_taps, tap = r - cb * cblock_taps;
             src = (cb * 32 + ci) * cblock_taps + tap;
         }
-        const float v = k < K ? w[(long long)co * K + src] : 0.0f;
+        long long at = (long long)co * K + src;
+        if (flip && k < K) {     // w'[co][c][tap] = w[c][co][taps - 1 - tap]
+            const int c = src / taps, tap = src - c * taps;
+            at = ((long long)c * Co + co) * taps + (taps - 1 - tap);
+        }
+        const float v = k < K ? w[at] : 0.0f;
         if (three) {
             const float h = tf32_hi(v);
             hi[e] = h;
@@ -463,7 +480,7 @@ int launch_conv2d(Device* dev, const Plan& plan, const float* x, const float* w,
         const int total = c.Co * q.Kpad;
         const int blocks = std::min(dev->prop.multiProcessorCount * 4, (total + 255) / 256);
         conv_prep_weights_kernel<<<blocks, 256, 0, dev->stream>>>(w, whi, wlo, c.Co, q.K, q.Kpad, q.three_pass,
-                                                                  q.mode == CV_CBLOCK ? q.taps : 0);
+                                                                  q.mode == CV_CBLOCK ? q.taps : 0, q.taps, c.flip);
         count_launch();
     }
     const int bn = c.Co <= 32 ? 32 : (c.Co <= 64 ? 64 : 128);
@@ -491,9 +508,11 @@ int launch_conv2d(Device* dev, const Plan& plan, const float* x, const float* w,
     const bool aligned = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
     int load_limit = 2;
     if (const char* e = getenv("EB200_CONV_LOAD")) load_limit = atoi(e);
-    if (load_limit >= 1 && aligned && c.pad == 0 && q.tiles_w == 1 && q.tiles_h == 1 && ((long long)q.CB * c.H * c.W) % 4 == 0 &&
-        ((long long)c.C * c.H * c.W) % 4 == 0) {
-        q.load_mode = CV_LOAD_BULK;          // PR == H and PW == W here
+    if (load_limit >= 1 && aligned && q.taps <= 32 && ((long long)q.CB * c.H * c.W) % 4 == 0 && ((long long)c.C * c.H * c.W) % 4 == 0 &&
+        (long long)q.CB * c.H * c.W * 4 <= CV_MAX_PATCH_BYTES) {
+        q.load_mode = CV_LOAD_BULK;          // whole channel planes, unpadded
+        q.PR = c.H;
+        q.PW = c.W;
     } else if (load_limit >= 2 && aligned && c.W % 4 == 0 && q.CB <= 256 && q.PR <= 256 && q.PW + 6 <= 256) {
         q.load_mode = CV_LOAD_TMA;
         q.pcol = (4 - c.pad % 4) % 4;

@@ -151,6 +151,7 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
         c.N = (int)d->shape[0]; c.C = (int)d->shape[1]; c.H = (int)d->shape[2]; c.W = (int)d->shape[3];
         c.Co = (int)d->shape[4]; c.KH = (int)d->shape[5]; c.KW = (int)d->shape[6]; c.pad = (int)d->shape[7];
         c.relu = (d->flags & 64) ? 1 : 0;
+        c.flip = (d->flags & 128) ? 1 : 0;
         c.has_bias = d->n_inputs == 3;
         c.mode = d->gemm_mode == EB200_GEMM_TF32 ? EB200_GEMM_TF32 : EB200_GEMM_3XTF32;
         EB_REQUIRE(conv2d_supported(c), EB200_ERR_UNSUPPORTED, "conv2d shape is not served by the implicit-GEMM kernel (C*KH*KW <= 2048, stride 1)");
@@ -177,7 +178,7 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
         pl.launches = 2;
         pl.algo_flops = 2 * M * c.Co * K;
         pl.algo_bytes = 4 * ((long long)c.N * c.C * c.H * c.W + (long long)c.Co * K + M * c.Co + (c.has_bias ? c.Co : 0));
-        snprintf(pl.name, sizeof(pl.name), "conv2d_igemm_%s", c.mode == EB200_GEMM_TF32 ? "tf32" : "3xtf32");
+        snprintf(pl.name, sizeof(pl.name), "conv2d_igemm_%s%s", c.mode == EB200_GEMM_TF32 ? "tf32" : "3xtf32", c.flip ? "_dgrad" : "");
         return EB200_OK;
     }
     EB_REQUIRE(d->ndim >= 0 && d->ndim <= EB200_MAX_DIMS, EB200_ERR_INVALID, "rank %d out of range", d->ndim);

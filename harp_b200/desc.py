@@ -37,6 +37,7 @@ DTYPE_NP = {F32: "float32", BOOL: "uint8", I32: "int32", I64: "int64"}
 K_ELEMENTWISE, K_REDUCE, K_COPY, K_SCATTER, K_SGD, K_CONV2D = 0, 1, 2, 3, 4, 5
 KCLASS_PREFIX = {K_ELEMENTWISE: "E", K_REDUCE: "R", K_COPY: "C", K_SCATTER: "S", K_SGD: "U", K_CONV2D: "CONV"}
 FLAG_RELU = 64
+FLAG_WFLIP = 128
 
 # eb200_reduce_op
 R_NONE, R_SUM, R_MAX, R_MIN, R_PROD = 0, 1, 2, 3, 4
@@ -359,14 +360,16 @@ def copy(shape, src: Operand, out: Optional[Operand] = None) -> KernelDesc:
     return KernelDesc(K_COPY, shape, [src], out or contiguous(shape, src.dtype), None)
 
 
-def conv2d(n, c, h, w, co, kh, kw, pad=0, bias=True, relu=False, mode: int = GEMM_DEFAULT) -> KernelDesc:
+def conv2d(n, c, h, w, co, kh, kw, pad=0, bias=True, relu=False, mode: int = GEMM_DEFAULT, flip=False) -> KernelDesc:
     """functional::conv2d (crates/nn/src/functional/conv.rs:113-184) as one kernel:
     x [N,C,H,W], weight [Co,C,KH,KW] (, bias [Co]) -> [N*Ho*Wo, Co] row-major, the
-    buffer the reference's GEMM step produces (its result is a permuted view of it)."""
+    buffer the reference's GEMM step produces (its result is a permuted view of it).
+    `flip`: the weight buffer holds [C, Co, KH, KW] (the forward layer's weights) and is
+    read transposed and flipped: the input-gradient convolution."""
     ho, wo = h + 2 * pad - kh + 1, w + 2 * pad - kw + 1
     z8 = [0] * 8
     ins = [Operand(z8, 0, F32, n * c * h * w), Operand(z8, 0, F32, co * c * kh * kw)]
     if bias:
         ins.append(Operand(z8, 0, F32, co))
     return KernelDesc(K_CONV2D, [n, c, h, w, co, kh, kw, pad], ins, Operand(z8, 0, F32, n * ho * wo * co),
-                      None, gemm_mode=mode, flags=FLAG_RELU if relu else 0)
+                      None, gemm_mode=mode, flags=(FLAG_RELU if relu else 0) | (FLAG_WFLIP if flip else 0))

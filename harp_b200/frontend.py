@@ -483,23 +483,54 @@ class Tensor:
         return y.reshape(n, ho, wo, co).permute(0, 3, 1, 2)
 
     def conv2d_fused(self, weight: "Tensor", bias: Optional["Tensor"] = None, padding=0, relu=False,
-                     mode: int = D.GEMM_DEFAULT) -> "Tensor":
+                     mode: int = D.GEMM_DEFAULT, _flip=False) -> "Tensor":
         """The same function as ``conv2d`` (stride 1) as ONE kernel: the window
         tensor the reference materialises twice (conv.rs:150-166) is gathered on
         the fly inside an implicit GEMM, bias and ReLU run in its epilogue.
-        Forward only: the training graphs keep the composed spelling, whose
-        backward the tape derives."""
-        assert not (self.requires_grad or weight.requires_grad or (bias is not None and bias.requires_grad)), \
-            "conv2d_fused is an inference kernel"
+
+        Gradients: the input gradient is the same kernel over the transposed,
+        flipped weights (what the reference reaches through unfold's VJP, a
+        scatter-add: src/grad/rules.rs:40-53); the weight gradient contracts the
+        output gradient with the unfolded input exactly as the composed spelling
+        does; the bias gradient is a column sum."""
         n, c, h, wd = self.shape
-        co, c2, kh, kw = weight.shape
+        if _flip:
+            c2, co, kh, kw = weight.shape
+        else:
+            co, c2, kh, kw = weight.shape
         assert c2 == c
         ho, wo = h + 2 * padding - kh + 1, wd + 2 * padding - kw + 1
-        ops = [t if t.view.is_contiguous() and not t.view.bounds else t.contiguous()
-               for t in ([self, weight] + ([bias] if bias is not None else []))]
-        node = Node("conv", (n * ho * wo, co), [(t.node, t.view) for t in ops], name="conv2d")
-        node.conv = (n, c, h, wd, co, kh, kw, padding, bool(relu), mode)
-        return Tensor(node).reshape(n, ho, wo, co).permute(0, 3, 1, 2)
+        ops = [t.contiguous() for t in ([self, weight] + ([bias] if bias is not None else []))]
+        node = Node("conv", (n, ho, wo, co), [(t.node, t.view) for t in ops], name="conv2d")
+        node.conv = (n, c, h, wd, co, kh, kw, padding, bool(relu), mode, bool(_flip))
+        out = Tensor(node)                                    # [N, Ho, Wo, Co]
+        if any(t.requires_grad for t in ops):
+            assert not relu and not _flip, "the fused ReLU and the gradient form are forward only"
+            assert kh == kw and kh - 1 - padding >= 0, "input gradient as a convolution needs a square window and pad <= k-1"
+            xc, wc = (Tensor(t.node, t.view) for t in ops[:2])     # detached: the backward graph is not differentiated again
+            m, kk = n * ho * wo, c * kh * kw
+            flat = {}
+
+            def g2(g):                                        # [M, Co], materialised once for both users
+                if id(g) not in flat:
+                    flat[id(g)] = g.reshape(m, co)
+                return flat[id(g)]
+
+            def back_x(g):
+                g4 = g.permute(0, 3, 1, 2).contiguous()       # NCHW; no copy when g is a permuted NCHW gradient
+                return g4.conv2d_fused(wc, None, padding=kh - 1 - padding, mode=mode, _flip=True)
+
+            def back_w(g):
+                xp = xc.pad([(0, 0), (0, 0), (padding, padding), (padding, padding)])
+                cols = xp.unfold([2, 3], [kh, kw], [1, 1], [1, 1]).permute(0, 2, 3, 1, 4, 5).contiguous().reshape(m, kk)
+                gw = (g2(g).unsqueeze(2).expand(m, co, kk) * cols.unsqueeze(1).expand(m, co, kk)).sum(0)
+                return gw.reshape(co, c, kh, kw)
+
+            parents = [(ops[0], back_x), (ops[1], back_w)]
+            if bias is not None:
+                parents.append((ops[2], lambda g: g2(g).sum(0)))
+            self._track(out, *parents)
+        return out.permute(0, 3, 1, 2)
 
     def max_pool2d(self, k: int) -> "Tensor":
         """crates/nn/src/functional/pool.rs:117-160: unfold windows, max over them."""
@@ -686,12 +717,12 @@ def _lower(k: _K, loc) -> D.KernelDesc:
         st[k.axis] = 0
         return D.reduce(list(k.shape), ins, k.expr, k.reduce_op, k.axis, out=D.Operand(st, out_off, D.F32, out_numel))
     if k.kind == "conv":
-        n, c, h, wd, co, kh, kw, pad, relu, mode = k.conv
+        n, c, h, wd, co, kh, kw, pad, relu, mode, flip = k.conv
         z8 = [0] * 8
         for op in ins:
             op.strides = z8
         return D.KernelDesc(D.K_CONV2D, [n, c, h, wd, co, kh, kw, pad], ins, D.Operand(z8, out_off, D.F32, out_numel),
-                            None, gemm_mode=mode, flags=D.FLAG_RELU if relu else 0, name=k.name)
+                            None, gemm_mode=mode, flags=(D.FLAG_RELU if relu else 0) | (D.FLAG_WFLIP if flip else 0), name=k.name)
     if k.kind == "fold":
         assert out_off == 0, "a scatter output owns its buffer (it is zero-filled as a whole)"
         return D.KernelDesc(D.K_SCATTER, k.shape, ins, k.out_view.operand(k.out_numel, D.F32), None, name=k.name)

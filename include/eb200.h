@@ -66,7 +66,11 @@ typedef enum {
                               * shape = {N, C, H, W, Co, KH, KW, pad}; inputs x [N,C,H,W], w [Co,C,KH,KW] and
                               * optionally bias [Co], all contiguous; output [N*Ho*Wo, Co] row-major (the buffer
                               * the reference's GEMM step writes before its final permute view); stride 1;
-                              * flags bit 6 = ReLU in the epilogue; gemm_mode picks TF32 / 3xTF32 */
+                              * flags bit 6 = ReLU in the epilogue; flags bit 7 = the weight buffer is the FORWARD
+                              * layer's [C, Co, KH, KW] and is read transposed and flipped, w'[co][c][kh][kw] =
+                              * w[c][co][KH-1-kh][KW-1-kw]: with pad' = KH-1-pad this is the input gradient of the
+                              * forward convolution (the VJP eclat derives through fold, src/grad/rules.rs:40-53);
+                              * gemm_mode picks TF32 / 3xTF32 */
 } eb200_kclass;
 
 /* ReduceOp (src/graph/node.rs:29-77). */

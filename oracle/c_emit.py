@@ -261,7 +261,11 @@ def emit_kernel_c(k: D.KernelDesc, fn_name: str = "kernel", openmp: bool = False
         xv = f"buf0[{o[0]} + ((((ridx0 * {c}) + ridx4) * {h} + {ih}) * {w_} + {iw})]"
         if pad:
             xv = f"((((!({ih} < 0)) && ({ih} < {h})) && ((!({iw} < 0)) && ({iw} < {w_}))) ? {xv} : 0.0f)"
-        line(f"acc = (acc + ({xv} * buf1[{o[1]} + ((((ridx3 * {c}) + ridx4) * {kh} + ridx5) * {kw} + ridx6)]));")
+        if k.flags & D.FLAG_WFLIP:      # forward weights [C, Co, KH, KW] read transposed and flipped
+            wv = f"buf1[{o[1]} + ((((ridx4 * {co}) + ridx3) * {kh} + ({kh - 1} + (-1 * ridx5))) * {kw} + ({kw - 1} + (-1 * ridx6)))]"
+        else:
+            wv = f"buf1[{o[1]} + ((((ridx3 * {c}) + ridx4) * {kh} + ridx5) * {kw} + ridx6)]"
+        line(f"acc = (acc + ({xv} * {wv}));")
         for _ in range(3):
             close_loop()
         val = f"(acc + buf2[{o[2]} + ridx3])" if len(k.inputs) == 3 else "acc"

@@ -562,3 +562,31 @@ def test_conv2d_fused_front_end_equals_composed_spelling(dev):
             assert [d.kclass for d in p.kernel_descs()] == [D.K_CONV2D, D.K_COPY]
     assert outs[0].shape == (3, 6, 12, 12)
     assert np.abs(outs[0] - outs[1]).max() <= 1e-4
+
+
+@pytest.mark.parametrize("mode,tol", [(D.GEMM_TF32, 1e-2), (D.GEMM_3XTF32, 1e-5)])
+@pytest.mark.parametrize("shape", [(3, 32, 13, 13, 64, 3, 0), (2, 3, 9, 10, 5, 3, 1), (2, 8, 12, 12, 16, 5, 2)])
+def test_conv2d_input_gradient_is_the_same_kernel_over_flipped_weights(dev, mode, tol, shape):
+    """dX of y = conv2d(x, w, pad) is conv2d(dy, w', k-1-pad) with w'[c][co][kh][kw] =
+    w[co][c][K-1-kh][K-1-kw] (descriptor flag 128 reads the forward weights that way):
+    checked against the float64 adjoint of the forward convolution."""
+    n, c, h, wd, co, k, pad = shape
+    ho, wo = h + 2 * pad - k + 1, wd + 2 * pad - k + 1
+    g, w_ = rnd([n, co, ho, wo], 70), rnd([co, c, k, k], 71)
+    kd = D.conv2d(n, co, ho, wo, c, k, k, pad=k - 1 - pad, bias=False, flip=True, mode=mode)
+    got, kern = run_gpu(dev, kd, [g, w_])
+    assert kern.impl.endswith("_dgrad"), kern.impl
+    # adjoint in float64: scatter every dy element times its window of weights
+    ref = np.zeros((n, c, h + 2 * pad, wd + 2 * pad)); scale = np.zeros_like(ref)
+    for i in range(k):
+        for j in range(k):
+            t = np.einsum("nohw,oc->nchw", g.astype(np.float64), w_[:, :, i, j].astype(np.float64))
+            ta = np.einsum("nohw,oc->nchw", np.abs(g).astype(np.float64), np.abs(w_[:, :, i, j]).astype(np.float64))
+            ref[:, :, i:i + ho, j:j + wo] += t; scale[:, :, i:i + ho, j:j + wo] += ta
+    sl = (slice(None), slice(None), slice(pad, pad + h), slice(pad, pad + wd))
+    ref, scale = ref[sl].transpose(0, 2, 3, 1).reshape(-1, c), scale[sl].transpose(0, 2, 3, 1).reshape(-1, c)
+    err = np.abs(got.reshape(ref.shape) - ref)
+    assert (err <= tol * scale + 1e-30).all(), float((err / np.maximum(scale, 1e-30)).max())
+    cpu = O.run(kd, [g, w_]).reshape(ref.shape)
+    assert (np.abs(got.reshape(ref.shape) - cpu) <= 2 * tol * scale + 1e-30).all()
+    dev.synchronize()
