@@ -90,6 +90,8 @@ struct KParams {
     KInsn prog[KMAX_INSNS];
     float consts[KMAX_CONSTS];
     const float* cptr[KMAX_CONSTS];  // non-null: constant slot is read from a one-element tensor
+    unsigned dmul[KMAX_DIMS];        // exact division of a 31-bit index by shape[d]: (n * dmul) >> dshr
+    unsigned dshr[KMAX_DIMS];
     int tuning;                      // copy of the descriptor's flags
     int _pad1;
     int* error_flag;                 // host-mapped word a kernel raises when a bounded wait runs out (may be null)
@@ -149,6 +151,7 @@ enum Impl {
     IMPL_GEMM_SIMT,       // dense contraction, fp32 FFMA tiles (exact-f32 fallback)
     IMPL_GEMM_TC,         // dense contraction, tcgen05 TF32 / 3xTF32
     IMPL_CONV2D,          // convolution as implicit GEMM on the tensor cores
+    IMPL_GEMM_TALL,       // one-tile output, reduction over millions of rows (small-layer weight gradients)
 };
 
 struct GemmShape {
@@ -184,6 +187,7 @@ struct Plan {
     int threads_per_row = 0;  // REDUCE_INNER: 1, 32 or 256
     GemmShape gemm;
     ConvShape conv;
+    bool narrow = false;          // outer reduce with few kept elements: column threads x row lanes
     TransposeShape tr;
     int64_t scratch_bytes = 0;
     int64_t algo_bytes = 0, algo_flops = 0;
@@ -219,6 +223,8 @@ int launch_splitk_reduce(Device* dev, const GemmShape& g, const float* partials,
 bool gemm_tc_supported(const GemmShape& g);
 void gemm_tc_scratch(const GemmShape& g, long long* a_span, long long* b_span);
 int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b, float* c, void* scratch);
+bool gemm_tall_supported(const GemmShape& g);
+int launch_gemm_tall(Device* dev, const Plan& plan, const float* a, const float* b, float* c, void* scratch);
 bool conv2d_supported(const ConvShape& c);
 long long conv2d_scratch_floats(const ConvShape& c);
 int launch_conv2d(Device* dev, const Plan& plan, const float* x, const float* w, const float* bias, float* out, void* scratch);

@@ -78,21 +78,37 @@ __global__ void __launch_bounds__(256) ew_kernel(const __grid_constant__ KParams
             }
         }
     } else {
-        const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-        for (long long e = tid; e < p.total; e += stride) {
-            long long idx[KMAX_DIMS];
-            decompose<ND>(p, e, idx);
-            float in[KMAX_IN][1];
+        // scalar path: EW_U independent elements per thread in flight (the loads of all of
+        // them are issued before the first is evaluated); a CTA owns EW_U consecutive
+        // 256-element segments per iteration
+        for (long long e0 = ((long long)blockIdx.x * EW_U) * blockDim.x + threadIdx.x; e0 < p.total; e0 += EW_U * stride) {
+            float in[EW_U][KMAX_IN][1];
+            long long oa[EW_U];
 #pragma unroll
-            for (int i = 0; i < (F::kCompiled ? n : KMAX_IN); ++i) {
-                if (i >= n) break;
-                const KOperand& o = p.in[i];
-                if (o.n_bounds && !bounds_ok(p, o, idx)) in[i][0] = o.pad;
-                else in[i][0] = load_elem(o, operand_index<ND>(p, o, idx));
+            for (int u = 0; u < EW_U; ++u) {
+                const long long e = e0 + (long long)u * blockDim.x;
+                if (e < p.total) {
+                    long long idx[KMAX_DIMS];
+                    decompose<ND>(p, e, idx);
+#pragma unroll
+                    for (int i = 0; i < (F::kCompiled ? n : KMAX_IN); ++i) {
+                        if (i >= n) break;
+                        const KOperand& o = p.in[i];
+                        if (o.n_bounds && !bounds_ok(p, o, idx)) in[u][i][0] = o.pad;
+                        else in[u][i][0] = load_elem(o, operand_index<ND>(p, o, idx));
+                    }
+                    oa[u] = operand_index<ND>(p, p.out, idx);
+                }
             }
-            float r[1];
-            F::template eval<1>(p, in, r, cl);
-            store_elem(p.out, operand_index<ND>(p, p.out, idx), r[0]);
+#pragma unroll
+            for (int u = 0; u < EW_U; ++u) {
+                const long long e = e0 + (long long)u * blockDim.x;
+                if (e < p.total) {
+                    float r[1];
+                    F::template eval<1>(p, in[u], r, cl);
+                    store_elem(p.out, oa[u], r[0]);
+                }
+            }
         }
     }
 }
@@ -101,16 +117,17 @@ template <class F>
 static int launch_one(Device* dev, const KParams& p) {
     long long work = p.vec == 4 ? (p.total >> 2) : p.total;
     if (work <= 0) return EB200_OK;
-    long long per_block = 256LL * (p.vec == 4 ? EW_U : 1);
+    long long per_block = 256LL * EW_U;
     long long blocks = (work + per_block - 1) / per_block;
     long long cap = (long long)dev->prop.multiProcessorCount * 32;
     if (blocks > cap) blocks = cap;
-    const int nd = (p.total < (1LL << 31) && p.ndim <= 3) ? p.ndim : 0;
+    const int nd = (p.total < (1LL << 31) && p.ndim <= 4) ? p.ndim : 0;
     const unsigned g = (unsigned)blocks;
     switch (nd) {
         case 1: ew_kernel<F, 1><<<g, 256, 0, dev->stream>>>(p); break;
         case 2: ew_kernel<F, 2><<<g, 256, 0, dev->stream>>>(p); break;
         case 3: ew_kernel<F, 3><<<g, 256, 0, dev->stream>>>(p); break;
+        case 4: ew_kernel<F, 4><<<g, 256, 0, dev->stream>>>(p); break;
         default: ew_kernel<F, 0><<<g, 256, 0, dev->stream>>>(p); break;
     }
     count_launch();

@@ -109,6 +109,77 @@ int launch_splitk_reduce(Device* dev, const GemmShape& g, const float* partials,
     return EB200_OK;
 }
 
+// Tall-and-skinny weight gradients: C[m][n] = sum_k A[k][m] * B[k][n] with m, n <= 32 and k in
+// the millions (conv1 of config 4: dW[32][9] over 2.8 M output positions).  The output is one
+// tile, so the generic kernels leave the machine idle; here every warp of the grid owns a
+// contiguous run of k: lane = m (one coalesced row of A per k), B's row is read with
+// warp-uniform loads, n accumulators live in registers.  Warps are summed through shared
+// memory in warp order, CTAs through the split-K partial buffer in CTA order (deterministic).
+template <int NB>
+__global__ void __launch_bounds__(256) gemm_tall_kernel(const __grid_constant__ GemmShape g, const float* __restrict__ A,
+                                                        const float* __restrict__ B, float* __restrict__ P) {
+    __shared__ float part[8][32][NB + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long warps = (long long)gridDim.x * 8;
+    const long long per = (g.k + warps - 1) / warps;
+    const long long k0 = ((long long)blockIdx.x * 8 + warp) * per;
+    const long long k1 = k0 + per < g.k ? k0 + per : g.k;
+    const bool mine = lane < g.m;
+    const int n = (int)g.n;
+    float acc[NB];
+#pragma unroll
+    for (int j = 0; j < NB; ++j) acc[j] = 0.0f;
+    const float* ap = A + g.a_off + (mine ? lane : 0);
+    const float* bp = B + g.b_off;
+    long long k = k0;
+    for (; k + 4 <= k1; k += 4) {
+        float a[4], b[4][NB];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            a[u] = mine ? __ldg(ap + (k + u) * g.a_sk) : 0.0f;
+#pragma unroll
+            for (int j = 0; j < NB; ++j) b[u][j] = j < n ? __ldg(bp + (k + u) * g.b_sk + j) : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int j = 0; j < NB; ++j) acc[j] = fmaf(a[u], b[u][j], acc[j]);
+    }
+    for (; k < k1; ++k) {
+        const float a = mine ? __ldg(ap + k * g.a_sk) : 0.0f;
+#pragma unroll
+        for (int j = 0; j < NB; ++j) acc[j] = fmaf(a, j < n ? __ldg(bp + k * g.b_sk + j) : 0.0f, acc[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < NB; ++j) part[warp][lane][j] = acc[j];
+    __syncthreads();
+    for (int e = threadIdx.x; e < (int)g.m * n; e += 256) {
+        const int row = e / n, col = e - row * n;
+        float sum = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) sum += part[w][row][col];
+        P[(long long)blockIdx.x * g.m * g.n + e] = sum;
+    }
+}
+
+bool gemm_tall_supported(const GemmShape& g) {
+    return g.batch == 1 && g.m >= 1 && g.m <= 32 && g.n >= 1 && g.n <= 32 && g.a_sm == 1 && g.b_sn == 1 && g.k >= 16384;
+}
+
+int launch_gemm_tall(Device* dev, const Plan& plan, const float* a, const float* b, float* c, void* scratch) {
+    const GemmShape& g = plan.gemm;
+    EB_REQUIRE(scratch && g.splits >= 1, EB200_ERR_INVALID, "tall GEMM launched without scratch");
+    float* partials = reinterpret_cast<float*>(scratch) + g.partial_off;
+    const unsigned grid = (unsigned)g.splits;
+    if (g.n <= 4) gemm_tall_kernel<4><<<grid, 256, 0, dev->stream>>>(g, a, b, partials);
+    else if (g.n <= 8) gemm_tall_kernel<8><<<grid, 256, 0, dev->stream>>>(g, a, b, partials);
+    else if (g.n <= 16) gemm_tall_kernel<16><<<grid, 256, 0, dev->stream>>>(g, a, b, partials);
+    else gemm_tall_kernel<32><<<grid, 256, 0, dev->stream>>>(g, a, b, partials);
+    count_launch();
+    EB_CHECK_CUDA(cudaGetLastError());
+    return launch_splitk_reduce(dev, g, partials, c);
+}
+
 int launch_gemm_simt(Device* dev, const Plan& plan, const float* a, const float* b, float* c, void* scratch) {
     const GemmShape& g = plan.gemm;
     if (g.m <= 0 || g.n <= 0 || g.batch <= 0) return EB200_OK;

@@ -23,7 +23,7 @@ __device__ __forceinline__ void decompose(const KParams& p, long long e, long lo
             if (d == skip) { idx[d] = 0; continue; }
             if (d == 0 && skip != 0) { idx[0] = r; break; }
             const unsigned s = (unsigned)p.shape[d];
-            const unsigned q = r / s;
+            const unsigned q = (unsigned)(((unsigned long long)r * p.dmul[d]) >> p.dshr[d]);     // r / s, exact for r < 2^31
             idx[d] = r - q * s;
             r = q;
         }
@@ -33,7 +33,7 @@ __device__ __forceinline__ void decompose(const KParams& p, long long e, long lo
         for (int d = KMAX_DIMS - 1; d >= 0; --d) {
             if (d >= p.ndim || d == skip) { idx[d] = 0; continue; }
             const unsigned s = (unsigned)p.shape[d];
-            const unsigned q = r / s;
+            const unsigned q = (unsigned)(((unsigned long long)r * p.dmul[d]) >> p.dshr[d]);
             idx[d] = r - q * s;
             r = q;
         }

@@ -291,6 +291,14 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
     p.n_in = d->n_inputs;
     p.total = total;
     for (int j = 0; j < nk; ++j) p.shape[j] = shape[j];
+    // magic numbers for exact n / shape[j], n < 2^31: M = ceil(2^(31+l) / s) < 2^32 with l = ceil(log2 s)
+    for (int j = 0; j < KMAX_DIMS; ++j) {
+        const unsigned long long sj = j < nk && shape[j] >= 1 && shape[j] < (1LL << 31) ? (unsigned long long)shape[j] : 1ULL;
+        int l = 0;
+        while ((1ULL << l) < sj) ++l;
+        p.dmul[j] = (unsigned)((((1ULL << (31 + l)) + sj - 1) / sj));
+        p.dshr[j] = (unsigned)(31 + l);
+    }
     p.raxis = raxis;
     p.rop = d->reduce_op;
     p.rlen = raxis >= 0 ? shape[raxis] : 1;
@@ -526,6 +534,11 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
                     // name: arithmetic mode, then which dim of A and of B is contiguous (k, m / k, n)
                     snprintf(pl.name, sizeof(pl.name), "gemm_tcgen05_%s_%c%c%s", three ? "3xtf32" : "tf32",
                              g.a_sk == 1 ? 'k' : 'm', g.b_sk == 1 ? 'k' : 'n', g.splits > 1 ? "_splitk" : "");
+                } else if (!force_simt && gemm_tall_supported(g) && (d->flags & 16) == 0) {
+                    pl.impl = IMPL_GEMM_TALL;
+                    g.splits = 2 * sm_count;          // one partial per CTA, two CTAs per SM
+                    g.k_chunk = 0;
+                    snprintf(pl.name, sizeof(pl.name), "gemm_tall_f32_splitk");
                 } else {
                     pl.impl = IMPL_GEMM_SIMT;
                     snprintf(pl.name, sizeof(pl.name), "gemm_simt_f32%s", g.splits > 1 ? "_splitk" : "");
@@ -575,10 +588,14 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
                 // enough thread blocks to fill the machine: split the reduce dim
                 long long threads = p.kept / p.vec;
                 long long blocks = (threads + 255) / 256;
+                // few kept elements: a CTA is (kept / 4) column threads x row lanes (flag 16 keeps the plain form)
+                pl.narrow = p.vec == 4 && threads <= 128 && p.rlen >= 256 && !(d->flags & 16);
                 if (blocks < 4LL * sm_count && p.rlen >= 64) {
                     // one full wave: 4 resident CTAs per SM, all with equal work
                     long long want = (4LL * sm_count) / std::max(1LL, blocks);
-                    int s = (int)std::max(1LL, std::min(want, std::min(p.rlen / 16, 1024LL)));
+                    // narrow: every CTA needs enough rows for its lanes (4 steps of 4 rows each at least)
+                    const long long min_rows = pl.narrow ? 16LL * (256 / std::max(1LL, threads)) : 16;
+                    int s = (int)std::max(1LL, std::min(want, std::min(p.rlen / min_rows, 1024LL)));
                     if (s > 1) {
                         long long chunk = (p.rlen + s - 1) / s;
                         s = (int)((p.rlen + chunk - 1) / chunk);
@@ -588,7 +605,8 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
                         pl.launches = 2;
                     }
                 }
-                snprintf(pl.name, sizeof(pl.name), "reduce_outer_v%d%s", p.vec, p.splits > 1 ? "_split" : "");
+                if (p.splits <= 1) p.chunk = p.rlen;
+                snprintf(pl.name, sizeof(pl.name), "reduce_outer_%sv%d%s", pl.narrow ? "narrow_" : "", p.vec, p.splits > 1 ? "_split" : "");
             }
             break;
         }

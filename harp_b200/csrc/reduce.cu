@@ -404,6 +404,92 @@ __global__ void __launch_bounds__(256) reduce_outer_kernel(const __grid_constant
     }
 }
 
+// The same reduce for NARROW outputs (at most 128 vectors of 4 kept elements, e.g. a bias
+// gradient [rows, 32] -> [32]): with a thread per vector only a few threads of a CTA
+// would work.  Here the CTA's 256 threads are (kept / 4) column threads x row lanes;
+// a warp reads whole consecutive rows (coalesced), every lane folds the rows
+// lane, lane + L, ... of the CTA's row chunk, and the lanes are combined through
+// shared memory in lane order (deterministic).
+template <class F>
+__global__ void __launch_bounds__(256) reduce_outer_narrow_kernel(const __grid_constant__ KParams p, float* __restrict__ scratch) {
+    constexpr int NI = F::kCompiled ? F::kNin : KMAX_IN;
+    const int ra = p.raxis;
+    const int n = F::nin(p);
+    float cl[F::kNconst];
+    load_consts<F>(p, cl);
+    __shared__ float part[256][4];
+    const int nwork = (int)(p.kept >> 2);
+    const int lanes = 256 / nwork;
+    const int lane_r = threadIdx.x / nwork, tc = threadIdx.x - lane_r * nwork;
+    const int split = blockIdx.y;
+    const long long r0 = (long long)split * p.chunk;
+    long long r1 = r0 + p.chunk;
+    if (r1 > p.rlen) r1 = p.rlen;
+    float a4[4];
+#pragma unroll
+    for (int v = 0; v < 4; ++v) a4[v] = red_identity(p.rop);
+    long long idx[KMAX_DIMS];
+    decompose(p, (long long)tc << 2, idx, ra);
+    if (lane_r < lanes) {
+        const int inner = p.ndim - 1;
+        const float* bp[NI];
+        long long rs[NI];
+        bool isvec[NI];
+#pragma unroll
+        for (int i = 0; i < NI; ++i) {
+            if (i >= n) break;
+            rs[i] = p.in[i].strides[ra] * lanes;
+            bp[i] = reinterpret_cast<const float*>(p.in[i].ptr) + operand_index(p, p.in[i], idx) + (r0 + lane_r) * p.in[i].strides[ra];
+            isvec[i] = p.in[i].strides[inner] == 1;
+        }
+        long long r = r0 + lane_r;
+        for (; r + (long long)(RO_U - 1) * lanes < r1; r += (long long)RO_U * lanes) {
+            float in[RO_U][NI][4];
+#pragma unroll
+            for (int u = 0; u < RO_U; ++u) {
+#pragma unroll
+                for (int i = 0; i < NI; ++i) {
+                    if (i >= n) break;
+                    if (isvec[i]) ldg4(bp[i], in[u][i]);
+                    else splat4(__ldg(bp[i]), in[u][i]);
+                    bp[i] += rs[i];
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < RO_U; ++u) {
+                float v4[4];
+                F::template eval<4>(p, in[u], v4, cl);
+#pragma unroll
+                for (int v = 0; v < 4; ++v) a4[v] = red_combine(p.rop, a4[v], v4[v]);
+            }
+        }
+        for (; r < r1; r += lanes) {
+            float in[NI][4], v4[4];
+#pragma unroll
+            for (int i = 0; i < NI; ++i) {
+                if (i >= n) break;
+                if (isvec[i]) ldg4(bp[i], in[i]);
+                else splat4(__ldg(bp[i]), in[i]);
+                bp[i] += rs[i];
+            }
+            F::template eval<4>(p, in, v4, cl);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) a4[v] = red_combine(p.rop, a4[v], v4[v]);
+        }
+    }
+#pragma unroll
+    for (int v = 0; v < 4; ++v) part[threadIdx.x][v] = a4[v];
+    __syncthreads();
+    if (lane_r == 0) {
+        for (int l = 1; l < lanes; ++l)
+#pragma unroll
+            for (int v = 0; v < 4; ++v) a4[v] = red_combine(p.rop, a4[v], part[l * nwork + tc][v]);
+        const float4 res = make_float4(a4[0], a4[1], a4[2], a4[3]);
+        if (p.splits > 1) *reinterpret_cast<float4*>(scratch + (long long)split * p.kept + ((long long)tc << 2)) = res;
+        else *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out.ptr) + operand_index(p, p.out, idx)) = res;
+    }
+}
+
 // Folds scratch partials [splits][kept] into the output operand.
 __global__ void __launch_bounds__(256) reduce_finish_kernel(const __grid_constant__ KParams p, const float* __restrict__ scratch) {
     const long long stride = (long long)gridDim.x * blockDim.x;
@@ -454,7 +540,8 @@ static int launch_one(Device* dev, const Plan& plan, const KParams& p, float* sc
         long long cap = (long long)sms * 32;
         if (bx > cap) bx = cap;
         dim3 grid((unsigned)bx, (unsigned)p.splits);
-        reduce_outer_kernel<F><<<grid, 256, 0, dev->stream>>>(p, scratch);
+        if (plan.narrow) reduce_outer_narrow_kernel<F><<<dim3(1, (unsigned)p.splits), 256, 0, dev->stream>>>(p, scratch);
+        else reduce_outer_kernel<F><<<grid, 256, 0, dev->stream>>>(p, scratch);
     }
     count_launch();
     EB_CHECK_CUDA(cudaGetLastError());

@@ -532,11 +532,51 @@ class Tensor:
             self._track(out, *parents)
         return out.permute(0, 3, 1, 2)
 
-    def max_pool2d(self, k: int) -> "Tensor":
-        """crates/nn/src/functional/pool.rs:117-160: unfold windows, max over them."""
+    def max_pool2d_unfold(self, k: int) -> "Tensor":
+        """crates/nn/src/functional/pool.rs:117-160 as written: unfold windows
+        (materialised), max over them; the gradient goes back through fold."""
         n, c, h, wd = self.shape
         u = self.unfold([2, 3], [k, k], [k, k], [1, 1])                 # [N, C, Ho, Wo, k, k]
         return u.reshape(n, c, u.shape[2], u.shape[3], k * k).max(4)
+
+    def max_pool2d(self, k: int) -> "Tensor":
+        """The same function without the window tensor: windows do not overlap
+        (stride = k), so the k*k taps are k*k strided VIEWS of the input and the
+        pool is one elementwise max over them; the gradient is one elementwise
+        kernel over the input's own layout (every input element sits in exactly one
+        window: the reference's mask-times-gradient followed by fold, pool.rs:117-160
+        with src/grad/rules.rs:40-53,379-399, is a permutation here).  Values and
+        gradients equal the unfold spelling bit for bit, ties included."""
+        n, c, h, wd = self.shape
+        if k * k > D.MAX_INPUTS or self.view.bounds:
+            return self.max_pool2d_unfold(k)
+        ho, wo = h // k, wd // k
+        uv = self.view.unfold([2, 3], [k, k], [k, k], [1, 1])           # [N, C, Ho, Wo, k, k] over the input, no copy
+        taps = [Tensor(self.node, View(uv.shape[:4], uv.strides[:4], uv.offset + i * uv.strides[4] + j * uv.strides[5]))
+                for i in range(k) for j in range(k)]
+
+        def fold_max(*a):
+            e = a[0]
+            for t in a[1:]:
+                e = e.maximum(t)
+            return e
+        y = Tensor._map(fold_max, *taps, name="maxpool")
+        if self.requires_grad:
+            x6 = Tensor(self.node, uv.permute((0, 1, 2, 4, 3, 5)))      # [N, C, Ho, k, Wo, k]: the input's own order
+            y_ = Tensor(y.node, y.view)
+
+            def back(g):
+                full = (n, c, ho, k, wo, k)
+                g6 = g.unsqueeze(3).unsqueeze(5).expand(*full)
+                y6 = y_.unsqueeze(3).unsqueeze(5).expand(*full)
+                gx = Tensor._map(lambda g_, x, m: Ast.select(x.lt(m), 0.0, g_), g6, x6, y6, name="maxpool_grad")
+                gx = gx.reshape(n, c, k * ho, k * wo)
+                if (k * ho, k * wo) != (h, wd):                         # rows / columns no window covers get no gradient
+                    gx = gx.pad([(0, 0), (0, 0), (0, h - k * ho), (0, wd - k * wo)])
+                return gx
+            y.requires_grad = True
+            y._parents.append((self, back))
+        return y
 
     def log_softmax(self, axis=-1) -> "Tensor":
         """crates/nn/src/functional/activation.rs:174-187."""

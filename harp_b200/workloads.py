@@ -103,7 +103,10 @@ def mlp_graph(batch: int = 65536, hidden: int = 256, seed: int = 3, weight_seed:
 def cnn_graph(n: int = 4096, seed: int = 4, label_seed: int = 40, weight_seed: int = 41, fused_conv: bool = False):
     """Config 4: MNIST-shaped CNN (conv 1->32 3x3, ReLU, maxpool 2, conv 32->64 3x3,
     ReLU, maxpool 2, flatten 1600, linear 128, ReLU, linear 10, softmax
-    cross-entropy) on synthetic images uniform[0,1] and uniform labels; Kaiming
+    cross-entropy) on synthetic images uniform[0,1] and uniform labels; `fused_conv`
+    selects this backend's forms of the same functions (one implicit-GEMM kernel per
+    convolution and per input gradient, pools over strided views) instead of the
+    reference's spelling; Kaiming
     normal weights from `weight_seed` (the reference's deterministic sin() init is
     not used), zero biases."""
     from .frontend import Tensor
@@ -122,9 +125,9 @@ def cnn_graph(n: int = 4096, seed: int = 4, label_seed: int = 40, weight_seed: i
     if fused_conv:      # each convolution (and its input gradient) as one implicit-GEMM kernel
         h = x.conv2d_fused(ps[0], ps[1]).relu().max_pool2d(2)
         h = h.conv2d_fused(ps[2], ps[3]).relu().max_pool2d(2)
-    else:               # the reference's spelling: pad, unfold, permute, contiguous, GEMM, bias
-        h = x.conv2d(ps[0], ps[1]).relu().max_pool2d(2)
-        h = h.conv2d(ps[2], ps[3]).relu().max_pool2d(2)
+    else:               # the reference's spelling: pad, unfold, permute, contiguous, GEMM, bias; pools through unfold/fold
+        h = x.conv2d(ps[0], ps[1]).relu().max_pool2d_unfold(2)
+        h = h.conv2d(ps[2], ps[3]).relu().max_pool2d_unfold(2)
     h = h.reshape(n, 1600).linear(ps[4], ps[5]).relu().linear(ps[6], ps[7])
     loss = -(h.log_softmax(1) * onehot).sum() * (1.0 / n)
     return loss, ps, loss.backward(ps), (x, onehot)

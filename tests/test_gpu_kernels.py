@@ -230,6 +230,29 @@ def test_reduce_outer_axis(dev, rows, cols, op):
         assert (np.abs(got.astype(np.float64) - ref) <= sum_tolerance(k, [x]) + 1e-30).all()
 
 
+@pytest.mark.parametrize("rows,cols,op", [(100000, 32, D.R_SUM), (5000, 36, D.R_SUM), (300, 512, D.R_MAX), (70001, 8, D.R_MAX), (4096, 64, D.R_SUM)])
+def test_reduce_outer_narrow_outputs_use_row_lanes(dev, rows, cols, op):
+    """Few kept columns (bias gradients): a CTA is (cols / 4) column threads x row lanes.
+    Same results as the thread-per-vector kernel (flag 16) and as the oracle; with a
+    pre-map and an operand broadcast along the rows."""
+    x, b = rnd([rows, cols], rows + 3 * cols), rnd([cols], 9)
+    bo = D.Operand([0, 1], 0, D.F32, cols)
+    expr = w(0) * w(1) if op == D.R_SUM else w(0) + w(1)
+    k = D.reduce([rows, cols], [D.contiguous([rows, cols]), bo], expr, op, 0)
+    got, kern = run_gpu(dev, k, [x, b])
+    assert kern.impl.startswith("reduce_outer_narrow_v4"), kern.impl
+    k.flags = 16
+    plain, kern2 = run_gpu(dev, k, [x, b])
+    assert kern2.impl.startswith("reduce_outer_v4"), kern2.impl
+    ref = O.run(k, [x, b])
+    if op == D.R_MAX:
+        assert (got == ref).all() and (plain == ref).all()
+    else:
+        tol = sum_tolerance(k, [x, b]) + 1e-30
+        assert (np.abs(got.astype(np.float64) - ref) <= tol).all()
+        assert (np.abs(plain.astype(np.float64) - ref) <= tol).all()
+
+
 @pytest.mark.parametrize("rows,cols,op", [(300, 2048, D.R_SUM), (1000, 4100, D.R_SUM), (160, 8192, D.R_MAX), (500, 2052, D.R_SUM)])
 def test_reduce_inner_bulk_copy_staged_variant(dev, rows, cols, op):
     """Descriptor flag 32: rows staged through shared memory by cp.async.bulk with
@@ -435,6 +458,26 @@ def test_gemm_weight_gradient_split_k(dev, b_, o_, i_):
     bound = 1e-5 * (np.abs(dy).astype(np.float64).T @ np.abs(x).astype(np.float64))
     assert (np.abs(got.reshape(o_, i_) - ref) <= bound).all(), kern.impl
     dev.synchronize()
+
+
+@pytest.mark.parametrize("b_,o_,i_", [(40000, 32, 9), (100001, 10, 32), (65536, 7, 5), (300000, 32, 27)])
+def test_gemm_tall_skinny_weight_gradient(dev, b_, o_, i_):
+    """dW[o, i] = sum_b dy[b, o] * x[b, i] with a one-tile output and a very long
+    reduction (conv1's weight gradient): lane per output row, warp-uniform loads of
+    x's row, partials per CTA summed in order.  Against float64 and the split-K f32 kernel."""
+    dy, x = rnd([b_, o_], 47), rnd([b_, i_], 48)
+    a = D.Operand([o_, 1, 0], 0, D.F32, dy.size)
+    b = D.Operand([i_, 0, 1], 0, D.F32, x.size)
+    k = D.reduce([b_, o_, i_], [a, b], w(0) * w(1), D.R_SUM, 0)
+    got, kern = run_gpu(dev, k, [dy, x])
+    assert kern.impl == "gemm_tall_f32_splitk", kern.impl
+    ref = dy.astype(np.float64).T @ x.astype(np.float64)
+    bound = 1e-5 * (np.abs(dy).astype(np.float64).T @ np.abs(x).astype(np.float64))
+    assert (np.abs(got.reshape(o_, i_) - ref) <= bound).all()
+    k.flags = 16
+    other, kern2 = run_gpu(dev, k, [dy, x])
+    assert kern2.impl.startswith("gemm_simt_f32")
+    assert (np.abs(other.reshape(o_, i_) - ref) <= bound).all()
 
 
 def test_gemm_misaligned_layout_stays_on_f32_kernel(dev):

@@ -109,8 +109,8 @@ def cnn(n, seed=4):
     vals = [kaiming(32, 1, 3, 3), np.zeros(32, np.float32), kaiming(64, 32, 3, 3), np.zeros(64, np.float32),
             kaiming(128, 1600), np.zeros(128, np.float32), kaiming(10, 128), np.zeros(10, np.float32)]
     ps = [Tensor.input(v, requires_grad=True) for v in vals]
-    h = Tensor.input(X).conv2d(ps[0], ps[1]).relu().max_pool2d(2)
-    h = h.conv2d(ps[2], ps[3]).relu().max_pool2d(2)
+    h = Tensor.input(X).conv2d(ps[0], ps[1]).relu().max_pool2d_unfold(2)
+    h = h.conv2d(ps[2], ps[3]).relu().max_pool2d_unfold(2)
     h = h.reshape(n, 1600).linear(ps[4], ps[5]).relu().linear(ps[6], ps[7])
     onehot = Tensor.input(np.eye(10, dtype=np.float32)[lab])
     loss = -(h.log_softmax(1) * onehot).sum() * (1.0 / n)

@@ -75,10 +75,16 @@ def test_weight_gradient_contractions_split_k():
     k = D.reduce([65536, 256, 256], [a, b], w(0) * w(1), D.R_SUM, 0)
     i = query(k)
     assert i.impl.decode() == "gemm_tcgen05_3xtf32_mn_splitk" and i.launches == 4
-    # conv1 weight gradient: ldb = 9 floats cannot be a TMA stride -> f32 kernel, still split
+    # conv1 weight gradient: ldb = 9 floats cannot be a TMA stride -> f32 kernels, still split:
+    # the one-tile tall form for long reductions, the tiled one when asked (flag 16) or short
     a = D.Operand([32, 1, 0], 0, D.F32, 346112 * 32)
     b = D.Operand([9, 0, 1], 0, D.F32, 346112 * 9)
-    i = query(D.reduce([346112, 32, 9], [a, b], w(0) * w(1), D.R_SUM, 0))
+    k = D.reduce([346112, 32, 9], [a, b], w(0) * w(1), D.R_SUM, 0)
+    i = query(k)
+    assert i.impl.decode() == "gemm_tall_f32_splitk" and i.scratch_bytes > 0
+    a = D.Operand([32, 1, 0], 0, D.F32, 8000 * 32)
+    b = D.Operand([9, 0, 1], 0, D.F32, 8000 * 9)
+    i = query(D.reduce([8000, 32, 9], [a, b], w(0) * w(1), D.R_SUM, 0))
     assert i.impl.decode() == "gemm_simt_f32_splitk" and i.scratch_bytes > 0
 
 
@@ -165,3 +171,20 @@ def test_conv2d_rejects_what_the_kernel_does_not_serve():
     with pytest.raises(capi.Eb200Error) as e:
         query(k)
     assert e.value.status == capi.ERR_BOUNDS
+
+
+def test_narrow_column_reduce_uses_row_lanes():
+    k = D.reduce([2768896, 32], [D.contiguous([2768896, 32])], w(0), D.R_SUM, 0)     # conv1 bias gradient of config 4
+    i = query(k)
+    assert i.impl.decode() == "reduce_outer_narrow_v4_split" and i.launches == 2
+    k.flags = 16
+    assert query(k).impl.decode() == "reduce_outer_v4_split"
+    assert query(W.cfg2_z()).impl.decode() == "reduce_outer_v4_split"            # wide outputs keep a thread per vector
+
+
+def test_conv1_weight_gradient_is_the_tall_kernel():
+    a = D.Operand([32, 1, 0], 0, D.F32, 2768896 * 32)
+    b = D.Operand([9, 0, 1], 0, D.F32, 2768896 * 9)
+    i = query(D.reduce([2768896, 32, 9], [a, b], w(0) * w(1), D.R_SUM, 0))
+    assert i.impl.decode() == "gemm_tall_f32_splitk" and i.launches == 2
+    assert i.scratch_bytes == 2 * 148 * 32 * 9 * 4
