@@ -469,38 +469,45 @@ def extra_measurements(reg, dev, rank, world, local_rank, quick=False):
         out["mlp_cfg3"] = {"ms_per_step": ms, "samples_per_s": 65536 / ms * 1e3, "kernels_per_step": len(prog.kernels) + len(prog.sgd_kernels),
                            "derived_tflops": 2.597e10 / ms / 1e9, "loss_after": float(prog.fetch(loss)), "steps": steps + 3 + 1}
         del prog
-    # config 4: CNN, global batch 4096 sharded over the ranks, gradient all-reduce
-    ex = B200Executor(dev, reg)
-    n_local = 4096 // world
-    loss, ps, grads, _ = W.cnn_graph(n_local, seed=4 + rank)
-    prog = Program([loss], ex, sgd=list(zip(ps, grads)), lr=1e-2 / world, persistent=True, flat=True)
-    between = None
-    if world > 1:
-        from harp_b200 import parallel
-        prog.capture(include_update=False)
-        between = parallel.make_allreduce(prog.grad_buffers(), "sum", dev, local_rank)
-    else:
-        prog.capture()
-    steps = 5 if quick else 20
-    for _ in range(3):
-        prog.run(between)
-    dev.synchronize()
-    if world > 1:
-        import torch.distributed as dist
-        dist.barrier()
-    dev.timer_begin()
-    for _ in range(steps):
-        prog.run(between)
-    ms = dev.timer_end() / steps
-    if world > 1:
-        import torch
-        import torch.distributed as dist
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    out["cnn_cfg4"] = {"ms_per_step": ms, "img_per_s": 4096 / ms * 1e3, "global_batch": 4096, "per_gpu_batch": n_local,
-                       "kernels_per_step": len(prog.kernels) + len(prog.sgd_kernels),
-                       "allreduce_bytes_per_step": 225034 * 4 if world > 1 else 0, "loss_after": float(prog.fetch(loss))}
+    # config 4: CNN, global batch 4096 sharded over the ranks, gradient all-reduce.
+    # "cnn_cfg4": this backend's forms of the same functions (one implicit-GEMM kernel per
+    # convolution / input gradient / weight gradient, pools over strided views);
+    # "cnn_cfg4_reference_spelling" (one GPU only): eclat's own composition of them.
+    def cnn_step(fused):
+        ex = B200Executor(dev, reg)
+        n_local = 4096 // world
+        loss, ps, grads, _ = W.cnn_graph(n_local, seed=4 + rank, fused_conv=fused)
+        prog = Program([loss], ex, sgd=list(zip(ps, grads)), lr=1e-2 / world, persistent=True, flat=True)
+        between = None
+        if world > 1:
+            from harp_b200 import parallel
+            prog.capture(include_update=False)
+            between = parallel.make_allreduce(prog.grad_buffers(), "sum", dev, local_rank)
+        else:
+            prog.capture()
+        steps = 5 if quick else 20
+        for _ in range(3):
+            prog.run(between)
+        dev.synchronize()
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        dev.timer_begin()
+        for _ in range(steps):
+            prog.run(between)
+        ms = dev.timer_end() / steps
+        if world > 1:
+            import torch
+            import torch.distributed as dist
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return {"ms_per_step": ms, "img_per_s": 4096 / ms * 1e3, "global_batch": 4096, "per_gpu_batch": n_local,
+                "kernels_per_step": len(prog.kernels) + len(prog.sgd_kernels),
+                "allreduce_bytes_per_step": 225034 * 4 if world > 1 else 0, "loss_after": float(prog.fetch(loss))}
+    out["cnn_cfg4"] = cnn_step(True)
+    if world == 1:
+        out["cnn_cfg4_reference_spelling"] = cnn_step(False)
     return out
 
 

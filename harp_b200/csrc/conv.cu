@@ -37,6 +37,7 @@ struct ConvParams {
     int Ho, Wo;
     int K, Kpad;        // C * KH * KW, rounded up to 32
     int relu, has_bias, three_pass;
+    int nchw;           // output as [N, Co, Ho, Wo] instead of [N*Ho*Wo, Co]
     int stages;         // A/B ring
     int mode;           // CV_CBLOCK / CV_TABLE
     int taps;           // KH * KW
@@ -399,7 +400,14 @@ conv2d_igemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     if (q.has_bias && col0 + i < q.Co) v[i] += __ldg(bias + col0 + i);
                     if (q.relu) v[i] = fmaxf(v[i], 0.0f);
                 }
-                if (col0 + 32 <= q.Co && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+                if (q.nchw) {
+                    // one plane per channel: the warp's 32 positions are consecutive in every plane
+                    const long long plane = (long long)q.Ho * q.Wo;
+                    float* d2 = out + (((long long)tc.n * q.Co + col0) * q.Ho + oh) * q.Wo + ow;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (col0 + i < q.Co) d2[i * plane] = v[i];
+                } else if (col0 + 32 <= q.Co && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
                 } else {
@@ -470,6 +478,7 @@ int launch_conv2d(Device* dev, const Plan& plan, const float* x, const float* w,
     q.K = c.C * c.KH * c.KW;
     q.Kpad = (q.K + 31) / 32 * 32;
     q.relu = c.relu; q.has_bias = bias != nullptr; q.three_pass = c.mode == EB200_GEMM_3XTF32;
+    q.nchw = c.nchw;
     q.error_flag = dev->error_flag_dev;
     if ((long long)c.N * q.Ho * q.Wo <= 0) return EB200_OK;
     q.taps = c.KH * c.KW;
@@ -558,6 +567,311 @@ int launch_conv2d(Device* dev, const Plan& plan, const float* x, const float* w,
     count_launch();
     EB_CHECK_CUDA(cudaGetLastError());
     return EB200_OK;
+}
+
+
+// =========================================================================================
+// Weight gradient of the same convolution, again without the window tensor:
+//     dW[co][k] = sum_m G[m][co] * A[m][k],   m = (n, oh, ow),  k = (c, kh, kw),
+// (the reference multiplies the output gradient with the materialised unfold and sums
+// over the batch and positions: src/grad/rules.rs:196-222 applied to conv.rs:150-170).
+// As an MMA: D[k][co], reduction over positions.  The grid is (row tiles of 128 k) x
+// (image streams); a CTA walks its images, stages each image's raw channel planes with one
+// bulk copy, and per block of 32 positions
+//   * TMA brings the G tile [32 positions][BN channels] (co contiguous: the N-major layout),
+//     split into hi/lo in place by the gather threads for 3xTF32;
+//   * 256 gather threads (two per row) build the A^T tile [128 k][32 positions] from the
+//     patch through a per-position table {window origin, valid taps};
+//   * one thread issues the MMAs into a single accumulator that lives for the whole kernel.
+// Per-CTA partials go to scratch and are summed in stream order (deterministic).
+struct WgradParams {
+    int N, C, H, W, Co, KH, KW, pad;
+    int Ho, Wo, P;      // positions per image
+    int K, taps;
+    int nb;             // 32-position blocks per image
+    int m_tiles, streams;
+    int three_pass, stages, pstages;
+    int patch_floats;   // C * H * W rounded up to 32
+    int* error_flag;
+};
+
+constexpr int WG_MAX_POS = 2048;
+constexpr int WG_MAX_PATCH_BYTES = 64 * 1024;
+
+template <int BN>
+__global__ void __launch_bounds__(CV_THREADS, 1)
+conv2d_wgrad_kernel(const __grid_constant__ CUtensorMap map_g, const __grid_constant__ WgradParams q,
+                    const float* __restrict__ x, float* __restrict__ partials) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr int G_TILE = BN * TC_BK * 4;
+    constexpr unsigned TMEM_COLS = BN < 32 ? 32 : BN;
+    const int stage_bytes = (q.three_pass ? 2 : 1) * (TC_TILE_BYTES + G_TILE);   // [A hi | A lo | G hi | G lo]
+    float* patch0 = reinterpret_cast<float*>(smem + (size_t)q.stages * stage_bytes);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(patch0 + (size_t)q.pstages * q.patch_floats);
+    uint64_t* empty_bar = full_bar + q.stages;
+    uint64_t* gfull = empty_bar + q.stages;           // G tile landed
+    uint64_t* pfull = gfull + q.stages;
+    uint64_t* pempty = pfull + q.pstages;
+    uint64_t* acc_full = pempty + q.pstages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+    int2* pos = reinterpret_cast<int2*>(tmem_slot + 2);           // per position: {window origin in the plane, valid taps}
+
+    const int warp = uniform_warp_idx(), lane = threadIdx.x & 31;
+    const int tile = (int)blockIdx.x % q.m_tiles, stream = (int)blockIdx.x / q.m_tiles;
+    const int n_images = stream < q.N ? (q.N - stream + q.streams - 1) / q.streams : 0;
+    const int g_off = (q.three_pass ? 2 : 1) * TC_TILE_BYTES;
+
+    for (int m = threadIdx.x; m < q.nb * TC_BK; m += CV_THREADS) {
+        int2 e = make_int2(0, 0);
+        if (m < q.P) {
+            const int oh = m / q.Wo, ow = m - oh * q.Wo;
+            e.x = (oh - q.pad) * q.W + (ow - q.pad);
+            unsigned vm = 0;
+            for (int kh = 0; kh < q.KH; ++kh)
+                for (int kw = 0; kw < q.KW; ++kw)
+                    if ((unsigned)(oh + kh - q.pad) < (unsigned)q.H && (unsigned)(ow + kw - q.pad) < (unsigned)q.W)
+                        vm |= 1u << (kh * q.KW + kw);
+            e.y = (int)vm;
+        }
+        pos[m] = e;
+    }
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < q.stages; ++s) { mbar_init(&full_bar[s], CV_GATHERERS); mbar_init(&empty_bar[s], 1); mbar_init(&gfull[s], 1); }
+        for (int p = 0; p < q.pstages; ++p) { mbar_init(&pfull[p], 1); mbar_init(&pempty[p], CV_GATHERERS); }
+        mbar_init(acc_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---- G tiles: BN / 32 boxes of [32 positions][32 channels] per block ----
+        int s = 0;
+        unsigned ph = 0;
+        bool ok = true;
+        for (int i = 0; i < n_images && ok; ++i) {
+            const int n = stream + i * q.streams;
+            for (int b = 0; b < q.nb; ++b, s = (s + 1 == q.stages ? 0 : s + 1), ph ^= (s == 0)) {
+                ok = __all_sync(0xffffffffu, mbar_wait(&empty_bar[s], ph ^ 1u, q.error_flag));
+                if (!ok) break;
+                if (elect_one()) {
+                    unsigned char* gt = smem + (size_t)s * stage_bytes + g_off;
+                    mbar_expect_tx(&gfull[s], (unsigned)G_TILE);
+#pragma unroll
+                    for (int j = 0; j < BN / 32; ++j) tma_load_3d(gt + j * 4096, &map_g, &gfull[s], j * 32, n * q.P + b * TC_BK, 0);
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp == 1) {
+        // ---- tensor core ----
+        const uint32_t idesc = umma_idesc_tf32(TC_BM, BN, 0, 1);       // A K-major, B N-major
+        const uint32_t smem_base = smem_u32(smem);
+        int s = 0;
+        unsigned ph = 0;
+        bool ok = true, first = true;
+        for (int i = 0; i < n_images && ok; ++i) {
+            for (int b = 0; b < q.nb; ++b, s = (s + 1 == q.stages ? 0 : s + 1), ph ^= (s == 0)) {
+                ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[s], ph, q.error_flag));
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_hi = smem_base + (uint32_t)s * (uint32_t)stage_bytes, a_lo = a_hi + TC_TILE_BYTES;
+                const uint32_t g_hi = a_hi + g_off, g_lo = g_hi + G_TILE;
+                const uint64_t da0 = umma_desc(a_hi, 16, 1024), dal0 = umma_desc(a_lo, 16, 1024);
+                const uint64_t db0 = umma_desc(g_hi, 4096, 512, 1), dbl0 = umma_desc(g_lo, 4096, 512, 1);
+                if (elect_one()) {
+#pragma unroll
+                    for (int j = 0; j < TC_BK / TC_UK; ++j) {
+                        const uint64_t as = (uint64_t)(j * TC_UK * 4) >> 4, bs = (uint64_t)(j * 1024) >> 4;
+                        umma_tf32(tmem_base, da0 + as, db0 + bs, idesc, (first && j == 0) ? 0u : 1u);
+                        if (q.three_pass) {
+                            umma_tf32(tmem_base, dal0 + as, db0 + bs, idesc, 1u);
+                            umma_tf32(tmem_base, da0 + as, dbl0 + bs, idesc, 1u);
+                        }
+                    }
+                    umma_commit(&empty_bar[s]);
+                }
+                first = false;
+                __syncwarp();
+            }
+        }
+        if (elect_one()) umma_commit(acc_full);
+        __syncwarp();
+    } else if (warp == 2) {
+        // ---- patches: the image's C channel planes, one bulk copy ----
+        if (lane == 0) {
+            int p = 0;
+            unsigned pph = 0;
+            const unsigned bytes = (unsigned)(q.C * q.H * q.W) * 4u;
+            for (int i = 0; i < n_images; ++i, p = (p + 1 == q.pstages ? 0 : p + 1), pph ^= (p == 0)) {
+                const int n = stream + i * q.streams;
+                if (!mbar_wait(&pempty[p], pph ^ 1u, q.error_flag)) break;
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_expect_tx(&pfull[p], bytes);
+                bulk_load(patch0 + (size_t)p * q.patch_floats, x + (long long)n * q.C * q.H * q.W, bytes, &pfull[p]);
+            }
+        }
+    } else if (warp >= 4 && warp < 12) {
+        // ---- gather: two threads per k row, 16 positions each ----
+        const int gt = threadIdx.x - 128;                   // 0..255
+        const int r = gt & 127, half = gt >> 7;
+        const int k = tile * TC_BM + r;
+        const bool krow = k < q.K;
+        int koff = 0;
+        unsigned kbit = 0;
+        if (krow) {
+            const int c = k / q.taps, tap = k - c * q.taps;
+            const int kh = tap / q.KW, kw = tap - kh * q.KW;
+            koff = c * q.H * q.W + kh * q.W + kw;
+            kbit = 1u << tap;
+        }
+        int s = 0, p = 0;
+        unsigned ph = 0, pph = 0;
+        bool ok = true;
+        for (int i = 0; i < n_images && ok; ++i, p = (p + 1 == q.pstages ? 0 : p + 1), pph ^= (p == 0)) {
+            ok = mbar_wait(&pfull[p], pph, q.error_flag);
+            if (!ok) break;
+            const float* pb = patch0 + (size_t)p * q.patch_floats + koff;
+            for (int b = 0; b < q.nb; ++b, s = (s + 1 == q.stages ? 0 : s + 1), ph ^= (s == 0)) {
+                ok = mbar_wait(&empty_bar[s], ph ^ 1u, q.error_flag);
+                if (!ok) break;
+                unsigned char* st = smem + (size_t)s * stage_bytes;
+                float v[16];
+                const int2* pt = pos + b * TC_BK + half * 16;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int2 e = pt[j];
+                    v[j] = ((unsigned)e.y & kbit) ? pb[e.x] : 0.0f;
+                }
+                unsigned char* a_hi = st + (size_t)r * 128;
+                unsigned char* a_lo = a_hi + TC_TILE_BYTES;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int chunk = ((half * 4 + j) ^ (r & 7)) * 16;
+                    const float v0 = v[4 * j], v1 = v[4 * j + 1], v2 = v[4 * j + 2], v3 = v[4 * j + 3];
+                    if (q.three_pass) {
+                        const float h0 = tf32_hi(v0), h1 = tf32_hi(v1), h2 = tf32_hi(v2), h3 = tf32_hi(v3);
+                        *reinterpret_cast<float4*>(a_hi + chunk) = make_float4(h0, h1, h2, h3);
+                        *reinterpret_cast<float4*>(a_lo + chunk) = make_float4(v0 - h0, v1 - h1, v2 - h2, v3 - h3);
+                    } else {
+                        *reinterpret_cast<float4*>(a_hi + chunk) = make_float4(v0, v1, v2, v3);
+                    }
+                }
+                if (q.three_pass) {
+                    // split the G tile TMA delivered: hi in place, lo beside it (elementwise, so the swizzle does not matter)
+                    ok = mbar_wait(&gfull[s], ph, q.error_flag);
+                    if (!ok) break;
+                    float4* gh = reinterpret_cast<float4*>(st + g_off);
+                    float4* gl = reinterpret_cast<float4*>(st + g_off + G_TILE);
+#pragma unroll
+                    for (int j = 0; j < G_TILE / 16 / CV_GATHERERS; ++j) {
+                        const float4 t = gh[gt + j * CV_GATHERERS];
+                        const float4 h = make_float4(tf32_hi(t.x), tf32_hi(t.y), tf32_hi(t.z), tf32_hi(t.w));
+                        gh[gt + j * CV_GATHERERS] = h;
+                        gl[gt + j * CV_GATHERERS] = make_float4(t.x - h.x, t.y - h.y, t.z - h.z, t.w - h.w);
+                    }
+                } else if (gt == 0) {
+                    ok = mbar_wait(&gfull[s], ph, q.error_flag);     // one thread vouches for the G tile
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(&full_bar[s]);
+            }
+            if (ok) mbar_arrive(&pempty[p]);
+        }
+    } else if (warp >= 12) {
+        // ---- epilogue, once: this CTA's partial D[k][co] -> partials[stream][k][co] ----
+        const int quarter = warp & 3;
+        const int k = tile * TC_BM + quarter * 32 + lane;
+        const bool ok = n_images > 0 && mbar_wait(acc_full, 0, q.error_flag);
+        tc_fence_after();
+        float* dst = partials + ((long long)stream * q.K + k) * q.Co;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+            float v[32];
+            if (n_images > 0) tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), v);
+            if (k >= q.K) continue;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if (c * 32 + i < q.Co) dst[c * 32 + i] = ok ? v[i] : 0.0f;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+bool conv2d_wgrad_supported(const ConvShape& c) {
+    if (!conv2d_supported(c)) return false;
+    const long long P = (long long)(c.H + 2 * c.pad - c.KH + 1) * (c.W + 2 * c.pad - c.KW + 1);
+    const long long plane = (long long)c.C * c.H * c.W;
+    return c.KH * c.KW <= 32 && (P + 31) / 32 * 32 <= WG_MAX_POS && plane * 4 <= WG_MAX_PATCH_BYTES && plane % 4 == 0 &&
+           c.Co % 4 == 0 && c.Co <= 128;
+}
+
+static int wgrad_streams(const ConvShape& c, int sms) {
+    const int m_tiles = (c.C * c.KH * c.KW + TC_BM - 1) / TC_BM;
+    return std::max(1, std::min(c.N, sms / m_tiles));
+}
+
+long long conv2d_wgrad_scratch_floats(const ConvShape& c, int sms) {
+    return (long long)wgrad_streams(c, sms) * c.C * c.KH * c.KW * c.Co;
+}
+
+int launch_conv2d_wgrad(Device* dev, const Plan& plan, const float* x, const float* g, float* dw, void* scratch) {
+    const ConvShape& c = plan.conv;
+    EB_REQUIRE(scratch, EB200_ERR_INVALID, "conv2d weight gradient launched without scratch");
+    EB_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(g) & 15) == 0, EB200_ERR_UNSUPPORTED,
+               "conv2d weight gradient needs 16-byte aligned operands");
+    WgradParams q{};
+    q.N = c.N; q.C = c.C; q.H = c.H; q.W = c.W; q.Co = c.Co; q.KH = c.KH; q.KW = c.KW; q.pad = c.pad;
+    q.Ho = c.H + 2 * c.pad - c.KH + 1;
+    q.Wo = c.W + 2 * c.pad - c.KW + 1;
+    q.P = q.Ho * q.Wo;
+    q.K = c.C * c.KH * c.KW;
+    q.taps = c.KH * c.KW;
+    q.nb = (q.P + TC_BK - 1) / TC_BK;
+    q.m_tiles = (q.K + TC_BM - 1) / TC_BM;
+    q.streams = wgrad_streams(c, dev->prop.multiProcessorCount);
+    q.three_pass = c.mode == EB200_GEMM_3XTF32;
+    q.error_flag = dev->error_flag_dev;
+    q.patch_floats = (c.C * c.H * c.W + 31) / 32 * 32;
+    const int bn = c.Co <= 32 ? 32 : (c.Co <= 64 ? 64 : 128);
+    const int stage_bytes = (q.three_pass ? 2 : 1) * (TC_TILE_BYTES + bn * TC_BK * 4);
+    const size_t fixed = 1024 + 256 + (size_t)q.nb * TC_BK * sizeof(int2);
+    const size_t budget = 220 * 1024;
+    q.pstages = 2;
+    EB_REQUIRE(fixed + 2 * (size_t)q.patch_floats * 4 + 2 * (size_t)stage_bytes <= budget, EB200_ERR_UNSUPPORTED,
+               "conv2d weight gradient does not fit shared memory");
+    q.stages = (int)std::min<size_t>(6, (budget - fixed - 2 * (size_t)q.patch_floats * 4) / stage_bytes);
+    const size_t smem = (size_t)q.stages * stage_bytes + 2 * (size_t)q.patch_floats * 4 + fixed;
+    // the output gradient as [M][Co] rows: boxes of 32 positions x 32 channels, channels contiguous
+    CUtensorMap mg;
+    int st;
+    if ((st = make_map(&mg, g, c.Co, (long long)c.N * q.P, 1, c.Co, 0, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))) return st;
+    static bool configured = false;
+    if (!configured) {
+        EB_CHECK_CUDA(cudaFuncSetAttribute(conv2d_wgrad_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+        EB_CHECK_CUDA(cudaFuncSetAttribute(conv2d_wgrad_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+        EB_CHECK_CUDA(cudaFuncSetAttribute(conv2d_wgrad_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
+        configured = true;
+    }
+    float* partials = reinterpret_cast<float*>(scratch);
+    const unsigned grid = (unsigned)(q.m_tiles * q.streams);
+    if (bn == 32) conv2d_wgrad_kernel<32><<<grid, CV_THREADS, smem, dev->stream>>>(mg, q, x, partials);
+    else if (bn == 64) conv2d_wgrad_kernel<64><<<grid, CV_THREADS, smem, dev->stream>>>(mg, q, x, partials);
+    else conv2d_wgrad_kernel<128><<<grid, CV_THREADS, smem, dev->stream>>>(mg, q, x, partials);
+    count_launch();
+    EB_CHECK_CUDA(cudaGetLastError());
+    // dW[co][k] = sum over streams of partials[stream][k][co]
+    GemmShape gs;
+    gs.batch = 1; gs.m = q.K; gs.n = c.Co; gs.k = 0;
+    gs.splits = q.streams;
+    gs.c_off = 0; gs.c_sb = 0; gs.c_sm = 1; gs.c_sn = q.K;
+    return launch_splitk_reduce(dev, gs, partials, dw);
 }
 
 }  // namespace eb200

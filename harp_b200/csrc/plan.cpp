@@ -152,7 +152,9 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
         c.Co = (int)d->shape[4]; c.KH = (int)d->shape[5]; c.KW = (int)d->shape[6]; c.pad = (int)d->shape[7];
         c.relu = (d->flags & 64) ? 1 : 0;
         c.flip = (d->flags & 128) ? 1 : 0;
-        c.has_bias = d->n_inputs == 3;
+        c.wgrad = (d->flags & 256) ? 1 : 0;
+        c.nchw = (d->flags & 512) ? 1 : 0;
+        c.has_bias = !c.wgrad && d->n_inputs == 3;
         c.mode = d->gemm_mode == EB200_GEMM_TF32 ? EB200_GEMM_TF32 : EB200_GEMM_3XTF32;
         EB_REQUIRE(conv2d_supported(c), EB200_ERR_UNSUPPORTED, "conv2d shape is not served by the implicit-GEMM kernel (C*KH*KW <= 2048, stride 1)");
         const long long Ho = c.H + 2 * c.pad - c.KH + 1, Wo = c.W + 2 * c.pad - c.KW + 1;
@@ -162,23 +164,31 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
             EB_REQUIRE(o.dtype == EB200_F32 && o.n_bounds == 0 && o.offset >= 0, EB200_ERR_UNSUPPORTED, "conv2d operands are plain contiguous f32 buffers");
         }
         EB_REQUIRE(d->inputs[0].numel - d->inputs[0].offset >= (long long)c.N * c.C * c.H * c.W, EB200_ERR_BOUNDS, "conv2d input buffer too small");
-        EB_REQUIRE(d->inputs[1].numel - d->inputs[1].offset >= (long long)c.Co * K, EB200_ERR_BOUNDS, "conv2d weight buffer too small");
-        EB_REQUIRE(!c.has_bias || d->inputs[2].numel - d->inputs[2].offset >= c.Co, EB200_ERR_BOUNDS, "conv2d bias buffer too small");
-        EB_REQUIRE(d->output.numel - d->output.offset >= M * c.Co, EB200_ERR_BOUNDS, "conv2d output buffer too small");
+        if (c.wgrad) {
+            // inputs x and the output gradient [M, Co]; output dW [Co, C, KH, KW]
+            EB_REQUIRE(d->n_inputs == 2 && !c.flip && !c.relu, EB200_ERR_INVALID, "conv2d weight gradient takes x and the output gradient");
+            EB_REQUIRE(conv2d_wgrad_supported(c), EB200_ERR_UNSUPPORTED, "conv2d weight gradient: image planes must fit shared memory, Co % 4 == 0, Co <= 128");
+            EB_REQUIRE(d->inputs[1].numel - d->inputs[1].offset >= M * c.Co, EB200_ERR_BOUNDS, "conv2d output-gradient buffer too small");
+            EB_REQUIRE(d->output.numel - d->output.offset >= c.Co * K, EB200_ERR_BOUNDS, "conv2d weight-gradient buffer too small");
+        } else {
+            EB_REQUIRE(d->inputs[1].numel - d->inputs[1].offset >= (long long)c.Co * K, EB200_ERR_BOUNDS, "conv2d weight buffer too small");
+            EB_REQUIRE(!c.has_bias || d->inputs[2].numel - d->inputs[2].offset >= c.Co, EB200_ERR_BOUNDS, "conv2d bias buffer too small");
+            EB_REQUIRE(d->output.numel - d->output.offset >= M * c.Co, EB200_ERR_BOUNDS, "conv2d output buffer too small");
+        }
         for (int i = 0; i < d->n_inputs; ++i) pl.p.in[i].offset = d->inputs[i].offset;
         pl.p.out.offset = d->output.offset;
-        pl.impl = IMPL_CONV2D;
+        pl.impl = c.wgrad ? IMPL_CONV2D_WGRAD : IMPL_CONV2D;
         pl.n_inputs = d->n_inputs;
         pl.p.n_in = d->n_inputs;
         for (int i = 0; i < d->n_inputs; ++i) { pl.in_dtype[i] = EB200_F32; pl.in_numel[i] = d->inputs[i].numel; pl.perm[i] = i; }
         for (int j = 0; j < KMAX_CONSTS; ++j) pl.dyn_input[j] = -1;
         pl.out_dtype = EB200_F32;
         pl.out_numel = d->output.numel;
-        pl.scratch_bytes = conv2d_scratch_floats(c) * 4;
+        pl.scratch_bytes = (c.wgrad ? conv2d_wgrad_scratch_floats(c, sm_count) : conv2d_scratch_floats(c)) * 4;
         pl.launches = 2;
         pl.algo_flops = 2 * M * c.Co * K;
         pl.algo_bytes = 4 * ((long long)c.N * c.C * c.H * c.W + (long long)c.Co * K + M * c.Co + (c.has_bias ? c.Co : 0));
-        snprintf(pl.name, sizeof(pl.name), "conv2d_igemm_%s%s", c.mode == EB200_GEMM_TF32 ? "tf32" : "3xtf32", c.flip ? "_dgrad" : "");
+        snprintf(pl.name, sizeof(pl.name), "conv2d_igemm_%s%s", c.mode == EB200_GEMM_TF32 ? "tf32" : "3xtf32", c.wgrad ? "_wgrad" : (c.flip ? "_dgrad" : ""));
         return EB200_OK;
     }
     EB_REQUIRE(d->ndim >= 0 && d->ndim <= EB200_MAX_DIMS, EB200_ERR_INVALID, "rank %d out of range", d->ndim);

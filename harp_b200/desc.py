@@ -38,6 +38,8 @@ K_ELEMENTWISE, K_REDUCE, K_COPY, K_SCATTER, K_SGD, K_CONV2D = 0, 1, 2, 3, 4, 5
 KCLASS_PREFIX = {K_ELEMENTWISE: "E", K_REDUCE: "R", K_COPY: "C", K_SCATTER: "S", K_SGD: "U", K_CONV2D: "CONV"}
 FLAG_RELU = 64
 FLAG_WFLIP = 128
+FLAG_WGRAD = 256
+FLAG_NCHW = 512
 
 # eb200_reduce_op
 R_NONE, R_SUM, R_MAX, R_MIN, R_PROD = 0, 1, 2, 3, 4
@@ -360,7 +362,7 @@ def copy(shape, src: Operand, out: Optional[Operand] = None) -> KernelDesc:
     return KernelDesc(K_COPY, shape, [src], out or contiguous(shape, src.dtype), None)
 
 
-def conv2d(n, c, h, w, co, kh, kw, pad=0, bias=True, relu=False, mode: int = GEMM_DEFAULT, flip=False) -> KernelDesc:
+def conv2d(n, c, h, w, co, kh, kw, pad=0, bias=True, relu=False, mode: int = GEMM_DEFAULT, flip=False, nchw=False) -> KernelDesc:
     """functional::conv2d (crates/nn/src/functional/conv.rs:113-184) as one kernel:
     x [N,C,H,W], weight [Co,C,KH,KW] (, bias [Co]) -> [N*Ho*Wo, Co] row-major, the
     buffer the reference's GEMM step produces (its result is a permuted view of it).
@@ -372,4 +374,14 @@ def conv2d(n, c, h, w, co, kh, kw, pad=0, bias=True, relu=False, mode: int = GEM
     if bias:
         ins.append(Operand(z8, 0, F32, co))
     return KernelDesc(K_CONV2D, [n, c, h, w, co, kh, kw, pad], ins, Operand(z8, 0, F32, n * ho * wo * co),
-                      None, gemm_mode=mode, flags=(FLAG_RELU if relu else 0) | (FLAG_WFLIP if flip else 0))
+                      None, gemm_mode=mode, flags=(FLAG_RELU if relu else 0) | (FLAG_WFLIP if flip else 0) | (FLAG_NCHW if nchw else 0))
+
+
+def conv2d_wgrad(n, c, h, w, co, kh, kw, pad=0, mode: int = GEMM_DEFAULT) -> KernelDesc:
+    """Weight gradient of ``conv2d``: x [N,C,H,W] and the output gradient [N*Ho*Wo, Co]
+    -> dW [Co,C,KH,KW], the unfolded input never materialised."""
+    ho, wo = h + 2 * pad - kh + 1, w + 2 * pad - kw + 1
+    z8 = [0] * 8
+    ins = [Operand(z8, 0, F32, n * c * h * w), Operand(z8, 0, F32, n * ho * wo * co)]
+    return KernelDesc(K_CONV2D, [n, c, h, w, co, kh, kw, pad], ins, Operand(z8, 0, F32, co * c * kh * kw),
+                      None, gemm_mode=mode, flags=FLAG_WGRAD)

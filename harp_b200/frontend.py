@@ -501,9 +501,11 @@ class Tensor:
         assert c2 == c
         ho, wo = h + 2 * padding - kh + 1, wd + 2 * padding - kw + 1
         ops = [t.contiguous() for t in ([self, weight] + ([bias] if bias is not None else []))]
-        node = Node("conv", (n, ho, wo, co), [(t.node, t.view) for t in ops], name="conv2d")
-        node.conv = (n, c, h, wd, co, kh, kw, padding, bool(relu), mode, bool(_flip))
-        out = Tensor(node)                                    # [N, Ho, Wo, Co]
+        # the kernel writes [N, Co, Ho, Wo] directly (a warp's 32 output positions are consecutive
+        # in every channel plane), so consumers see the function's own layout, unit stride innermost
+        node = Node("conv", (n, co, ho, wo), [(t.node, t.view) for t in ops], name="conv2d")
+        node.conv = (n, c, h, wd, co, kh, kw, padding, bool(relu), mode, bool(_flip), False)
+        out = Tensor(node)                                    # [N, Co, Ho, Wo]
         if any(t.requires_grad for t in ops):
             assert not relu and not _flip, "the fused ReLU and the gradient form are forward only"
             assert kh == kw and kh - 1 - padding >= 0, "input gradient as a convolution needs a square window and pad <= k-1"
@@ -511,16 +513,22 @@ class Tensor:
             m, kk = n * ho * wo, c * kh * kw
             flat = {}
 
-            def g2(g):                                        # [M, Co], materialised once for both users
+            def g2(g):                                        # [M, Co] rows, materialised once for both users
                 if id(g) not in flat:
-                    flat[id(g)] = g.reshape(m, co)
+                    flat[id(g)] = g.permute(0, 2, 3, 1).reshape(m, co)
                 return flat[id(g)]
 
             def back_x(g):
-                g4 = g.permute(0, 3, 1, 2).contiguous()       # NCHW; no copy when g is a permuted NCHW gradient
-                return g4.conv2d_fused(wc, None, padding=kh - 1 - padding, mode=mode, _flip=True)
+                return g.contiguous().conv2d_fused(wc, None, padding=kh - 1 - padding, mode=mode, _flip=True)
 
             def back_w(g):
+                plane, pos = c * h * wd, ho * wo
+                if kh * kw <= 32 and plane % 4 == 0 and plane * 4 <= 64 * 1024 and (pos + 31) // 32 * 32 <= 2048 \
+                        and co % 4 == 0 and co <= 128:
+                    # positions contracted on the tensor cores, the unfolded input never materialised
+                    wnode = Node("conv", (co, c, kh, kw), [(xc.node, xc.view), (g2(g).node, g2(g).view)], name="conv2d_wgrad")
+                    wnode.conv = (n, c, h, wd, co, kh, kw, padding, False, mode, False, True)
+                    return Tensor(wnode)
                 xp = xc.pad([(0, 0), (0, 0), (padding, padding), (padding, padding)])
                 cols = xp.unfold([2, 3], [kh, kw], [1, 1], [1, 1]).permute(0, 2, 3, 1, 4, 5).contiguous().reshape(m, kk)
                 gw = (g2(g).unsqueeze(2).expand(m, co, kk) * cols.unsqueeze(1).expand(m, co, kk)).sum(0)
@@ -530,7 +538,7 @@ class Tensor:
             if bias is not None:
                 parents.append((ops[2], lambda g: g2(g).sum(0)))
             self._track(out, *parents)
-        return out.permute(0, 3, 1, 2)
+        return out
 
     def max_pool2d_unfold(self, k: int) -> "Tensor":
         """crates/nn/src/functional/pool.rs:117-160 as written: unfold windows
@@ -757,12 +765,12 @@ def _lower(k: _K, loc) -> D.KernelDesc:
         st[k.axis] = 0
         return D.reduce(list(k.shape), ins, k.expr, k.reduce_op, k.axis, out=D.Operand(st, out_off, D.F32, out_numel))
     if k.kind == "conv":
-        n, c, h, wd, co, kh, kw, pad, relu, mode, flip = k.conv
+        n, c, h, wd, co, kh, kw, pad, relu, mode, flip, wgrad = k.conv
         z8 = [0] * 8
         for op in ins:
             op.strides = z8
         return D.KernelDesc(D.K_CONV2D, [n, c, h, wd, co, kh, kw, pad], ins, D.Operand(z8, out_off, D.F32, out_numel),
-                            None, gemm_mode=mode, flags=(D.FLAG_RELU if relu else 0) | (D.FLAG_WFLIP if flip else 0), name=k.name)
+                            None, gemm_mode=mode, flags=(D.FLAG_RELU if relu else 0) | (D.FLAG_WFLIP if flip else 0) | (D.FLAG_WGRAD if wgrad else D.FLAG_NCHW), name=k.name)
     if k.kind == "fold":
         assert out_off == 0, "a scatter output owns its buffer (it is zero-filled as a whole)"
         return D.KernelDesc(D.K_SCATTER, k.shape, ins, k.out_view.operand(k.out_numel, D.F32), None, name=k.name)

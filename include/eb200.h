@@ -70,6 +70,11 @@ typedef enum {
                               * layer's [C, Co, KH, KW] and is read transposed and flipped, w'[co][c][kh][kw] =
                               * w[c][co][KH-1-kh][KW-1-kw]: with pad' = KH-1-pad this is the input gradient of the
                               * forward convolution (the VJP eclat derives through fold, src/grad/rules.rs:40-53);
+                              * flags bit 9 = write the output as [N, Co, Ho, Wo] (the layout of the function's result)
+                              * instead of [N*Ho*Wo, Co];
+                              * flags bit 8 = weight gradient: inputs are x and the output gradient [N*Ho*Wo, Co],
+                              * the output is dW [Co, C, KH, KW] (the contraction the reference spells as a broadcast
+                              * multiply of the gradient with the materialised unfold, summed over batch and positions);
                               * gemm_mode picks TF32 / 3xTF32 */
 } eb200_kclass;
 

@@ -249,6 +249,29 @@ def emit_kernel_c(k: D.KernelDesc, fn_name: str = "kernel", openmp: bool = False
         n, c, h, w_, co, kh, kw, pad = k.shape
         ho, wo = h + 2 * pad - kh + 1, w_ + 2 * pad - kw + 1
         relu = bool(k.flags & D.FLAG_RELU)
+        if k.flags & D.FLAG_WGRAD:
+            # dW[co][c][kh][kw] = sum over (n, oh, ow) of g[(n,oh,ow)][co] * x[n][c][oh+kh-pad][ow+kw-pad]:
+            # the R_ kernel of the reference's gradient, reduce loop innermost in (n, oh, ow) order
+            o = [op.offset for op in k.inputs]
+            for d, e in enumerate((co, c, kh, kw)):
+                open_loop(d, e)
+            line("float acc;")
+            line("acc = 0.0f;")
+            pragma_done[0] = True
+            for d, e in ((4, n), (5, ho), (6, wo)):
+                open_loop(d, e)
+            ih, iw = f"((ridx5 + ridx2) + {-pad})", f"((ridx6 + ridx3) + {-pad})"
+            xv = f"buf0[{o[0]} + ((((ridx4 * {c}) + ridx1) * {h} + {ih}) * {w_} + {iw})]"
+            if pad:
+                xv = f"((((!({ih} < 0)) && ({ih} < {h})) && ((!({iw} < 0)) && ({iw} < {w_}))) ? {xv} : 0.0f)"
+            line(f"acc = (acc + ({xv} * buf1[{o[1]} + ((((ridx4 * {ho}) + ridx5) * {wo} + ridx6) * {co} + ridx0)]));")
+            for _ in range(3):
+                close_loop()
+            line(f"out[{k.output.offset} + ((((ridx0 * {c}) + ridx1) * {kh} + ridx2) * {kw} + ridx3)] = acc;")
+            for _ in range(4):
+                close_loop()
+            src += "}\n"
+            return src
         for d, e in enumerate((n, ho, wo, co)):
             open_loop(d, e)
         line("float acc;")
@@ -271,7 +294,10 @@ def emit_kernel_c(k: D.KernelDesc, fn_name: str = "kernel", openmp: bool = False
         val = f"(acc + buf2[{o[2]} + ridx3])" if len(k.inputs) == 3 else "acc"
         if relu:
             val = f"fmaxf({val}, 0.0f)"
-        line(f"out[{k.output.offset} + ((((ridx0 * {ho}) + ridx1) * {wo} + ridx2) * {co} + ridx3)] = {val};")
+        if k.flags & D.FLAG_NCHW:
+            line(f"out[{k.output.offset} + ((((ridx0 * {co}) + ridx3) * {ho} + ridx1) * {wo} + ridx2)] = {val};")
+        else:
+            line(f"out[{k.output.offset} + ((((ridx0 * {ho}) + ridx1) * {wo} + ridx2) * {co} + ridx3)] = {val};")
         for _ in range(4):
             close_loop()
     elif k.kclass == D.K_SGD:

@@ -573,17 +573,21 @@ def _conv_ref64(x, w_, b, pad, relu):
 def test_conv2d_implicit_gemm_matches_direct_convolution(dev, mode, tol, shape):
     n, c, h, wd, co, kh, kw, pad = shape
     x, w_, b = rnd([n, c, h, wd], 60), rnd([co, c, kh, kw], 61), rnd([co], 62)
-    for bias, relu in ((True, True), (False, False)):
-        kd = D.conv2d(n, c, h, wd, co, kh, kw, pad=pad, bias=bias, relu=relu, mode=mode)
+    ho, wo = h + 2 * pad - kh + 1, wd + 2 * pad - kw + 1
+    for bias, relu, nchw in ((True, True, False), (False, False, True)):
+        kd = D.conv2d(n, c, h, wd, co, kh, kw, pad=pad, bias=bias, relu=relu, mode=mode, nchw=nchw)
         ins = [x, w_, b] if bias else [x, w_]
         got, kern = run_gpu(dev, kd, ins)
         assert kern.impl.startswith("conv2d_igemm"), kern.impl
         ref, scale = _conv_ref64(x, w_, b if bias else None, pad, relu)
+        cpu = O.run(kd, ins)
+        if nchw:      # flag 512: [N, Co, Ho, Wo] instead of [N*Ho*Wo, Co]
+            got = got.reshape(n, co, ho, wo).transpose(0, 2, 3, 1)
+            cpu = cpu.reshape(n, co, ho, wo).transpose(0, 2, 3, 1)
         err = np.abs(got.reshape(ref.shape) - ref)
         assert (err <= tol * scale + 1e-30).all(), (shape, bias, float((err / np.maximum(scale, 1e-30)).max()))
         # and against the CPU oracle's loop nest (same bound: the summation orders differ)
-        cpu = O.run(kd, ins).reshape(ref.shape)
-        assert (np.abs(got.reshape(ref.shape) - cpu) <= 2 * tol * scale + 1e-30).all()
+        assert (np.abs(got.reshape(ref.shape) - cpu.reshape(ref.shape)) <= 2 * tol * scale + 1e-30).all()
     dev.synchronize()     # would raise TIMEOUT had a bounded wait in the kernel run out
 
 
@@ -602,7 +606,7 @@ def test_conv2d_fused_front_end_equals_composed_spelling(dev):
         p.run()
         outs.append(p.fetch(y))
         if fused:
-            assert [d.kclass for d in p.kernel_descs()] == [D.K_CONV2D, D.K_COPY]
+            assert [d.kclass for d in p.kernel_descs()] == [D.K_CONV2D]      # the kernel writes NCHW itself
     assert outs[0].shape == (3, 6, 12, 12)
     assert np.abs(outs[0] - outs[1]).max() <= 1e-4
 
@@ -631,5 +635,34 @@ def test_conv2d_input_gradient_is_the_same_kernel_over_flipped_weights(dev, mode
     err = np.abs(got.reshape(ref.shape) - ref)
     assert (err <= tol * scale + 1e-30).all(), float((err / np.maximum(scale, 1e-30)).max())
     cpu = O.run(kd, [g, w_]).reshape(ref.shape)
+    assert (np.abs(got.reshape(ref.shape) - cpu) <= 2 * tol * scale + 1e-30).all()
+    dev.synchronize()
+
+
+@pytest.mark.parametrize("mode,tol", [(D.GEMM_TF32, 1e-2), (D.GEMM_3XTF32, 1e-5)])
+@pytest.mark.parametrize("shape", [
+    (5, 1, 28, 28, 32, 3, 0),          # conv1 of config 4: K = 9, 676 positions per image (22 blocks, the last ragged)
+    (6, 32, 13, 13, 64, 3, 0),         # conv2: K = 288 = three row tiles, 121 positions
+    (3, 4, 9, 10, 20, 3, 1),           # padding, Co not a multiple of 32
+    (400, 8, 6, 6, 8, 3, 1),           # more images than CTAs per row tile: every stream walks several images
+    (2, 16, 8, 8, 128, 5, 2),          # 5x5 window, K = 400 (four row tiles), 128 output channels
+])
+def test_conv2d_weight_gradient_contracts_positions_on_the_tensor_cores(dev, mode, tol, shape):
+    """dW[co, c, kh, kw] = sum_{n, oh, ow} g[n, oh, ow, co] x[n, c, oh+kh-p, ow+kw-p] as one kernel
+    (flag 256) against float64 and against the oracle's loop nest."""
+    n, c, h, wd, co, k, pad = shape
+    ho, wo = h + 2 * pad - k + 1, wd + 2 * pad - k + 1
+    x, g = rnd([n, c, h, wd], 80), rnd([n * ho * wo, co], 81)
+    kd = D.conv2d_wgrad(n, c, h, wd, co, k, k, pad=pad, mode=mode)
+    got, kern = run_gpu(dev, kd, [x, g])
+    assert kern.impl.endswith("_wgrad") and kern.launches == 2, kern.impl
+    xp = np.zeros((n, c, h + 2 * pad, wd + 2 * pad)); xp[:, :, pad:pad + h, pad:pad + wd] = x
+    win = np.lib.stride_tricks.sliding_window_view(xp, (k, k), axis=(2, 3))       # [n, c, ho, wo, k, k]
+    cols = win.transpose(0, 2, 3, 1, 4, 5).reshape(n * ho * wo, c * k * k)
+    ref = g.astype(np.float64).T @ cols
+    scale = np.abs(g).astype(np.float64).T @ np.abs(cols)
+    err = np.abs(got.reshape(ref.shape) - ref)
+    assert (err <= tol * scale + 1e-30).all(), float((err / np.maximum(scale, 1e-30)).max())
+    cpu = O.run(kd, [x, g]).reshape(ref.shape)
     assert (np.abs(got.reshape(ref.shape) - cpu) <= 2 * tol * scale + 1e-30).all()
     dev.synchronize()

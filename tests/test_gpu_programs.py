@@ -132,8 +132,8 @@ def test_cfg4_cnn_step_matches_oracle(dev, registry):
 
 
 def test_cfg4_cnn_with_one_kernel_convolutions_matches_the_reference_spelling(dev, registry):
-    """The CNN step with each convolution (and conv2's input gradient) as one
-    implicit-GEMM kernel on the GPU, against the reference's spelling of the same
+    """The CNN step with each convolution, conv2's input gradient and both weight
+    gradients as one implicit-GEMM kernel each on the GPU, against the reference's spelling of the same
     graph on the CPU oracle: loss and all eight gradients."""
     from harp_b200 import workloads as W
 
@@ -145,7 +145,8 @@ def test_cfg4_cnn_with_one_kernel_convolutions_matches_the_reference_spelling(de
     g, pg = run(True, B200Executor(dev, registry), "chains")
     o, _ = run(False, OracleExecutor(), "reference")
     impls = [k.impl for _, _, k, _ in pg.kernels]
-    assert sum(i.startswith("conv2d_igemm") for i in impls) == 3 and any(i.endswith("_dgrad") for i in impls)
+    assert sum(i.startswith("conv2d_igemm") for i in impls) == 5
+    assert sum(i.endswith("_dgrad") for i in impls) == 1 and sum(i.endswith("_wgrad") for i in impls) == 2
     assert not any(d.kclass == D.K_SCATTER and len(d.shape) == 6 and d.shape[-1] == 3 for d in pg.kernel_descs())   # no 3x3 fold left
     assert abs(float(g[0]) - float(o[0])) <= 1e-5 * abs(float(o[0]))
     for a, b in zip(g[1:], o[1:]):

@@ -188,3 +188,14 @@ def test_conv1_weight_gradient_is_the_tall_kernel():
     i = query(D.reduce([2768896, 32, 9], [a, b], w(0) * w(1), D.R_SUM, 0))
     assert i.impl.decode() == "gemm_tall_f32_splitk" and i.launches == 2
     assert i.scratch_bytes == 2 * 148 * 32 * 9 * 4
+
+
+def test_conv2d_gradient_forms():
+    i = query(D.conv2d(64, 64, 11, 11, 32, 3, 3, pad=2, bias=False, flip=True))
+    assert i.impl.decode() == "conv2d_igemm_3xtf32_dgrad"
+    i = query(D.conv2d_wgrad(4096, 32, 13, 13, 64, 3, 3))
+    assert i.impl.decode() == "conv2d_igemm_3xtf32_wgrad" and i.launches == 2
+    assert i.scratch_bytes == (148 // 3) * 288 * 64 * 4          # one partial per image stream, three row tiles of k
+    with pytest.raises(capi.Eb200Error) as e:
+        query(D.conv2d_wgrad(8, 64, 56, 56, 64, 3, 3, pad=1))   # image planes (802 KB) do not fit shared memory
+    assert e.value.status == capi.ERR_UNSUPPORTED
