@@ -151,6 +151,8 @@ enum Impl {
     IMPL_GEMM_SIMT,       // dense contraction, fp32 FFMA tiles (exact-f32 fallback)
     IMPL_GEMM_TC,         // dense contraction, tcgen05 TF32 / 3xTF32
     IMPL_CONV2D,          // convolution as implicit GEMM on the tensor cores
+    IMPL_CONV2D_DIRECT,   // convolution with a tiny reduction (C*KH*KW <= 32): streaming FFMA kernel
+    IMPL_CONV2D_DIRECT_WGRAD,
     IMPL_CONV2D_WGRAD,    // weight gradient of a convolution, positions contracted on the tensor cores
     IMPL_GEMM_TALL,       // one-tile output, reduction over millions of rows (small-layer weight gradients)
 };
@@ -170,7 +172,7 @@ struct GemmShape {
 
 struct ConvShape {
     int N = 0, C = 0, H = 0, W = 0, Co = 0, KH = 0, KW = 0, pad = 0;
-    int relu = 0, mode = EB200_GEMM_3XTF32, has_bias = 0, flip = 0, wgrad = 0, nchw = 0;
+    int relu = 0, mode = EB200_GEMM_3XTF32, has_bias = 0, flip = 0, wgrad = 0, nchw = 0, g_nchw = 0, direct = 0;
 };
 
 struct TransposeShape {
@@ -228,6 +230,10 @@ bool gemm_tall_supported(const GemmShape& g);
 int launch_gemm_tall(Device* dev, const Plan& plan, const float* a, const float* b, float* c, void* scratch);
 bool conv2d_supported(const ConvShape& c);
 bool conv2d_wgrad_supported(const ConvShape& c);
+bool conv2d_direct_supported(const ConvShape& c);
+long long conv2d_direct_wgrad_scratch_floats(const ConvShape& c, int sms);
+int launch_conv2d_direct(Device* dev, const Plan& plan, const float* x, const float* w, const float* bias, float* out);
+int launch_conv2d_direct_wgrad(Device* dev, const Plan& plan, const float* x, const float* g, float* dw, void* scratch);
 long long conv2d_wgrad_scratch_floats(const ConvShape& c, int sms);
 int launch_conv2d_wgrad(Device* dev, const Plan& plan, const float* x, const float* g, float* dw, void* scratch);
 long long conv2d_scratch_floats(const ConvShape& c);

@@ -121,13 +121,17 @@ static int launch_one(Device* dev, const KParams& p) {
     long long blocks = (work + per_block - 1) / per_block;
     long long cap = (long long)dev->prop.multiProcessorCount * 32;
     if (blocks > cap) blocks = cap;
-    const int nd = (p.total < (1LL << 31) && p.ndim <= 4) ? p.ndim : 0;
+    // ranks 1-4 have their own instantiation; scalar kernels of rank 5 and 6 share the rank-6 one
+    // (dims past the rank have extent 1 and stride 0); everything else takes the any-rank form
+    int nd = 0;
+    if (p.total < (1LL << 31)) nd = p.ndim <= 4 ? p.ndim : (p.ndim <= 6 && p.vec != 4 ? 6 : 0);
     const unsigned g = (unsigned)blocks;
     switch (nd) {
         case 1: ew_kernel<F, 1><<<g, 256, 0, dev->stream>>>(p); break;
         case 2: ew_kernel<F, 2><<<g, 256, 0, dev->stream>>>(p); break;
         case 3: ew_kernel<F, 3><<<g, 256, 0, dev->stream>>>(p); break;
         case 4: ew_kernel<F, 4><<<g, 256, 0, dev->stream>>>(p); break;
+        case 6: ew_kernel<F, 6><<<g, 256, 0, dev->stream>>>(p); break;
         default: ew_kernel<F, 0><<<g, 256, 0, dev->stream>>>(p); break;
     }
     count_launch();

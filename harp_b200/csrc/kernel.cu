@@ -58,7 +58,7 @@ static void fill_info(const Plan& plan, eb200_kernel_info* info) {
     strncpy(info->impl, plan.name, sizeof(info->impl) - 1);
     info->launches = plan.launches;
     info->specialised = plan.chain >= 0 || plan.impl == IMPL_TRANSPOSE || plan.impl == IMPL_SCATTER ||
-                        plan.impl == IMPL_SGD || plan.impl == IMPL_GEMM_SIMT || plan.impl == IMPL_GEMM_TC || plan.impl == IMPL_CONV2D || plan.impl == IMPL_GEMM_TALL || plan.impl == IMPL_CONV2D_WGRAD;
+                        plan.impl == IMPL_SGD || plan.impl == IMPL_GEMM_SIMT || plan.impl == IMPL_GEMM_TC || plan.impl == IMPL_CONV2D || plan.impl == IMPL_GEMM_TALL || plan.impl == IMPL_CONV2D_WGRAD || plan.impl == IMPL_CONV2D_DIRECT || plan.impl == IMPL_CONV2D_DIRECT_WGRAD;
     info->scratch_bytes = plan.scratch_bytes;
     info->algo_bytes = plan.algo_bytes;
     info->algo_flops = plan.algo_flops;
@@ -133,6 +133,15 @@ int eb200_kernel_launch(eb200_kernel* k, eb200_buffer* const* inputs, int n_inpu
             return launch_gemm_tc(dev, plan, reinterpret_cast<const float*>(p.in[plan.gemm.a_input].ptr),
                                   reinterpret_cast<const float*>(p.in[plan.gemm.b_input].ptr),
                                   reinterpret_cast<float*>(p.out.ptr), scratch);
+        case IMPL_CONV2D_DIRECT:
+            return launch_conv2d_direct(dev, plan, reinterpret_cast<const float*>(p.in[0].ptr) + p.in[0].offset,
+                                        reinterpret_cast<const float*>(p.in[1].ptr) + p.in[1].offset,
+                                        plan.n_inputs == 3 ? reinterpret_cast<const float*>(p.in[2].ptr) + p.in[2].offset : nullptr,
+                                        reinterpret_cast<float*>(p.out.ptr) + p.out.offset);
+        case IMPL_CONV2D_DIRECT_WGRAD:
+            return launch_conv2d_direct_wgrad(dev, plan, reinterpret_cast<const float*>(p.in[0].ptr) + p.in[0].offset,
+                                              reinterpret_cast<const float*>(p.in[1].ptr) + p.in[1].offset,
+                                              reinterpret_cast<float*>(p.out.ptr) + p.out.offset, scratch);
         case IMPL_CONV2D_WGRAD:
             return launch_conv2d_wgrad(dev, plan, reinterpret_cast<const float*>(p.in[0].ptr) + p.in[0].offset,
                                        reinterpret_cast<const float*>(p.in[1].ptr) + p.in[1].offset,

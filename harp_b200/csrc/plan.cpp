@@ -154,6 +154,7 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
         c.flip = (d->flags & 128) ? 1 : 0;
         c.wgrad = (d->flags & 256) ? 1 : 0;
         c.nchw = (d->flags & 512) ? 1 : 0;
+        c.g_nchw = (d->flags & 1024) ? 1 : 0;
         c.has_bias = !c.wgrad && d->n_inputs == 3;
         c.mode = d->gemm_mode == EB200_GEMM_TF32 ? EB200_GEMM_TF32 : EB200_GEMM_3XTF32;
         EB_REQUIRE(conv2d_supported(c), EB200_ERR_UNSUPPORTED, "conv2d shape is not served by the implicit-GEMM kernel (C*KH*KW <= 2048, stride 1)");
@@ -164,10 +165,13 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
             EB_REQUIRE(o.dtype == EB200_F32 && o.n_bounds == 0 && o.offset >= 0, EB200_ERR_UNSUPPORTED, "conv2d operands are plain contiguous f32 buffers");
         }
         EB_REQUIRE(d->inputs[0].numel - d->inputs[0].offset >= (long long)c.N * c.C * c.H * c.W, EB200_ERR_BOUNDS, "conv2d input buffer too small");
+        // tiny reductions stream through FFMA code instead (flag 2048 keeps the tensor-core form)
+        c.direct = !(d->flags & 2048) && conv2d_direct_supported(c);
         if (c.wgrad) {
             // inputs x and the output gradient [M, Co]; output dW [Co, C, KH, KW]
             EB_REQUIRE(d->n_inputs == 2 && !c.flip && !c.relu, EB200_ERR_INVALID, "conv2d weight gradient takes x and the output gradient");
-            EB_REQUIRE(conv2d_wgrad_supported(c), EB200_ERR_UNSUPPORTED, "conv2d weight gradient: image planes must fit shared memory, Co % 4 == 0, Co <= 128");
+            EB_REQUIRE(c.direct || !c.g_nchw, EB200_ERR_UNSUPPORTED, "the tensor-core weight gradient reads the output gradient as [N*Ho*Wo, Co] rows");
+            EB_REQUIRE(c.direct || conv2d_wgrad_supported(c), EB200_ERR_UNSUPPORTED, "conv2d weight gradient: image planes must fit shared memory, Co % 4 == 0, Co <= 128");
             EB_REQUIRE(d->inputs[1].numel - d->inputs[1].offset >= M * c.Co, EB200_ERR_BOUNDS, "conv2d output-gradient buffer too small");
             EB_REQUIRE(d->output.numel - d->output.offset >= c.Co * K, EB200_ERR_BOUNDS, "conv2d weight-gradient buffer too small");
         } else {
@@ -177,18 +181,20 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
         }
         for (int i = 0; i < d->n_inputs; ++i) pl.p.in[i].offset = d->inputs[i].offset;
         pl.p.out.offset = d->output.offset;
-        pl.impl = c.wgrad ? IMPL_CONV2D_WGRAD : IMPL_CONV2D;
+        pl.impl = c.direct ? (c.wgrad ? IMPL_CONV2D_DIRECT_WGRAD : IMPL_CONV2D_DIRECT) : (c.wgrad ? IMPL_CONV2D_WGRAD : IMPL_CONV2D);
         pl.n_inputs = d->n_inputs;
         pl.p.n_in = d->n_inputs;
         for (int i = 0; i < d->n_inputs; ++i) { pl.in_dtype[i] = EB200_F32; pl.in_numel[i] = d->inputs[i].numel; pl.perm[i] = i; }
         for (int j = 0; j < KMAX_CONSTS; ++j) pl.dyn_input[j] = -1;
         pl.out_dtype = EB200_F32;
         pl.out_numel = d->output.numel;
-        pl.scratch_bytes = (c.wgrad ? conv2d_wgrad_scratch_floats(c, sm_count) : conv2d_scratch_floats(c)) * 4;
-        pl.launches = 2;
+        if (c.direct) pl.scratch_bytes = c.wgrad ? conv2d_direct_wgrad_scratch_floats(c, sm_count) * 4 : 0;
+        else pl.scratch_bytes = (c.wgrad ? conv2d_wgrad_scratch_floats(c, sm_count) : conv2d_scratch_floats(c)) * 4;
+        pl.launches = c.direct && !c.wgrad ? 1 : 2;
         pl.algo_flops = 2 * M * c.Co * K;
         pl.algo_bytes = 4 * ((long long)c.N * c.C * c.H * c.W + (long long)c.Co * K + M * c.Co + (c.has_bias ? c.Co : 0));
-        snprintf(pl.name, sizeof(pl.name), "conv2d_igemm_%s%s", c.mode == EB200_GEMM_TF32 ? "tf32" : "3xtf32", c.wgrad ? "_wgrad" : (c.flip ? "_dgrad" : ""));
+        if (c.direct) snprintf(pl.name, sizeof(pl.name), "conv2d_direct_f32%s", c.wgrad ? "_wgrad" : (c.flip ? "_dgrad" : ""));
+        else snprintf(pl.name, sizeof(pl.name), "conv2d_igemm_%s%s", c.mode == EB200_GEMM_TF32 ? "tf32" : "3xtf32", c.wgrad ? "_wgrad" : (c.flip ? "_dgrad" : ""));
         return EB200_OK;
     }
     EB_REQUIRE(d->ndim >= 0 && d->ndim <= EB200_MAX_DIMS, EB200_ERR_INVALID, "rank %d out of range", d->ndim);
@@ -300,7 +306,7 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
     p.ndim = nk;
     p.n_in = d->n_inputs;
     p.total = total;
-    for (int j = 0; j < nk; ++j) p.shape[j] = shape[j];
+    for (int j = 0; j < KMAX_DIMS; ++j) p.shape[j] = j < nk ? shape[j] : 1;     // dims past the rank: extent 1 (strides stay 0)
     // magic numbers for exact n / shape[j], n < 2^31: M = ceil(2^(31+l) / s) < 2^32 with l = ceil(log2 s)
     for (int j = 0; j < KMAX_DIMS; ++j) {
         const unsigned long long sj = j < nk && shape[j] >= 1 && shape[j] < (1LL << 31) ? (unsigned long long)shape[j] : 1ULL;

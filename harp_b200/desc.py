@@ -40,6 +40,8 @@ FLAG_RELU = 64
 FLAG_WFLIP = 128
 FLAG_WGRAD = 256
 FLAG_NCHW = 512
+FLAG_G_NCHW = 1024
+FLAG_TENSOR_CORE = 2048
 
 # eb200_reduce_op
 R_NONE, R_SUM, R_MAX, R_MIN, R_PROD = 0, 1, 2, 3, 4
@@ -377,11 +379,12 @@ def conv2d(n, c, h, w, co, kh, kw, pad=0, bias=True, relu=False, mode: int = GEM
                       None, gemm_mode=mode, flags=(FLAG_RELU if relu else 0) | (FLAG_WFLIP if flip else 0) | (FLAG_NCHW if nchw else 0))
 
 
-def conv2d_wgrad(n, c, h, w, co, kh, kw, pad=0, mode: int = GEMM_DEFAULT) -> KernelDesc:
+def conv2d_wgrad(n, c, h, w, co, kh, kw, pad=0, mode: int = GEMM_DEFAULT, g_nchw=False) -> KernelDesc:
     """Weight gradient of ``conv2d``: x [N,C,H,W] and the output gradient [N*Ho*Wo, Co]
-    -> dW [Co,C,KH,KW], the unfolded input never materialised."""
+    -> dW [Co,C,KH,KW], the unfolded input never materialised.  `g_nchw`: the gradient is
+    given as [N,Co,Ho,Wo] instead (layers with C*KH*KW <= 12 only)."""
     ho, wo = h + 2 * pad - kh + 1, w + 2 * pad - kw + 1
     z8 = [0] * 8
     ins = [Operand(z8, 0, F32, n * c * h * w), Operand(z8, 0, F32, n * ho * wo * co)]
     return KernelDesc(K_CONV2D, [n, c, h, w, co, kh, kw, pad], ins, Operand(z8, 0, F32, co * c * kh * kw),
-                      None, gemm_mode=mode, flags=FLAG_WGRAD)
+                      None, gemm_mode=mode, flags=FLAG_WGRAD | (FLAG_G_NCHW if g_nchw else 0))

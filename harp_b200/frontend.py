@@ -504,7 +504,7 @@ class Tensor:
         # the kernel writes [N, Co, Ho, Wo] directly (a warp's 32 output positions are consecutive
         # in every channel plane), so consumers see the function's own layout, unit stride innermost
         node = Node("conv", (n, co, ho, wo), [(t.node, t.view) for t in ops], name="conv2d")
-        node.conv = (n, c, h, wd, co, kh, kw, padding, bool(relu), mode, bool(_flip), False)
+        node.conv = (n, c, h, wd, co, kh, kw, padding, bool(relu), mode, bool(_flip), False, False)
         out = Tensor(node)                                    # [N, Co, Ho, Wo]
         if any(t.requires_grad for t in ops):
             assert not relu and not _flip, "the fused ReLU and the gradient form are forward only"
@@ -523,11 +523,17 @@ class Tensor:
 
             def back_w(g):
                 plane, pos = c * h * wd, ho * wo
+                if kk <= 12:
+                    # tiny reduction: streaming f32 kernel, reads the gradient in its own [N, Co, Ho, Wo] layout
+                    gc = g.contiguous()
+                    wnode = Node("conv", (co, c, kh, kw), [(xc.node, xc.view), (gc.node, gc.view)], name="conv2d_wgrad")
+                    wnode.conv = (n, c, h, wd, co, kh, kw, padding, False, mode, False, True, True)
+                    return Tensor(wnode)
                 if kh * kw <= 32 and plane % 4 == 0 and plane * 4 <= 64 * 1024 and (pos + 31) // 32 * 32 <= 2048 \
                         and co % 4 == 0 and co <= 128:
                     # positions contracted on the tensor cores, the unfolded input never materialised
                     wnode = Node("conv", (co, c, kh, kw), [(xc.node, xc.view), (g2(g).node, g2(g).view)], name="conv2d_wgrad")
-                    wnode.conv = (n, c, h, wd, co, kh, kw, padding, False, mode, False, True)
+                    wnode.conv = (n, c, h, wd, co, kh, kw, padding, False, mode, False, True, False)
                     return Tensor(wnode)
                 xp = xc.pad([(0, 0), (0, 0), (padding, padding), (padding, padding)])
                 cols = xp.unfold([2, 3], [kh, kw], [1, 1], [1, 1]).permute(0, 2, 3, 1, 4, 5).contiguous().reshape(m, kk)
@@ -536,7 +542,10 @@ class Tensor:
 
             parents = [(ops[0], back_x), (ops[1], back_w)]
             if bias is not None:
-                parents.append((ops[2], lambda g: g2(g).sum(0)))
+                if kk <= 12:      # nobody else needs the [M, Co] rows: reduce the planes where they lie
+                    parents.append((ops[2], lambda g: g.contiguous().reshape(n, co, ho * wo).sum(2).sum(0)))
+                else:
+                    parents.append((ops[2], lambda g: g2(g).sum(0)))
             self._track(out, *parents)
         return out
 
@@ -765,12 +774,12 @@ def _lower(k: _K, loc) -> D.KernelDesc:
         st[k.axis] = 0
         return D.reduce(list(k.shape), ins, k.expr, k.reduce_op, k.axis, out=D.Operand(st, out_off, D.F32, out_numel))
     if k.kind == "conv":
-        n, c, h, wd, co, kh, kw, pad, relu, mode, flip, wgrad = k.conv
+        n, c, h, wd, co, kh, kw, pad, relu, mode, flip, wgrad, g_nchw = k.conv
         z8 = [0] * 8
         for op in ins:
             op.strides = z8
         return D.KernelDesc(D.K_CONV2D, [n, c, h, wd, co, kh, kw, pad], ins, D.Operand(z8, out_off, D.F32, out_numel),
-                            None, gemm_mode=mode, flags=(D.FLAG_RELU if relu else 0) | (D.FLAG_WFLIP if flip else 0) | (D.FLAG_WGRAD if wgrad else D.FLAG_NCHW), name=k.name)
+                            None, gemm_mode=mode, flags=(D.FLAG_RELU if relu else 0) | (D.FLAG_WFLIP if flip else 0) | (D.FLAG_WGRAD if wgrad else D.FLAG_NCHW) | (D.FLAG_G_NCHW if g_nchw else 0), name=k.name)
     if k.kind == "fold":
         assert out_off == 0, "a scatter output owns its buffer (it is zero-filled as a whole)"
         return D.KernelDesc(D.K_SCATTER, k.shape, ins, k.out_view.operand(k.out_numel, D.F32), None, name=k.name)

@@ -70,6 +70,9 @@ typedef enum {
                               * layer's [C, Co, KH, KW] and is read transposed and flipped, w'[co][c][kh][kw] =
                               * w[c][co][KH-1-kh][KW-1-kw]: with pad' = KH-1-pad this is the input gradient of the
                               * forward convolution (the VJP eclat derives through fold, src/grad/rules.rs:40-53);
+                              * flags bit 10 = (weight gradient) the output gradient is given as [N, Co, Ho, Wo]; served for
+                              * C*KH*KW <= 12 only; flags bit 11 = keep a layer with C*KH*KW <= 32 on the tensor-core kernel
+                              * (such layers otherwise run a streaming f32 FFMA kernel);
                               * flags bit 9 = write the output as [N, Co, Ho, Wo] (the layout of the function's result)
                               * instead of [N*Ho*Wo, Co];
                               * flags bit 8 = weight gradient: inputs are x and the output gradient [N*Ho*Wo, Co],

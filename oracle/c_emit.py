@@ -264,7 +264,11 @@ def emit_kernel_c(k: D.KernelDesc, fn_name: str = "kernel", openmp: bool = False
             xv = f"buf0[{o[0]} + ((((ridx4 * {c}) + ridx1) * {h} + {ih}) * {w_} + {iw})]"
             if pad:
                 xv = f"((((!({ih} < 0)) && ({ih} < {h})) && ((!({iw} < 0)) && ({iw} < {w_}))) ? {xv} : 0.0f)"
-            line(f"acc = (acc + ({xv} * buf1[{o[1]} + ((((ridx4 * {ho}) + ridx5) * {wo} + ridx6) * {co} + ridx0)]));")
+            if k.flags & D.FLAG_G_NCHW:
+                gv = f"buf1[{o[1]} + ((((ridx4 * {co}) + ridx0) * {ho} + ridx5) * {wo} + ridx6)]"
+            else:
+                gv = f"buf1[{o[1]} + ((((ridx4 * {ho}) + ridx5) * {wo} + ridx6) * {co} + ridx0)]"
+            line(f"acc = (acc + ({xv} * {gv}));")
             for _ in range(3):
                 close_loop()
             line(f"out[{k.output.offset} + ((((ridx0 * {c}) + ridx1) * {kh} + ridx2) * {kw} + ridx3)] = acc;")

@@ -576,6 +576,7 @@ def test_conv2d_implicit_gemm_matches_direct_convolution(dev, mode, tol, shape):
     ho, wo = h + 2 * pad - kh + 1, wd + 2 * pad - kw + 1
     for bias, relu, nchw in ((True, True, False), (False, False, True)):
         kd = D.conv2d(n, c, h, wd, co, kh, kw, pad=pad, bias=bias, relu=relu, mode=mode, nchw=nchw)
+        kd.flags |= D.FLAG_TENSOR_CORE       # layers with C*KH*KW <= 32 would otherwise take the streaming f32 kernel
         ins = [x, w_, b] if bias else [x, w_]
         got, kern = run_gpu(dev, kd, ins)
         assert kern.impl.startswith("conv2d_igemm"), kern.impl
@@ -621,8 +622,9 @@ def test_conv2d_input_gradient_is_the_same_kernel_over_flipped_weights(dev, mode
     ho, wo = h + 2 * pad - k + 1, wd + 2 * pad - k + 1
     g, w_ = rnd([n, co, ho, wo], 70), rnd([co, c, k, k], 71)
     kd = D.conv2d(n, co, ho, wo, c, k, k, pad=k - 1 - pad, bias=False, flip=True, mode=mode)
+    kd.flags |= D.FLAG_TENSOR_CORE
     got, kern = run_gpu(dev, kd, [g, w_])
-    assert kern.impl.endswith("_dgrad"), kern.impl
+    assert kern.impl.startswith("conv2d_igemm") and kern.impl.endswith("_dgrad"), kern.impl
     # adjoint in float64: scatter every dy element times its window of weights
     ref = np.zeros((n, c, h + 2 * pad, wd + 2 * pad)); scale = np.zeros_like(ref)
     for i in range(k):
@@ -654,8 +656,9 @@ def test_conv2d_weight_gradient_contracts_positions_on_the_tensor_cores(dev, mod
     ho, wo = h + 2 * pad - k + 1, wd + 2 * pad - k + 1
     x, g = rnd([n, c, h, wd], 80), rnd([n * ho * wo, co], 81)
     kd = D.conv2d_wgrad(n, c, h, wd, co, k, k, pad=pad, mode=mode)
+    kd.flags |= D.FLAG_TENSOR_CORE
     got, kern = run_gpu(dev, kd, [x, g])
-    assert kern.impl.endswith("_wgrad") and kern.launches == 2, kern.impl
+    assert kern.impl.startswith("conv2d_igemm") and kern.impl.endswith("_wgrad") and kern.launches == 2, kern.impl
     xp = np.zeros((n, c, h + 2 * pad, wd + 2 * pad)); xp[:, :, pad:pad + h, pad:pad + wd] = x
     win = np.lib.stride_tricks.sliding_window_view(xp, (k, k), axis=(2, 3))       # [n, c, ho, wo, k, k]
     cols = win.transpose(0, 2, 3, 1, 4, 5).reshape(n * ho * wo, c * k * k)
@@ -666,3 +669,47 @@ def test_conv2d_weight_gradient_contracts_positions_on_the_tensor_cores(dev, mod
     cpu = O.run(kd, [x, g]).reshape(ref.shape)
     assert (np.abs(got.reshape(ref.shape) - cpu) <= 2 * tol * scale + 1e-30).all()
     dev.synchronize()
+
+
+@pytest.mark.parametrize("shape", [
+    (5, 1, 28, 28, 32, 3, 3, 0),       # conv1 of config 4
+    (3, 3, 9, 11, 20, 3, 3, 1),        # K = 27, padding, Co not a multiple of 4
+    (2, 2, 8, 8, 7, 2, 4, 1),          # K = 16, rectangular window
+    (300, 1, 12, 12, 5, 5, 5, 2),      # K = 25; more positions than one grid pass
+])
+def test_conv2d_tiny_reduction_streams_through_the_f32_kernel(dev, shape):
+    """C*KH*KW <= 32: forward (both output layouts, bias, ReLU), the input gradient through
+    flipped weights, and for K <= 12 the weight gradient (both gradient layouts) on the
+    streaming FFMA kernels: within 1e-5 of sum |terms| of float64, like 3xTF32."""
+    n, c, h, wd, co, kh, kw, pad = shape
+    ho, wo = h + 2 * pad - kh + 1, wd + 2 * pad - kw + 1
+    x, w_, b = rnd([n, c, h, wd], 90), rnd([co, c, kh, kw], 91), rnd([co], 92)
+    for nchw in (False, True):
+        kd = D.conv2d(n, c, h, wd, co, kh, kw, pad=pad, bias=True, relu=True, nchw=nchw)
+        got, kern = run_gpu(dev, kd, [x, w_, b])
+        assert kern.impl == "conv2d_direct_f32" and kern.launches == 1, kern.impl
+        ref, scale = _conv_ref64(x, w_, b, pad, True)
+        if nchw:
+            got = got.reshape(n, co, ho, wo).transpose(0, 2, 3, 1)
+        assert (np.abs(got.reshape(ref.shape) - ref) <= 1e-5 * scale + 1e-30).all()
+    if c * kh * kw <= 12:
+        g = rnd([n, co, ho, wo], 93)
+        xp = np.zeros((n, c, h + 2 * pad, wd + 2 * pad)); xp[:, :, pad:pad + h, pad:pad + wd] = x
+        cols = np.lib.stride_tricks.sliding_window_view(xp, (kh, kw), axis=(2, 3)).transpose(0, 2, 3, 1, 4, 5).reshape(n * ho * wo, -1)
+        grows = g.transpose(0, 2, 3, 1).reshape(n * ho * wo, co)
+        ref = grows.astype(np.float64).T @ cols
+        scale = np.abs(grows).astype(np.float64).T @ np.abs(cols)
+        for g_nchw, gin in ((True, g), (False, np.ascontiguousarray(grows))):
+            kd = D.conv2d_wgrad(n, c, h, wd, co, kh, kw, pad=pad, g_nchw=g_nchw)
+            got, kern = run_gpu(dev, kd, [x, gin])
+            assert kern.impl == "conv2d_direct_f32_wgrad", kern.impl
+            assert (np.abs(got.reshape(ref.shape) - ref) <= 1e-5 * scale + 1e-30).all()
+            cpu = O.run(kd, [x, gin]).reshape(ref.shape)
+            assert (np.abs(got.reshape(ref.shape) - cpu) <= 2e-5 * scale + 1e-30).all()
+    if kh == kw and kh - 1 - pad >= 0 and co * kh * kw <= 32:
+        g = rnd([n, co, ho, wo], 94)
+        kd = D.conv2d(n, co, ho, wo, c, kh, kw, pad=kh - 1 - pad, bias=False, flip=True)
+        got, kern = run_gpu(dev, kd, [g, w_])
+        assert kern.impl == "conv2d_direct_f32_dgrad", kern.impl
+        cpu = O.run(kd, [g, w_])
+        assert np.abs(got - cpu).max() <= 1e-4 * max(1.0, np.abs(cpu).max())

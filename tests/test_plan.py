@@ -156,7 +156,11 @@ def test_conv2d_is_one_implicit_gemm_with_weight_scratch():
     assert i.launches == 2                                   # weight split/pad + the implicit GEMM
     assert i.scratch_bytes == 2 * 64 * 288 * 4               # hi and lo weights, K = 288 already a multiple of 32
     assert i.algo_flops == 2 * 64 * 28 * 28 * 64 * 288
-    i = query(D.conv2d(8, 1, 28, 28, 32, 3, 3, pad=0, mode=D.GEMM_TF32))
+    k = D.conv2d(8, 1, 28, 28, 32, 3, 3, pad=0, mode=D.GEMM_TF32)
+    i = query(k)
+    assert i.impl.decode() == "conv2d_direct_f32" and i.launches == 1 and i.scratch_bytes == 0     # K = 9: streaming f32 kernel
+    k.flags |= D.FLAG_TENSOR_CORE
+    i = query(k)
     assert i.impl.decode() == "conv2d_igemm_tf32" and i.scratch_bytes == 2 * 32 * 32 * 4     # K = 9 padded to 32
 
 
