@@ -397,8 +397,9 @@ CONV_SHAPES = [("cnn_conv1_1x28x28_to_32", (4096, 1, 28, 28, 32, 3, 3, 0)),
 
 
 def conv_measurements(reg, dev, rng, quick=False, shapes=None, reps=None):
-    """conv2d as one implicit-GEMM kernel (bias + ReLU in the epilogue): the two
-    layers of config 4 at batch 4096 and one padded 64->128 layer, TF32 and 3xTF32.
+    """conv2d as one kernel (bias + ReLU in the epilogue, output [N, Co, Ho, Wo]): the two
+    layers of config 4 at batch 4096 and one padded 64->128 layer, TF32 and 3xTF32
+    (the first layer, K = 9, runs the streaming f32 kernel whatever the mode).
     Inputs are larger than L2 except where `shapes` asks for a small profiling case."""
     from harp_b200 import desc as D
     res = {}
@@ -410,7 +411,7 @@ def conv_measurements(reg, dev, rng, quick=False, shapes=None, reps=None):
         bw.write_vec(rng.uniform(-1, 1, co * c * kh * kw).astype(np.float32))
         bb.write_vec(rng.uniform(-1, 1, co).astype(np.float32))
         for mode, mname in ((D.GEMM_TF32, "tf32"), (D.GEMM_3XTF32, "3xtf32")):
-            kern = reg.compile_ast(dev, D.conv2d(n, c, h, w_, co, kh, kw, pad=pad, relu=True, mode=mode))
+            kern = reg.compile_ast(dev, D.conv2d(n, c, h, w_, co, kh, kw, pad=pad, relu=True, mode=mode, nchw=True))
             ms = time_kernel(dev, kern, [bx, bw, bb], [bo], reps=reps or (3 if quick else 10))
             res[f"{name}_{mname}"] = {"impl": kern.impl, "ms": ms, "tflops": 2.0 * n * ho * wo * co * c * kh * kw / ms / 1e9,
                                       "gbs_x_plus_out": 4.0 * (n * c * h * w_ + n * ho * wo * co) / ms / 1e6}

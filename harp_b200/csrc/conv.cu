@@ -456,7 +456,8 @@ bool conv2d_supported(const ConvShape& c) {
     const long long K = (long long)c.C * c.KH * c.KW;
     if (c.N < 1 || c.C < 1 || c.Co < 1 || c.KH < 1 || c.KW < 1 || c.pad < 0) return false;
     if (c.H + 2 * c.pad < c.KH || c.W + 2 * c.pad < c.KW) return false;
-    if (K > CV_MAX_K || c.KH >= 32768 || c.KW >= 32768) return false;
+    // the per-k offset table bounds K only when the channels are not blocked by 32
+    if ((c.C % 32 != 0 && K > CV_MAX_K) || K > (1 << 20) || c.KH >= 32768 || c.KW >= 32768) return false;
     const long long M = (long long)c.N * (c.H + 2 * c.pad - c.KH + 1) * (c.W + 2 * c.pad - c.KW + 1);
     if (M >= (1LL << 31)) return false;
     if ((long long)c.N * c.C * c.H * c.W >= (1LL << 31)) return false;     // 32-bit window offsets

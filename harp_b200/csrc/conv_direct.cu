@@ -69,22 +69,42 @@ __global__ void __launch_bounds__(256) conv2d_direct_kernel(const __grid_constan
         }
         float* o_nchw = out + (long long)n * q.Co * q.P + pos;
         float* o_rows = out + (long long)m * q.Co;
-        for (int co = 0; co < q.Co; ++co) {
-            const float4* wr = reinterpret_cast<const float4*>(ws + (size_t)co * q.K4);
-            float acc = bs[co];
+        const bool rows4 = !q.nchw_out && (q.Co & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+        // four output channels at a time: in the rows layout they leave as one 128-bit store
+        for (int co = 0; co < q.Co; co += 4) {
+            float acc[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[j] = co + j < q.Co ? bs[co + j] : 0.0f;
 #pragma unroll
             for (int k4 = 0; k4 < KT / 4; ++k4) {
                 if (k4 * 4 < q.K) {
-                    const float4 t = wr[k4];          // same address in every lane: one shared-memory wavefront
-                    acc = fmaf(xv[4 * k4], t.x, acc);
-                    acc = fmaf(xv[4 * k4 + 1], t.y, acc);
-                    acc = fmaf(xv[4 * k4 + 2], t.z, acc);
-                    acc = fmaf(xv[4 * k4 + 3], t.w, acc);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (co + j < q.Co) {
+                            const float4 t = reinterpret_cast<const float4*>(ws + (size_t)(co + j) * q.K4)[k4];   // warp-uniform address
+                            acc[j] = fmaf(xv[4 * k4], t.x, acc[j]);
+                            acc[j] = fmaf(xv[4 * k4 + 1], t.y, acc[j]);
+                            acc[j] = fmaf(xv[4 * k4 + 2], t.z, acc[j]);
+                            acc[j] = fmaf(xv[4 * k4 + 3], t.w, acc[j]);
+                        }
+                    }
                 }
             }
-            if (q.relu) acc = fmaxf(acc, 0.0f);
-            if (q.nchw_out) o_nchw[(long long)co * q.P] = acc;     // a warp writes 32 consecutive positions of one plane
-            else o_rows[co] = acc;
+            if (q.relu) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[j] = fmaxf(acc[j], 0.0f);
+            }
+            if (rows4) {
+                *reinterpret_cast<float4*>(o_rows + co) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (co + j < q.Co) {
+                        if (q.nchw_out) o_nchw[(long long)(co + j) * q.P] = acc[j];     // a warp writes 32 consecutive positions of one plane
+                        else o_rows[co + j] = acc[j];
+                    }
+                }
+            }
         }
     }
 }

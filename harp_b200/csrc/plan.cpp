@@ -157,7 +157,7 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
         c.g_nchw = (d->flags & 1024) ? 1 : 0;
         c.has_bias = !c.wgrad && d->n_inputs == 3;
         c.mode = d->gemm_mode == EB200_GEMM_TF32 ? EB200_GEMM_TF32 : EB200_GEMM_3XTF32;
-        EB_REQUIRE(conv2d_supported(c), EB200_ERR_UNSUPPORTED, "conv2d shape is not served by the implicit-GEMM kernel (C*KH*KW <= 2048, stride 1)");
+        EB_REQUIRE(conv2d_supported(c), EB200_ERR_UNSUPPORTED, "conv2d shape is not served by the implicit-GEMM kernel (C*KH*KW <= 2048 unless C % 32 == 0, stride 1)");
         const long long Ho = c.H + 2 * c.pad - c.KH + 1, Wo = c.W + 2 * c.pad - c.KW + 1;
         const long long M = (long long)c.N * Ho * Wo, K = (long long)c.C * c.KH * c.KW;
         for (int i = 0; i <= d->n_inputs; ++i) {

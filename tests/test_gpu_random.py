@@ -90,3 +90,64 @@ def test_random_padded_gather_is_bit_exact(dev, seed):
     k = D.copy([h + pt + pb, wd + pl + pr], op)
     got, _ = run_gpu(dev, k, [x])
     assert got.tobytes() == O.run(k, [x]).tobytes()
+
+
+# ---- convolutions: forward, input gradient, weight gradient, every kernel form -----------------------
+
+def conv_case(seed):
+    rng = np.random.default_rng(1000 + seed)
+    k = int(rng.choice([1, 2, 3, 3, 3, 5]))
+    pad = int(rng.integers(0, k))                      # 0 .. k-1
+    c = int(rng.choice([1, 2, 3, 8, 16, 32, 64]))
+    co = int(rng.choice([4, 8, 12, 20, 32, 64, 96, 132]))
+    h = int(rng.integers(max(k - 2 * pad, 1), 15)) + (2 if k == 5 else 0)
+    wd = int(rng.integers(max(k - 2 * pad, 1), 15)) + (2 if k == 5 else 0)
+    n = int(rng.integers(1, 6))
+    while c * k * k > 2048:
+        c //= 2
+    return n, c, h, wd, co, k, pad
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_convolutions_all_forms(dev, seed):
+    """Seeded random layers through whichever kernel the library picks (tensor cores with
+    TMA / bulk / cp.async patch staging or direct gathers, channel-blocked or table k order,
+    the streaming f32 kernels for tiny reductions): forward with bias and ReLU in both
+    output layouts, the input gradient, the weight gradient where a one-kernel form is
+    served.  Reference: the oracle's loop nests; bound 1e-5 * sum |terms| (3xTF32 / f32)."""
+    n, c, h, wd, co, k, pad = conv_case(seed)
+    ho, wo = h + 2 * pad - k + 1, wd + 2 * pad - k + 1
+    rng = np.random.default_rng(seed)
+    x = rng.uniform(-1, 1, (n, c, h, wd)).astype(np.float32)
+    w_ = rng.uniform(-1, 1, (co, c, k, k)).astype(np.float32)
+    b = rng.uniform(-1, 1, co).astype(np.float32)
+    g = rng.uniform(-1, 1, (n, co, ho, wo)).astype(np.float32)
+    bound = 1e-5 * (c * k * k + 1)                       # |x|, |w|, |b| <= 1: sum |terms| <= K + 1
+    for nchw in (False, True):
+        kd = D.conv2d(n, c, h, wd, co, k, k, pad=pad, relu=True, nchw=nchw)
+        got, kern = run_gpu(dev, kd, [x, w_, b])
+        assert kern.impl.startswith("conv2d_"), kern.impl
+        assert np.abs(got - O.run(kd, [x, w_, b])).max() <= bound, (kern.impl, n, c, h, wd, co, k, pad)
+    # input gradient: the same class over flipped weights (pad' = k-1-pad >= 0 by construction)
+    from harp_b200 import capi
+    kd = D.conv2d(n, co, ho, wo, c, k, k, pad=k - 1 - pad, bias=False, flip=True, nchw=True)
+    if co % 32 == 0 or co * k * k <= 2048:               # else the per-k table would not fit: composed form instead
+        got, kern = run_gpu(dev, kd, [g, w_])
+        assert kern.impl.endswith("_dgrad"), kern.impl
+        assert np.abs(got - O.run(kd, [g, w_])).max() <= 1e-5 * (co * k * k + 1), kern.impl
+    else:
+        with pytest.raises(capi.Eb200Error) as e:
+            run_gpu(dev, kd, [g, w_])
+        assert e.value.status == capi.ERR_UNSUPPORTED
+    # weight gradient: rows layout always, planes layout for tiny reductions
+    grows = np.ascontiguousarray(g.transpose(0, 2, 3, 1)).reshape(n * ho * wo, co)
+    for g_nchw, gin in ((False, grows), (True, g)):
+        kd = D.conv2d_wgrad(n, c, h, wd, co, k, k, pad=pad, g_nchw=g_nchw)
+        try:
+            got, kern = run_gpu(dev, kd, [x, gin])
+        except capi.Eb200Error as e:                     # planes too large for shared memory, Co % 4 != 0, ...: composed form instead
+            assert e.status == capi.ERR_UNSUPPORTED
+            continue
+        assert kern.impl.endswith("_wgrad"), kern.impl
+        assert np.abs(got - O.run(kd, [x, gin])).max() <= 1e-5 * (n * ho * wo + 1), kern.impl
+    dev.synchronize()

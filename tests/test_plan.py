@@ -166,8 +166,9 @@ def test_conv2d_is_one_implicit_gemm_with_weight_scratch():
 
 def test_conv2d_rejects_what_the_kernel_does_not_serve():
     with pytest.raises(capi.Eb200Error) as e:
-        query(D.conv2d(1, 256, 8, 8, 16, 3, 3))              # K = 2304 > 2048
+        query(D.conv2d(1, 250, 8, 8, 16, 3, 3))              # K = 2250 > 2048 and the channels are not a multiple of 32
     assert e.value.status == capi.ERR_UNSUPPORTED
+    assert query(D.conv2d(1, 256, 8, 8, 16, 3, 3)).impl.decode() == "conv2d_igemm_3xtf32"     # K = 2304, channel-blocked: no table
     with pytest.raises(capi.Eb200Error):
         query(D.conv2d(1, 1, 2, 2, 4, 3, 3))                 # window larger than the padded image
     k = D.conv2d(2, 3, 8, 8, 4, 3, 3)
