@@ -56,6 +56,7 @@ struct KOperand {
     int bound_begin;
     int n_bounds;
     float pad;
+    int flat;                  // f32, unmasked and laid out exactly like the iteration space: element e sits at offset + e
 };
 
 struct KBound {

@@ -47,6 +47,10 @@ struct ConvParams {
     // patch geometry: PR x PW input pixels x CB channels, channel stride CH floats
     int staged, pstages, PR, PW, CB, CH, patch_floats;
     int load_mode;      // CV_LOAD_ROWS / CV_LOAD_BULK / CV_LOAD_TMA
+    int linear;         // CV_LOAD_BULK only: a tile is 128 consecutive positions of the flattened (n, oh, ow) space and may
+                        // span images (whole-row tiles would waste rows: 13 x 13 outputs fill 169 of 256); its patch
+                        // holds the planes of every image it touches
+    int P, Mtot;        // positions per image, positions in all
     int pcol;           // column of the tile's first window inside a patch row
     int patches_per_tile, kb_per_patch;
     int* error_flag;
@@ -228,6 +232,14 @@ conv2d_igemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         if (!ok) break;
                         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the gather's reads of this slot precede the copy
                         float* dst = patch0 + (size_t)p * q.patch_floats;
+                        if (q.linear) {
+                            const int mt = tile / q.n_tiles;
+                            const int n_lo = (mt * TC_BM) / q.P, n_hi = min(q.N - 1, (mt * TC_BM + TC_BM - 1) / q.P);
+                            mbar_expect_tx(&pfull[p], bytes * (unsigned)(n_hi - n_lo + 1));
+                            for (int n = n_lo; n <= n_hi; ++n)
+                                bulk_load(dst + (size_t)(n - n_lo) * q.CB * q.CH, x + ((long long)n * q.C + (long long)pp * q.CB) * q.H * q.W, bytes, &pfull[p]);
+                            continue;
+                        }
                         mbar_expect_tx(&pfull[p], bytes);
                         const long long plane = (long long)tc.n * q.C + (long long)pp * q.CB;
                         if (q.load_mode == CV_LOAD_BULK) bulk_load(dst, x + plane * q.H * q.W, bytes, &pfull[p]);     // CH == H * W
@@ -289,14 +301,21 @@ conv2d_igemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         bool ok = true;
         for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
             const TileCoord tc = tile_coord(q, tile / q.n_tiles);
-            const int oh = tc.oh0 + r_oh, ow = tc.ow0 + r_ow;
-            const bool live = r_oh < q.Rt && oh < q.Ho && ow < q.Wo;
+            int oh = tc.oh0 + r_oh, ow = tc.ow0 + r_ow, slot = 0;
+            bool live = r_oh < q.Rt && oh < q.Ho && ow < q.Wo;
+            if (q.linear) {
+                const int mt = tile / q.n_tiles, m = mt * TC_BM + t;
+                live = m < q.Mtot;
+                const int n = live ? m / q.P : 0, pos = live ? m - n * q.P : 0;
+                oh = pos / q.Wo; ow = pos - oh * q.Wo;
+                slot = n - (mt * TC_BM) / q.P;
+            }
             // staged: offset of this row's window origin inside the patch; direct: pointer into x
             int base_r = live ? r_oh * q.PW + r_ow + q.pcol : 0;
             unsigned vm = live ? 0xffffffffu : 0u;            // staged: which taps of this row's window to read
             if (q.staged && q.load_mode == CV_LOAD_BULK && live) {
                 // the patch is the raw image: the window origin may lie outside it, one bit per tap inside
-                base_r = (oh - q.pad) * q.W + (ow - q.pad);
+                base_r = slot * q.CB * q.CH + (oh - q.pad) * q.W + (ow - q.pad);
                 vm = 0;
                 for (int kh = 0; kh < q.KH; ++kh)
                     for (int kw = 0; kw < q.KW; ++kw)
@@ -377,9 +396,16 @@ conv2d_igemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++ti) {
             const unsigned buf = ti & 1u;
             const TileCoord tc = tile_coord(q, tile / q.n_tiles);
-            const int oh = tc.oh0 + r_oh, ow = tc.ow0 + r_ow;
-            const bool live = r_oh < q.Rt && oh < q.Ho && ow < q.Wo;
-            const long long orow = ((long long)tc.n * q.Ho + oh) * q.Wo + ow;
+            int oh = tc.oh0 + r_oh, ow = tc.ow0 + r_ow, n_img = tc.n;
+            bool live = r_oh < q.Rt && oh < q.Ho && ow < q.Wo;
+            if (q.linear) {
+                const int m = (tile / q.n_tiles) * TC_BM + r;
+                live = m < q.Mtot;
+                n_img = live ? m / q.P : 0;
+                const int pos = live ? m - n_img * q.P : 0;
+                oh = pos / q.Wo; ow = pos - oh * q.Wo;
+            }
+            const long long orow = ((long long)n_img * q.Ho + oh) * q.Wo + ow;
             const int n0 = (tile % q.n_tiles) * BN;
             ok = mbar_wait(&acc_full[buf], (ti >> 1) & 1u, q.error_flag);
             if (!ok) break;
@@ -403,7 +429,7 @@ conv2d_igemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 if (q.nchw) {
                     // one plane per channel: the warp's 32 positions are consecutive in every plane
                     const long long plane = (long long)q.Ho * q.Wo;
-                    float* d2 = out + (((long long)tc.n * q.Co + col0) * q.Ho + oh) * q.Wo + ow;
+                    float* d2 = out + (((long long)n_img * q.Co + col0) * q.Ho + oh) * q.Wo + ow;
 #pragma unroll
                     for (int i = 0; i < 32; ++i)
                         if (col0 + i < q.Co) d2[i * plane] = v[i];
@@ -504,11 +530,9 @@ int launch_conv2d(Device* dev, const Plan& plan, const float* x, const float* w,
     q.Rt = q.Wo <= TC_BM ? std::max(1, std::min(q.Ho, TC_BM / q.Wt)) : 1;
     q.tiles_w = (q.Wo + q.Wt - 1) / q.Wt;
     q.tiles_h = (q.Ho + q.Rt - 1) / q.Rt;
-    const long long m_tiles = (long long)c.N * q.tiles_h * q.tiles_w;
+    long long m_tiles = (long long)c.N * q.tiles_h * q.tiles_w;
+    int linear_imgs = 1;
     q.n_tiles = (c.Co + bn - 1) / bn;
-    EB_REQUIRE(m_tiles * q.n_tiles < (1LL << 31) - (1 << 20), EB200_ERR_UNSUPPORTED, "conv2d has too many tiles");
-    q.m_tiles = (int)m_tiles;
-    q.tiles = q.m_tiles * q.n_tiles;
     q.patches_per_tile = q.mode == CV_CBLOCK ? c.C / 32 : 1;
     q.kb_per_patch = q.mode == CV_CBLOCK ? q.taps : q.Kpad / TC_BK;
     // patch: the input pixels the tile's windows touch
@@ -523,6 +547,18 @@ int launch_conv2d(Device* dev, const Plan& plan, const float* x, const float* w,
         q.load_mode = CV_LOAD_BULK;          // whole channel planes, unpadded
         q.PR = c.H;
         q.PW = c.W;
+        q.P = q.Ho * q.Wo;
+        q.Mtot = c.N * q.P;
+        // whole-row tiles leave rows empty when Ho * Wo is not close to a multiple of 128: tile the
+        // flattened position space instead when that saves a fifth of the tiles and the patch still fits
+        const int per_image = q.tiles_h * q.tiles_w, imgs = (TC_BM - 1) / q.P + 2;
+        int linear_ok = 1;
+        if (const char* e = getenv("EB200_CONV_LINEAR")) linear_ok = atoi(e);
+        if (linear_ok && (long long)per_image * TC_BM * 5 >= (long long)q.P * 6 &&
+            (long long)imgs * q.CB * c.H * c.W * 4 <= CV_MAX_PATCH_BYTES) {
+            q.linear = 1;
+            linear_imgs = imgs;
+        }
     } else if (load_limit >= 2 && aligned && c.W % 4 == 0 && q.CB <= 256 && q.PR <= 256 && q.PW + 6 <= 256) {
         q.load_mode = CV_LOAD_TMA;
         q.pcol = (4 - c.pad % 4) % 4;
@@ -531,7 +567,7 @@ int launch_conv2d(Device* dev, const Plan& plan, const float* x, const float* w,
         q.load_mode = CV_LOAD_ROWS;
     }
     q.CH = q.PR * q.PW;
-    q.patch_floats = (q.CB * q.CH + 31) / 32 * 32;
+    q.patch_floats = (linear_imgs * q.CB * q.CH + 31) / 32 * 32;
 
     const int stage_bytes = (q.three_pass ? 2 : 1) * (TC_TILE_BYTES + bn * TC_BK * 4);
     const size_t ktab_bytes = (size_t)(q.mode == CV_CBLOCK ? q.taps : q.Kpad) * sizeof(int2);
@@ -544,7 +580,11 @@ int launch_conv2d(Device* dev, const Plan& plan, const float* x, const float* w,
         q.pstages = patch_bytes * 3 + 2 * (size_t)stage_bytes + fixed <= budget ? 3 : 2;
         if (patch_bytes * q.pstages + 2 * (size_t)stage_bytes + fixed > budget) q.staged = 0;
     }
-    if (!q.staged) { q.pstages = 1; q.patch_floats = 0; }
+    if (!q.staged) { q.pstages = 1; q.patch_floats = 0; q.linear = 0; }
+    if (q.linear) m_tiles = ((long long)q.Mtot + TC_BM - 1) / TC_BM;
+    EB_REQUIRE(m_tiles * q.n_tiles < (1LL << 31) - (1 << 20), EB200_ERR_UNSUPPORTED, "conv2d has too many tiles");
+    q.m_tiles = (int)m_tiles;
+    q.tiles = q.m_tiles * q.n_tiles;
     q.stages = (int)std::min<size_t>(6, (budget - fixed - (size_t)q.pstages * q.patch_floats * 4) / stage_bytes);
     EB_REQUIRE(q.stages >= 2, EB200_ERR_UNSUPPORTED, "conv2d tile does not fit shared memory");
     const size_t smem = (size_t)q.stages * stage_bytes + (size_t)q.pstages * q.patch_floats * 4 + fixed;

@@ -77,6 +77,57 @@ __global__ void __launch_bounds__(256) ew_kernel(const __grid_constant__ KParams
                 }
             }
         }
+    } else if (p.vec == 2) {
+        // groups of four consecutive elements per thread (see the planner): one decomposition, the
+        // multi-index then advances with carries; EW_G groups in flight
+        constexpr int EW_G = 2;
+        constexpr int RK = ND > 0 ? ND : KMAX_DIMS;
+        const long long ngrp = p.total >> 2;
+        for (long long g0 = ((long long)blockIdx.x * EW_G) * blockDim.x + threadIdx.x; g0 < ngrp; g0 += EW_G * stride) {
+            float in[EW_G][KMAX_IN][4];
+#pragma unroll
+            for (int u = 0; u < EW_G; ++u) {
+                const long long g = g0 + (long long)u * blockDim.x;
+                if (g < ngrp) {
+                    long long idx[KMAX_DIMS];
+                    decompose<ND>(p, g << 2, idx);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                        for (int i = 0; i < (F::kCompiled ? n : KMAX_IN); ++i) {
+                            if (i >= n) break;
+                            const KOperand& o = p.in[i];
+                            if (o.flat) {
+                                if (j == 0) {
+                                    const float4 t = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(o.ptr) + o.offset + (g << 2)));
+                                    in[u][i][0] = t.x; in[u][i][1] = t.y; in[u][i][2] = t.z; in[u][i][3] = t.w;
+                                }
+                            } else if (o.n_bounds && !bounds_ok(p, o, idx)) {
+                                in[u][i][j] = o.pad;
+                            } else {
+                                in[u][i][j] = load_elem(o, operand_index<ND>(p, o, idx));
+                            }
+                        }
+                        // next element: innermost index + 1, carries outward
+#pragma unroll
+                        for (int d = RK - 1; d >= 0; --d) {
+                            if (ND == 0 && d >= p.ndim) continue;
+                            if (++idx[d] < p.shape[d]) break;
+                            idx[d] = 0;
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < EW_G; ++u) {
+                const long long g = g0 + (long long)u * blockDim.x;
+                if (g < ngrp) {
+                    float r[4];
+                    F::template eval<4>(p, in[u], r, cl);
+                    *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out.ptr) + p.out.offset + (g << 2)) = make_float4(r[0], r[1], r[2], r[3]);
+                }
+            }
+        }
     } else {
         // scalar path: EW_U independent elements per thread in flight (the loads of all of
         // them are issued before the first is evaluated); a CTA owns EW_U consecutive
@@ -115,9 +166,9 @@ __global__ void __launch_bounds__(256) ew_kernel(const __grid_constant__ KParams
 
 template <class F>
 static int launch_one(Device* dev, const KParams& p) {
-    long long work = p.vec == 4 ? (p.total >> 2) : p.total;
+    long long work = p.vec == 1 ? p.total : (p.total >> 2);
     if (work <= 0) return EB200_OK;
-    long long per_block = 256LL * EW_U;
+    long long per_block = 256LL * (p.vec == 2 ? 2 : EW_U);
     long long blocks = (work + per_block - 1) / per_block;
     long long cap = (long long)dev->prop.multiProcessorCount * 32;
     if (blocks > cap) blocks = cap;
@@ -125,6 +176,7 @@ static int launch_one(Device* dev, const KParams& p) {
     // (dims past the rank have extent 1 and stride 0); everything else takes the any-rank form
     int nd = 0;
     if (p.total < (1LL << 31)) nd = p.ndim <= 4 ? p.ndim : (p.ndim <= 6 && p.vec != 4 ? 6 : 0);
+    if (p.vec == 2 && nd == 1) nd = 0;      // (rank 1 never plans groups of four; keep the switch total)
     const unsigned g = (unsigned)blocks;
     switch (nd) {
         case 1: ew_kernel<F, 1><<<g, 256, 0, dev->stream>>>(p); break;

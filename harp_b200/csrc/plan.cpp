@@ -509,6 +509,27 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
                 for (int i = 0; v && i < p.n_in; ++i) v = vec_ok(p.in[i], inner, false);
                 p.vec = v ? 4 : 1;
                 snprintf(pl.name, sizeof(pl.name), "ew_chain_v%d", p.vec);
+                if (!v && nk >= 2 && total % 4 == 0 && total >= 1024) {
+                    // "groups of four": the output is a plain contiguous f32 array, so a thread can own four
+                    // consecutive elements (one index decomposition, one 128-bit store) even when some
+                    // operand is strided, broadcast or masked along the inner dims: those are read element
+                    // by element, operands laid out like the iteration space with one 128-bit load
+                    auto flat = [&](const KOperand& ko) {
+                        if (ko.dtype != EB200_F32 || ko.n_bounds || ko.offset % 4) return false;
+                        long long acc = 1;
+                        for (int j = nk - 1; j >= 0; --j) { if (shape[j] > 1 && ko.strides[j] != acc) return false; acc *= shape[j]; }
+                        return true;
+                    };
+                    // worth it only when some operand comes in with 128-bit loads: with every operand
+                    // strided the four per-element index computations cost more than they save
+                    int n_flat = 0;
+                    for (int i = 0; i < p.n_in; ++i) n_flat += flat(p.in[i]) ? 1 : 0;
+                    if (flat(p.out) && n_flat > 0) {
+                        p.vec = 2;
+                        for (int i = 0; i < p.n_in; ++i) p.in[i].flat = flat(p.in[i]) ? 1 : 0;
+                        snprintf(pl.name, sizeof(pl.name), "ew_chain_g4");
+                    }
+                }
             }
             break;
         }

@@ -204,3 +204,18 @@ def test_conv2d_gradient_forms():
     with pytest.raises(capi.Eb200Error) as e:
         query(D.conv2d_wgrad(8, 64, 56, 56, 64, 3, 3, pad=1))   # image planes (802 KB) do not fit shared memory
     assert e.value.status == capi.ERR_UNSUPPORTED
+
+
+def test_groups_of_four_when_an_operand_is_laid_out_like_the_output():
+    # max-pool gradient: the input (laid out like the output) against broadcast pooled value and gradient
+    full = [4096, 32, 13, 2, 13, 2]
+    x6 = D.contiguous(full)
+    bc = D.Operand([5408, 169, 13, 0, 1, 0], 0, D.F32, 4096 * 32 * 169)
+    k = D.KernelDesc(D.K_ELEMENTWISE, full, [bc, x6, bc], D.contiguous(full), Ast.select(w(1).lt(w(2)), 0.0, w(0)))
+    assert query(k).impl.decode() == "ew_chain_g4"
+    # every operand strided (max-pool forward as four taps): the plain scalar kernel is faster
+    taps = [D.Operand([5408 * 4, 676, 52, 2], off, D.F32, 4096 * 32 * 676) for off in (0, 1, 26, 27)]
+    k = D.KernelDesc(D.K_ELEMENTWISE, [4096, 32, 13, 13], taps, D.contiguous([4096, 32, 13, 13]),
+                     w(0).maximum(w(1)).maximum(w(2)).maximum(w(3)))
+    assert query(k).impl.decode() == "ew_chain_v1"
+    assert query(W.cfg2_t()).impl.decode() == "transpose_copy"
