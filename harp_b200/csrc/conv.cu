@@ -893,12 +893,14 @@ int launch_conv2d_wgrad(Device* dev, const Plan& plan, const float* x, const flo
     CUtensorMap mg;
     int st;
     if ((st = make_map(&mg, g, c.Co, (long long)c.N * q.P, 1, c.Co, 0, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))) return st;
-    static bool configured = false;
-    if (!configured) {
+    // function attributes are per device: one bit per device index
+    static unsigned long long configured_devices = 0;
+    const unsigned long long dev_bit = 1ULL << (dev->index & 63);
+    if (!(configured_devices & dev_bit)) {
         EB_CHECK_CUDA(cudaFuncSetAttribute(conv2d_wgrad_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
         EB_CHECK_CUDA(cudaFuncSetAttribute(conv2d_wgrad_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
         EB_CHECK_CUDA(cudaFuncSetAttribute(conv2d_wgrad_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024));
-        configured = true;
+        configured_devices |= dev_bit;
     }
     float* partials = reinterpret_cast<float*>(scratch);
     const unsigned grid = (unsigned)(q.m_tiles * q.streams);

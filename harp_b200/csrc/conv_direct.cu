@@ -6,6 +6,8 @@
 // values in registers, the weights sit in shared memory and are read warp-uniformly.
 // Accumulation is f32 FMA in the reference's (c, kh, kw) order
 // (crates/nn/src/functional/conv.rs:113-184 lowers to a sequential sum over k).
+#include <stdlib.h>
+
 #include <algorithm>
 
 #include "common.h"
@@ -17,7 +19,7 @@ struct DirectParams {
     int Ho, Wo, P, K, K4;      // positions per image; K rounded up to a multiple of 4
     long long M;               // N * P
     int relu, has_bias, flip, nchw_out, g_nchw;
-    int streams, chunks;       // weight gradient: position streams x 8-channel chunks
+    int streams, chunks;       // weight gradient: position streams x channel chunks (8 or 4 channels per warp)
 };
 
 __device__ __forceinline__ void window_offsets(const DirectParams& q, int k, int& off, int& kh, int& kw) {
@@ -113,7 +115,7 @@ __global__ void __launch_bounds__(256) conv2d_direct_kernel(const __grid_constan
 // dW[co][k] = sum_m g[m][co] * x_k[m].  A warp owns one chunk of 8 output channels and a stream
 // of positions (lane = position); 8 x K accumulators per thread, folded over the lanes by
 // shuffles at the end, one partial per stream summed in stream order afterwards.
-template <int KT>
+template <int KT, int CHN, int UP>
 __global__ void __launch_bounds__(256) conv2d_direct_wgrad_kernel(const __grid_constant__ DirectParams q, const float* __restrict__ x,
                                                                   const float* __restrict__ g, float* __restrict__ partials) {
     __shared__ int2 ktab[KT];                       // per k: {offset of the tap in the window, kh | kw << 16}
@@ -127,18 +129,18 @@ __global__ void __launch_bounds__(256) conv2d_direct_wgrad_kernel(const __grid_c
     const int wg = (int)blockIdx.x * 8 + (threadIdx.x >> 5);
     const int chunk = wg % q.chunks, stream = wg / q.chunks;
     if (stream >= q.streams) return;
-    const int co0 = chunk * 8;
+    const int co0 = chunk * CHN;
     const unsigned M = (unsigned)q.M, step = (unsigned)q.streams * 32u;
-    float acc[8][KT];
+    float acc[CHN][KT];
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
+    for (int j = 0; j < CHN; ++j)
 #pragma unroll
         for (int k = 0; k < KT; ++k) acc[j][k] = 0.0f;
-    // two positions per lane in flight: their loads are all issued before the first FMA
-    for (unsigned m0 = (unsigned)stream * 32u + lane; m0 < M; m0 += 2u * step) {
-        float xv[2][KT], gv[2][8];
+    // UP positions per lane in flight: their loads are all issued before the first FMA
+    for (unsigned m0 = (unsigned)stream * 32u + lane; m0 < M; m0 += (unsigned)UP * step) {
+        float xv[UP][KT], gv[UP][CHN];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < UP; ++u) {
             const unsigned m = m0 + u * step;
             const bool live = m < M;
             const unsigned n = live ? m / (unsigned)q.P : 0u, pos = live ? m - n * (unsigned)q.P : 0u;
@@ -154,17 +156,17 @@ __global__ void __launch_bounds__(256) conv2d_direct_wgrad_kernel(const __grid_c
             const float* gp = q.g_nchw ? g + ((long long)n * q.Co + co0) * q.P + pos : g + (long long)m * q.Co + co0;
             const long long gs = q.g_nchw ? (long long)q.P : 1LL;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) gv[u][j] = (live && co0 + j < q.Co) ? __ldg(gp + j * gs) : 0.0f;
+            for (int j = 0; j < CHN; ++j) gv[u][j] = (live && co0 + j < q.Co) ? __ldg(gp + j * gs) : 0.0f;
         }
 #pragma unroll
-        for (int u = 0; u < 2; ++u)
+        for (int u = 0; u < UP; ++u)
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
+            for (int j = 0; j < CHN; ++j)
 #pragma unroll
                 for (int k = 0; k < KT; ++k) acc[j][k] = fmaf(gv[u][j], xv[u][k], acc[j][k]);
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
+    for (int j = 0; j < CHN; ++j)
 #pragma unroll
         for (int k = 0; k < KT; ++k) {
             float v = acc[j][k];
@@ -194,9 +196,16 @@ bool conv2d_direct_supported(const ConvShape& c) {
     return K <= 32 && (long long)c.Co * ((K + 3) / 4 * 4 + 1) * 4 <= 48 * 1024;
 }
 
+static int direct_variant() {        // 8: 8 channels x 2 positions, 4: 4 x 4, 2: 4 x 2 (measurement switch)
+    static int v = 0;
+    if (!v) { const char* e = getenv("EB200_DWGRAD"); v = e ? atoi(e) : 2; if (v != 8 && v != 4) v = 2; }
+    return v;
+}
+static int direct_chn() { return direct_variant() == 8 ? 8 : 4; }
+
 static int direct_streams(const ConvShape& c, int sms) {
-    const int chunks = (c.Co + 7) / 8;
-    return std::max(1, (sms * 16) / chunks);       // two CTAs of eight warps per SM
+    const int chunks = (c.Co + direct_chn() - 1) / direct_chn();
+    return std::max(1, (sms * 32) / chunks);       // four CTAs of eight warps per SM
 }
 
 long long conv2d_direct_wgrad_scratch_floats(const ConvShape& c, int sms) {
@@ -222,12 +231,16 @@ int launch_conv2d_direct_wgrad(Device* dev, const Plan& plan, const float* x, co
     const ConvShape& c = plan.conv;
     EB_REQUIRE(scratch, EB200_ERR_INVALID, "conv2d weight gradient launched without scratch");
     DirectParams q = direct_params(c);
-    q.chunks = (c.Co + 7) / 8;
+    q.chunks = (c.Co + direct_chn() - 1) / direct_chn();
     q.streams = direct_streams(c, dev->prop.multiProcessorCount);
     float* partials = reinterpret_cast<float*>(scratch);
     const unsigned grid = (unsigned)((q.streams * q.chunks + 7) / 8);
     EB_REQUIRE(q.K <= 12, EB200_ERR_UNSUPPORTED, "direct weight gradient serves K <= 12");
-    conv2d_direct_wgrad_kernel<12><<<grid, 256, 0, dev->stream>>>(q, x, g, partials);
+    // measured on conv1 of config 4 (batch 4096): 4 channels x 2 positions per lane (128 registers, two
+    // CTAs per SM) 0.43 ms, 8 x 2 (191 registers) 0.52 ms, 4 x 4 (164 registers) 0.59 ms
+    if (direct_variant() == 8) conv2d_direct_wgrad_kernel<12, 8, 2><<<grid, 256, 0, dev->stream>>>(q, x, g, partials);
+    else if (direct_variant() == 2) conv2d_direct_wgrad_kernel<12, 4, 2><<<grid, 256, 0, dev->stream>>>(q, x, g, partials);
+    else conv2d_direct_wgrad_kernel<12, 4, 4><<<grid, 256, 0, dev->stream>>>(q, x, g, partials);
     count_launch();
     EB_CHECK_CUDA(cudaGetLastError());
     // dW[co][k] = sum over streams of partials[stream][co][k]

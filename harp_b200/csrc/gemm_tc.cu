@@ -46,6 +46,7 @@ struct TcParams {
     int stages;
     int raster;        // tile rows per band
     int tiles_n;
+    int ks;            // two-CTA kernel: 32-wide k blocks per pipeline stage (2 halves the barrier round trips per MMA)
     int* error_flag;
 };
 
@@ -250,7 +251,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     constexpr int BN = 256, HALF = 128;                // pair tile columns; columns staged per CTA
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    const int stage_bytes = (q.three_pass ? 4 : 2) * TC_TILE_BYTES;   // A and B half tiles are both 128 x 32
+    const int sub_bytes = (q.three_pass ? 4 : 2) * TC_TILE_BYTES;     // A and B half tiles are both 128 x 32
+    const int stage_bytes = q.ks * sub_bytes;                          // a stage holds q.ks consecutive k blocks
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)q.stages * stage_bytes);
     uint64_t* empty_bar = full_bar + q.stages;
     uint64_t* acc_bar = empty_bar + q.stages;
@@ -270,7 +272,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int bz = (int)blockIdx.z / q.splits, split = (int)blockIdx.z % q.splits;
     const int total_kb = (int)((q.k + TC_BK - 1) / TC_BK);
     const int kb_begin = split * q.kb_per_split;
-    const int num_kb = min(total_kb - kb_begin, q.kb_per_split);
+    const int num_kb32 = min(total_kb - kb_begin, q.kb_per_split);
+    const int num_kb = (num_kb32 + q.ks - 1) / q.ks;     // pipeline stages to walk; a k block past K arrives as zeros (TMA fill)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < q.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -294,33 +297,35 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             for (int kb = 0; kb < num_kb; ++kb, s = (s + 1 == q.stages ? 0 : s + 1), phase ^= (s == 0)) {
                 if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], phase ^ 1u, q.error_flag))) break;
                 if (elect_one()) {
-                    unsigned char* st = smem + (size_t)s * stage_bytes;
                     // every load of the pair completes on the even CTA's barrier
                     const uint32_t lead = map_to_cta(smem_u32(&full_bar[s]), 0);
                     if (rank == 0) mbar_expect_tx(&full_bar[s], 2u * (unsigned)stage_bytes);
-                    const int kx = (kb_begin + kb) * TC_BK;
-                    unsigned char* a_hi = st;
-                    unsigned char* b_hi = st + (q.three_pass ? 2 : 1) * TC_TILE_BYTES;
                     const int nb = (int)n0 + (int)rank * HALF;    // this CTA's half of the columns
-                    if (q.a_mmajor) {
+                    for (int u = 0; u < q.ks; ++u) {
+                        unsigned char* st = smem + (size_t)s * stage_bytes + (size_t)u * sub_bytes;
+                        const int kx = (kb_begin + kb * q.ks + u) * TC_BK;
+                        unsigned char* a_hi = st;
+                        unsigned char* b_hi = st + (q.three_pass ? 2 : 1) * TC_TILE_BYTES;
+                        if (q.a_mmajor) {
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            tma_load_3d_pair(a_hi + j * 4096, &map_a, lead, (int)m0 + j * 32, kx, bz * a_zmul);
-                            if (q.three_pass) tma_load_3d_pair(st + TC_TILE_BYTES + j * 4096, &map_alo, lead, (int)m0 + j * 32, kx, bz * a_zmul);
+                            for (int j = 0; j < 4; ++j) {
+                                tma_load_3d_pair(a_hi + j * 4096, &map_a, lead, (int)m0 + j * 32, kx, bz * a_zmul);
+                                if (q.three_pass) tma_load_3d_pair(st + TC_TILE_BYTES + j * 4096, &map_alo, lead, (int)m0 + j * 32, kx, bz * a_zmul);
+                            }
+                        } else {
+                            tma_load_3d_pair(a_hi, &map_a, lead, kx, (int)m0, bz * a_zmul);
+                            if (q.three_pass) tma_load_3d_pair(st + TC_TILE_BYTES, &map_alo, lead, kx, (int)m0, bz * a_zmul);
                         }
-                    } else {
-                        tma_load_3d_pair(a_hi, &map_a, lead, kx, (int)m0, bz * a_zmul);
-                        if (q.three_pass) tma_load_3d_pair(st + TC_TILE_BYTES, &map_alo, lead, kx, (int)m0, bz * a_zmul);
-                    }
-                    if (q.b_nmajor) {
+                        if (q.b_nmajor) {
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            tma_load_3d_pair(b_hi + j * 4096, &map_b, lead, nb + j * 32, kx, bz * b_zmul);
-                            if (q.three_pass) tma_load_3d_pair(b_hi + TC_TILE_BYTES + j * 4096, &map_blo, lead, nb + j * 32, kx, bz * b_zmul);
+                            for (int j = 0; j < 4; ++j) {
+                                tma_load_3d_pair(b_hi + j * 4096, &map_b, lead, nb + j * 32, kx, bz * b_zmul);
+                                if (q.three_pass) tma_load_3d_pair(b_hi + TC_TILE_BYTES + j * 4096, &map_blo, lead, nb + j * 32, kx, bz * b_zmul);
+                            }
+                        } else {
+                            tma_load_3d_pair(b_hi, &map_b, lead, kx, nb, bz * b_zmul);
+                            if (q.three_pass) tma_load_3d_pair(b_hi + TC_TILE_BYTES, &map_blo, lead, kx, nb, bz * b_zmul);
                         }
-                    } else {
-                        tma_load_3d_pair(b_hi, &map_b, lead, kx, nb, bz * b_zmul);
-                        if (q.three_pass) tma_load_3d_pair(b_hi + TC_TILE_BYTES, &map_blo, lead, kx, nb, bz * b_zmul);
                     }
                 }
                 __syncwarp();
@@ -339,17 +344,19 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 for (int kb = 0; kb < num_kb; ++kb, s = (s + 1 == q.stages ? 0 : s + 1), phase ^= (s == 0)) {
                     if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[s], phase, q.error_flag))) break;
                     tc_fence_after();
-                    const uint32_t st = smem_base + (uint32_t)s * (uint32_t)stage_bytes;
-                    const uint64_t da0 = umma_desc(st, a_lbo, a_sbo, a_layout), dal0 = umma_desc(st + TC_TILE_BYTES, a_lbo, a_sbo, a_layout);
-                    const uint64_t db0 = umma_desc(st + b_off, b_lbo, b_sbo, b_layout), dbl0 = umma_desc(st + b_off + TC_TILE_BYTES, b_lbo, b_sbo, b_layout);
                     if (elect_one()) {
+                        for (int u = 0; u < q.ks; ++u) {
+                            const uint32_t st = smem_base + (uint32_t)s * (uint32_t)stage_bytes + (uint32_t)u * (uint32_t)sub_bytes;
+                            const uint64_t da0 = umma_desc(st, a_lbo, a_sbo, a_layout), dal0 = umma_desc(st + TC_TILE_BYTES, a_lbo, a_sbo, a_layout);
+                            const uint64_t db0 = umma_desc(st + b_off, b_lbo, b_sbo, b_layout), dbl0 = umma_desc(st + b_off + TC_TILE_BYTES, b_lbo, b_sbo, b_layout);
 #pragma unroll
-                        for (int j = 0; j < TC_BK / TC_UK; ++j) {
-                            const uint64_t da = da0 + j * a_jstep, db = db0 + j * b_jstep;
-                            umma_tf32_pair(tmem_base, da, db, idesc, (kb > 0 || j > 0) ? 1u : 0u);
-                            if (q.three_pass) {
-                                umma_tf32_pair(tmem_base, dal0 + j * a_jstep, db, idesc, 1u);
-                                umma_tf32_pair(tmem_base, da, dbl0 + j * b_jstep, idesc, 1u);
+                            for (int j = 0; j < TC_BK / TC_UK; ++j) {
+                                const uint64_t da = da0 + j * a_jstep, db = db0 + j * b_jstep;
+                                umma_tf32_pair(tmem_base, da, db, idesc, (kb > 0 || u > 0 || j > 0) ? 1u : 0u);
+                                if (q.three_pass) {
+                                    umma_tf32_pair(tmem_base, dal0 + j * a_jstep, db, idesc, 1u);
+                                    umma_tf32_pair(tmem_base, da, dbl0 + j * b_jstep, idesc, 1u);
+                                }
                             }
                         }
                         umma_commit_pair(&empty_bar[s]);
@@ -511,6 +518,7 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
         q.c_off = 0; q.c_sm = g.n; q.c_sn = 1; q.c_sb = g.m * g.n;
     }
     q.three_pass = three ? 1 : 0;
+    q.ks = 1;
     // two-CTA pairs (256 x 256 per pair) when there are enough pair tiles to fill the machine
     const long long pair_tiles = ((g.m + 255) / 256) * ((g.n + 255) / 256) * g.batch * g.splits;
     bool two_cta = g.m > 128 && pair_tiles * 2 >= dev->prop.multiProcessorCount;
@@ -531,8 +539,12 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
             if ((st = make_map(&mb, b_hi, g.k, g.n, b_b, g.b_sn, g.b_sb, 128))) return st;
             if ((st = make_map(&mbl, b_lo, g.k, g.n, b_b, g.b_sn, g.b_sb, 128))) return st;
         }
-        const int stage_bytes = (three ? 4 : 2) * TC_TILE_BYTES;
+        // plain TF32 with a long K: two k blocks per stage, half as many barrier round trips per MMA
+        q.ks = (!three && g.splits == 1 && g.k >= 256) ? 2 : 1;
+        if (const char* e = getenv("EB200_TC_KS")) q.ks = atoi(e) == 2 && g.splits == 1 ? 2 : 1;
+        const int stage_bytes = q.ks * (three ? 4 : 2) * TC_TILE_BYTES;
         q.stages = std::min(8, (196 * 1024) / stage_bytes);
+        EB_REQUIRE(q.stages >= 2, EB200_ERR_UNSUPPORTED, "GEMM stage does not fit shared memory twice");
         const size_t smem = (size_t)q.stages * stage_bytes + 1024 + 256;
         const long long tm2 = (g.m + 255) / 256, tn2 = (g.n + 255) / 256;
         const long long bands = (tm2 + q.raster - 1) / q.raster;

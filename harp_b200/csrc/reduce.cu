@@ -522,10 +522,11 @@ static int launch_one(Device* dev, const Plan& plan, const KParams& p, float* sc
                          p.error_flag != nullptr && p.kept >= sms;
         if (tma) {
             const size_t smem = (size_t)RT_WARPS * RT_ST * RT_CH * 4 + RT_WARPS * RT_ST * 8;
-            static bool configured = false;
-            if (!configured) {
+            static unsigned long long configured_devices = 0;      // function attributes are per device
+            const unsigned long long dev_bit = 1ULL << (dev->index & 63);
+            if (!(configured_devices & dev_bit)) {
                 EB_CHECK_CUDA(cudaFuncSetAttribute(reduce_inner_tma_kernel<F>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-                configured = true;
+                configured_devices |= dev_bit;
             }
             long long g = std::min<long long>(sms, (p.kept + RT_WARPS - 1) / RT_WARPS);
             reduce_inner_tma_kernel<F><<<(unsigned)g, RT_WARPS * 32, smem, dev->stream>>>(p);
