@@ -47,6 +47,7 @@ struct TcParams {
     int raster;        // tile rows per band
     int tiles_n;
     int ks;            // two-CTA kernel: 32-wide k blocks per pipeline stage (2 halves the barrier round trips per MMA)
+    int nh;            // two-CTA kernel: 256-column halves per pair tile (2: a 256 x 512 tile, the whole tensor memory)
     int* error_flag;
 };
 
@@ -248,10 +249,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_alo,
                 const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_blo,
                 const __grid_constant__ TcParams q, float* __restrict__ C, int a_zmul, int b_zmul) {
-    constexpr int BN = 256, HALF = 128;                // pair tile columns; columns staged per CTA
+    constexpr int HALF = 128;                           // columns of one 256-wide MMA that each CTA stages
+    const int BN = 256 * q.nh;                          // pair tile columns: one or two 256-wide MMA halves
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    const int sub_bytes = (q.three_pass ? 4 : 2) * TC_TILE_BYTES;     // A and B half tiles are both 128 x 32
+    const int sub_bytes = (q.three_pass ? 2 : 1) * (1 + q.nh) * TC_TILE_BYTES;     // A tile and nh B tiles, all 128 x 32
     const int stage_bytes = q.ks * sub_bytes;                          // a stage holds q.ks consecutive k blocks
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)q.stages * stage_bytes);
     uint64_t* empty_bar = full_bar + q.stages;
@@ -305,7 +307,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         unsigned char* st = smem + (size_t)s * stage_bytes + (size_t)u * sub_bytes;
                         const int kx = (kb_begin + kb * q.ks + u) * TC_BK;
                         unsigned char* a_hi = st;
-                        unsigned char* b_hi = st + (q.three_pass ? 2 : 1) * TC_TILE_BYTES;
                         if (q.a_mmajor) {
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
@@ -316,15 +317,20 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                             tma_load_3d_pair(a_hi, &map_a, lead, kx, (int)m0, bz * a_zmul);
                             if (q.three_pass) tma_load_3d_pair(st + TC_TILE_BYTES, &map_alo, lead, kx, (int)m0, bz * a_zmul);
                         }
-                        if (q.b_nmajor) {
+                        for (int h = 0; h < q.nh; ++h) {
+                            // layout of a k block: [A hi | (A lo) | B(h=0) hi | (lo) | B(h=1) hi | (lo)]
+                            unsigned char* b_hi = st + (q.three_pass ? 2 : 1) * (1 + h) * TC_TILE_BYTES;
+                            const int nbh = nb + h * 256;
+                            if (q.b_nmajor) {
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                tma_load_3d_pair(b_hi + j * 4096, &map_b, lead, nb + j * 32, kx, bz * b_zmul);
-                                if (q.three_pass) tma_load_3d_pair(b_hi + TC_TILE_BYTES + j * 4096, &map_blo, lead, nb + j * 32, kx, bz * b_zmul);
+                                for (int j = 0; j < 4; ++j) {
+                                    tma_load_3d_pair(b_hi + j * 4096, &map_b, lead, nbh + j * 32, kx, bz * b_zmul);
+                                    if (q.three_pass) tma_load_3d_pair(b_hi + TC_TILE_BYTES + j * 4096, &map_blo, lead, nbh + j * 32, kx, bz * b_zmul);
+                                }
+                            } else {
+                                tma_load_3d_pair(b_hi, &map_b, lead, kx, nbh, bz * b_zmul);
+                                if (q.three_pass) tma_load_3d_pair(b_hi + TC_TILE_BYTES, &map_blo, lead, kx, nbh, bz * b_zmul);
                             }
-                        } else {
-                            tma_load_3d_pair(b_hi, &map_b, lead, kx, nb, bz * b_zmul);
-                            if (q.three_pass) tma_load_3d_pair(b_hi + TC_TILE_BYTES, &map_blo, lead, kx, nb, bz * b_zmul);
                         }
                     }
                 }
@@ -332,7 +338,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             }
         } else if (warp == 1) {
             if (rank == 0) {
-                const uint32_t idesc = umma_idesc_tf32(256, BN, q.a_mmajor, q.b_nmajor);
+                const uint32_t idesc = umma_idesc_tf32(256, 256, q.a_mmajor, q.b_nmajor);
                 const uint32_t a_lbo = q.a_mmajor ? 4096 : 16, a_sbo = q.a_mmajor ? 512 : 1024, a_layout = q.a_mmajor ? 1 : 2;
                 const uint32_t b_lbo = q.b_nmajor ? 4096 : 16, b_sbo = q.b_nmajor ? 512 : 1024, b_layout = q.b_nmajor ? 1 : 2;
                 const uint64_t a_jstep = (q.a_mmajor ? 1024u : (unsigned)(TC_UK * 4)) >> 4;
@@ -348,14 +354,18 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         for (int u = 0; u < q.ks; ++u) {
                             const uint32_t st = smem_base + (uint32_t)s * (uint32_t)stage_bytes + (uint32_t)u * (uint32_t)sub_bytes;
                             const uint64_t da0 = umma_desc(st, a_lbo, a_sbo, a_layout), dal0 = umma_desc(st + TC_TILE_BYTES, a_lbo, a_sbo, a_layout);
-                            const uint64_t db0 = umma_desc(st + b_off, b_lbo, b_sbo, b_layout), dbl0 = umma_desc(st + b_off + TC_TILE_BYTES, b_lbo, b_sbo, b_layout);
+                            for (int h = 0; h < q.nh; ++h) {
+                                const uint32_t bh = st + b_off * (1 + h);
+                                const uint64_t db0 = umma_desc(bh, b_lbo, b_sbo, b_layout), dbl0 = umma_desc(bh + TC_TILE_BYTES, b_lbo, b_sbo, b_layout);
+                                const uint32_t acc = tmem_base + h * 256;          // columns of this half
 #pragma unroll
-                            for (int j = 0; j < TC_BK / TC_UK; ++j) {
-                                const uint64_t da = da0 + j * a_jstep, db = db0 + j * b_jstep;
-                                umma_tf32_pair(tmem_base, da, db, idesc, (kb > 0 || u > 0 || j > 0) ? 1u : 0u);
-                                if (q.three_pass) {
-                                    umma_tf32_pair(tmem_base, dal0 + j * a_jstep, db, idesc, 1u);
-                                    umma_tf32_pair(tmem_base, da, dbl0 + j * b_jstep, idesc, 1u);
+                                for (int j = 0; j < TC_BK / TC_UK; ++j) {
+                                    const uint64_t da = da0 + j * a_jstep, db = db0 + j * b_jstep;
+                                    umma_tf32_pair(acc, da, db, idesc, (kb > 0 || u > 0 || j > 0) ? 1u : 0u);
+                                    if (q.three_pass) {
+                                        umma_tf32_pair(acc, dal0 + j * a_jstep, db, idesc, 1u);
+                                        umma_tf32_pair(acc, da, dbl0 + j * b_jstep, idesc, 1u);
+                                    }
                                 }
                             }
                         }
@@ -519,6 +529,7 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
     }
     q.three_pass = three ? 1 : 0;
     q.ks = 1;
+    q.nh = 1;
     // two-CTA pairs (256 x 256 per pair) when there are enough pair tiles to fill the machine
     const long long pair_tiles = ((g.m + 255) / 256) * ((g.n + 255) / 256) * g.batch * g.splits;
     bool two_cta = g.m > 128 && pair_tiles * 2 >= dev->prop.multiProcessorCount;
@@ -540,13 +551,20 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
             if ((st = make_map(&mbl, b_lo, g.k, g.n, b_b, g.b_sn, g.b_sb, 128))) return st;
         }
         // plain TF32 with a long K: two k blocks per stage, half as many barrier round trips per MMA
-        q.ks = (!three && g.splits == 1 && g.k >= 256) ? 2 : 1;
+        // Two measured variants that are off by default because neither moved the 8192^3 TF32 time
+        // (1.57 ms either way, the kernel runs at the sustained tensor rate of the part, as cuBLAS does):
+        // EB200_TC_KS=2 puts two k blocks in a pipeline stage (half the barrier round trips per MMA),
+        // EB200_TC_NH=2 makes the pair tile 256 x 512 (the whole tensor memory; a third less operand
+        // traffic per flop).  Both pass the GEMM parity tests.
+        q.ks = 1;
         if (const char* e = getenv("EB200_TC_KS")) q.ks = atoi(e) == 2 && g.splits == 1 ? 2 : 1;
-        const int stage_bytes = q.ks * (three ? 4 : 2) * TC_TILE_BYTES;
+        q.nh = 1;
+        if (const char* e = getenv("EB200_TC_NH")) q.nh = atoi(e) == 2 && !three ? 2 : 1;
+        const int stage_bytes = q.ks * (three ? 2 : 1) * (1 + q.nh) * TC_TILE_BYTES;
         q.stages = std::min(8, (196 * 1024) / stage_bytes);
         EB_REQUIRE(q.stages >= 2, EB200_ERR_UNSUPPORTED, "GEMM stage does not fit shared memory twice");
         const size_t smem = (size_t)q.stages * stage_bytes + 1024 + 256;
-        const long long tm2 = (g.m + 255) / 256, tn2 = (g.n + 255) / 256;
+        const long long tm2 = (g.m + 255) / 256, tn2 = (g.n + 256 * q.nh - 1) / (256 * q.nh);
         const long long bands = (tm2 + q.raster - 1) / q.raster;
         q.tiles_n = (int)tn2;
         cudaLaunchConfig_t cfg = {};
