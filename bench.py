@@ -421,12 +421,36 @@ def conv_measurements(reg, dev, rng, quick=False, shapes=None, reps=None):
 
 
 def run_only_conv(args):
-    """`--only conv2d`: a small case of the convolution kernel alone (for profiler captures)."""
+    """`--only conv2d`: a small case of the convolution kernel alone (for profiler captures);
+    `--only conv2d_grad`: the gradient forms and the streaming small-K kernels of config 4's layers at batch 1024."""
+    from harp_b200 import desc as D
     from harp_b200.backend import B200BackendRegistry
     reg = B200BackendRegistry()
     dev = reg.create_device(0)
-    res = conv_measurements(reg, dev, np.random.default_rng(5), shapes=[("cnn_conv2_batch2048", (2048, 32, 13, 13, 64, 3, 3, 0))], reps=2)
-    print(json.dumps({"only": "conv2d", "conv2d": res}))
+    rng = np.random.default_rng(5)
+    if args.only == "conv2d":
+        res = conv_measurements(reg, dev, rng, shapes=[("cnn_conv2_batch2048", (2048, 32, 13, 13, 64, 3, 3, 0))], reps=2)
+        print(json.dumps({"only": "conv2d", "conv2d": res}))
+        return
+    n = 1024
+    res = {}
+
+    def run(name, kd, sizes, out_size):
+        bufs = []
+        for sz in sizes:
+            b = reg.allocate_buffer(dev, [sz])
+            b.write_vec(rng.uniform(-1, 1, sz).astype(np.float32))
+            bufs.append(b)
+        bo = reg.allocate_buffer(dev, [out_size])
+        kern = reg.compile_ast(dev, kd)
+        res[name] = {"impl": kern.impl, "ms": time_kernel(dev, kern, bufs, [bo], reps=2, warm=1)}
+    # conv2 of config 4: input gradient (flag 128) and weight gradient (flag 256) on the tensor cores
+    run("conv2_dgrad", D.conv2d(n, 64, 11, 11, 32, 3, 3, pad=2, bias=False, flip=True, nchw=True), [n * 64 * 121, 64 * 32 * 9], n * 32 * 169)
+    run("conv2_wgrad", D.conv2d_wgrad(n, 32, 13, 13, 64, 3, 3), [n * 32 * 169, n * 121 * 64], 64 * 288)
+    # conv1 (K = 9): streaming f32 kernels
+    run("conv1_forward", D.conv2d(n, 1, 28, 28, 32, 3, 3, relu=True, nchw=True), [n * 784, 288, 32], n * 32 * 676)
+    run("conv1_wgrad", D.conv2d_wgrad(n, 1, 28, 28, 32, 3, 3, g_nchw=True), [n * 784, n * 32 * 676], 288)
+    print(json.dumps({"only": "conv2d_grad", "kernels": res}))
 
 
 def extra_measurements(reg, dev, rank, world, local_rank, quick=False):
@@ -520,9 +544,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extra", action="store_true", help="only config 2 (skip matmul / MLP / CNN measurements)")
-    ap.add_argument("--only", default="", choices=["", "conv2d"], help="run one small kernel case alone (profiler captures); prints no bench line")
+    ap.add_argument("--only", default="", choices=["", "conv2d", "conv2d_grad"], help="run one small kernel case alone (profiler captures); prints no bench line")
     args = ap.parse_args()
-    if args.only == "conv2d":
+    if args.only:
         run_only_conv(args)
     elif args.impl == "reference":
         run_reference(args)
