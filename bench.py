@@ -130,14 +130,14 @@ def run_cpu_workload(x, openmp: bool, rows: int):
     return step, bytes_step
 
 
-def cpu_baseline(x, budget_s: float = 20.0):
+def cpu_baseline(x, seconds_allowed: float = 20.0):
     cores = os.cpu_count() or 1
     os.environ.setdefault("OMP_NUM_THREADS", str(cores))
     step, nbytes = run_cpu_workload(x, True, ROWS)
     t0 = time.perf_counter(); step(); first = time.perf_counter() - t0
     best = first
     reps = 1
-    while reps < 3 and (reps + 1) * first < budget_s:
+    while reps < 3 and (reps + 1) * first < seconds_allowed:
         t0 = time.perf_counter(); step(); best = min(best, time.perf_counter() - t0)
         reps += 1
     out = {"value": nbytes / best / 1e9, "unit": UNIT, "cores": cores, "kind": "port",

@@ -572,20 +572,20 @@ int launch_conv2d(Device* dev, const Plan& plan, const float* x, const float* w,
     const int stage_bytes = (q.three_pass ? 2 : 1) * (TC_TILE_BYTES + bn * TC_BK * 4);
     const size_t ktab_bytes = (size_t)(q.mode == CV_CBLOCK ? q.taps : q.Kpad) * sizeof(int2);
     const size_t fixed = 1024 + 256 + ktab_bytes;
-    const size_t budget = 220 * 1024;
+    const size_t smem_limit = 220 * 1024;
     const size_t patch_bytes = (size_t)q.patch_floats * 4;
     q.staged = patch_bytes <= (size_t)CV_MAX_PATCH_BYTES;
     if (const char* e = getenv("EB200_CONV_DIRECT")) if (atoi(e)) q.staged = 0;
     if (q.staged) {
-        q.pstages = patch_bytes * 3 + 2 * (size_t)stage_bytes + fixed <= budget ? 3 : 2;
-        if (patch_bytes * q.pstages + 2 * (size_t)stage_bytes + fixed > budget) q.staged = 0;
+        q.pstages = patch_bytes * 3 + 2 * (size_t)stage_bytes + fixed <= smem_limit ? 3 : 2;
+        if (patch_bytes * q.pstages + 2 * (size_t)stage_bytes + fixed > smem_limit) q.staged = 0;
     }
     if (!q.staged) { q.pstages = 1; q.patch_floats = 0; q.linear = 0; }
     if (q.linear) m_tiles = ((long long)q.Mtot + TC_BM - 1) / TC_BM;
     EB_REQUIRE(m_tiles * q.n_tiles < (1LL << 31) - (1 << 20), EB200_ERR_UNSUPPORTED, "conv2d has too many tiles");
     q.m_tiles = (int)m_tiles;
     q.tiles = q.m_tiles * q.n_tiles;
-    q.stages = (int)std::min<size_t>(6, (budget - fixed - (size_t)q.pstages * q.patch_floats * 4) / stage_bytes);
+    q.stages = (int)std::min<size_t>(6, (smem_limit - fixed - (size_t)q.pstages * q.patch_floats * 4) / stage_bytes);
     EB_REQUIRE(q.stages >= 2, EB200_ERR_UNSUPPORTED, "conv2d tile does not fit shared memory");
     const size_t smem = (size_t)q.stages * stage_bytes + (size_t)q.pstages * q.patch_floats * 4 + fixed;
     if (!dev->conv_configured) {
@@ -883,11 +883,11 @@ int launch_conv2d_wgrad(Device* dev, const Plan& plan, const float* x, const flo
     const int bn = c.Co <= 32 ? 32 : (c.Co <= 64 ? 64 : 128);
     const int stage_bytes = (q.three_pass ? 2 : 1) * (TC_TILE_BYTES + bn * TC_BK * 4);
     const size_t fixed = 1024 + 256 + (size_t)q.nb * TC_BK * sizeof(int2);
-    const size_t budget = 220 * 1024;
+    const size_t smem_limit = 220 * 1024;
     q.pstages = 2;
-    EB_REQUIRE(fixed + 2 * (size_t)q.patch_floats * 4 + 2 * (size_t)stage_bytes <= budget, EB200_ERR_UNSUPPORTED,
+    EB_REQUIRE(fixed + 2 * (size_t)q.patch_floats * 4 + 2 * (size_t)stage_bytes <= smem_limit, EB200_ERR_UNSUPPORTED,
                "conv2d weight gradient does not fit shared memory");
-    q.stages = (int)std::min<size_t>(6, (budget - fixed - 2 * (size_t)q.patch_floats * 4) / stage_bytes);
+    q.stages = (int)std::min<size_t>(6, (smem_limit - fixed - 2 * (size_t)q.patch_floats * 4) / stage_bytes);
     const size_t smem = (size_t)q.stages * stage_bytes + 2 * (size_t)q.patch_floats * 4 + fixed;
     // the output gradient as [M][Co] rows: boxes of 32 positions x 32 channels, channels contiguous
     CUtensorMap mg;
