@@ -100,15 +100,16 @@ def conv_case(seed):
     pad = int(rng.integers(0, k))                      # 0 .. k-1
     c = int(rng.choice([1, 2, 3, 8, 16, 32, 64]))
     co = int(rng.choice([4, 8, 12, 20, 32, 64, 96, 132]))
-    h = int(rng.integers(max(k - 2 * pad, 1), 15)) + (2 if k == 5 else 0)
-    wd = int(rng.integers(max(k - 2 * pad, 1), 15)) + (2 if k == 5 else 0)
+    top = 15 if seed % 3 else 41          # every third layer is large enough to leave the whole-image staging path
+    h = int(rng.integers(max(k - 2 * pad, 1), top)) + (2 if k == 5 else 0)
+    wd = int(rng.integers(max(k - 2 * pad, 1), top)) + (2 if k == 5 else 0)
     n = int(rng.integers(1, 6))
     while c * k * k > 2048:
         c //= 2
     return n, c, h, wd, co, k, pad
 
 
-@pytest.mark.parametrize("seed", range(24))
+@pytest.mark.parametrize("seed", range(int(__import__("os").environ.get("EB200_TEST_CONV_SEEDS", "24"))))
 def test_random_convolutions_all_forms(dev, seed):
     """Seeded random layers through whichever kernel the library picks (tensor cores with
     TMA / bulk / cp.async patch staging or direct gathers, channel-blocked or table k order,
