@@ -57,6 +57,7 @@ struct KOperand {
     int n_bounds;
     float pad;
     int flat;                  // f32, unmasked and laid out exactly like the iteration space: element e sits at offset + e
+    long long delta[KMAX_DIMS]; // odometer steps: address change when dim d ticks and every dim after it wraps to 0
 };
 
 struct KBound {

@@ -5,25 +5,31 @@
 // copies of the 9x-inflated window tensor and a scalar triple loop.  Here the
 // window tensor never exists:  out[(n,oh,ow), co] = sum_k A[(n,oh,ow), k] * W[co, k].
 //
-// Persistent CTAs walk output tiles of up to 128 positions (whole output rows of
-// one image).  Per tile:
-//   loaders   copy the input patch the tile's windows touch (32 channels, or all
-//             channels when C is not a multiple of 32) into shared memory with
-//             4-byte asynchronous copies, zero filling what lies outside the image,
-//             so every input element crosses L2 -> SM once per tile instead of once
-//             per window tap;
-//   gather    four warps build the 128 x 32 A tile of each k block from the patch,
-//             shared memory to shared memory, in the 128-byte-swizzled K-major layout
-//             the tensor core expects (what a TMA load would have produced);
+// Persistent CTAs (one per SM, 512 threads) walk output tiles of up to 128 positions: whole
+// output rows of one image, or 128 consecutive positions of the flattened (n, oh, ow) space
+// when small images would otherwise leave rows of the tile empty.  Per tile:
+//   loader    brings the input patch the tile's windows touch (32 channels, or all channels
+//             when C is not a multiple of 32) into shared memory once: one bulk copy of the
+//             raw channel planes for small images, one tiled TMA box with zero fill when
+//             W % 4 == 0, else 4-byte asynchronous copies row by row; every input element
+//             crosses L2 -> SM once per tile instead of once per window tap;
+//   gather    eight warps in two groups (alternate k blocks) build the 128 x 32 A tile of
+//             each k block from the patch, shared memory to shared memory, in the
+//             128-byte-swizzled K-major layout the tensor core expects (what a TMA load would
+//             have produced);
 //   TMA       brings the matching weight tile;
-//   MMA       one thread issues tcgen05.mma kind::tf32 into a double-buffered
-//             accumulator in tensor memory;
-//   epilogue  four warps drain the accumulator: bias, optional ReLU, 128-bit stores
-//             of [M, Co] rows, while the next tile is already being gathered.
-// 3xTF32 splits A into hi/lo on the fly in the gather; the weights are split (and
-// reordered / padded to a multiple of 32 in K) by a small prep kernel.
-// Patches that do not fit shared memory fall back to gathering from global memory.
-// Stride 1, symmetric zero padding.  All mbarrier waits are bounded.
+//   MMA       the MMA warp runs a warp-uniform loop, one elected lane issues tcgen05.mma
+//             kind::tf32 into a double-buffered accumulator in tensor memory;
+//   epilogue  four warps drain the accumulator: bias, optional ReLU, then either 128-bit
+//             stores of [M, Co] rows or, for the [N, Co, Ho, Wo] layout, one coalesced store
+//             per channel plane (a warp's lanes are 32 consecutive positions), while the next
+//             tile is already being gathered.
+// 3xTF32 splits A into hi/lo on the fly in the gather; the weights are split (reordered,
+// padded to a multiple of 32 in K, and for the input gradient transposed and flipped) by a
+// small prep kernel.  Patches that do not fit shared memory fall back to gathering from
+// global memory.  Stride 1, symmetric zero padding.  All mbarrier waits are bounded.
+// The weight gradient is a second kernel further down; layers with C*KH*KW <= 32 run the
+// streaming kernels of conv_direct.cu instead.
 #include <stdlib.h>
 
 #include <algorithm>

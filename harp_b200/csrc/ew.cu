@@ -91,6 +91,13 @@ __global__ void __launch_bounds__(256) ew_kernel(const __grid_constant__ KParams
                 if (g < ngrp) {
                     long long idx[KMAX_DIMS];
                     decompose<ND>(p, g << 2, idx);
+                    // element addresses of the strided operands: computed once, then moved like an odometer
+                    long long addr[KMAX_IN];
+#pragma unroll
+                    for (int i = 0; i < (F::kCompiled ? n : KMAX_IN); ++i) {
+                        if (i >= n) break;
+                        addr[i] = p.in[i].flat ? 0 : operand_index<ND>(p, p.in[i], idx);
+                    }
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
 #pragma unroll
@@ -105,15 +112,22 @@ __global__ void __launch_bounds__(256) ew_kernel(const __grid_constant__ KParams
                             } else if (o.n_bounds && !bounds_ok(p, o, idx)) {
                                 in[u][i][j] = o.pad;
                             } else {
-                                in[u][i][j] = load_elem(o, operand_index<ND>(p, o, idx));
+                                in[u][i][j] = load_elem(o, addr[i]);
                             }
                         }
-                        // next element: innermost index + 1, carries outward
+                        if (j == 3) break;
+                        // next element: innermost index + 1, carries outward; `tick` is the dim that moved
+                        int tick = 0;
 #pragma unroll
                         for (int d = RK - 1; d >= 0; --d) {
                             if (ND == 0 && d >= p.ndim) continue;
-                            if (++idx[d] < p.shape[d]) break;
+                            if (++idx[d] < p.shape[d]) { tick = d; break; }
                             idx[d] = 0;
+                        }
+#pragma unroll
+                        for (int i = 0; i < (F::kCompiled ? n : KMAX_IN); ++i) {
+                            if (i >= n) break;
+                            addr[i] += p.in[i].delta[tick];
                         }
                     }
                 }

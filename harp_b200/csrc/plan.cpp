@@ -526,7 +526,16 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
                     for (int i = 0; i < p.n_in; ++i) n_flat += flat(p.in[i]) ? 1 : 0;
                     if (flat(p.out) && n_flat > 0) {
                         p.vec = 2;
-                        for (int i = 0; i < p.n_in; ++i) p.in[i].flat = flat(p.in[i]) ? 1 : 0;
+                        for (int i = 0; i < p.n_in; ++i) {
+                            p.in[i].flat = flat(p.in[i]) ? 1 : 0;
+                            // stepping to the next element in row-major order ticks some dim d and wraps the
+                            // dims after it: the operand's address moves by this much
+                            for (int dd = 0; dd < KMAX_DIMS; ++dd) {
+                                long long dl = dd < nk ? p.in[i].strides[dd] : 0;
+                                for (int e2 = dd + 1; e2 < nk; ++e2) dl -= (shape[e2] - 1) * p.in[i].strides[e2];
+                                p.in[i].delta[dd] = dl;
+                            }
+                        }
                         snprintf(pl.name, sizeof(pl.name), "ew_chain_g4");
                     }
                 }
