@@ -227,6 +227,7 @@ int launch_gemm_simt(Device* dev, const Plan& plan, const float* a, const float*
 int launch_splitk_reduce(Device* dev, const GemmShape& g, const float* partials, float* c);
 bool gemm_tc_supported(const GemmShape& g);
 void gemm_tc_scratch(const GemmShape& g, long long* a_span, long long* b_span);
+bool gemm_tc_convert(const GemmShape& g);
 int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b, float* c, void* scratch);
 bool gemm_tall_supported(const GemmShape& g);
 int launch_gemm_tall(Device* dev, const Plan& plan, const float* a, const float* b, float* c, void* scratch);

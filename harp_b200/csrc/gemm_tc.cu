@@ -47,6 +47,7 @@ struct TcParams {
     int raster;        // tile rows per band
     int tiles_n;
     int ks;            // two-CTA kernel: 32-wide k blocks per pipeline stage (2 halves the barrier round trips per MMA)
+    int convert;       // one-CTA kernel, 3xTF32: TMA brings the raw f32 tiles, the epilogue warps split them into hi / lo in shared memory
     int nh;            // two-CTA kernel: 256-column halves per pair tile (2: a 256 x 512 tile, the whole tensor memory)
     int* error_flag;
 };
@@ -66,7 +67,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int stage_bytes = (q.three_pass ? 2 : 1) * (TC_TILE_BYTES + B_TILE_BYTES);
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)q.stages * stage_bytes);
     uint64_t* empty_bar = full_bar + q.stages;
-    uint64_t* acc_bar = empty_bar + q.stages;
+    uint64_t* conv_bar = empty_bar + q.stages;       // tiles split into hi / lo (convert mode)
+    uint64_t* acc_bar = conv_bar + q.stages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
 
     const int warp = uniform_warp_idx(), lane = threadIdx.x & 31;
@@ -86,7 +88,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int num_kb = min(total_kb - kb_begin, q.kb_per_split);   // k blocks of this CTA (>= 1 by construction)
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < q.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int s = 0; s < q.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); mbar_init(&conv_bar[s], 128); }
         mbar_init(acc_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -108,7 +110,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], phase ^ 1u, q.error_flag))) break;
             if (elect_one()) {
                 unsigned char* st = smem + (size_t)s * stage_bytes;
-                mbar_expect_tx(&full_bar[s], (unsigned)stage_bytes);
+                mbar_expect_tx(&full_bar[s], q.convert ? (unsigned)(TC_TILE_BYTES + B_TILE_BYTES) : (unsigned)stage_bytes);
                 const int kx = (kb_begin + kb) * TC_BK;
                 unsigned char* a_hi = st;
                 unsigned char* b_hi = st + (q.three_pass ? 2 : 1) * TC_TILE_BYTES;   // [A hi | A lo | B hi | B lo]
@@ -117,22 +119,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                     for (int j = 0; j < TC_BM / 32; ++j) {
                         tma_load_3d(a_hi + j * 4096, &map_a, &full_bar[s], (int)m0 + j * 32, kx, bz * a_zmul);
-                        if (q.three_pass) tma_load_3d(st + TC_TILE_BYTES + j * 4096, &map_alo, &full_bar[s], (int)m0 + j * 32, kx, bz * a_zmul);
+                        if (q.three_pass && !q.convert) tma_load_3d(st + TC_TILE_BYTES + j * 4096, &map_alo, &full_bar[s], (int)m0 + j * 32, kx, bz * a_zmul);
                     }
                 } else {
                     tma_load_3d(a_hi, &map_a, &full_bar[s], kx, (int)m0, bz * a_zmul);
-                    if (q.three_pass) tma_load_3d(st + TC_TILE_BYTES, &map_alo, &full_bar[s], kx, (int)m0, bz * a_zmul);
+                    if (q.three_pass && !q.convert) tma_load_3d(st + TC_TILE_BYTES, &map_alo, &full_bar[s], kx, (int)m0, bz * a_zmul);
                 }
                 if (q.b_nmajor) {
                     // four [32 k][32 n] boxes side by side along n
 #pragma unroll
                     for (int j = 0; j < TC_BN / 32; ++j) {
                         tma_load_3d(b_hi + j * 4096, &map_b, &full_bar[s], (int)n0 + j * 32, kx, bz * b_zmul);
-                        if (q.three_pass) tma_load_3d(b_hi + B_TILE_BYTES + j * 4096, &map_blo, &full_bar[s], (int)n0 + j * 32, kx, bz * b_zmul);
+                        if (q.three_pass && !q.convert) tma_load_3d(b_hi + B_TILE_BYTES + j * 4096, &map_blo, &full_bar[s], (int)n0 + j * 32, kx, bz * b_zmul);
                     }
                 } else {
                     tma_load_3d(b_hi, &map_b, &full_bar[s], kx, (int)n0, bz * b_zmul);
-                    if (q.three_pass) tma_load_3d(b_hi + B_TILE_BYTES, &map_blo, &full_bar[s], kx, (int)n0, bz * b_zmul);
+                    if (q.three_pass && !q.convert) tma_load_3d(b_hi + B_TILE_BYTES, &map_blo, &full_bar[s], kx, (int)n0, bz * b_zmul);
                 }
             }
             __syncwarp();
@@ -152,7 +154,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         int s = 0;
         unsigned phase = 0;
         for (int kb = 0; kb < num_kb; ++kb, s = (s + 1 == q.stages ? 0 : s + 1), phase ^= (s == 0)) {
-            if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[s], phase, q.error_flag))) break;
+            if (!__all_sync(0xffffffffu, mbar_wait(q.convert ? &conv_bar[s] : &full_bar[s], phase, q.error_flag))) break;
             tc_fence_after();
             const uint32_t st = smem_base + (uint32_t)s * (uint32_t)stage_bytes;
             const uint64_t da0 = umma_desc(st, a_lbo, a_sbo, a_layout), dal0 = umma_desc(st + TC_TILE_BYTES, a_lbo, a_sbo, a_layout);
@@ -176,6 +178,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else {
         // ---- epilogue: warps 2..5 own tensor-memory lanes 32*(warp%4) .. +31 ----
         const int quarter = warp & 3;
+        if (q.convert) {
+            // 3xTF32 without the pre-split passes over HBM: the raw f32 tiles TMA delivered are split here,
+            // hi (tf32-exact) in place, lo = x - hi beside it.  Elementwise, so the swizzle does not matter.
+            const int ct = threadIdx.x - 64;                 // 0..127
+            int s = 0;
+            unsigned phase = 0;
+            for (int kb = 0; kb < num_kb; ++kb, s = (s + 1 == q.stages ? 0 : s + 1), phase ^= (s == 0)) {
+                if (!mbar_wait(&full_bar[s], phase, q.error_flag)) break;
+                unsigned char* st = smem + (size_t)s * stage_bytes;
+                float4* ah = reinterpret_cast<float4*>(st);
+                float4* al = reinterpret_cast<float4*>(st + TC_TILE_BYTES);
+                float4* bh = reinterpret_cast<float4*>(st + 2 * TC_TILE_BYTES);
+                float4* bl = reinterpret_cast<float4*>(st + 2 * TC_TILE_BYTES + B_TILE_BYTES);
+#pragma unroll 4
+                for (int i = ct; i < TC_TILE_BYTES / 16; i += 128) {
+                    const float4 t = ah[i];
+                    float4 h;
+                    h.x = __uint_as_float((__float_as_uint(t.x) + 0x1000u) & 0xffffe000u);
+                    h.y = __uint_as_float((__float_as_uint(t.y) + 0x1000u) & 0xffffe000u);
+                    h.z = __uint_as_float((__float_as_uint(t.z) + 0x1000u) & 0xffffe000u);
+                    h.w = __uint_as_float((__float_as_uint(t.w) + 0x1000u) & 0xffffe000u);
+                    ah[i] = h;
+                    al[i] = make_float4(t.x - h.x, t.y - h.y, t.z - h.z, t.w - h.w);
+                }
+#pragma unroll 4
+                for (int i = ct; i < B_TILE_BYTES / 16; i += 128) {
+                    const float4 t = bh[i];
+                    float4 h;
+                    h.x = __uint_as_float((__float_as_uint(t.x) + 0x1000u) & 0xffffe000u);
+                    h.y = __uint_as_float((__float_as_uint(t.y) + 0x1000u) & 0xffffe000u);
+                    h.z = __uint_as_float((__float_as_uint(t.z) + 0x1000u) & 0xffffe000u);
+                    h.w = __uint_as_float((__float_as_uint(t.w) + 0x1000u) & 0xffffe000u);
+                    bh[i] = h;
+                    bl[i] = make_float4(t.x - h.x, t.y - h.y, t.z - h.z, t.w - h.w);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&conv_bar[s])) : "memory");
+            }
+        }
         const bool ok = mbar_wait(acc_bar, 0, q.error_flag);
         tc_fence_after();
         const long long row = m0 + quarter * 32 + lane;
@@ -456,6 +497,17 @@ static long long span_of(long long batch, long long sb, long long rows, long lon
     return (batch - 1) * sb + (rows - 1) * srow + inner;
 }
 
+// 3xTF32 with the hi / lo split done inside the kernel (no scratch copies, no extra passes over the
+// operands): for contractions that are short on arithmetic per operand byte, where the two pre-split
+// passes cost more than the MMAs (an MLP layer [65536, 256] x [256, 256]: 64 flop per byte).
+bool gemm_tc_convert(const GemmShape& g) {
+    if (g.mode != EB200_GEMM_3XTF32) return false;
+    if (const char* e = getenv("EB200_TC_CONVERT")) return atoi(e) != 0;
+    const double flops = 2.0 * (double)g.batch * g.m * g.n * g.k;
+    const double bytes = 4.0 * (double)g.batch * ((double)g.m * g.k + (double)g.k * g.n + (double)g.m * g.n);
+    return flops / bytes < 200.0;
+}
+
 void gemm_tc_scratch(const GemmShape& g, long long* a_span, long long* b_span) {
     const bool b_kmajor = g.b_sk == 1;
     long long a = g.a_sk == 1 ? span_of(g.batch, g.a_sb, g.m, g.a_sm, g.k) : span_of(g.batch, g.a_sb, g.k, g.a_sk, g.m);
@@ -474,7 +526,8 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
     EB_REQUIRE((reinterpret_cast<uintptr_t>(a_src) & 15) == 0 && (reinterpret_cast<uintptr_t>(b_src) & 15) == 0,
                EB200_ERR_INVALID, "GEMM operands must be 16-byte aligned");
     const float *a_hi = a_src, *a_lo = a_src, *b_hi = b_src, *b_lo = b_src;
-    if (three) {
+    const bool convert = gemm_tc_convert(g);
+    if (three && !convert) {
         EB_REQUIRE(scratch, EB200_ERR_INVALID, "3xTF32 launched without scratch");
         long long a_span, b_span;
         gemm_tc_scratch(g, &a_span, &b_span);
@@ -528,12 +581,14 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
         q.c_off = 0; q.c_sm = g.n; q.c_sn = 1; q.c_sb = g.m * g.n;
     }
     q.three_pass = three ? 1 : 0;
+    q.convert = convert ? 1 : 0;
     q.ks = 1;
     q.nh = 1;
     // two-CTA pairs (256 x 256 per pair) when there are enough pair tiles to fill the machine
     const long long pair_tiles = ((g.m + 255) / 256) * ((g.n + 255) / 256) * g.batch * g.splits;
     bool two_cta = g.m > 128 && pair_tiles * 2 >= dev->prop.multiProcessorCount;
     if (const char* e = getenv("EB200_TC_2CTA")) two_cta = atoi(e) != 0;
+    if (convert) two_cta = false;      // the in-kernel split lives in the one-CTA kernel
     q.error_flag = dev->error_flag_dev;
     q.raster = 8;
     if (const char* e = getenv("EB200_TC_RASTER")) q.raster = std::max(1, atoi(e));

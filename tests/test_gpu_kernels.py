@@ -480,6 +480,33 @@ def test_gemm_tall_skinny_weight_gradient(dev, b_, o_, i_):
     assert (np.abs(other.reshape(o_, i_) - ref) <= bound).all()
 
 
+@pytest.mark.parametrize("form", ["nn", "tn", "wgrad"])
+def test_gemm_3xtf32_split_in_the_kernel_equals_split_beforehand(dev, form, monkeypatch):
+    """3xTF32 either splits the operands into hi / lo copies with two passes beforehand (large,
+    compute-bound contractions) or inside the kernel after the TMA load (everything below 200
+    flop per operand byte).  Same hi / lo values, same MMAs: the results are equal bit for bit."""
+    m, k_, n = 384, 200, 320
+    a, b = rnd([m, k_], 55), rnd([k_, n], 56)
+    if form == "nn":
+        kd, ins = W.matmul_desc(m, k_, n), [a, b]
+    elif form == "tn":
+        kd, ins = W.linear_desc(m, k_, n), [a, np.ascontiguousarray(b.T)]
+    else:
+        dy, x = rnd([4096, 64], 57), rnd([4096, 96], 58)
+        kd = D.reduce([4096, 64, 96], [D.Operand([64, 1, 0], 0, D.F32, dy.size), D.Operand([96, 0, 1], 0, D.F32, x.size)],
+                      w(0) * w(1), D.R_SUM, 0)
+        ins = [dy, x]
+    outs = {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("EB200_TC_CONVERT", mode)
+        got, kern = run_gpu(dev, kd, ins)
+        assert kern.impl.startswith("gemm_tcgen05_3xtf32"), kern.impl
+        assert (kern.scratch_bytes == 0) == (mode == "1" and "splitk" not in kern.impl) or "splitk" in kern.impl
+        outs[mode] = got
+    assert np.array_equal(outs["1"], outs["0"])
+    dev.synchronize()
+
+
 def test_gemm_misaligned_layout_stays_on_f32_kernel(dev):
     # lda = 30 floats is not a multiple of 16 bytes: TMA cannot address it
     a, b = rnd([64, 30], 35), rnd([30, 64], 36)
