@@ -51,7 +51,16 @@ __global__ void __launch_bounds__(256) conv2d_direct_kernel(const __grid_constan
         ws[e] = v;
     }
     for (int e = threadIdx.x; e < q.Co; e += 256) bs[e] = q.has_bias ? bias[e] : 0.0f;
+    __shared__ int2 ktab[KT];                       // per k: {offset of the tap in the window, kh | kw << 16}
+    if (threadIdx.x < KT) {
+        int off = 0, kh = 0, kw = 0;
+        if ((int)threadIdx.x < q.K) window_offsets(q, threadIdx.x, off, kh, kw);
+        ktab[threadIdx.x] = make_int2(off, kh | (kw << 16));
+    }
     __syncthreads();
+    int koff[KT];
+#pragma unroll
+    for (int k = 0; k < KT; ++k) koff[k] = ktab[k].x;
 
     const unsigned stride = gridDim.x * 256u, M = (unsigned)q.M;
     for (unsigned m = blockIdx.x * 256u + threadIdx.x; m < M; m += stride) {
@@ -59,14 +68,16 @@ __global__ void __launch_bounds__(256) conv2d_direct_kernel(const __grid_constan
         const int oh = pos / q.Wo, ow = pos - oh * q.Wo;
         const float* xb = x + ((long long)n * q.C * q.H + (oh - q.pad)) * q.W + (ow - q.pad);
         float xv[KT];
+        if (q.pad == 0) {
 #pragma unroll
-        for (int k = 0; k < KT; ++k) {
-            xv[k] = 0.0f;
-            if (k < q.K) {
-                int off, kh, kw;
-                window_offsets(q, k, off, kh, kw);
-                const bool in = (unsigned)(oh + kh - q.pad) < (unsigned)q.H && (unsigned)(ow + kw - q.pad) < (unsigned)q.W;
-                if (in) xv[k] = __ldg(xb + off);
+            for (int k = 0; k < KT; ++k) xv[k] = k < q.K ? __ldg(xb + koff[k]) : 0.0f;
+        } else {
+#pragma unroll
+            for (int k = 0; k < KT; ++k) {
+                const int2 e = ktab[k];
+                const bool in = k < q.K && (unsigned)(oh + (e.y & 0xffff) - q.pad) < (unsigned)q.H &&
+                                (unsigned)(ow + (e.y >> 16) - q.pad) < (unsigned)q.W;
+                xv[k] = in ? __ldg(xb + e.x) : 0.0f;
             }
         }
         float* o_nchw = out + (long long)n * q.Co * q.P + pos;
@@ -131,6 +142,9 @@ __global__ void __launch_bounds__(256) conv2d_direct_wgrad_kernel(const __grid_c
     if (stream >= q.streams) return;
     const int co0 = chunk * CHN;
     const unsigned M = (unsigned)q.M, step = (unsigned)q.streams * 32u;
+    int koff[KT];                                    // tap offsets, kept in registers
+#pragma unroll
+    for (int k = 0; k < KT; ++k) koff[k] = ktab[k].x;
     float acc[CHN][KT];
 #pragma unroll
     for (int j = 0; j < CHN; ++j)
@@ -146,12 +160,17 @@ __global__ void __launch_bounds__(256) conv2d_direct_wgrad_kernel(const __grid_c
             const unsigned n = live ? m / (unsigned)q.P : 0u, pos = live ? m - n * (unsigned)q.P : 0u;
             const int oh = (int)(pos / (unsigned)q.Wo), ow = (int)(pos - (unsigned)oh * (unsigned)q.Wo);
             const float* xb = x + ((long long)n * q.C * q.H + (oh - q.pad)) * q.W + (ow - q.pad);
+            if (q.pad == 0) {                                  // every tap of a live position is inside the image
 #pragma unroll
-            for (int k = 0; k < KT; ++k) {
-                const int2 e = ktab[k];
-                const bool in = live && k < q.K && (unsigned)(oh + (e.y & 0xffff) - q.pad) < (unsigned)q.H &&
-                                (unsigned)(ow + (e.y >> 16) - q.pad) < (unsigned)q.W;
-                xv[u][k] = in ? __ldg(xb + e.x) : 0.0f;
+                for (int k = 0; k < KT; ++k) xv[u][k] = (live && k < q.K) ? __ldg(xb + koff[k]) : 0.0f;
+            } else {
+#pragma unroll
+                for (int k = 0; k < KT; ++k) {
+                    const int2 e = ktab[k];
+                    const bool in = live && k < q.K && (unsigned)(oh + (e.y & 0xffff) - q.pad) < (unsigned)q.H &&
+                                    (unsigned)(ow + (e.y >> 16) - q.pad) < (unsigned)q.W;
+                    xv[u][k] = in ? __ldg(xb + e.x) : 0.0f;
+                }
             }
             const float* gp = q.g_nchw ? g + ((long long)n * q.Co + co0) * q.P + pos : g + (long long)m * q.Co + co0;
             const long long gs = q.g_nchw ? (long long)q.P : 1LL;
