@@ -359,6 +359,62 @@ class B200BackendRegistry:
         return False
 
 
+class B200Comm:
+    """Communicator over the GPUs of one box (``eb200_comm_*``): one process per
+    GPU.  Rank 0 calls ``B200Comm.unique_id()`` and hands the 128 bytes to the
+    other ranks over whatever channel the host program has; every rank then
+    constructs its communicator.  The reference has nothing like it (no
+    distributed code); it serves batch-sharded training and row-sharded
+    reductions."""
+
+    COMM_ID_BYTES = 128
+
+    def __init__(self, device: B200Device, rank: int, nranks: int, unique_id: Optional[bytes] = None):
+        self.device, self.rank, self.nranks = device, rank, nranks
+        self._h = C.c_void_p()
+        idbuf = None
+        if nranks > 1:
+            assert unique_id is not None and len(unique_id) == self.COMM_ID_BYTES
+            idbuf = (C.c_char * self.COMM_ID_BYTES).from_buffer_copy(unique_id)
+        capi.call("eb200_comm_init", device._h, rank, nranks, idbuf, C.byref(self._h))
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = (C.c_char * B200Comm.COMM_ID_BYTES)()
+        capi.call("eb200_comm_unique_id", buf)
+        return bytes(buf)
+
+    def info(self) -> dict:
+        r, n, o = C.c_int(), C.c_int(), C.c_int()
+        a, b = C.c_int64(), C.c_int64()
+        capi.call("eb200_comm_info", self._h, C.byref(r), C.byref(n), C.byref(o), C.byref(a), C.byref(b))
+        return {"rank": r.value, "nranks": n.value, "one_shot": bool(o.value), "calls_one_shot": a.value, "calls_nccl": b.value}
+
+    def allreduce(self, buf: B200Buffer, op: int = D.R_SUM, offset: int = 0, count: Optional[int] = None, side_stream: bool = False):
+        n = buf.numel() - offset if count is None else count
+        capi.call("eb200_comm_allreduce_async" if side_stream else "eb200_comm_allreduce", self._h, buf._h, offset, n, op)
+
+    def allreduce_sgd(self, params: B200Buffer, grads: B200Buffer, lr: float, offset: int = 0, count: Optional[int] = None,
+                      side_stream: bool = False):
+        """params -= lr * (sum of grads over the ranks), one kernel."""
+        n = params.numel() - offset if count is None else count
+        capi.call("eb200_comm_allreduce_sgd_async" if side_stream else "eb200_comm_allreduce_sgd",
+                  self._h, params._h, grads._h, offset, n, lr)
+
+    def join(self):
+        """The compute stream waits for what was issued with ``side_stream=True``."""
+        capi.call("eb200_comm_join", self._h)
+
+    def attach(self, kernel: B200Kernel):
+        """The reduce kernel's output becomes the all-reduce over the ranks of its local result."""
+        capi.call("eb200_kernel_set_allreduce", kernel._h, self._h)
+
+    def destroy(self):
+        if self._h:
+            capi.call("eb200_comm_destroy", self._h)
+            self._h = None
+
+
 class PinnedArray:
     """A numpy array over page-locked host memory (staging for async copies)."""
 

@@ -81,6 +81,16 @@ SIGNATURES = {
     "eb200_kernel_release": [_p],
     "eb200_reduce_cols_static": [_p, C.c_int64, C.c_int64, C.c_int, _p, _p],
     "eb200_launch_count": [C.POINTER(C.c_int64)],
+    "eb200_comm_unique_id": [_p],
+    "eb200_comm_init": [_p, C.c_int, C.c_int, _p, _pp],
+    "eb200_comm_info": [_p, C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int), C.POINTER(C.c_int64), C.POINTER(C.c_int64)],
+    "eb200_comm_allreduce": [_p, _p, C.c_int64, C.c_int64, C.c_int],
+    "eb200_comm_allreduce_async": [_p, _p, C.c_int64, C.c_int64, C.c_int],
+    "eb200_comm_join": [_p],
+    "eb200_comm_allreduce_sgd": [_p, _p, _p, C.c_int64, C.c_int64, C.c_float],
+    "eb200_comm_allreduce_sgd_async": [_p, _p, _p, C.c_int64, C.c_int64, C.c_float],
+    "eb200_kernel_set_allreduce": [_p, _p],
+    "eb200_comm_destroy": [_p],
 }
 
 _lib = None

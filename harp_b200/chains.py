@@ -45,7 +45,7 @@ CHAINS = [
     ("add_const", w(0) + c(1.0)),
     ("max_const", w(0).maximum(c(0.0))),
     ("axpb", w(0) * c(0.5) + c(1.0)),
-    # BASELINE config 2: sum(exp(c0*x + c1) * x), constants as tensors or folded
+    # config 2: sum(exp(c0*x + c1) * x), constants as tensors or folded
     ("cfg2_tensor_consts", ((w(0) * w(1)) + w(2)).exp() * w(1)),
     ("cfg2_folded", ((w(0) * c(0.5)) + c(1.0)).exp() * w(0)),
     # dense contraction body (GEMM-as-reduce) and squared error

@@ -157,6 +157,9 @@ enum Impl {
     IMPL_CONV2D_DIRECT_WGRAD,
     IMPL_CONV2D_WGRAD,    // weight gradient of a convolution, positions contracted on the tensor cores
     IMPL_GEMM_TALL,       // one-tile output, reduction over millions of rows (small-layer weight gradients)
+    IMPL_SCAN,            // cumulative op along an axis (P_ kernels)
+    IMPL_SGD_MOMENTUM,    // v = momentum*v - lr*g; p += v
+    IMPL_ADAM,            // Adam step with device-resident moments and step counter
 };
 
 struct GemmShape {
@@ -195,9 +198,11 @@ struct Plan {
     bool narrow = false;          // outer reduce with few kept elements: column threads x row lanes
     TransposeShape tr;
     int64_t scratch_bytes = 0;
+    bool scratch_zero = false;    // the scratch must start at zero (set once, at kernel creation)
     int64_t algo_bytes = 0, algo_flops = 0;
     int launches = 1;
     float scalar = 0.f;
+    float hyper[7] = {0};     // optimizer hyper-parameters of the descriptor
     int n_inputs = 0;         // inputs of the descriptor
     int perm[KMAX_IN] = {0};  // kernel operand c is descriptor input perm[c]
     int dyn_input[KMAX_CONSTS];   // constant slot j is read from descriptor input dyn_input[j] (-1: literal)
@@ -219,10 +224,15 @@ const char* chain_name(int chain);
 
 // launchers (one per .cu)
 int launch_ew(Device* dev, const Plan& plan, const KParams& p);
-int launch_reduce(Device* dev, const Plan& plan, const KParams& p, void* scratch);
+int launch_reduce(Device* dev, const Plan& plan, const KParams& p, void* scratch, bool finish = true);
 int launch_transpose(Device* dev, const Plan& plan, const void* in, void* out);
 int launch_scatter(Device* dev, const Plan& plan, const KParams& p);
 int launch_sgd(Device* dev, const Plan& plan, const float* p, const float* g, float* out, long long n);
+int launch_sgd_momentum(Device* dev, const Plan& plan, const float* p, const float* g, float* v, float* out, long long n);
+int launch_adam(Device* dev, const Plan& plan, const float* p, const float* g, float* m, float* v, int* t, float* out,
+                long long n, void* scratch);
+long long scan_scratch_floats(const KParams& p, int sms);
+int launch_scan(Device* dev, const Plan& plan, const KParams& p, void* scratch);
 int launch_gemm_simt(Device* dev, const Plan& plan, const float* a, const float* b, float* c, void* scratch);
 int launch_splitk_reduce(Device* dev, const GemmShape& g, const float* partials, float* c);
 bool gemm_tc_supported(const GemmShape& g);
@@ -241,6 +251,10 @@ long long conv2d_wgrad_scratch_floats(const ConvShape& c, int sms);
 int launch_conv2d_wgrad(Device* dev, const Plan& plan, const float* x, const float* g, float* dw, void* scratch);
 long long conv2d_scratch_floats(const ConvShape& c);
 int launch_conv2d(Device* dev, const Plan& plan, const float* x, const float* w, const float* bias, float* out, void* scratch);
+// comm.cu: collectives used by kernels that carry an attached communicator
+bool comm_can_fuse(eb200_comm* c, long long count);
+int comm_reduce_finish_allreduce(eb200_comm* c, const float* partials, int splits, long long kept, int rop, float* out);
+int comm_allreduce_buffer(eb200_comm* c, float* data, long long count, int rop);
 // EB200_ERR_TIMEOUT if a kernel on this device reported a timed-out wait (clears the flag)
 int check_device_flag(Device* dev);
 
@@ -251,4 +265,5 @@ struct eb200_kernel {
     eb200::Device* dev = nullptr;
     eb200::Plan plan;
     std::shared_ptr<eb200::Storage> scratch;
+    eb200_comm* comm = nullptr;   // set: the output is all-reduced over the ranks as part of the launch
 };

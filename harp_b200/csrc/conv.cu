@@ -546,8 +546,7 @@ int launch_conv2d(Device* dev, const Plan& plan, const float* x, const float* w,
     q.PW = q.Wt + c.KW - 1;
     q.CB = q.mode == CV_CBLOCK ? 32 : c.C;
     const bool aligned = (reinterpret_cast<uintptr_t>(x) & 15) == 0;
-    int load_limit = 2;
-    if (const char* e = getenv("EB200_CONV_LOAD")) load_limit = atoi(e);
+    const int load_limit = 2;
     if (load_limit >= 1 && aligned && q.taps <= 32 && ((long long)q.CB * c.H * c.W) % 4 == 0 && ((long long)c.C * c.H * c.W) % 4 == 0 &&
         (long long)q.CB * c.H * c.W * 4 <= CV_MAX_PATCH_BYTES) {
         q.load_mode = CV_LOAD_BULK;          // whole channel planes, unpadded
@@ -558,9 +557,7 @@ int launch_conv2d(Device* dev, const Plan& plan, const float* x, const float* w,
         // whole-row tiles leave rows empty when Ho * Wo is not close to a multiple of 128: tile the
         // flattened position space instead when that saves a fifth of the tiles and the patch still fits
         const int per_image = q.tiles_h * q.tiles_w, imgs = (TC_BM - 1) / q.P + 2;
-        int linear_ok = 1;
-        if (const char* e = getenv("EB200_CONV_LINEAR")) linear_ok = atoi(e);
-        if (linear_ok && (long long)per_image * TC_BM * 5 >= (long long)q.P * 6 &&
+        if ((long long)per_image * TC_BM * 5 >= (long long)q.P * 6 &&
             (long long)imgs * q.CB * c.H * c.W * 4 <= CV_MAX_PATCH_BYTES) {
             q.linear = 1;
             linear_imgs = imgs;
@@ -581,7 +578,6 @@ int launch_conv2d(Device* dev, const Plan& plan, const float* x, const float* w,
     const size_t smem_limit = 220 * 1024;
     const size_t patch_bytes = (size_t)q.patch_floats * 4;
     q.staged = patch_bytes <= (size_t)CV_MAX_PATCH_BYTES;
-    if (const char* e = getenv("EB200_CONV_DIRECT")) if (atoi(e)) q.staged = 0;
     if (q.staged) {
         q.pstages = patch_bytes * 3 + 2 * (size_t)stage_bytes + fixed <= smem_limit ? 3 : 2;
         if (patch_bytes * q.pstages + 2 * (size_t)stage_bytes + fixed > smem_limit) q.staged = 0;

@@ -215,11 +215,7 @@ bool conv2d_direct_supported(const ConvShape& c) {
     return K <= 32 && (long long)c.Co * ((K + 3) / 4 * 4 + 1) * 4 <= 48 * 1024;
 }
 
-static int direct_variant() {        // 8: 8 channels x 2 positions, 4: 4 x 4, 2: 4 x 2 (measurement switch)
-    static int v = 0;
-    if (!v) { const char* e = getenv("EB200_DWGRAD"); v = e ? atoi(e) : 2; if (v != 8 && v != 4) v = 2; }
-    return v;
-}
+static int direct_variant() { return 2; }   // 8: 8 channels x 2 positions, 4: 4 x 4, 2: 4 x 2 (the fastest measured)
 static int direct_chn() { return direct_variant() == 8 ? 8 : 4; }
 
 static int direct_streams(const ConvShape& c, int sms) {

@@ -286,14 +286,16 @@ int launch_scatter(Device* dev, const Plan& plan, const KParams& p) {
 }
 
 // ---- SGD ------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) sgd_kernel(const float* __restrict__ p, const float* __restrict__ g,
-                                                  float* __restrict__ out, long long n, float lr) {
+// `out` may be `p` itself (the update runs in place), so neither is __restrict__
+// and p is read with plain loads.
+__global__ void __launch_bounds__(256) sgd_kernel(const float* p, const float* __restrict__ g,
+                                                  float* out, long long n, float lr) {
     const long long stride = (long long)gridDim.x * blockDim.x;
     const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const bool aligned = ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
     const long long nvec = aligned ? (n >> 2) : 0;
     for (long long v = tid; v < nvec; v += stride) {
-        const float4 a = __ldg(reinterpret_cast<const float4*>(p) + v);
+        const float4 a = reinterpret_cast<const float4*>(p)[v];
         const float4 b = __ldg(reinterpret_cast<const float4*>(g) + v);
         float4 r;
         r.x = __fsub_rn(a.x, __fmul_rn(lr, b.x));

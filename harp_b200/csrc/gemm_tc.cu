@@ -502,7 +502,6 @@ static long long span_of(long long batch, long long sb, long long rows, long lon
 // passes cost more than the MMAs (an MLP layer [65536, 256] x [256, 256]: 64 flop per byte).
 bool gemm_tc_convert(const GemmShape& g) {
     if (g.mode != EB200_GEMM_3XTF32) return false;
-    if (const char* e = getenv("EB200_TC_CONVERT")) return atoi(e) != 0;
     const double flops = 2.0 * (double)g.batch * g.m * g.n * g.k;
     const double bytes = 4.0 * (double)g.batch * ((double)g.m * g.k + (double)g.k * g.n + (double)g.m * g.n);
     return flops / bytes < 200.0;
@@ -559,7 +558,6 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
     // leave SMs idle
     const long long tiles_m = (g.m + TC_BM - 1) / TC_BM;
     int bn = (tiles_m * ((g.n + 255) / 256) * g.batch * g.splits >= 2LL * dev->prop.multiProcessorCount) ? 256 : 128;
-    if (const char* e = getenv("EB200_TC_BN")) bn = atoi(e) == 256 ? 256 : 128;
     if (b_nmajor) {
         if ((st = make_map(&mb, b_hi, g.n, g.k, b_b, g.b_sk, g.b_sb, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))) return st;
         if ((st = make_map(&mbl, b_lo, g.n, g.k, b_b, g.b_sk, g.b_sb, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B))) return st;
@@ -587,11 +585,9 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
     // two-CTA pairs (256 x 256 per pair) when there are enough pair tiles to fill the machine
     const long long pair_tiles = ((g.m + 255) / 256) * ((g.n + 255) / 256) * g.batch * g.splits;
     bool two_cta = g.m > 128 && pair_tiles * 2 >= dev->prop.multiProcessorCount;
-    if (const char* e = getenv("EB200_TC_2CTA")) two_cta = atoi(e) != 0;
     if (convert) two_cta = false;      // the in-kernel split lives in the one-CTA kernel
     q.error_flag = dev->error_flag_dev;
     q.raster = 8;
-    if (const char* e = getenv("EB200_TC_RASTER")) q.raster = std::max(1, atoi(e));
     if (!dev->tc_configured) {
         EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
@@ -612,9 +608,7 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
         // EB200_TC_NH=2 makes the pair tile 256 x 512 (the whole tensor memory; a third less operand
         // traffic per flop).  Both pass the GEMM parity tests.
         q.ks = 1;
-        if (const char* e = getenv("EB200_TC_KS")) q.ks = atoi(e) == 2 && g.splits == 1 ? 2 : 1;
         q.nh = 1;
-        if (const char* e = getenv("EB200_TC_NH")) q.nh = atoi(e) == 2 && !three ? 2 : 1;
         const int stage_bytes = q.ks * (three ? 2 : 1) * (1 + q.nh) * TC_TILE_BYTES;
         q.stages = std::min(8, (196 * 1024) / stage_bytes);
         EB_REQUIRE(q.stages >= 2, EB200_ERR_UNSUPPORTED, "GEMM stage does not fit shared memory twice");

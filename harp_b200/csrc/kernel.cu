@@ -46,7 +46,7 @@ int eb200_kernel_create(eb200_device* dev, const eb200_kernel_desc* desc, eb200_
     if (st) { delete k; return st; }
     if (k->plan.scratch_bytes > 0) {
         cudaSetDevice(dev->index);
-        st = storage_alloc(dev, (size_t)k->plan.scratch_bytes, false, &k->scratch);
+        st = storage_alloc(dev, (size_t)k->plan.scratch_bytes, k->plan.scratch_zero, &k->scratch);
         if (st) { delete k; return st; }
     }
     *out = k;
@@ -58,7 +58,7 @@ static void fill_info(const Plan& plan, eb200_kernel_info* info) {
     strncpy(info->impl, plan.name, sizeof(info->impl) - 1);
     info->launches = plan.launches;
     info->specialised = plan.chain >= 0 || plan.impl == IMPL_TRANSPOSE || plan.impl == IMPL_SCATTER ||
-                        plan.impl == IMPL_SGD || plan.impl == IMPL_GEMM_SIMT || plan.impl == IMPL_GEMM_TC || plan.impl == IMPL_CONV2D || plan.impl == IMPL_GEMM_TALL || plan.impl == IMPL_CONV2D_WGRAD || plan.impl == IMPL_CONV2D_DIRECT || plan.impl == IMPL_CONV2D_DIRECT_WGRAD;
+                        plan.impl == IMPL_SGD || plan.impl == IMPL_SGD_MOMENTUM || plan.impl == IMPL_ADAM || plan.impl == IMPL_GEMM_SIMT || plan.impl == IMPL_GEMM_TC || plan.impl == IMPL_CONV2D || plan.impl == IMPL_GEMM_TALL || plan.impl == IMPL_CONV2D_WGRAD || plan.impl == IMPL_CONV2D_DIRECT || plan.impl == IMPL_CONV2D_DIRECT_WGRAD;
     info->scratch_bytes = plan.scratch_bytes;
     info->algo_bytes = plan.algo_bytes;
     info->algo_flops = plan.algo_flops;
@@ -102,9 +102,14 @@ int eb200_kernel_launch(eb200_kernel* k, eb200_buffer* const* inputs, int n_inpu
     // bytes the kernel does not overwrite
     int st = buffer_unshare(ob, true);
     if (st) return st;
+    const bool optimizer = plan.impl == IMPL_SGD || plan.impl == IMPL_SGD_MOMENTUM || plan.impl == IMPL_ADAM;
     for (int i = 0; i < n_inputs; ++i)
-        EB_REQUIRE(inputs[i]->storage->ptr != ob->storage->ptr || plan.impl == IMPL_SGD, EB200_ERR_INVALID,
+        EB_REQUIRE(inputs[i]->storage->ptr != ob->storage->ptr || (optimizer && i == 0), EB200_ERR_INVALID,
                    "input %d aliases the output", i);
+    // optimizer state (velocity, moments, step counter) is updated in place: give it its own storage first
+    if (plan.impl == IMPL_SGD_MOMENTUM || plan.impl == IMPL_ADAM)
+        for (int i = 2; i < n_inputs; ++i)
+            if ((st = buffer_unshare(inputs[i], true))) return st;
 
     KParams p = plan.p;
     for (int c = 0; c < p.n_in; ++c) p.in[c].ptr = reinterpret_cast<char*>(inputs[plan.perm[c]]->storage->ptr);
@@ -118,13 +123,36 @@ int eb200_kernel_launch(eb200_kernel* k, eb200_buffer* const* inputs, int n_inpu
     switch (plan.impl) {
         case IMPL_EW: return launch_ew(dev, plan, p);
         case IMPL_REDUCE_INNER:
-        case IMPL_REDUCE_OUTER: return launch_reduce(dev, plan, p, scratch);
+        case IMPL_REDUCE_OUTER: {
+            if (!k->comm) return launch_reduce(dev, plan, p, scratch);
+            // sharded reduce: this rank's result is combined with the peers' as part of the launch
+            float* out = reinterpret_cast<float*>(p.out.ptr) + p.out.offset;
+            if (p.splits > 1 && comm_can_fuse(k->comm, p.kept)) {
+                if ((st = launch_reduce(dev, plan, p, scratch, false))) return st;
+                return comm_reduce_finish_allreduce(k->comm, reinterpret_cast<const float*>(scratch), p.splits, p.kept, p.rop, out);
+            }
+            if ((st = launch_reduce(dev, plan, p, scratch))) return st;
+            return comm_allreduce_buffer(k->comm, out, p.kept, p.rop);
+        }
         case IMPL_TRANSPOSE: return launch_transpose(dev, plan, p.in[0].ptr, p.out.ptr);
         case IMPL_SCATTER: return launch_scatter(dev, plan, p);
         case IMPL_SGD:
             return launch_sgd(dev, plan, reinterpret_cast<const float*>(p.in[0].ptr) + p.in[0].offset,
                               reinterpret_cast<const float*>(p.in[1].ptr) + p.in[1].offset,
                               reinterpret_cast<float*>(p.out.ptr) + p.out.offset, p.total);
+        case IMPL_SGD_MOMENTUM:
+            return launch_sgd_momentum(dev, plan, reinterpret_cast<const float*>(p.in[0].ptr) + p.in[0].offset,
+                                       reinterpret_cast<const float*>(p.in[1].ptr) + p.in[1].offset,
+                                       reinterpret_cast<float*>(p.in[2].ptr) + p.in[2].offset,
+                                       reinterpret_cast<float*>(p.out.ptr) + p.out.offset, p.total);
+        case IMPL_ADAM:
+            return launch_adam(dev, plan, reinterpret_cast<const float*>(p.in[0].ptr) + p.in[0].offset,
+                               reinterpret_cast<const float*>(p.in[1].ptr) + p.in[1].offset,
+                               reinterpret_cast<float*>(p.in[2].ptr) + p.in[2].offset,
+                               reinterpret_cast<float*>(p.in[3].ptr) + p.in[3].offset,
+                               reinterpret_cast<int*>(p.in[4].ptr) + p.in[4].offset,
+                               reinterpret_cast<float*>(p.out.ptr) + p.out.offset, p.total, scratch);
+        case IMPL_SCAN: return launch_scan(dev, plan, p, scratch);
         case IMPL_GEMM_SIMT:
             return launch_gemm_simt(dev, plan, reinterpret_cast<const float*>(p.in[plan.gemm.a_input].ptr),
                                     reinterpret_cast<const float*>(p.in[plan.gemm.b_input].ptr),
@@ -157,6 +185,25 @@ int eb200_kernel_launch(eb200_kernel* k, eb200_buffer* const* inputs, int n_inpu
                                  reinterpret_cast<float*>(p.out.ptr) + p.out.offset, scratch);
         default: return set_error(EB200_ERR_UNSUPPORTED, "kernel implementation %d is not built", (int)plan.impl);
     }
+}
+
+int eb200_kernel_set_allreduce(eb200_kernel* k, eb200_comm* comm) {
+    EB_REQUIRE(k, EB200_ERR_INVALID, "kernel is null");
+    if (!comm) { k->comm = nullptr; return EB200_OK; }
+    const Plan& plan = k->plan;
+    EB_REQUIRE(plan.impl == IMPL_REDUCE_INNER || plan.impl == IMPL_REDUCE_OUTER, EB200_ERR_UNSUPPORTED,
+               "only reduce kernels take an attached all-reduce (%s)", plan.name);
+    const KParams& p = plan.p;
+    EB_REQUIRE(p.out.dtype == EB200_F32, EB200_ERR_UNSUPPORTED, "all-reduce of a non-f32 output");
+    // the kept elements must sit at out.offset + k: contiguous strides over the dims that are not reduced
+    long long acc = 1;
+    for (int d = p.ndim - 1; d >= 0; --d) {
+        if (d == p.raxis) continue;
+        EB_REQUIRE(p.shape[d] == 1 || p.out.strides[d] == acc, EB200_ERR_UNSUPPORTED, "the reduce output is not a contiguous range");
+        acc *= p.shape[d];
+    }
+    k->comm = comm;
+    return EB200_OK;
 }
 
 int eb200_kernel_release(eb200_kernel* k) {

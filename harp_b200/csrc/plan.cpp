@@ -57,6 +57,104 @@ void affine_range(const TC* coef, long long c, const TS* shape, int nd, int skip
     *hi = mx;
 }
 
+// Address range of a masked operand over the iterations where all of its bounds
+// hold.  Bounds are affine conditions lo <= c + coef.idx < hi (what pad, slice and
+// unfold produce, src/graph/shape/view.rs:980-1054,1162-1381).  Bounds with equal
+// coefficient vectors form a group; when the groups touch disjoint dims and the
+// operand's strides over a group's dims are a multiple alpha of its coefficients,
+// the address is offset + sum alpha_g * t_g + (free dims), with t_g = coef_g.idx
+// confined to an interval, so the range is exact.  Any other form is checked by
+// enumeration when the iteration space is small.  Returns 1 with [*lo, *hi],
+// 0 when no iteration satisfies the bounds, -1 when the form cannot be validated.
+int masked_range(const eb200_operand& o, const int64_t* shape, int nd, long long total, long long* lo, long long* hi) {
+    struct Group { int64_t coef[KMAX_DIMS]; long long tlo, thi; };
+    std::vector<Group> groups;
+    for (int b = 0; b < o.n_bounds; ++b) {
+        const eb200_bound& bd = o.bounds[b];
+        Group* g = nullptr;
+        for (auto& q : groups) {
+            bool same = true;
+            for (int d = 0; d < nd; ++d) same = same && q.coef[d] == bd.coef[d];
+            if (same) { g = &q; break; }
+        }
+        const long long tlo = bd.lo - bd.c, thi = bd.hi - 1 - bd.c;     // lo <= c + t <= hi - 1
+        if (g) { g->tlo = std::max(g->tlo, tlo); g->thi = std::min(g->thi, thi); continue; }
+        Group ng{};
+        for (int d = 0; d < nd; ++d) ng.coef[d] = bd.coef[d];
+        long long mn, mx;
+        affine_range(bd.coef, 0, shape, nd, -1, &mn, &mx);
+        ng.tlo = std::max(tlo, mn); ng.thi = std::min(thi, mx);
+        groups.push_back(ng);
+    }
+    bool analytic = true;
+    bool used[KMAX_DIMS] = {false};
+    long long alpha[16] = {0};
+    for (size_t gi = 0; gi < groups.size() && analytic; ++gi) {
+        const Group& g = groups[gi];
+        bool have = false;
+        for (int d = 0; d < nd && analytic; ++d) {
+            if (g.coef[d] == 0 || shape[d] <= 1) continue;
+            if (used[d]) { analytic = false; break; }
+            used[d] = true;
+            if (o.strides[d] % g.coef[d] != 0) { analytic = false; break; }
+            const long long a = o.strides[d] / g.coef[d];
+            if (have && a != alpha[gi]) { analytic = false; break; }
+            alpha[gi] = a; have = true;
+        }
+        if (gi >= 15) analytic = false;
+    }
+    if (analytic) {
+        long long mn = o.offset, mx = o.offset;
+        for (size_t gi = 0; gi < groups.size(); ++gi) {
+            Group& g = groups[gi];
+            // one active dim: t = k * idx only takes multiples of k, so round the interval inwards
+            int active = -1, n_active = 0;
+            for (int d = 0; d < nd; ++d) if (g.coef[d] != 0 && shape[d] > 1) { active = d; ++n_active; }
+            if (n_active == 1 && g.tlo <= g.thi) {
+                const long long k = g.coef[active];
+                auto fdiv = [](long long a, long long b) { long long q = a / b; return (a % b != 0 && ((a < 0) != (b < 0))) ? q - 1 : q; };
+                auto cdiv = [&](long long a, long long b) { return -fdiv(-a, b); };
+                long long i0 = k > 0 ? cdiv(g.tlo, k) : cdiv(g.thi, k), i1 = k > 0 ? fdiv(g.thi, k) : fdiv(g.tlo, k);
+                i0 = std::max(i0, 0LL); i1 = std::min(i1, (long long)shape[active] - 1);
+                if (i0 > i1) return 0;
+                g.tlo = std::min(k * i0, k * i1); g.thi = std::max(k * i0, k * i1);
+            }
+            if (g.tlo > g.thi) return 0;
+            const long long e0 = alpha[gi] * g.tlo, e1 = alpha[gi] * g.thi;
+            mn += std::min(e0, e1); mx += std::max(e0, e1);
+        }
+        for (int d = 0; d < nd; ++d) {
+            if (used[d] || shape[d] <= 1) continue;
+            const long long e = (long long)o.strides[d] * (shape[d] - 1);
+            if (e < 0) mn += e; else mx += e;
+        }
+        *lo = mn; *hi = mx;
+        return 1;
+    }
+    if (total > (1LL << 22)) return -1;
+    long long idx[KMAX_DIMS] = {0};
+    bool any = false;
+    long long mn = 0, mx = 0;
+    for (long long e = 0; e < total; ++e) {
+        bool ok = true;
+        for (int b = 0; b < o.n_bounds && ok; ++b) {
+            long long v = o.bounds[b].c;
+            for (int d = 0; d < nd; ++d) v += o.bounds[b].coef[d] * idx[d];
+            ok = v >= o.bounds[b].lo && v < o.bounds[b].hi;
+        }
+        if (ok) {
+            long long a = o.offset;
+            for (int d = 0; d < nd; ++d) a += o.strides[d] * idx[d];
+            if (!any) { mn = mx = a; any = true; }
+            else { mn = std::min(mn, a); mx = std::max(mx, a); }
+        }
+        for (int d = nd - 1; d >= 0; --d) { if (++idx[d] < shape[d]) break; idx[d] = 0; }
+    }
+    if (!any) return 0;
+    *lo = mn; *hi = mx;
+    return 1;
+}
+
 int check_program(const eb200_kernel_desc* d) {
     int depth = 0, maxdepth = 0;
     for (int i = 0; i < d->n_insns; ++i) {
@@ -139,7 +237,7 @@ bool try_gemm(const KParams& p, Plan* plan, int mode) {
 
 int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
     EB_REQUIRE(d && plan, EB200_ERR_INVALID, "null argument");
-    EB_REQUIRE(d->kclass >= EB200_K_ELEMENTWISE && d->kclass <= EB200_K_CONV2D, EB200_ERR_INVALID, "unknown kernel class %d", d->kclass);
+    EB_REQUIRE(d->kclass >= EB200_K_ELEMENTWISE && d->kclass <= EB200_K_ADAM, EB200_ERR_INVALID, "unknown kernel class %d", d->kclass);
     if (d->kclass == EB200_K_CONV2D) {
         // structured descriptor: shape = {N, C, H, W, Co, KH, KW, pad}
         EB_REQUIRE(d->ndim == 8, EB200_ERR_INVALID, "conv2d descriptor wants 8 shape entries, got %d", d->ndim);
@@ -215,7 +313,8 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
     if (st) return st;
 
     const bool is_reduce = d->kclass == EB200_K_REDUCE;
-    if (is_reduce) {
+    const bool is_scan = d->kclass == EB200_K_SCAN;
+    if (is_reduce || is_scan) {
         EB_REQUIRE(d->reduce_op >= EB200_R_SUM && d->reduce_op <= EB200_R_PROD, EB200_ERR_INVALID, "reduce op %d", d->reduce_op);
         EB_REQUIRE(d->reduce_axis >= 0 && d->reduce_axis < d->ndim, EB200_ERR_INVALID, "reduce axis %d of rank %d", d->reduce_axis, d->ndim);
     } else {
@@ -230,10 +329,18 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
     if (total > 0) {
         for (int i = 0; i <= d->n_inputs; ++i) {
             const eb200_operand& o = i < d->n_inputs ? d->inputs[i] : d->output;
-            if (o.n_bounds) continue;  // masked loads are guarded element by element
             long long lo, hi;
-            int skip = (i == d->n_inputs && is_reduce) ? d->reduce_axis : -1;
-            affine_range(o.strides, o.offset, d->shape, d->ndim, skip, &lo, &hi);
+            if (o.n_bounds) {
+                // a masked load is only dereferenced where every bound holds: validate
+                // the addresses of exactly those iterations
+                int r = masked_range(o, d->shape, d->ndim, total, &lo, &hi);
+                if (r == 0) continue;   // the bounds never hold together: nothing is loaded
+                EB_REQUIRE(r > 0, EB200_ERR_BOUNDS,
+                           "input %d: bound conditions of this form cannot be validated against the buffer size", i);
+            } else {
+                int skip = (i == d->n_inputs && is_reduce) ? d->reduce_axis : -1;
+                affine_range(o.strides, o.offset, d->shape, d->ndim, skip, &lo, &hi);
+            }
             EB_REQUIRE(lo >= 0 && hi < o.numel, EB200_ERR_BOUNDS,
                        "%s %d addresses elements [%lld, %lld] of a buffer of %lld",
                        i < d->n_inputs ? "input" : "output", i < d->n_inputs ? i : 0, lo, hi, (long long)o.numel);
@@ -243,7 +350,7 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
     // ---- normalise: drop extent-1 dims and provably true bounds, collapse
     int keep[KMAX_DIMS], nk = 0, raxis = -1;
     for (int i = 0; i < d->ndim; ++i) {
-        bool is_r = is_reduce && i == d->reduce_axis;
+        bool is_r = (is_reduce || is_scan) && i == d->reduce_axis;
         if (d->shape[i] != 1 || is_r) {
             if (is_r) raxis = nk;
             keep[nk++] = i;
@@ -257,7 +364,7 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
         Op& q = ops[i];
         q.dtype = o.dtype; q.offset = o.offset; q.numel = o.numel; q.pad = o.pad_value;
         for (int j = 0; j < nk; ++j) q.strides[j] = o.strides[keep[j]];
-        if (i == d->n_inputs && raxis >= 0) q.strides[raxis] = 0;
+        if (i == d->n_inputs && raxis >= 0 && is_reduce) q.strides[raxis] = 0;
         for (int b = 0; b < o.n_bounds; ++b) {
             eb200_bound nb{};
             for (int j = 0; j < nk; ++j) nb.coef[j] = o.bounds[b].coef[keep[j]];
@@ -300,6 +407,29 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
         --nk;
     }
 
+    // a scan walks the axis and every dim after it as ONE sequence
+    // (src/lowerer/loop_gen.rs:237-327): fold that tail into the axis where all
+    // operands walk it contiguously
+    while (is_scan && raxis >= 0 && raxis + 1 < nk) {
+        const int j = raxis;
+        bool ok = true;
+        for (auto& q : ops) {
+            if (q.strides[j] != q.strides[j + 1] * shape[j + 1]) { ok = false; break; }
+            for (auto& b : q.bounds)
+                if (b.coef[j] != b.coef[j + 1] * shape[j + 1]) { ok = false; break; }
+            if (!ok) break;
+        }
+        if (!ok) break;
+        shape[j + 1] *= shape[j];
+        for (int t = j; t < nk - 1; ++t) shape[t] = shape[t + 1];
+        for (auto& q : ops) {
+            for (int t = j; t < nk - 1; ++t) q.strides[t] = q.strides[t + 1];
+            for (auto& b : q.bounds)
+                for (int t = j; t < nk - 1; ++t) b.coef[t] = b.coef[t + 1];
+        }
+        --nk;
+    }
+
     Plan& pl = *plan;
     pl = Plan();
     KParams& p = pl.p;
@@ -324,6 +454,11 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
         long long k = 1;
         for (int j = 0; j < nk; ++j) if (j != raxis) k *= shape[j];
         p.kept = k;
+    }
+    if (is_scan) {
+        // rows = the dims before the axis; a row = the axis and everything after it
+        p.rlen = 1; p.kept = 1;
+        for (int j = 0; j < nk; ++j) (j < raxis ? p.kept : p.rlen) *= shape[j];
     }
     p.splits = 1;
     p.chunk = p.rlen;
@@ -356,6 +491,7 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
     pl.out_dtype = d->output.dtype;
     pl.out_numel = d->output.numel;
     pl.scalar = d->scalar;
+    for (int i = 0; i < 7; ++i) pl.hyper[i] = d->hyper[i];
 
     // ---- algorithmic traffic: every operand element that is addressed, once
     {
@@ -389,7 +525,7 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
     //      same compiled functor whatever order their inputs were declared in
     for (int j = 0; j < KMAX_CONSTS; ++j) pl.dyn_input[j] = -1;
     for (int i = 0; i < KMAX_IN; ++i) pl.perm[i] = i;
-    if (d->kclass == EB200_K_ELEMENTWISE || d->kclass == EB200_K_REDUCE) {
+    if (d->kclass == EB200_K_ELEMENTWISE || d->kclass == EB200_K_REDUCE || d->kclass == EB200_K_SCAN) {
         KOperand old_in[KMAX_IN];
         for (int i = 0; i < KMAX_IN; ++i) old_in[i] = p.in[i];
         // (1) expression tree from the postfix program; one-element loads marked constant
@@ -473,6 +609,42 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
             snprintf(pl.name, sizeof(pl.name), "sgd_update");
             break;
         }
+        case EB200_K_SGD_MOMENTUM:
+        case EB200_K_ADAM: {
+            const bool adam = d->kclass == EB200_K_ADAM;
+            const int nf = adam ? 4 : 3;     // flat f32 inputs: p, g, (m,) v
+            EB_REQUIRE(d->n_inputs == (adam ? 5 : 3) && nk <= 1, EB200_ERR_UNSUPPORTED,
+                       adam ? "adam wants p, g, m, v and the step counter" : "sgd with momentum wants p, g and v");
+            for (int i = 0; i < nf; ++i)
+                EB_REQUIRE(p.in[i].dtype == EB200_F32 && (total <= 1 || p.in[i].strides[0] == 1), EB200_ERR_UNSUPPORTED, "optimizer operands must be flat f32");
+            EB_REQUIRE(p.out.dtype == EB200_F32 && (total <= 1 || p.out.strides[0] == 1), EB200_ERR_UNSUPPORTED, "optimizer output must be flat f32");
+            if (adam) {
+                EB_REQUIRE(p.in[4].dtype == EB200_I32 && p.in[4].strides[0] == 0, EB200_ERR_UNSUPPORTED, "adam's step counter is one I32 element");
+                pl.impl = IMPL_ADAM;
+                pl.scratch_bytes = 256;      // the ticket word that picks the last CTA
+                pl.scratch_zero = true;
+                pl.algo_bytes = 28 * total;
+                snprintf(pl.name, sizeof(pl.name), "adam_update");
+            } else {
+                pl.impl = IMPL_SGD_MOMENTUM;
+                pl.algo_bytes = 20 * total;
+                snprintf(pl.name, sizeof(pl.name), "sgd_momentum_update");
+            }
+            break;
+        }
+        case EB200_K_SCAN: {
+            EB_REQUIRE(p.out.dtype == EB200_F32, EB200_ERR_UNSUPPORTED, "scan writes f32");
+            pl.impl = IMPL_SCAN;
+            const bool tail_flat = raxis == nk - 1;
+            bool v = tail_flat && p.rlen % 4 == 0 && p.rlen >= 4 && vec_ok(p.out, raxis, true);
+            for (int i = 0; v && i < p.n_in; ++i) v = vec_ok(p.in[i], raxis, false);
+            p.vec = v ? 4 : 1;
+            pl.scratch_bytes = scan_scratch_floats(p, sm_count) * 4;
+            pl.launches = pl.scratch_bytes ? 2 : 1;
+            if (pl.scratch_bytes) pl.algo_bytes += (pl.algo_bytes - 4 * total > 0 ? pl.algo_bytes - 4 * total : 0);   // the two-pass form reads its inputs twice
+            snprintf(pl.name, sizeof(pl.name), "scan_%s_v%d", pl.scratch_bytes ? "tiles" : (p.rlen <= 1024 ? "warp_rows" : "cta_rows"), p.vec);
+            break;
+        }
         case EB200_K_SCATTER: {
             EB_REQUIRE(d->n_inputs == 1 && identity, EB200_ERR_UNSUPPORTED, "scatter takes one input and no map");
             EB_REQUIRE(p.in[0].dtype == EB200_F32 && p.out.dtype == EB200_F32, EB200_ERR_UNSUPPORTED, "scatter-add is f32 only");
@@ -545,7 +717,14 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
             break;
         }
         case EB200_K_REDUCE: {
-            if (try_gemm(p, &pl, d->gemm_mode)) {
+            // a contraction is served as a GEMM only when some GEMM kernel's grid can hold it
+            // (grid.z carries batch x splits, grid.y the column tiles of the f32 kernel);
+            // anything else stays a plain reduce
+            auto gemm_fits = [&](const GemmShape& g) {
+                if ((d->flags & 8) == 0 && gemm_tc_supported(g) && 2 * g.batch * g.m * g.n * g.k >= (1LL << 22)) return true;
+                return g.batch <= 65535 && (g.n + 63) / 64 <= 65535;
+            };
+            if (try_gemm(p, &pl, d->gemm_mode) && gemm_fits(pl.gemm)) {
                 pl.algo_flops = 2 * pl.gemm.batch * pl.gemm.m * pl.gemm.n * pl.gemm.k;
                 // tensor cores when the operand layout allows it and the problem
                 // is more than a few tiles of work; f32 FFMA tiles otherwise
@@ -659,7 +838,7 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
             break;
         }
     }
-    if (pl.impl == IMPL_EW || pl.impl == IMPL_REDUCE_INNER || pl.impl == IMPL_REDUCE_OUTER) {
+    if (pl.impl == IMPL_EW || pl.impl == IMPL_REDUCE_INNER || pl.impl == IMPL_REDUCE_OUTER || pl.impl == IMPL_SCAN) {
         pl.chain = find_chain(p.prog, p.n_insns);
     }
     return EB200_OK;

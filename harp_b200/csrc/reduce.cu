@@ -503,7 +503,7 @@ __global__ void __launch_bounds__(256) reduce_finish_kernel(const __grid_constan
 }
 
 template <class F>
-static int launch_one(Device* dev, const Plan& plan, const KParams& p, float* scratch) {
+static int launch_one(Device* dev, const Plan& plan, const KParams& p, float* scratch, bool finish) {
     const int sms = dev->prop.multiProcessorCount;
     if (p.kept <= 0) return EB200_OK;
     if (plan.impl == IMPL_REDUCE_INNER) {
@@ -546,7 +546,7 @@ static int launch_one(Device* dev, const Plan& plan, const KParams& p, float* sc
     }
     count_launch();
     EB_CHECK_CUDA(cudaGetLastError());
-    if (p.splits > 1) {
+    if (p.splits > 1 && finish) {
         long long blocks = (p.kept + 255) / 256;
         long long cap = (long long)sms * 8;
         if (blocks > cap) blocks = cap;
@@ -557,14 +557,16 @@ static int launch_one(Device* dev, const Plan& plan, const KParams& p, float* sc
     return EB200_OK;
 }
 
-int launch_reduce(Device* dev, const Plan& plan, const KParams& p, void* scratch) {
+// `finish` false leaves the partials of a split reduction in scratch (the caller folds them,
+// e.g. fused with an all-reduce).
+int launch_reduce(Device* dev, const Plan& plan, const KParams& p, void* scratch, bool finish) {
     float* s = reinterpret_cast<float*>(scratch);
     EB_REQUIRE(p.splits == 1 || s, EB200_ERR_INVALID, "split reduction launched without scratch");
     switch (plan.chain) {
-#define X(i) case i: return launch_one<Compiled<Chain##i>>(dev, plan, p, s);
+#define X(i) case i: return launch_one<Compiled<Chain##i>>(dev, plan, p, s, finish);
         EB_FOR_EACH_CHAIN(X)
 #undef X
-        default: return launch_one<Interp>(dev, plan, p, s);
+        default: return launch_one<Interp>(dev, plan, p, s, finish);
     }
 }
 

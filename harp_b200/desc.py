@@ -34,8 +34,9 @@ DTYPE_SIZE = {F32: 4, BOOL: 1, I32: 4, I64: 8}
 DTYPE_NP = {F32: "float32", BOOL: "uint8", I32: "int32", I64: "int64"}
 
 # eb200_kclass
-K_ELEMENTWISE, K_REDUCE, K_COPY, K_SCATTER, K_SGD, K_CONV2D = 0, 1, 2, 3, 4, 5
-KCLASS_PREFIX = {K_ELEMENTWISE: "E", K_REDUCE: "R", K_COPY: "C", K_SCATTER: "S", K_SGD: "U", K_CONV2D: "CONV"}
+K_ELEMENTWISE, K_REDUCE, K_COPY, K_SCATTER, K_SGD, K_CONV2D, K_SCAN, K_SGD_MOMENTUM, K_ADAM = 0, 1, 2, 3, 4, 5, 6, 7, 8
+KCLASS_PREFIX = {K_ELEMENTWISE: "E", K_REDUCE: "R", K_COPY: "C", K_SCATTER: "S", K_SGD: "U", K_CONV2D: "CONV",
+                 K_SCAN: "P", K_SGD_MOMENTUM: "UM", K_ADAM: "UA"}
 FLAG_RELU = 64
 FLAG_WFLIP = 128
 FLAG_WGRAD = 256
@@ -218,6 +219,7 @@ class KernelDesc:
     scalar: float = 0.0
     name: str = ""
     flags: int = 0
+    hyper: Sequence[float] = ()
 
     def __post_init__(self):
         self.shape = [int(s) for s in self.shape]
@@ -257,6 +259,8 @@ class KernelDesc:
         d.gemm_mode = self.gemm_mode
         d.scalar = self.scalar
         d.flags = self.flags
+        for i, h in enumerate(self.hyper):
+            d.hyper[i] = float(h)
         prog = self.program()
         if len(prog) > MAX_INSNS:
             raise ValueError(f"map program of {len(prog)} instructions exceeds {MAX_INSNS}")
@@ -307,7 +311,7 @@ class CKernelDesc(C.Structure):
         ("kclass", C.c_int32), ("ndim", C.c_int32), ("shape", C.c_int64 * MAX_DIMS),
         ("n_inputs", C.c_int32), ("reduce_op", C.c_int32), ("reduce_axis", C.c_int32),
         ("n_insns", C.c_int32), ("gemm_mode", C.c_int32), ("flags", C.c_int32),
-        ("scalar", C.c_float), ("_pad", C.c_int32),
+        ("scalar", C.c_float), ("hyper", C.c_float * 7),
         ("inputs", COperand * MAX_INPUTS), ("output", COperand),
         ("prog", CInsn * MAX_INSNS),
     ]
@@ -358,6 +362,25 @@ def reduce(shape, inputs: List[Operand], expr: Ast, op: int, axis: int,
         st[axis] = 0
         out = Operand(st, 0, F32, math.prod(kept))
     return KernelDesc(K_REDUCE, shape, inputs, out, expr, op, axis, gemm_mode)
+
+
+def scan(shape, inputs: List[Operand], expr: Ast, op: int, axis: int, out: Optional[Operand] = None) -> KernelDesc:
+    """Cumulative op along `axis` (P_ kernel, src/lowerer/lower.rs:691-735); the
+    output has the iteration shape."""
+    return KernelDesc(K_SCAN, shape, inputs, out or contiguous(shape), expr, op, axis)
+
+
+def sgd_momentum(n: int, lr: float, momentum: float) -> KernelDesc:
+    """SGD with momentum over flat buffers (crates/nn/src/optim/sgd.rs:84-89):
+    inputs p, g, v (v updated in place), output p."""
+    return KernelDesc(K_SGD_MOMENTUM, [n], [contiguous([n])] * 3, contiguous([n]), scalar=lr, hyper=[momentum])
+
+
+def adam(n: int, lr: float, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8) -> KernelDesc:
+    """Adam over flat buffers (crates/nn/src/optim/adam.rs:104-147): inputs p, g, m, v
+    and the one-element I32 step counter (m, v, t updated in place), output p."""
+    ins = [contiguous([n])] * 4 + [Operand([0], 0, I32, 1)]
+    return KernelDesc(K_ADAM, [n], ins, contiguous([n]), scalar=lr, hyper=[beta1, beta2, eps])
 
 
 def copy(shape, src: Operand, out: Optional[Operand] = None) -> KernelDesc:

@@ -797,9 +797,27 @@ class Program:
 
     def __init__(self, roots: Sequence[Tensor], executor, fuse: str = "chains",
                  sgd: Sequence[Tuple[Tensor, Tensor]] = (), lr: float = 0.0, persistent: bool = False,
-                 flat: bool = False):
+                 flat: bool = False, optimizer: str = "sgd", momentum: float = 0.0,
+                 betas: Tuple[float, float] = (0.9, 0.999), eps: float = 1e-8, comm=None, overlap: bool = True):
         """`flat=True` lays all parameters out in one buffer and all gradients in
-        another (same offsets): one all-reduce and one update kernel per step."""
+        another (same offsets): one all-reduce and one update kernel per step.
+
+        `optimizer`: "sgd" (crates/nn/src/optim/sgd.rs:91-95), "momentum"
+        (sgd.rs:84-89) or "adam" (adam.rs:104-147); the stateful ones keep their
+        velocity / moments / step counter in device buffers laid out like the flat
+        parameters.
+
+        `comm` (a ``B200Comm`` or the CPU stand-in ``HostComm``) makes the step
+        data parallel: the gradients are summed over the ranks before the update
+        (pass lr / world size for the gradient mean).  With plain SGD the
+        all-reduce and the update are one kernel, and with `overlap` the part of the
+        flat buffer whose gradients are complete early in the backward pass is
+        reduced and updated on the communicator's side stream while the rest of the
+        backward pass runs."""
+        assert optimizer in ("sgd", "momentum", "adam")
+        assert optimizer == "sgd" or flat, "stateful optimizers run over the flat parameter buffer"
+        assert comm is None or flat, "a data-parallel step all-reduces the flat gradient buffer"
+        self.optimizer, self.lr, self.comm, self.overlap = optimizer, lr, comm, overlap
         self.ex = executor
         self.persistent = persistent      # keep every intermediate buffer between runs (no per-step allocation)
         self.graph = None
@@ -863,10 +881,19 @@ class Program:
             if s not in keep and self.where[s][0] == s:
                 self.release_after[pos].append(s)
         self.sgd_kernels = []
+        self.state: List[object] = []        # optimizer state buffers (velocity | moments and step counter)
+        self.buckets: List[Tuple[int, int, int]] = []     # (offset, count, kernel position after which it may go) of the async part
         if self.flat:
             n = self.cnumel[_FLAT_P]
-            d = D.KernelDesc(D.K_SGD, [n], [D.contiguous([n]), D.contiguous([n])], D.contiguous([n]), scalar=lr)
+            if optimizer == "momentum":
+                d = D.sgd_momentum(n, lr, momentum)
+            elif optimizer == "adam":
+                d = D.adam(n, lr, betas[0], betas[1], eps)
+            else:
+                d = D.KernelDesc(D.K_SGD, [n], [D.contiguous([n]), D.contiguous([n])], D.contiguous([n]), scalar=lr)
             self.sgd_kernels.append((_FLAT_P, _FLAT_G, self.ex.compile(d)))
+            if comm is not None and optimizer == "sgd" and overlap and comm.info()["nranks"] > 1:
+                self.buckets = self._plan_buckets(pids, gids)
         else:
             for p, g in self.sgd:
                 n = p.node.out_numel
@@ -882,6 +909,13 @@ class Program:
             self.ex.upload(self.buf[_FLAT_P], host)
             self.buf[_FLAT_G] = self.ex.alloc(host.size)
             self.ex.upload(self.buf[_FLAT_G], np.zeros_like(host))
+            if optimizer in ("momentum", "adam"):
+                for _ in range(1 if optimizer == "momentum" else 2):
+                    b = self.ex.alloc(host.size)
+                    self.ex.upload(b, np.zeros_like(host))
+                    self.state.append(b)
+                if optimizer == "adam":
+                    self.state.append(self.ex.alloc_counter())
         for i, k in self.inputs.items():
             if self.where[i][0] != i:
                 continue
@@ -898,8 +932,45 @@ class Program:
     def kernel_descs(self) -> List[D.KernelDesc]:
         return [d for _, d, _, _ in self.kernels]
 
+    def _plan_buckets(self, pids, gids):
+        """Which contiguous part of the flat buffers can be reduced and updated
+        before the backward pass has finished: the part whose gradients are
+        written, and whose parameters are last read, earliest.  Scored by size
+        times the number of kernels still to run behind it."""
+        pos_of = {i: pos for pos, (i, _, _, _) in enumerate(self.kernels)}
+        last_read: Dict[int, int] = {}
+        for pos, (_, _, _, srcs) in enumerate(self.kernels):
+            for s_ in srcs:
+                last_read[s_] = pos
+        items = []
+        total = self.cnumel[_FLAT_P]
+        for j, (pid, gid) in enumerate(zip(pids, gids)):
+            off = self.where[pid][1]
+            end = self.where[pids[j + 1]][1] if j + 1 < len(pids) else total
+            items.append((off, end - off, max(pos_of.get(gid, -1), last_read.get(pid, -1), last_read.get(gid, -1))))
+        n = len(self.kernels)
+        best = None
+        for k in range(1, len(items)):
+            for early in (items[k:], items[:k]):
+                ready = max(it[2] for it in early)
+                count = sum(it[1] for it in early)
+                score = count * (n - 1 - ready)
+                if ready < n - 1 and (best is None or score > best[0]):
+                    best = (score, early[0][0], count, ready)
+        return [best[1:]] if best else []
+
+    def _rest_of_flat(self):
+        """The (offset, count) ranges of the flat buffers no early bucket covers."""
+        total = self.cnumel[_FLAT_P]
+        if not self.buckets:
+            return [(0, total)]
+        off, cnt, _ = self.buckets[0]
+        return [r for r in ((0, off), (off + cnt, total - off - cnt)) if r[1] > 0]
+
     def run_forward(self):
-        """All kernels up to and including the gradients (no parameter update)."""
+        """All kernels up to and including the gradients.  In a data-parallel step
+        with overlap, the early bucket's all-reduce + update is issued on the
+        communicator's side stream as soon as its gradients are complete."""
         for pos, (i, d, kern, srcs) in enumerate(self.kernels):
             c = self.where[i][0]
             if c not in self.buf:
@@ -908,15 +979,25 @@ class Program:
             if not self.persistent:
                 for s in self.release_after[pos]:
                     self.ex.free(self.buf.pop(s))
+            for off, cnt, ready in self.buckets:
+                if ready == pos:
+                    self.comm.allreduce_sgd(self.buf[_FLAT_P], self.buf[_FLAT_G], self.lr, off, cnt, side_stream=True)
 
     def run_update(self):
+        if self.comm is not None and self.optimizer == "sgd":
+            # gradient all-reduce and p -= lr * sum as one kernel per range
+            for off, cnt in self._rest_of_flat():
+                self.comm.allreduce_sgd(self.buf[_FLAT_P], self.buf[_FLAT_G], self.lr, off, cnt)
+            self.comm.join()
+            return
+        if self.comm is not None:
+            self.comm.allreduce(self.buf[_FLAT_G], D.R_SUM)
         for pid, gid, kern in self.sgd_kernels:
-            kern.execute([self.buf[pid], self.buf[gid]], [self.buf[pid]])
+            kern.execute([self.buf[pid], self.buf[gid]] + self.state, [self.buf[pid]])
 
     def run(self, between=None):
         """One step.  `between` (optional callable) runs after the gradients are
-        complete and before the parameter update -- where a data-parallel job
-        all-reduces its gradients."""
+        complete and before the parameter update."""
         if self.graph is not None:
             self.graph.launch()
         else:
@@ -932,7 +1013,10 @@ class Program:
         parameter update stays a separate launch sequence (so a collective can sit
         between them).  Needs ``persistent=True`` and the CUDA executor."""
         assert self.persistent, "capture needs persistent buffers"
+        assert include_update or not self.buckets, "an overlapped data-parallel step is recorded as a whole"
         self.run_forward()                              # allocates every buffer, warms every kernel
+        if self.buckets:
+            self.run_update()                           # (a whole step: the early bucket's update has been issued)
         self.ex.synchronize()
         self.ex.dev.graph_begin()
         try:
@@ -982,6 +1066,11 @@ class B200Executor:
 
     def download(self, buf, numel):
         return buf.read_vec()
+
+    def alloc_counter(self):
+        """One zeroed I32 element (Adam's step counter)."""
+        from .backend import B200Buffer
+        return B200Buffer.allocate(self.dev, [1], D.I32, zero=True)
 
     def compile(self, d):
         return self.reg.compile_ast(self.dev, d)

@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define EB200_ABI_VERSION 1
+#define EB200_ABI_VERSION 2
 
 #define EB200_MAX_DIMS 8     /* iteration-space rank (reference tensors are D0..D8) */
 #define EB200_MAX_INPUTS 8   /* the C backend caps a kernel at 6 pointers; fused chains may need more */
@@ -62,7 +62,7 @@ typedef enum {
     EB200_K_COPY = 2,        /* C_: lower_view, lower.rs:448-501 */
     EB200_K_SCATTER = 3,     /* S_: lower_scatter, lower.rs:580-683 */
     EB200_K_SGD = 4,         /* p <- p - lr*g (crates/nn/src/optim/sgd.rs:73-103), device resident */
-    EB200_K_CONV2D = 5       /* functional::conv2d as one kernel (crates/nn/src/functional/conv.rs:113-184):
+    EB200_K_CONV2D = 5,      /* functional::conv2d as one kernel (crates/nn/src/functional/conv.rs:113-184):
                               * shape = {N, C, H, W, Co, KH, KW, pad}; inputs x [N,C,H,W], w [Co,C,KH,KW] and
                               * optionally bias [Co], all contiguous; output [N*Ho*Wo, Co] row-major (the buffer
                               * the reference's GEMM step writes before its final permute view); stride 1;
@@ -79,6 +79,16 @@ typedef enum {
                               * the output is dW [Co, C, KH, KW] (the contraction the reference spells as a broadcast
                               * multiply of the gradient with the materialised unfold, summed over batch and positions);
                               * gemm_mode picks TF32 / 3xTF32 */
+    EB200_K_SCAN = 6,        /* P_: lower_scan, lower.rs:691-735; loops loop_gen.rs:237-327.  reduce_op / reduce_axis
+                              * name the scan.  As in the reference's loop nest, ONE accumulator per index of the dims
+                              * before the axis runs over the axis and every dim after it in row-major order (a plain
+                              * cumulative op when the axis is innermost); the output has the iteration shape */
+    EB200_K_SGD_MOMENTUM = 7,/* v <- momentum*v - lr*g; p <- p + v (crates/nn/src/optim/sgd.rs:84-89): inputs p, g, v;
+                              * the output receives p, input 2 (v) is updated IN PLACE; scalar = lr, hyper[0] = momentum */
+    EB200_K_ADAM = 8         /* Adam::step (crates/nn/src/optim/adam.rs:104-147): inputs p, g, m, v and a one-element
+                              * I32 step counter t; the output receives p; m, v and t are updated IN PLACE (t <- t + 1
+                              * on the device, so a captured step can be replayed); scalar = lr, hyper[0..2] = beta1,
+                              * beta2, eps; bias corrections 1 - beta^t use the repeated-squaring powi of f32::powi */
 } eb200_kclass;
 
 /* ReduceOp (src/graph/node.rs:29-77). */
@@ -164,8 +174,8 @@ typedef struct {
     int32_t n_insns;      /* 0 = identity map of input 0 (COPY / SCATTER) */
     int32_t gemm_mode;    /* eb200_gemm_mode */
     int32_t flags;        /* tuning hints, 0 = automatic; bits 0-2 force the row-reduce group (1 thread, 2 warp, 3 CTA, 4 half CTA per row); bit 3 keeps a contraction on the f32 FFMA kernel; bit 4 disables split-K (and keeps a narrow column reduce on the thread-per-vector kernel); bit 5 stages long reduce rows through shared memory with bulk async copies */
-    float   scalar;       /* SGD: learning rate */
-    int32_t _pad;
+    float   scalar;       /* optimizer kernels: learning rate */
+    float   hyper[7];     /* optimizer kernels: further hyper-parameters (see eb200_kclass) */
     eb200_operand inputs[EB200_MAX_INPUTS];
     eb200_operand output; /* store address; for REDUCE the reduce-axis stride is ignored (index := 0) */
     eb200_insn prog[EB200_MAX_INSNS];
@@ -308,6 +318,42 @@ int eb200_kernel_release(eb200_kernel* k);
  * whose kernels overlap on the GPU (different streams) race on it. */
 int eb200_reduce_cols_static(const float* x, int64_t rows, int64_t cols, int reduce_op,
                              float* out, void* stream);
+/* ---- collectives.  No counterpart in the reference (it has no distributed code: no collective
+ *      call site, an Rc-based single-thread graph, src/graph/node.rs:222); they serve the
+ *      data-parallel training step (batch shards, one gradient all-reduce per step: the update
+ *      loop of crates/nn/src/optim/sgd.rs:73-103 once per rank) and row-sharded reductions.
+ *      One process per GPU.  Rank 0 makes a unique id, the host passes it to the other ranks by
+ *      any channel it has, every rank calls eb200_comm_init.  Messages of up to 524 288 floats go
+ *      through a one-shot kernel over NVLink (each rank stores its part into an inbox in every
+ *      peer's memory, then reduces from its own memory); larger ones, and all of them when the
+ *      peers' memory cannot be mapped, through NCCL (loaded at run time).  All ranks must issue
+ *      the same collectives in the same order.  A rank whose peers do not arrive gives up after
+ *      about a second; eb200_device_sync then returns EB200_ERR_TIMEOUT. */
+typedef struct { char bytes[128]; } eb200_comm_id;
+int eb200_comm_unique_id(eb200_comm_id* id);
+int eb200_comm_init(eb200_device* dev, int rank, int nranks, const eb200_comm_id* id, eb200_comm** comm);
+/* rank, size, whether the one-shot transport is up, and how many collectives took each transport */
+int eb200_comm_info(eb200_comm* comm, int* rank, int* nranks, int* one_shot, int64_t* calls_one_shot, int64_t* calls_nccl);
+/* In-place all-reduce of f32 elements [offset, offset + count) of `buf` with an eb200_reduce_op,
+ * ordered on the device's compute stream like a kernel launch. */
+int eb200_comm_allreduce(eb200_comm* comm, eb200_buffer* buf, int64_t offset, int64_t count, int reduce_op);
+/* The same on the communicator's own high-priority stream: it starts once the work queued on the
+ * compute stream so far is done and runs beside what is queued afterwards; eb200_comm_join makes
+ * the compute stream wait for it.  Both may be issued while a step is recorded by eb200_graph_begin
+ * (join before eb200_graph_end). */
+int eb200_comm_allreduce_async(eb200_comm* comm, eb200_buffer* buf, int64_t offset, int64_t count, int reduce_op);
+int eb200_comm_join(eb200_comm* comm);
+/* Gradient all-reduce fused with the SGD update, one kernel: params[i] -= lr * sum over ranks of
+ * grads[i] for i in [offset, offset + count) (gradient mean: pass lr / nranks).  grads keeps this
+ * rank's own values.  The _async form runs on the communicator's stream (see above). */
+int eb200_comm_allreduce_sgd(eb200_comm* comm, eb200_buffer* params, eb200_buffer* grads, int64_t offset, int64_t count, float lr);
+int eb200_comm_allreduce_sgd_async(eb200_comm* comm, eb200_buffer* params, eb200_buffer* grads, int64_t offset, int64_t count, float lr);
+/* Makes a REDUCE kernel's output the all-reduce over the ranks of what it computes locally (a
+ * row-sharded sum / max): for a split column reduce the pass that folds the split partials also
+ * pushes them to the peers and reduces theirs (one kernel); other reduce kernels are followed by
+ * an all-reduce of the output.  The output must be a contiguous f32 range.  NULL detaches. */
+int eb200_kernel_set_allreduce(eb200_kernel* k, eb200_comm* comm);
+int eb200_comm_destroy(eb200_comm* comm);
 /* Number of device kernel launches issued through this library so far. */
 int eb200_launch_count(int64_t* count);
 

@@ -304,10 +304,53 @@ def emit_kernel_c(k: D.KernelDesc, fn_name: str = "kernel", openmp: bool = False
             line(f"out[{k.output.offset} + ((((ridx0 * {ho}) + ridx1) * {wo} + ridx2) * {co} + ridx3)] = {val};")
         for _ in range(4):
             close_loop()
+    elif k.kclass == D.K_SCAN:
+        # generate_scan (src/lowerer/loop_gen.rs:237-327): loops before the axis outside, then
+        # `acc = identity`, then the scan loop with the loops of the later dims INSIDE it; the body
+        # updates the one accumulator and stores it at every position
+        ax = k.reduce_axis
+        for d in range(ax):
+            open_loop(d, k.shape[d])
+        line("float acc;")
+        line(f"acc = {f32_literal(_IDENTITY[k.reduce_op])};")
+        pragma_done[0] = True
+        for d in range(ax, nd):
+            open_loop(d, k.shape[d])
+        val = render_expr(k.map, loads, fma) if k.map is not None else loads[0]
+        line(f"acc = {_combine(k.reduce_op, 'acc', val, False, None)};")
+        line(f"out[{_affine(k.output.offset, k.output.strides)}] = acc;")
+        for _ in range(nd):
+            close_loop()
     elif k.kclass == D.K_SGD:
-        # host loop of SGD::step (crates/nn/src/optim/sgd.rs:73-103): p - lr*g
+        # host loop of SGD::step (crates/nn/src/optim/sgd.rs:91-95): p - lr*g
         open_loop(0, k.shape[0])
         line(f"out[ridx0] = (buf0[ridx0] - ({f32_literal(k.scalar)} * buf1[ridx0]));")
+        close_loop()
+    elif k.kclass == D.K_SGD_MOMENTUM:
+        # crates/nn/src/optim/sgd.rs:84-89: v = momentum*v - lr*g; p = p + v (v kept between steps)
+        open_loop(0, k.shape[0])
+        line(f"buf2[ridx0] = (({f32_literal(k.hyper[0])} * buf2[ridx0]) - ({f32_literal(k.scalar)} * buf1[ridx0]));")
+        line("out[ridx0] = (buf0[ridx0] + buf2[ridx0]);")
+        close_loop()
+    elif k.kclass == D.K_ADAM:
+        # Adam::step (crates/nn/src/optim/adam.rs:104-147); f32::powi is the runtime's
+        # repeated-squaring __powisf2
+        b1, b2, eps = (f32_literal(h) for h in k.hyper[:3])
+        src = src.replace("// === Kernel Functions ===\n", "// === Kernel Functions ===\n"
+                          "static float powi_f32(float a, int b) {\n"
+                          "    float r = 1.0f;\n"
+                          "    while (1) { if (b & 1) r *= a; b /= 2; if (b == 0) break; a *= a; }\n"
+                          "    return r;\n}\n")
+        line("buf4[0] = (buf4[0] + 1);")
+        line(f"float bias_correction1 = (1.0f - powi_f32({b1}, buf4[0]));")
+        line(f"float bias_correction2 = (1.0f - powi_f32({b2}, buf4[0]));")
+        open_loop(0, k.shape[0])
+        line("float g = buf1[ridx0];")
+        line(f"buf2[ridx0] = (({b1} * buf2[ridx0]) + ((1.0f - {b1}) * g));")
+        line(f"buf3[ridx0] = (({b2} * buf3[ridx0]) + (((1.0f - {b2}) * g) * g));")
+        line("float m_hat = (buf2[ridx0] / bias_correction1);")
+        line("float v_hat = (buf3[ridx0] / bias_correction2);")
+        line(f"out[ridx0] = (buf0[ridx0] - (({f32_literal(k.scalar)} * m_hat) / (sqrtf(v_hat) + {eps})));")
         close_loop()
     else:
         raise ValueError(f"kernel class {k.kclass}")
@@ -315,24 +358,27 @@ def emit_kernel_c(k: D.KernelDesc, fn_name: str = "kernel", openmp: bool = False
     return src
 
 
-def gcc_flags(openmp: bool) -> List[str]:
+def gcc_flags(openmp: bool, strict: bool = False) -> List[str]:
+    if strict:
+        # the optimizer steps are Rust host loops, not emitted C: IEEE f32, no contraction, no reassociation
+        return ["-O2", "-ffp-contract=off", "-shared", "-fPIC"]
     flags = ["-O3", "-ffast-math", "-shared", "-fPIC"]
     if openmp:
         flags.insert(2, "-fopenmp")
     return flags
 
 
-def compile_c(source: str, openmp: bool = False) -> str:
+def compile_c(source: str, openmp: bool = False, strict: bool = False) -> str:
     """Compile with the reference's flags; returns the path of the .so (cached)."""
     os.makedirs(_CACHE_DIR, exist_ok=True)
-    h = hashlib.sha256((source + str(openmp)).encode()).hexdigest()[:24]
+    h = hashlib.sha256((source + str(openmp) + ("strict" if strict else "")).encode()).hexdigest()[:24]
     so = os.path.join(_CACHE_DIR, f"lib{h}.so")
     if not os.path.exists(so):
         cfile = os.path.join(_CACHE_DIR, f"k{h}.c")
         with open(cfile, "w") as f:
             f.write(source)
         tmp = so + f".{os.getpid()}.tmp"
-        cmd = ["gcc"] + gcc_flags(openmp) + ["-o", tmp, cfile, "-lm"]
+        cmd = ["gcc"] + gcc_flags(openmp, strict) + ["-o", tmp, cfile, "-lm"]
         subprocess.run(cmd, check=True, capture_output=True)
         os.replace(tmp, so)
     return so
@@ -344,7 +390,8 @@ class OracleKernel:
     def __init__(self, k: D.KernelDesc, openmp: bool = False, fma: bool = False):
         self.desc = k
         self.source = emit_kernel_c(k, "kernel", openmp, fma)
-        self.lib = ctypes.CDLL(compile_c(self.source, openmp))
+        strict = k.kclass in (D.K_SGD, D.K_SGD_MOMENTUM, D.K_ADAM)
+        self.lib = ctypes.CDLL(compile_c(self.source, openmp and not strict, strict))
         self.fn = self.lib.kernel
         self.fn.restype = None
 
@@ -354,6 +401,7 @@ class OracleKernel:
         args = []
         keep = []
         for a, o in zip(inputs, k.inputs):
+            # optimizer state is updated in place: a conforming array is passed as it is
             a = np.ascontiguousarray(a, dtype=D.DTYPE_NP[o.dtype])
             keep.append(a)
             args.append(a.ctypes.data_as(ctypes.c_void_p))

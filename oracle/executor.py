@@ -21,6 +21,9 @@ class OracleExecutor:
     def alloc(self, numel):
         return np.zeros(int(numel), np.float32)
 
+    def alloc_counter(self):
+        return np.zeros(1, np.int32)
+
     def free(self, buf):
         pass
 

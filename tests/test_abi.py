@@ -32,7 +32,7 @@ def test_binding_covers_every_declared_symbol():
 
 def test_abi_version_and_struct_sizes():
     lib = capi.load()
-    assert lib.eb200_abi_version() == 1
+    assert lib.eb200_abi_version() == 2
     a, b, c, d = C.c_size_t(), C.c_size_t(), C.c_size_t(), C.c_size_t()
     capi.call("eb200_abi_sizes", C.byref(a), C.byref(b), C.byref(c), C.byref(d))
     assert a.value == C.sizeof(D.CKernelDesc)

@@ -362,7 +362,7 @@ def gemm_check(dev, k, a, b, ref64, rel):
 
 
 def test_cfg1_matmul_512(dev):
-    """BASELINE config 1: A, B uniform[-1,1] from seed 0 (A first), 512^3."""
+    """Config 1: A, B uniform[-1,1] from seed 0 (A first), 512^3."""
     rng = np.random.default_rng(0)
     a = rng.uniform(-1, 1, (512, 512)).astype(np.float32)
     b = rng.uniform(-1, 1, (512, 512)).astype(np.float32)
@@ -538,7 +538,7 @@ def test_sgd_update_bit_exact(dev, n):
     assert got.tobytes() == (p - lr * g).astype(np.float32).tobytes()
 
 
-# ---- BASELINE config 2 at full size -------------------------------------------------------------------
+# ---- config 2 at full size -------------------------------------------------------------------
 
 def test_cfg2_full_size(dev, registry):
     x = W.cfg2_input()

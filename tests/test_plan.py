@@ -222,3 +222,44 @@ def test_groups_of_four_when_an_operand_is_laid_out_like_the_output():
                      w(0).maximum(w(1)).maximum(w(2)).maximum(w(3)))
     assert query(k).impl.decode() == "ew_chain_v1"
     assert query(W.cfg2_t()).impl.decode() == "transpose_copy"
+
+
+def _padded_conv_window_operand(offset_error=0):
+    """x [2, 3, 6, 6] padded by 1 and unfolded 3x3: iteration [2, 3, 6, 6, 3, 3], the load
+    sits at n*108 + c*36 + (oh+kh-1)*6 + (ow+kw-1) and is masked where the window leaves
+    the image (View::padded then unfold, src/graph/shape/view.rs:980-1054,1162-1381)."""
+    st = [108, 36, 6, 1, 6, 1]
+    bounds = [D.Bound([0, 0, 1, 0, 1, 0], -1, 0, 6), D.Bound([0, 0, 0, 1, 0, 1], -1, 0, 6)]
+    return D.Operand(st, -7 + offset_error, D.F32, 2 * 3 * 36, bounds)
+
+
+def test_masked_operand_addresses_are_validated_at_create():
+    shape = [2, 3, 6, 6, 3, 3]
+    ok = D.KernelDesc(D.K_COPY, shape, [_padded_conv_window_operand()], D.contiguous(shape), None)
+    assert query(ok).impl.decode().startswith("ew_chain")
+    # the same view with a wrong offset would read past the end wherever the mask holds
+    bad = D.KernelDesc(D.K_COPY, shape, [_padded_conv_window_operand(+40)], D.contiguous(shape), None)
+    with pytest.raises(capi.Eb200Error) as e:
+        query(bad)
+    assert e.value.status == capi.ERR_BOUNDS
+    bad = D.KernelDesc(D.K_COPY, shape, [_padded_conv_window_operand(-1)], D.contiguous(shape), None)
+    with pytest.raises(capi.Eb200Error) as e:
+        query(bad)
+    assert e.value.status == capi.ERR_BOUNDS
+    # a mask that never holds loads nothing: any addressing is acceptable
+    never = D.Operand([1], 10 ** 9, D.F32, 4, [D.Bound([1], 100, 0, 4)])
+    assert query(D.KernelDesc(D.K_COPY, [4], [never], D.contiguous([4]), None)).impl.decode().startswith("ew_chain")
+    # strides that do not follow the bound's coefficients: validated by enumeration
+    odd = D.Operand([3, 1], 0, D.F32, 12, [D.Bound([1, 1], 0, 0, 4)])
+    assert query(D.KernelDesc(D.K_COPY, [4, 4], [odd], D.contiguous([4, 4]), None)).impl.decode().startswith("ew_chain")
+    odd_bad = D.Operand([3, 1], 0, D.F32, 6, [D.Bound([1, 1], 0, 0, 4)])       # (3, 0) -> 9 is past 6
+    with pytest.raises(capi.Eb200Error) as e:
+        query(D.KernelDesc(D.K_COPY, [4, 4], [odd_bad], D.contiguous([4, 4]), None))
+    assert e.value.status == capi.ERR_BOUNDS
+
+
+def test_contraction_beyond_the_gemm_grids_stays_a_reduce():
+    # 100 000 batches of 8x8x8: no GEMM kernel's grid.z holds the batch; the generic reduce serves it
+    i = query(W.matmul_desc(8, 8, 8, batch=100000))
+    assert i.impl.decode().startswith("reduce_"), i.impl
+    assert query(W.matmul_desc(8, 8, 8, batch=60000)).impl.decode().startswith("gemm")
