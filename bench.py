@@ -1,15 +1,17 @@
 #!/usr/bin/env python
-"""Benchmark of the hot path on B200: BASELINE config 2 (fused elementwise +
-reduce, column max, transposing copy over x f32 [8192, 8192]).
+"""Benchmark of the hot path on B200: config 2 (fused elementwise + reduce,
+column max, transposing copy over x f32 [8192, 8192]).
 
 One step = one pass of the three lowered kernels over one x:
-    y = sum(exp(0.5*x + 1.0) * x, axis=1)   fused chain + row reduce   268 468 224 B
+    y = sum(exp(0.5*x + 1.0) * x, axis=1)   fused chain + row reduce   268 468 232 B
     z = max(x, axis=0)                       column reduce              268 468 224 B
     t = x.permute(1,0).contiguous()          transposing copy           536 870 912 B
-Algorithmic bytes per step = 1 073 807 360 (each kernel reads x once; outputs
+Algorithmic bytes per step = 1 073 807 368 (each kernel reads x once; outputs
 written once).  With N GPUs every rank holds its own [8192, 8192] row block of a
 global [8192*N, 8192] tensor (weak scaling); y and t need no exchange, the
-column-max partials are combined by one 32 KB MAX-allreduce per step.
+column-max partials are combined by one 32 KB MAX all-reduce per step through the
+library's own communicator (eb200_comm_*: a one-shot NVLink kernel), issued on
+its side stream so the transposing copy overlaps it.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
 
@@ -17,10 +19,16 @@ Prints ONE JSON line (rank 0).  `value` is device-timed with inputs resident in
 HBM; `e2e` goes through the same C-ABI calls with host buffers, host<->device
 copies inside the timed region.  `--impl reference` times the reference's CPU
 path (the oracle's emitted C with OpenMP, all host threads) on a bounded sample.
+`extra` carries the other configurations: dense contractions (configs 1 and 5,
+row- / batch-sharded over the ranks), the MLP step (config 3, batch-sharded), the
+CNN step (config 4, batch-sharded, gradient all-reduce fused with the update),
+config 2 split by rows of ONE tensor (strong scaling), and single-kernel
+measurements of the remaining kernel classes.
 """
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import sys
@@ -40,18 +48,23 @@ BYTES_T = 8 * ROWS * COLS
 BYTES_STEP = BYTES_Y + BYTES_Z + BYTES_T
 METRIC = "fused_elemwise_reduce_throughput"
 UNIT = "GB/s"
+WORKLOAD = ("config 2: y=sum(exp(.5x+1)*x,axis=1), z=max(x,axis=0), t=x.permute(1,0).contiguous(); "
+            "x f32 [8192,8192] N(0,1) seed 2")
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures
 # summarised under profiles/ (None until a capture exists for that kernel).
-NCU_TRAFFIC = {"reduce_inner": 272_698_000, "reduce_outer": 272_148_000, "transpose_copy": 489_688_000}
+NCU_TRAFFIC = {"reduce_inner": 272_698_000, "reduce_outer": 272_148_000, "transpose_copy": None}
 
 
 def measured_peaks():
+    """(HBM GB/s, dense bf16 TFLOP/s burst, source): the driver-written measurement of this pool's
+    B200s when present, else the stated fallback."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+            j = json.load(f)
+        return float(j["hbm_gbs"]), float(j.get("bf16_tflops", 1590.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
 
 
 class ClockSampler(threading.Thread):
@@ -113,6 +126,20 @@ def dist_env():
 
 
 # ---------------------------------------------------------------------------------------
+def use_all_host_threads() -> int:
+    """Makes OpenMP use every host core and returns the thread count it reports.
+    A launcher may have exported OMP_NUM_THREADS=1 (torch.distributed.run does): the
+    variable is overwritten, and a runtime that is already loaded is told directly."""
+    cores = os.cpu_count() or 1
+    os.environ["OMP_NUM_THREADS"] = str(cores)
+    try:
+        gomp = ctypes.CDLL("libgomp.so.1")
+        gomp.omp_set_num_threads(cores)
+        return int(gomp.omp_get_max_threads())
+    except OSError:
+        return cores
+
+
 def run_cpu_workload(x, openmp: bool, rows: int):
     """One pass of the three kernels on the CPU oracle over the first `rows` rows."""
     from harp_b200 import workloads as W
@@ -131,8 +158,7 @@ def run_cpu_workload(x, openmp: bool, rows: int):
 
 
 def cpu_baseline(x, seconds_allowed: float = 20.0):
-    cores = os.cpu_count() or 1
-    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    threads = use_all_host_threads()
     step, nbytes = run_cpu_workload(x, True, ROWS)
     t0 = time.perf_counter(); step(); first = time.perf_counter() - t0
     best = first
@@ -140,8 +166,8 @@ def cpu_baseline(x, seconds_allowed: float = 20.0):
     while reps < 3 and (reps + 1) * first < seconds_allowed:
         t0 = time.perf_counter(); step(); best = min(best, time.perf_counter() - t0)
         reps += 1
-    out = {"value": nbytes / best / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
-           "sample": f"full [8192,8192] workload, emitted C with OpenMP (gcc -O3 -ffast-math -fopenmp), best of {reps}",
+    out = {"value": nbytes / best / 1e9, "unit": UNIT, "cores": threads, "kind": "port",
+           "sample": f"full [8192,8192] workload, emitted C with OpenMP (gcc -O3 -ffast-math -fopenmp) on {threads} threads, best of {reps}",
            "seconds": best}
     # single-thread C backend on a quarter of the rows
     step1, nbytes1 = run_cpu_workload(x, False, ROWS // 4)
@@ -155,8 +181,7 @@ def run_reference(args):
     if rank != 0:
         return
     from harp_b200 import workloads as W
-    cores = os.cpu_count() or 1
-    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    threads = use_all_host_threads()
     x = W.cfg2_input(ROWS, COLS)
     # size the per-step sample so that warmup+steps end within ~2 minutes
     step, nbytes = run_cpu_workload(x, True, ROWS)
@@ -174,14 +199,13 @@ def run_reference(args):
         step()
     dt = time.perf_counter() - t0
     value = nbytes * args.steps / dt / 1e9
-    sample = f"rows [0,{rows}) of x [8192,8192] per step; emitted C with OpenMP on {cores} host threads"
+    sample = f"rows [0,{rows}) of x [8192,8192] per step; emitted C with OpenMP on {threads} host threads (of {os.cpu_count()} cores)"
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "config 2: y=sum(exp(.5x+1)*x,axis=1), z=max(x,axis=0), t=x.permute(1,0).contiguous(); x f32 [8192,8192] N(0,1) seed 2",
-                   "l2": "inputs larger than L2"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "config": {"workload": WORKLOAD, "l2": "inputs larger than L2 (x is 256 MiB, L2 126 MB)"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -189,19 +213,51 @@ def run_reference(args):
 
 
 # ---------------------------------------------------------------------------------------
+class Ranks:
+    """The processes of a multi-GPU run: barrier and max-over-ranks of device timings
+    (torch.distributed is the host-side rendezvous only; data-path collectives go
+    through the library's communicator)."""
+
+    def __init__(self, rank, local_rank, world):
+        self.rank, self.local_rank, self.world = rank, local_rank, world
+        if world > 1:
+            import torch
+            import torch.distributed as dist
+            torch.cuda.set_device(local_rank)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+            self.torch, self.dist = torch, dist
+
+    def barrier(self, dev):
+        dev.synchronize()
+        if self.world > 1:
+            self.dist.barrier()
+            self.torch.cuda.synchronize()
+
+    def max(self, values):
+        if self.world == 1:
+            return list(values)
+        t = self.torch.tensor(list(values), device="cuda", dtype=self.torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return t.tolist()
+
+    def close(self):
+        if self.world > 1:
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+
+
 def run_b200(args):
     rank, local_rank, world = dist_env()
     n = args.gpus
-    if world > 1:
-        import torch
-        import torch.distributed as dist
-        torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ranks = Ranks(rank, local_rank, world)
+    from harp_b200 import desc as D
+    from harp_b200 import parallel
     from harp_b200 import workloads as W
     from harp_b200.backend import B200BackendRegistry, PinnedArray, launch_count
 
     reg = B200BackendRegistry()
     dev = reg.create_device(local_rank)
+    comm = parallel.init_comm(dev, rank, world) if world > 1 else None
     sampler = ClockSampler(local_rank)
     c0, c1 = W.cfg2_consts()
     x_host = PinnedArray((ROWS, COLS))
@@ -218,34 +274,30 @@ def run_b200(args):
     kt = reg.compile_ast(dev, W.cfg2_t())
     dev.synchronize()
 
-    allreduce_z = None
-    if world > 1:
-        from harp_b200 import parallel
-        allreduce_z = parallel.make_allreduce([bz], "max", dev, local_rank)   # on the library's own stream
+    # the column-max partials of the ranks: "async" = one-shot all-reduce on the communicator's side
+    # stream, overlapped with the transposing copy; "fused" = pushed to the peers by the pass that
+    # folds the split reduce's partials (one kernel, on the compute stream)
+    z_mode = args.z_allreduce if comm is not None else "none"
+    if z_mode == "fused":
+        comm.attach(kz)
 
-    def step():
-        ky.execute([b0, bx, b1], [by])
-        kz.execute([bx], [bz])
-        if allreduce_z:
-            allreduce_z()
-        kt.execute([bx], [bt])
-
-    def barrier():
-        if world > 1:
-            import torch
-            import torch.distributed as dist
-            dist.barrier()
-            torch.cuda.synchronize()
-        dev.synchronize()
+    def step(x=bx, oy=by, oz=bz, ot=bt):
+        ky.execute([b0, x, b1], [oy])
+        kz.execute([x], [oz])
+        if z_mode == "async":
+            comm.allreduce(oz, D.R_MAX, side_stream=True)
+        kt.execute([x], [ot])
+        if z_mode == "async":
+            comm.join()
 
     sampler.start()
     for _ in range(max(args.warmup, 3)):
         step()
-    barrier()
+    ranks.barrier(dev)
 
     # ---- device-timed region: K steps between two events; on every 8th step three more events
-    #      separate the kernels (recording an event between every pair of kernels on every step
-    #      cost the region ~10 us per step: 196 vs 185.5 us) ---------------------------------
+    #      separate the kernels (an event between every pair of kernels on every step cost the
+    #      region ~10 us per step) ------------------------------------------------------------
     K = args.steps
     SAMPLE = 8
     evs = {s_: [dev.event() for _ in range(4)] for s_ in range(0, K, SAMPLE)}
@@ -260,12 +312,14 @@ def run_b200(args):
             continue
         e[0].record(); ky.execute([b0, bx, b1], [by])
         e[1].record(); kz.execute([bx], [bz])
-        if allreduce_z:
-            allreduce_z()
+        if z_mode == "async":
+            comm.allreduce(bz, D.R_MAX, side_stream=True)
         e[2].record(); kt.execute([bx], [bt])
         e[3].record()
+        if z_mode == "async":
+            comm.join()
     e_end.record()
-    barrier()
+    ranks.barrier(dev)
     w1 = time.perf_counter()
     launches = launch_count() - l0
     total_ms = e_begin.elapsed_ms(e_end)
@@ -289,68 +343,80 @@ def run_b200(args):
     ev_down = [dev.event(), dev.event()]     # download of outs[i] finished
 
     def e2e_run(steps):
-        for i in range(steps + 1):
+        for i in range(steps):
             sl = i & 1
-            if i < steps:                      # upload batch i (needs the kernels that last read this slot)
-                if i >= 2:
-                    dev.wait_event(ev_k[sl], up)
-                xs[sl].write_on(up, x_host.ptr, x_host.nbytes)
-                ev_up[sl].record(up)
-                dev.wait_event(ev_up[sl])      # compute stream: kernels of batch i wait for its upload
-                if i >= 2:
-                    dev.wait_event(ev_down[sl])    # ... and for the previous results of this slot to have left
-                if allreduce_z and i >= 1:
-                    dev.wait_event(ev_down[1 - sl])   # both slots share the all-reduced z buffer
-                oy, oz, ot = outs[sl]
-                ky.execute([b0, xs[sl], b1], [oy])
-                kz.execute([xs[sl]], [oz])
-                if allreduce_z:
-                    allreduce_z()
-                kt.execute([xs[sl]], [ot])
-                ev_k[sl].record()
-                dev.wait_event(ev_k[sl], down)  # download batch i's results
-                oy.read_on(down, y_host.ptr, y_host.nbytes)
-                oz.read_on(down, z_host.ptr, z_host.nbytes)
-                ot.read_on(down, t_host.ptr, t_host.nbytes)
-                ev_down[sl].record(down)
+            if i >= 2:                         # the kernels that last read this slot must be done
+                dev.wait_event(ev_k[sl], up)
+            xs[sl].write_on(up, x_host.ptr, x_host.nbytes)
+            ev_up[sl].record(up)
+            dev.wait_event(ev_up[sl])          # compute stream: kernels of batch i wait for its upload
+            if i >= 2:
+                dev.wait_event(ev_down[sl])    # ... and for the previous results of this slot to have left
+            oy, oz, ot = outs[sl]
+            step(xs[sl], oy, oz, ot)
+            ev_k[sl].record()
+            dev.wait_event(ev_k[sl], down)     # download batch i's results
+            oy.read_on(down, y_host.ptr, y_host.nbytes)
+            oz.read_on(down, z_host.ptr, z_host.nbytes)
+            ot.read_on(down, t_host.ptr, t_host.nbytes)
+            ev_down[sl].record(down)
         down.synchronize()                     # the caller holds every result
         dev.synchronize()
-    if allreduce_z:                            # the collective aliases bz only: keep slot outputs on bz
-        outs[1] = (outs[1][0], bz, outs[1][2])
     e2e_run(2)
-    barrier()
+    ranks.barrier(dev)
     ea, eb = dev.event(), dev.event()
     w2 = time.perf_counter()
     ea.record()
     e2e_run(KE)
     eb.record()
-    barrier()
+    ranks.barrier(dev)
     w3 = time.perf_counter()
     e2e_ms = ea.elapsed_ms(eb)
     sampler.stop()
 
+    # the other way of combining the column maxima, for the record (multi-GPU runs only)
+    z_other = None
+    if comm is not None:
+        other = "fused" if z_mode == "async" else "async"
+        kz2 = reg.compile_ast(dev, W.cfg2_z())
+        if other == "fused":
+            comm.attach(kz2)
+
+        def step_other():
+            ky.execute([b0, bx, b1], [by])
+            kz2.execute([bx], [bz])
+            if other == "async":
+                comm.allreduce(bz, D.R_MAX, side_stream=True)
+            kt.execute([bx], [bt])
+            if other == "async":
+                comm.join()
+        for _ in range(3):
+            step_other()
+        ranks.barrier(dev)
+        dev.timer_begin()
+        for _ in range(K):
+            step_other()
+        ms_other = ranks.max([dev.timer_end() / K])[0]
+        z_other = {"z_allreduce": other, "ms_per_step": ms_other, "value_gbs": BYTES_STEP * n / (ms_other * 1e-3) / 1e9}
+        ranks.barrier(dev)
+
     # release the config 2 buffers, then time the other configurations
     extra = None
     if not args.no_extra:
-        for b_ in (bx, by, bz, bt, xs[1], outs[1][0], outs[1][2]):
+        for b_ in (bx, by, bz, bt, xs[1], outs[1][0], outs[1][1], outs[1][2]):
             b_.release()
         for h_ in (y_host, z_host, t_host):
             h_.free()
-        extra = extra_measurements(reg, dev, rank, world, local_rank, quick=args.steps < 20)
-    if world > 1:
-        import torch
-        import torch.distributed as dist
-        tm = torch.tensor([total_ms, e2e_ms, t_y, t_z, t_t], device="cuda", dtype=torch.float64)
-        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
-        total_ms, e2e_ms, t_y, t_z, t_t = tm.tolist()
+        extra = extra_measurements(reg, dev, ranks, comm, quick=args.steps < 20)
+        if z_other:
+            extra["cfg2_z_allreduce_other_way"] = z_other
+    total_ms, e2e_ms, t_y, t_z, t_t = ranks.max([total_ms, e2e_ms, t_y, t_z, t_t])
+    comm_info = comm.info() if comm is not None else None
     if rank != 0:
-        if world > 1:
-            import torch.distributed as dist
-            dist.barrier()
-            dist.destroy_process_group()
+        ranks.close()
         return
 
-    peak, peak_kind = measured_peaks()
+    peak, peak_tf, peak_kind = measured_peaks()
     value = BYTES_STEP * n * K / (total_ms * 1e-3) / 1e9
     e2e = BYTES_STEP * n * KE / (e2e_ms * 1e-3) / 1e9
     kernels = {}
@@ -364,32 +430,35 @@ def run_b200(args):
     roofline = {"bound": "hbm", "kernel": top[1]["impl"], "achieved": top[1]["achieved_gbs"], "peak": peak,
                 "peak_source": f"{peak_kind} copy bandwidth (MEASURED_PEAKS.json)" if peak_kind == "measured" else "fallback 6650 GB/s",
                 "unit": "GB/s", "frac": top[1]["achieved_gbs"] / peak, "traffic": traffic,
-                "time_share": top[1]["ms"] / (t_y + t_z + t_t)}
+                "time_share": top[1]["ms"] / (t_y + t_z + t_t),
+                "step_frac": BYTES_STEP / (total_ms / K * 1e-3) / 1e9 / peak}
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": n, "steps": K, "warmup": max(args.warmup, 3),
         "ms_per_step": total_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "config 2: y=sum(exp(.5x+1)*x,axis=1), z=max(x,axis=0), t=x.permute(1,0).contiguous(); x f32 [8192,8192] N(0,1) seed 2 per GPU",
+        "config": {"workload": WORKLOAD,
                    "l2": "inputs larger than L2 (x is 256 MiB, L2 126 MB)",
-                   "sharding": "row blocks of a global [8192*N, 8192] tensor; MAX-allreduce of the 32 KB column-max partials" if n > 1 else "single GPU",
+                   "per_gpu": "every GPU holds its own [8192,8192] block (seed 2 + rank)",
+                   "sharding": ("row blocks of a global [8192*N, 8192] tensor; MAX all-reduce of the 32 KB column-max partials: " +
+                                ("one-shot NVLink kernel on a side stream, overlapped with the transposing copy" if z_mode == "async"
+                                 else "pushed to the peers by the pass that folds the split reduce's partials")) if n > 1 else "single GPU",
                    "algo_bytes_per_step_per_gpu": BYTES_STEP,
                    "kernel_events": f"per-kernel durations from events on every {SAMPLE}th timed step ({ns} of {K})"},
         "roofline": roofline, "kernels": kernels,
         "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": int(x_host.nbytes),
-                "d2h_bytes_per_step": int(y_host.nbytes + z_host.nbytes + t_host.nbytes), "steps": KE,
+                "d2h_bytes_per_step": int(4 * ROWS + 4 * COLS + 4 * ROWS * COLS), "steps": KE,
                 "ms_per_step": e2e_ms / KE},
         "gpu_launches": int(launches),
         "clocks": sampler.summary([(w0, w1), (w2, w3)]),
     }
+    if comm_info is not None:
+        line["comm"] = comm_info
     if n == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(x_host.array)
     if extra is not None:
         line["extra"] = extra
     print(json.dumps(line))
-    if world > 1:
-        import torch.distributed as dist
-        dist.barrier()
-        dist.destroy_process_group()
+    ranks.close()
 
 
 def time_kernel(dev, kern, ins, outs, reps=5, warm=2):
@@ -464,87 +533,235 @@ def run_only_conv(args):
     print(json.dumps({"only": "conv2d_grad", "kernels": res}))
 
 
-def extra_measurements(reg, dev, rank, world, local_rank, quick=False):
-    """The other BASELINE configurations, timed with CUDA events on the library's
-    stream: dense contractions (configs 1 and 5, rank 0 only), the MLP step
-    (config 3, rank 0 only) and the data-parallel CNN step (config 4, all ranks)."""
+def kernel_table(dev, prog, reps=3):
+    """CUDA-event time of every kernel of a program on its own (not inside the graph):
+    [impl, ms, algorithmic MB, algorithmic GFLOP] per kernel, in launch order."""
+    rows = []
+    for i, d, kern, srcs in prog.kernels:
+        ins, out = [prog._b(s_) for s_ in srcs], [prog.buf[prog.where[i][0]]]
+        ms = time_kernel(dev, kern, ins, out, reps=reps, warm=1)
+        rows.append([kern.impl, round(ms * 1e3, 2), round(kern.algo_bytes / 1e6, 3), round(kern.algo_flops / 1e9, 4)])
+    return rows
+
+
+def step_bound_ms(prog, hbm_gbs, tf32_tflops):
+    """Lower bound of a step from its kernels' algorithmic work: each kernel can go no faster than its
+    bytes over the HBM copy bandwidth or its flops over the tensor peak of its arithmetic mode."""
     from harp_b200 import desc as D
+    t = 0.0
+    for _, d, kern, _ in prog.kernels:
+        three = d.gemm_mode != D.GEMM_TF32
+        t += max(kern.algo_bytes / (hbm_gbs * 1e9), kern.algo_flops * (3 if three else 1) / (tf32_tflops * 1e12))
+    return t * 1e3
+
+
+def extra_measurements(reg, dev, ranks, comm, quick=False):
+    """The other configurations, timed with CUDA events on the library's stream, every
+    rank working on its shard (max over ranks): dense contractions (config 1 on rank 0;
+    config 5 with A and C split by rows and B replicated, the batched form split by batch
+    index), the MLP step (config 3) and the CNN step (config 4) batch-sharded with the
+    gradient all-reduce fused into the update, config 2 split by rows of ONE tensor, and on
+    one GPU the convolution layers and the remaining kernel classes alone."""
+    from harp_b200 import desc as D
+    from harp_b200 import parallel
     from harp_b200 import workloads as W
     from harp_b200.frontend import B200Executor, Program
-    out = {}
+    rank, world = ranks.rank, ranks.world
+    hbm, bf16_tf, peak_kind = measured_peaks()
+    tf32_peak = bf16_tf / 2.0
+    out = {"peaks": {"hbm_gbs": hbm, "tf32_tflops": tf32_peak, "source": peak_kind + " (TF32 taken as half the dense bf16 figure)"}}
     rng = np.random.default_rng(5)
-    if rank == 0:
-        gemm = {}
-        shapes = [("cfg1_512", 512, 512, 512, 0), ("cfg5_8192", 8192, 8192, 8192, 0), ("cfg5_batched_64x1024", 1024, 1024, 1024, 64)]
-        for name, m, k_, n, batch in shapes:
-            bs = max(batch, 1)
-            ba = reg.allocate_buffer(dev, [bs * m * k_]); bb = reg.allocate_buffer(dev, [bs * k_ * n])
-            bo = reg.allocate_buffer(dev, [bs * m * n])
-            ba.write_vec(rng.uniform(-1, 1, bs * m * k_).astype(np.float32))
-            bb.write_vec(rng.uniform(-1, 1, bs * k_ * n).astype(np.float32))
-            for mode, mname in ((D.GEMM_TF32, "tf32"), (D.GEMM_3XTF32, "3xtf32")):
-                kern = reg.compile_ast(dev, W.matmul_desc(m, k_, n, batch=batch, mode=mode))
-                ms = time_kernel(dev, kern, [ba, bb], [bo], reps=3 if quick else 10)
-                gemm[f"{name}_{mname}"] = {"impl": kern.impl, "ms": ms, "tflops": 2.0 * bs * m * k_ * n / ms / 1e9}
-            for b_ in (ba, bb, bo):
-                b_.release()
-        out["matmul"] = gemm
-        out["conv2d"] = conv_measurements(reg, dev, rng, quick)
-        # config 3: MLP training step, whole step as one CUDA graph
-        ex = B200Executor(dev, reg)
-        loss, ps, grads, _ = W.mlp_graph(65536, 256)
-        prog = Program([loss], ex, sgd=list(zip(ps, grads)), lr=1e-3, persistent=True, flat=True)
-        prog.capture()
+    w = D.Ast.w
+
+    # ---- configs 1 and 5: dense contractions ------------------------------------------------
+    gemm = {}
+    shapes = [("cfg1_512", 512, 512, 512, 0, False), ("cfg5_8192", 8192, 8192, 8192, 0, True),
+              ("cfg5_batched_64x1024", 1024, 1024, 1024, 64, True)]
+    for name, m, k_, n, batch, sharded in shapes:
+        if not sharded and rank != 0:
+            continue
+        if batch:
+            lo, hi = parallel.batch_shard(batch, rank, world)
+            bs, ml = hi - lo, m
+        else:
+            sh = parallel.gemm_row_shard(m, k_, n, rank, world) if sharded else {"m_local": m}
+            bs, ml = 1, sh["m_local"]
+        ba = reg.allocate_buffer(dev, [bs * ml * k_]); bb = reg.allocate_buffer(dev, [bs * k_ * n])
+        bo = reg.allocate_buffer(dev, [bs * ml * n])
+        ba.write_vec(rng.uniform(-1, 1, bs * ml * k_).astype(np.float32))
+        bb.write_vec(rng.uniform(-1, 1, bs * k_ * n).astype(np.float32))       # B: replicated in this GPU's own memory
+        for mode, mname in ((D.GEMM_TF32, "tf32"), (D.GEMM_3XTF32, "3xtf32")):
+            kern = reg.compile_ast(dev, W.matmul_desc(ml, k_, n, batch=bs if batch else 0, mode=mode))
+            if sharded:
+                ranks.barrier(dev)
+            ms = time_kernel(dev, kern, [ba, bb], [bo], reps=3 if quick else 10)
+            if sharded:
+                ms = ranks.max([ms])[0]
+            flops = 2.0 * max(batch, 1) * m * k_ * n
+            tf = flops / ms / 1e9
+            gemm[f"{name}_{mname}"] = {"impl": kern.impl, "ms": ms, "tflops": tf,
+                                       "frac_of_tf32_peak": tf * (3 if mode == D.GEMM_3XTF32 else 1) / tf32_peak,
+                                       "per_gpu": f"A,C rows {ml} of {m}, B replicated" if not batch else f"batches {bs} of {batch}",
+                                       "n_gpus": world if sharded else 1}
+        for b_ in (ba, bb, bo):
+            b_.release()
+    out["matmul"] = gemm
+
+    # ---- config 2 split by rows of ONE [8192, 8192] tensor (strong scaling) -----------------
+    if world > 1:
+        lo, hi = parallel.shard_range(ROWS, rank, world)
+        rl = hi - lo
+        x = W.cfg2_input(ROWS, COLS)[lo:hi]
+        c0, c1 = W.cfg2_consts()
+        bx = reg.allocate_buffer(dev, [rl, COLS]); bx.write_vec(x)
+        b0 = reg.allocate_buffer(dev, [1]); b0.write_vec(c0)
+        b1 = reg.allocate_buffer(dev, [1]); b1.write_vec(c1)
+        by, bz, bt = reg.allocate_buffer(dev, [rl]), reg.allocate_buffer(dev, [COLS]), reg.allocate_buffer(dev, [COLS * rl])
+        ky, kz, kt = (reg.compile_ast(dev, f(rl, COLS)) for f in (W.cfg2_y, W.cfg2_z, W.cfg2_t))
+
+        def strong_step():
+            ky.execute([b0, bx, b1], [by])
+            kz.execute([bx], [bz])
+            comm.allreduce(bz, D.R_MAX, side_stream=True)
+            kt.execute([bx], [bt])
+            comm.join()
+        for _ in range(3):
+            strong_step()
+        ranks.barrier(dev)
         steps = 20 if quick else 100
+        dev.timer_begin()
+        for _ in range(steps):
+            strong_step()
+        ms = ranks.max([dev.timer_end() / steps])[0]
+        out["cfg2_strong"] = {"ms_per_step": ms, "value_gbs": BYTES_STEP / (ms * 1e-3) / 1e9, "rows_per_gpu": rl,
+                              "sharding": "rows [r*8192/g, (r+1)*8192/g) of ONE [8192,8192] tensor; y and t stay sharded, z by a 32 KB MAX all-reduce",
+                              "algo_bytes_per_step_total": BYTES_STEP}
+        for b_ in (bx, by, bz, bt):
+            b_.release()
+
+    if world == 1:
+        out["conv2d"] = conv_measurements(reg, dev, rng, quick)
+        out["kernels_alone"] = misc_kernel_measurements(reg, dev, rng, hbm, quick)
+
+    # ---- configs 3 and 4: training steps, batch-sharded, whole step as one CUDA graph -------
+    one_shot = comm is None or comm.info()["one_shot"]
+
+    def train_step(build, n_global, lr, steps, tables=False):
+        ex = B200Executor(dev, reg)
+        n_local = n_global // world
+        loss, ps, grads, _ = build(n_local)
+        prog = Program([loss], ex, sgd=list(zip(ps, grads)), lr=lr / world, persistent=True, flat=True,
+                       comm=comm, overlap=one_shot)
+        # with the one-shot transport the collective is part of the recorded step; a communicator that
+        # fell back to NCCL keeps its collective outside the graph
+        prog.capture(include_update=one_shot)
         for _ in range(3):
             prog.run()
-        dev.synchronize(); dev.timer_begin()
+        ranks.barrier(dev)
+        dev.timer_begin()
         for _ in range(steps):
             prog.run()
-        ms = dev.timer_end() / steps
-        out["mlp_cfg3"] = {"ms_per_step": ms, "samples_per_s": 65536 / ms * 1e3, "kernels_per_step": len(prog.kernels) + len(prog.sgd_kernels),
-                           "derived_tflops": 2.597e10 / ms / 1e9, "loss_after": float(prog.fetch(loss)), "steps": steps + 3 + 1}
-        del prog
-    # config 4: CNN, global batch 4096 sharded over the ranks, gradient all-reduce.
+        ms = ranks.max([dev.timer_end() / steps])[0]
+        res = {"ms_per_step": ms, "global_batch": n_global, "per_gpu_batch": n_local,
+               "kernels_per_step": len(prog.kernels) + (len(prog.sgd_kernels) if comm is None else 1 + len(prog.buckets)),
+               "all_specialised": all(k.specialised for _, _, k, _ in prog.kernels),
+               "allreduce_bytes_per_step": 4 * prog.cnumel[-1] if comm is not None else 0,
+               "overlapped_bucket": [list(b) for b in prog.buckets],
+               "loss_after": float(prog.fetch(loss)), "steps": steps + 3 + 1}
+        bound = step_bound_ms(prog, hbm, tf32_peak)
+        res["roofline"] = {"bound_ms": bound, "frac": bound / ms,
+                           "how": "sum over the step's kernels of max(algorithmic bytes / HBM copy bandwidth, executed flops / TF32 peak)"}
+        if tables and rank == 0:
+            res["kernel_table_us"] = kernel_table(dev, prog)
+        return res, prog
+
+    steps = 20 if quick else 100
+    res, prog = train_step(lambda nl: W.mlp_graph(nl, 256, seed=3 + rank), 65536, 1e-3, steps)
+    res["samples_per_s"] = 65536 / res["ms_per_step"] * 1e3
+    res["derived_tflops"] = 2.597e10 / res["ms_per_step"] / 1e9
+    out["mlp_cfg3"] = res
+    del prog
     # "cnn_cfg4": this backend's forms of the same functions (one implicit-GEMM kernel per
     # convolution / input gradient / weight gradient, pools over strided views);
     # "cnn_cfg4_reference_spelling" (one GPU only): eclat's own composition of them.
-    def cnn_step(fused):
-        ex = B200Executor(dev, reg)
-        n_local = 4096 // world
-        loss, ps, grads, _ = W.cnn_graph(n_local, seed=4 + rank, fused_conv=fused)
-        prog = Program([loss], ex, sgd=list(zip(ps, grads)), lr=1e-2 / world, persistent=True, flat=True)
-        between = None
-        if world > 1:
-            from harp_b200 import parallel
-            prog.capture(include_update=False)
-            between = parallel.make_allreduce(prog.grad_buffers(), "sum", dev, local_rank)
-        else:
-            prog.capture()
-        steps = 5 if quick else 20
-        for _ in range(3):
-            prog.run(between)
-        dev.synchronize()
-        if world > 1:
-            import torch.distributed as dist
-            dist.barrier()
-        dev.timer_begin()
-        for _ in range(steps):
-            prog.run(between)
-        ms = dev.timer_end() / steps
-        if world > 1:
-            import torch
-            import torch.distributed as dist
-            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return {"ms_per_step": ms, "img_per_s": 4096 / ms * 1e3, "global_batch": 4096, "per_gpu_batch": n_local,
-                "kernels_per_step": len(prog.kernels) + len(prog.sgd_kernels),
-                "allreduce_bytes_per_step": 225034 * 4 if world > 1 else 0, "loss_after": float(prog.fetch(loss))}
-    out["cnn_cfg4"] = cnn_step(True)
+    res, prog = train_step(lambda nl: W.cnn_graph(nl, seed=4 + rank, fused_conv=True), 4096, 1e-2, 5 if quick else 20, tables=True)
+    res["img_per_s"] = 4096 / res["ms_per_step"] * 1e3
+    out["cnn_cfg4"] = res
+    del prog
     if world == 1:
-        out["cnn_cfg4_reference_spelling"] = cnn_step(False)
+        # the 8-GPU shard size on one GPU: what does not shrink with the shard shows here
+        res, prog = train_step(lambda nl: W.cnn_graph(512, seed=4, fused_conv=True), 512, 1e-2, 5 if quick else 20, tables=True)
+        res["img_per_s"] = 512 / res["ms_per_step"] * 1e3
+        out["cnn_cfg4_shard_512"] = res
+        del prog
+        res, prog = train_step(lambda nl: W.cnn_graph(nl, seed=4, fused_conv=False), 4096, 1e-2, 3 if quick else 10)
+        res["img_per_s"] = 4096 / res["ms_per_step"] * 1e3
+        out["cnn_cfg4_reference_spelling"] = res
+        del prog
     return out
+
+
+def misc_kernel_measurements(reg, dev, rng, hbm, quick=False):
+    """Kernel classes that no configuration's headline covers, each alone on inputs larger
+    than L2: scans, optimizer updates, scatter-add, a plain elementwise add."""
+    from harp_b200 import desc as D
+    w = D.Ast.w
+    res = {}
+
+    def run(name, kd, sizes, out_size, dtypes=None, in_place=None):
+        bufs = []
+        for j, sz in enumerate(sizes):
+            dt = dtypes[j] if dtypes else D.F32
+            b = reg.allocate_buffer(dev, [sz], dt)
+            if dt == D.F32:
+                b.write_vec(rng.uniform(-1, 1, sz).astype(np.float32))
+            bufs.append(b)
+        bo = bufs[in_place] if in_place is not None else reg.allocate_buffer(dev, [out_size])
+        kern = reg.compile_ast(dev, kd)
+        ms = time_kernel(dev, kern, bufs, [bo], reps=3 if quick else 10)
+        gbs = kern.algo_bytes / ms / 1e6
+        res[name] = {"impl": kern.impl, "ms": ms, "algo_bytes": kern.algo_bytes, "gbs": gbs, "frac_of_hbm": gbs / hbm}
+        for b in bufs + ([] if in_place is not None else [bo]):
+            b.release()
+    n = 1 << 26                      # 256 MiB per operand
+    run("ew_add", D.elementwise([n], [D.contiguous([n])] * 2, w(0) + w(1)), [n, n], n)
+    run("cumsum_rows_8192x8192", D.scan([8192, 8192], [D.contiguous([8192, 8192])], w(0), D.R_SUM, 1), [n], n)
+    run("cumsum_rows_65536x1024", D.scan([65536, 1024], [D.contiguous([65536, 1024])], w(0), D.R_SUM, 1), [n], n)
+    run("cumsum_4_long_rows", D.scan([4, n // 4], [D.contiguous([4, n // 4])], w(0), D.R_SUM, 1), [n], n)
+    run("sgd_update", D.KernelDesc(D.K_SGD, [n], [D.contiguous([n])] * 2, D.contiguous([n]), scalar=0.01), [n, n], n, in_place=0)
+    run("sgd_momentum_update", D.sgd_momentum(n, 0.01, 0.9), [n, n, n], n, in_place=0)
+    run("adam_update", D.adam(n, 1e-3), [n, n, n, n, 1], n, dtypes=[D.F32] * 4 + [D.I32], in_place=0)
+    # fold of 3x3 windows, the scatter-add the reference reaches through unfold's gradient: [512,32,11,11,3,3] -> [512,32,13,13]
+    from harp_b200.frontend import View
+    src_shape, dst_shape = [512, 32, 11, 11, 3, 3], [512, 32, 13, 13]
+    dst = View.contiguous(dst_shape).unfold([2, 3], [3, 3], [1, 1], [1, 1])
+    kd = D.KernelDesc(D.K_SCATTER, src_shape, [D.contiguous(src_shape)], dst.operand(int(np.prod(dst_shape)), D.F32), None)
+    run("scatter_add_fold3x3", kd, [int(np.prod(src_shape))], int(np.prod(dst_shape)))
+    return res
+
+
+def run_only_small(args):
+    """`--only gemm`: the tensor-core contraction on a 2048^3 case; `--only kernels`: the kernel
+    classes of misc_kernel_measurements on 32 M-element inputs (profiler captures)."""
+    from harp_b200 import desc as D
+    from harp_b200 import workloads as W
+    from harp_b200.backend import B200BackendRegistry
+    reg = B200BackendRegistry()
+    dev = reg.create_device(0)
+    rng = np.random.default_rng(5)
+    hbm, _, _ = measured_peaks()
+    if args.only == "gemm":
+        res = {}
+        n = 2048
+        ba, bb, bo = (reg.allocate_buffer(dev, [n * n]) for _ in range(3))
+        ba.write_vec(rng.uniform(-1, 1, n * n).astype(np.float32)); bb.write_vec(rng.uniform(-1, 1, n * n).astype(np.float32))
+        for mode, mname in ((D.GEMM_TF32, "tf32"), (D.GEMM_3XTF32, "3xtf32")):
+            kern = reg.compile_ast(dev, W.matmul_desc(n, n, n, mode=mode))
+            ms = time_kernel(dev, kern, [ba, bb], [bo], reps=2, warm=1)
+            res[mname] = {"impl": kern.impl, "ms": ms, "tflops": 2.0 * n ** 3 / ms / 1e9}
+        print(json.dumps({"only": "gemm", "gemm_2048": res}))
+        return
+    print(json.dumps({"only": "kernels", "kernels": misc_kernel_measurements(reg, dev, rng, hbm, quick=True)}))
 
 
 def main():
@@ -555,10 +772,15 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-extra", action="store_true", help="only config 2 (skip matmul / MLP / CNN measurements)")
-    ap.add_argument("--only", default="", choices=["", "conv2d", "conv2d_grad"], help="run one small kernel case alone (profiler captures); prints no bench line")
+    ap.add_argument("--z-allreduce", default="async", choices=["async", "fused"],
+                    help="multi-GPU: how the column-max partials are combined (side-stream all-reduce, or fused into the reduce's finish pass)")
+    ap.add_argument("--only", default="", choices=["", "conv2d", "conv2d_grad", "gemm", "kernels"],
+                    help="run one small kernel case alone (profiler captures); prints no bench line")
     args = ap.parse_args()
-    if args.only:
+    if args.only in ("conv2d", "conv2d_grad"):
         run_only_conv(args)
+    elif args.only:
+        run_only_small(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

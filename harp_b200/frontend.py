@@ -410,6 +410,43 @@ class Tensor:
         # crates/nn/src/functional/activation.rs:70-76 (whose scale() is a no-op)
         return (self * 2.0).sigmoid() * 2.0 - 1.0
 
+    # ---- the reference's own spellings, quirks included ----
+    # What eclat's Tensor API really builds for these functions (graph-level
+    # behaviours that change numerics; kernel-level parity is unaffected because
+    # both sides run the same lowered kernels).  Used by the *_reference graphs.
+    def ones_like(self) -> "Tensor":
+        """A full-size tensor of ones as a REAL input buffer: the reference builds
+        constants named ones / zeros on the host and uploads them at every realize
+        (src/tensor/realize.rs:391-502)."""
+        return Tensor.input(np.ones(self.shape, np.float32), name="ones")
+
+    def zeros_like(self) -> "Tensor":
+        return Tensor.input(np.zeros(self.shape, np.float32), name="zeros")
+
+    def scale_ref(self, _factor: float) -> "Tensor":
+        """Tensor::scale ignores its factor and multiplies by ones (src/tensor/ops.rs:699-707)."""
+        return self * self.ones_like()
+
+    def exp_ref(self) -> "Tensor":
+        """exp whose VJP is categorised as Exp2: the gradient is g * 2^x * ones
+        (src/grad/rules.rs:254-259,752,854-860)."""
+        out = Tensor._map(lambda a: a.exp(), self, grads=[None], name="exp")
+        src = self
+        return self._track(out, (self, lambda g: g * Tensor._map(lambda a: a.exp2(), Tensor(src.node, src.view)) * src.ones_like()))
+
+    def sigmoid_ref(self) -> "Tensor":
+        """crates/nn/src/functional/activation.rs:50-58 with ones as a tensor."""
+        return (self.ones_like() + (-self).exp_ref()).recip()
+
+    def tanh_ref(self) -> "Tensor":
+        """crates/nn/src/functional/activation.rs:70-76: with scale() a no-op this
+        evaluates sigmoid(x) - 1."""
+        return self.scale_ref(2.0).sigmoid_ref().scale_ref(2.0) - self.ones_like()
+
+    def relu_ref(self) -> "Tensor":
+        """max(x, zeros) with zeros a full-size input buffer (activation.rs:18-21)."""
+        return self.maximum(self.zeros_like())
+
     # ---- reductions ----
     def _reduce(self, op, axis, keepdim) -> "Tensor":
         axis = axis % self.ndim

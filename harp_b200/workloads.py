@@ -131,3 +131,57 @@ def cnn_graph(n: int = 4096, seed: int = 4, label_seed: int = 40, weight_seed: i
     h = h.reshape(n, 1600).linear(ps[4], ps[5]).relu().linear(ps[6], ps[7])
     loss = -(h.log_softmax(1) * onehot).sum() * (1.0 / n)
     return loss, ps, loss.backward(ps), (x, onehot)
+
+
+# ---- the same models as eclat's own Tensor API would build them --------------------------
+
+def mlp_graph_reference(batch: int = 512, hidden: int = 64, seed: int = 3, weight_seed: int = 30):
+    """Config 3 with the reference's graph-level behaviours kept: `tanh` evaluates
+    sigmoid(x) - 1 because Tensor::scale ignores its factor
+    (crates/nn/src/functional/activation.rs:70-76, src/tensor/ops.rs:699-707), the
+    constants are full-size `ones` input buffers (src/tensor/realize.rs:391-502),
+    exp's gradient is 2^x (src/grad/rules.rs:254-259), and the loss is the SUM of
+    squared errors (`mean` returns the sum, src/tensor/ops.rs:230-245)."""
+    from .frontend import Tensor
+    rng = np.random.default_rng(seed)
+    X = rng.uniform(-np.pi, np.pi, (batch, 1)).astype(np.float32)
+    T = np.sin(X.astype(np.float64)).astype(np.float32)
+    prng = np.random.default_rng(weight_seed)
+
+    def xavier(o, i):
+        b = np.sqrt(6.0 / (i + o))
+        return prng.uniform(-b, b, (o, i)).astype(np.float32)
+    vals = [xavier(hidden, 1), np.zeros(hidden, np.float32), xavier(hidden, hidden), np.zeros(hidden, np.float32),
+            xavier(1, hidden), np.zeros(1, np.float32)]
+    ps = [Tensor.input(v, requires_grad=True) for v in vals]
+    x, t = Tensor.input(X), Tensor.input(T)
+    h = x.linear(ps[0], ps[1]).tanh_ref().linear(ps[2], ps[3]).tanh_ref().linear(ps[4], ps[5])
+    d = h - t
+    loss = (d * d).sum()
+    return loss, ps, loss.backward(ps), (x, t)
+
+
+def cnn_graph_reference(n: int = 8, seed: int = 4, label_seed: int = 40, weight_seed: int = 41):
+    """Config 4 as eclat spells it, graph-level behaviours kept: ReLU against a
+    full-size `zeros` input buffer (crates/nn/src/functional/activation.rs:18-21),
+    convolutions and pools through unfold / fold, and cross_entropy_loss returning
+    +sum(one_hot * log_softmax) because its final scale(-1/N) multiplies by ones
+    (crates/nn/src/functional/loss.rs:32-65)."""
+    from .frontend import Tensor
+    X = np.random.default_rng(seed).uniform(0, 1, (n, 1, 28, 28)).astype(np.float32)
+    lab = np.random.default_rng(label_seed).integers(0, 10, n)
+    prng = np.random.default_rng(weight_seed)
+
+    def kaiming(*shape):
+        fan_in = int(np.prod(shape[1:]))
+        return (prng.standard_normal(shape) * np.sqrt(2.0 / fan_in)).astype(np.float32)
+    vals = [kaiming(32, 1, 3, 3), np.zeros(32, np.float32), kaiming(64, 32, 3, 3), np.zeros(64, np.float32),
+            kaiming(128, 1600), np.zeros(128, np.float32), kaiming(10, 128), np.zeros(10, np.float32)]
+    ps = [Tensor.input(v, requires_grad=True) for v in vals]
+    x = Tensor.input(X)
+    onehot = Tensor.input(np.eye(10, dtype=np.float32)[lab])
+    h = x.conv2d(ps[0], ps[1]).relu_ref().max_pool2d_unfold(2)
+    h = h.conv2d(ps[2], ps[3]).relu_ref().max_pool2d_unfold(2)
+    h = h.reshape(n, 1600).linear(ps[4], ps[5]).relu_ref().linear(ps[6], ps[7])
+    loss = (h.log_softmax(1) * onehot).sum().scale_ref(-1.0 / n)
+    return loss, ps, loss.backward(ps), (x, onehot)
