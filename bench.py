@@ -533,13 +533,26 @@ def run_only_conv(args):
     print(json.dumps({"only": "conv2d_grad", "kernels": res}))
 
 
-def kernel_table(dev, prog, reps=3):
-    """CUDA-event time of every kernel of a program on its own (not inside the graph):
-    [impl, ms, algorithmic MB, algorithmic GFLOP] per kernel, in launch order."""
+def kernel_table(dev, prog, reps=10):
+    """Device time of every kernel of a program on its own: `reps` launches of the kernel recorded
+    into a CUDA graph and replayed (so host launch cost stays out of it; the figure includes the
+    ~1-2 us gap between dependent launches, as the captured step does):
+    [impl, us, algorithmic MB, algorithmic GFLOP] per kernel, in launch order."""
     rows = []
     for i, d, kern, srcs in prog.kernels:
         ins, out = [prog._b(s_) for s_ in srcs], [prog.buf[prog.where[i][0]]]
-        ms = time_kernel(dev, kern, ins, out, reps=reps, warm=1)
+        dev.synchronize()
+        dev.graph_begin()
+        try:
+            for _ in range(reps):
+                kern.execute(ins, out)
+        finally:
+            graph = dev.graph_end()
+        graph.launch()
+        dev.synchronize()
+        dev.timer_begin()
+        graph.launch()
+        ms = dev.timer_end() / reps
         rows.append([kern.impl, round(ms * 1e3, 2), round(kern.algo_bytes / 1e6, 3), round(kern.algo_flops / 1e9, 4)])
     return rows
 
@@ -676,7 +689,7 @@ def extra_measurements(reg, dev, ranks, comm, quick=False):
         return res, prog
 
     steps = 20 if quick else 100
-    res, prog = train_step(lambda nl: W.mlp_graph(nl, 256, seed=3 + rank), 65536, 1e-3, steps)
+    res, prog = train_step(lambda nl: W.mlp_graph(nl, 256, seed=3 + rank), 65536, 1e-3, steps, tables=True)
     res["samples_per_s"] = 65536 / res["ms_per_step"] * 1e3
     res["derived_tflops"] = 2.597e10 / res["ms_per_step"] / 1e9
     out["mlp_cfg3"] = res

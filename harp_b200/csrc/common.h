@@ -160,6 +160,7 @@ enum Impl {
     IMPL_SCAN,            // cumulative op along an axis (P_ kernels)
     IMPL_SGD_MOMENTUM,    // v = momentum*v - lr*g; p += v
     IMPL_ADAM,            // Adam step with device-resident moments and step counter
+    IMPL_SOFTMAX_XENT,    // log-softmax + cross-entropy, loss and logits gradient in one kernel
 };
 
 struct GemmShape {
@@ -231,6 +232,7 @@ int launch_sgd(Device* dev, const Plan& plan, const float* p, const float* g, fl
 int launch_sgd_momentum(Device* dev, const Plan& plan, const float* p, const float* g, float* v, float* out, long long n);
 int launch_adam(Device* dev, const Plan& plan, const float* p, const float* g, float* m, float* v, int* t, float* out,
                 long long n, void* scratch);
+int launch_softmax_xent(Device* dev, const Plan& plan, const float* logits, const float* onehot, float* out, void* scratch);
 long long scan_scratch_floats(const KParams& p, int sms);
 int launch_scan(Device* dev, const Plan& plan, const KParams& p, void* scratch);
 int launch_gemm_simt(Device* dev, const Plan& plan, const float* a, const float* b, float* c, void* scratch);

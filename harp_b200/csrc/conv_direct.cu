@@ -220,7 +220,12 @@ static int direct_chn() { return direct_variant() == 8 ? 8 : 4; }
 
 static int direct_streams(const ConvShape& c, int sms) {
     const int chunks = (c.Co + direct_chn() - 1) / direct_chn();
-    return std::max(1, (sms * 32) / chunks);       // four CTAs of eight warps per SM
+    const int full = std::max(1, (sms * 32) / chunks);       // four CTAs of eight warps per SM
+    // small batches: at least 16 steps of 2 x 32 positions per stream, so the per-stream fold (36 shuffle
+    // trees, one partial row) and the sum over the streams stay small next to the streaming work
+    const long long Ho = c.H + 2 * c.pad - c.KH + 1, Wo = c.W + 2 * c.pad - c.KW + 1;
+    const long long by_work = ((long long)c.N * Ho * Wo + 1023) / 1024;
+    return (int)std::max(1LL, std::min<long long>(full, by_work));
 }
 
 long long conv2d_direct_wgrad_scratch_floats(const ConvShape& c, int sms) {

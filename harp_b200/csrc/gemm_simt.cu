@@ -10,6 +10,8 @@
 // f32-faithful path for shapes or strides the tensor-core kernel does not take.
 // 64x64 output tile per CTA, 16-deep k slices through shared memory, 4x4
 // register micro-tile per thread; any A/B/C strides, batched over gridDim.z.
+#include <algorithm>
+
 #include "common.h"
 
 namespace eb200 {
@@ -98,12 +100,38 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const __grid_constan
     }
 }
 
+// The same for few outputs and many splits (per-CTA partials of the tall kernels, per-stream
+// partials of the streaming weight gradients): a warp per output, lane l adds the splits
+// l, l + 32, ... in increasing order, the lanes are folded by a fixed shuffle tree.  The plain
+// kernel would leave each of a few hundred threads with hundreds of dependent-latency loads.
+__global__ void __launch_bounds__(256) splitk_reduce_warp_kernel(const __grid_constant__ GemmShape g,
+                                                                 const float* __restrict__ P, float* __restrict__ C) {
+    const long long mn = g.m * g.n, total = g.batch * mn;
+    const int lane = threadIdx.x & 31;
+    const long long warps = ((long long)gridDim.x * blockDim.x) >> 5;
+    for (long long e = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; e < total; e += warps) {
+        const long long bz = e / mn, r = e - bz * mn;
+        const long long row = r / g.n, col = r - row * g.n;
+        const float* src = P + bz * g.splits * mn + r;
+        float acc = 0.0f;
+        for (int s = lane; s < g.splits; s += 32) acc += src[(long long)s * mn];
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+        if (lane == 0) C[g.c_off + bz * g.c_sb + row * g.c_sm + col * g.c_sn] = acc;
+    }
+}
+
 int launch_splitk_reduce(Device* dev, const GemmShape& g, const float* partials, float* c) {
     const long long total = g.batch * g.m * g.n;
-    long long blocks = (total + 255) / 256;
     const long long cap = (long long)dev->prop.multiProcessorCount * 16;
-    if (blocks > cap) blocks = cap;
-    splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, dev->stream>>>(g, partials, c);
+    if (g.splits >= 64 && total * 32 <= cap * 256) {
+        long long blocks = (total * 32 + 255) / 256;
+        splitk_reduce_warp_kernel<<<(unsigned)std::max(1LL, blocks), 256, 0, dev->stream>>>(g, partials, c);
+    } else {
+        long long blocks = (total + 255) / 256;
+        if (blocks > cap) blocks = cap;
+        splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, dev->stream>>>(g, partials, c);
+    }
     count_launch();
     EB_CHECK_CUDA(cudaGetLastError());
     return EB200_OK;

@@ -58,7 +58,7 @@ static void fill_info(const Plan& plan, eb200_kernel_info* info) {
     strncpy(info->impl, plan.name, sizeof(info->impl) - 1);
     info->launches = plan.launches;
     info->specialised = plan.chain >= 0 || plan.impl == IMPL_TRANSPOSE || plan.impl == IMPL_SCATTER ||
-                        plan.impl == IMPL_SGD || plan.impl == IMPL_SGD_MOMENTUM || plan.impl == IMPL_ADAM || plan.impl == IMPL_GEMM_SIMT || plan.impl == IMPL_GEMM_TC || plan.impl == IMPL_CONV2D || plan.impl == IMPL_GEMM_TALL || plan.impl == IMPL_CONV2D_WGRAD || plan.impl == IMPL_CONV2D_DIRECT || plan.impl == IMPL_CONV2D_DIRECT_WGRAD;
+                        plan.impl == IMPL_SGD || plan.impl == IMPL_SGD_MOMENTUM || plan.impl == IMPL_ADAM || plan.impl == IMPL_SOFTMAX_XENT || plan.impl == IMPL_GEMM_SIMT || plan.impl == IMPL_GEMM_TC || plan.impl == IMPL_CONV2D || plan.impl == IMPL_GEMM_TALL || plan.impl == IMPL_CONV2D_WGRAD || plan.impl == IMPL_CONV2D_DIRECT || plan.impl == IMPL_CONV2D_DIRECT_WGRAD;
     info->scratch_bytes = plan.scratch_bytes;
     info->algo_bytes = plan.algo_bytes;
     info->algo_flops = plan.algo_flops;
@@ -153,6 +153,10 @@ int eb200_kernel_launch(eb200_kernel* k, eb200_buffer* const* inputs, int n_inpu
                                reinterpret_cast<int*>(p.in[4].ptr) + p.in[4].offset,
                                reinterpret_cast<float*>(p.out.ptr) + p.out.offset, p.total, scratch);
         case IMPL_SCAN: return launch_scan(dev, plan, p, scratch);
+        case IMPL_SOFTMAX_XENT:
+            return launch_softmax_xent(dev, plan, reinterpret_cast<const float*>(p.in[0].ptr) + p.in[0].offset,
+                                       reinterpret_cast<const float*>(p.in[1].ptr) + p.in[1].offset,
+                                       reinterpret_cast<float*>(p.out.ptr) + p.out.offset, scratch);
         case IMPL_GEMM_SIMT:
             return launch_gemm_simt(dev, plan, reinterpret_cast<const float*>(p.in[plan.gemm.a_input].ptr),
                                     reinterpret_cast<const float*>(p.in[plan.gemm.b_input].ptr),

@@ -102,3 +102,73 @@ int launch_adam(Device* dev, const Plan& plan, const float* p, const float* g, f
 }
 
 }  // namespace eb200
+
+// ---- log-softmax + cross-entropy, forward and backward -------------------------------------
+// The reference composes the loss from a dozen tiny kernels (row max, subtract, exp, row sum,
+// ln, subtract, multiply by the one-hot targets, two sums, scale: crates/nn/src/functional/
+// activation.rs:174-187, loss.rs:32-65) and its gradient from as many again.  On [N, 10]
+// logits each of them is launch latency only.  Here one kernel does both directions in the
+// reference's arithmetic (exp = exp2(x * log2e), ln = log2(x) * (1 / log2e), classes summed
+// in index order): a thread per row, per-CTA loss partials added in CTA order by the last
+// CTA to finish (deterministic).
+namespace eb200 {
+
+constexpr int XENT_MAX_CTAS = 512;
+
+__global__ void __launch_bounds__(256) softmax_xent_kernel(const float* __restrict__ logits, const float* __restrict__ onehot,
+                                                           float* __restrict__ out, int n, int c, float scale,
+                                                           float* partials, unsigned* ticket) {
+    const float log2e = 1.4426950408889634f;       // std::f32::consts::LOG2_E
+    const float inv_log2e = 1.0f / log2e;
+    __shared__ float warp_sum[8];
+    float* grad = out + 64;
+    float local = 0.0f;
+    for (int row = blockIdx.x * blockDim.x + threadIdx.x; row < n; row += gridDim.x * blockDim.x) {
+        const float* x = logits + (long long)row * c;
+        const float* t = onehot + (long long)row * c;
+        float m = -INFINITY;
+        for (int j = 0; j < c; ++j) m = fmaxf(m, x[j]);
+        float s = 0.0f, tsum = 0.0f;
+        for (int j = 0; j < c; ++j) { s += exp2f((x[j] - m) * log2e); tsum += t[j]; }
+        const float lse = log2f(s) * inv_log2e;
+        const float inv_s = 1.0f / s;
+        float acc = 0.0f;
+        for (int j = 0; j < c; ++j) {
+            const float z = x[j] - m;
+            acc += t[j] * (z - lse);
+            grad[(long long)row * c + j] = scale * (t[j] - exp2f(z * log2e) * inv_s * tsum);
+        }
+        local += acc;
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) local += __shfl_xor_sync(0xffffffffu, local, o);
+    if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = local;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float cta = 0.0f;
+        for (int w = 0; w < 8; ++w) cta += warp_sum[w];
+        partials[blockIdx.x] = cta;
+        __threadfence();
+        if (atomicAdd(ticket, 1u) == gridDim.x - 1) {
+            float total = 0.0f;
+            for (unsigned b = 0; b < gridDim.x; ++b) total += __ldcg(partials + b);
+            out[0] = scale * total;
+            *ticket = 0u;
+            __threadfence();
+        }
+    }
+}
+
+int launch_softmax_xent(Device* dev, const Plan& plan, const float* logits, const float* onehot, float* out, void* scratch) {
+    EB_REQUIRE(scratch, EB200_ERR_INVALID, "softmax cross-entropy launched without scratch");
+    const int n = (int)plan.p.shape[0], c = (int)plan.p.shape[1];
+    float* partials = reinterpret_cast<float*>(scratch);
+    unsigned* ticket = reinterpret_cast<unsigned*>(partials + XENT_MAX_CTAS);
+    const unsigned grid = (unsigned)std::max(1, std::min(XENT_MAX_CTAS, (n + 255) / 256));
+    softmax_xent_kernel<<<grid, 256, 0, dev->stream>>>(logits, onehot, out, n, c, plan.scalar, partials, ticket);
+    count_launch();
+    EB_CHECK_CUDA(cudaGetLastError());
+    return EB200_OK;
+}
+
+}  // namespace eb200

@@ -237,7 +237,7 @@ bool try_gemm(const KParams& p, Plan* plan, int mode) {
 
 int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
     EB_REQUIRE(d && plan, EB200_ERR_INVALID, "null argument");
-    EB_REQUIRE(d->kclass >= EB200_K_ELEMENTWISE && d->kclass <= EB200_K_ADAM, EB200_ERR_INVALID, "unknown kernel class %d", d->kclass);
+    EB_REQUIRE(d->kclass >= EB200_K_ELEMENTWISE && d->kclass <= EB200_K_SOFTMAX_XENT, EB200_ERR_INVALID, "unknown kernel class %d", d->kclass);
     if (d->kclass == EB200_K_CONV2D) {
         // structured descriptor: shape = {N, C, H, W, Co, KH, KW, pad}
         EB_REQUIRE(d->ndim == 8, EB200_ERR_INVALID, "conv2d descriptor wants 8 shape entries, got %d", d->ndim);
@@ -294,6 +294,34 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
         pl.algo_bytes = 4 * ((long long)c.N * c.C * c.H * c.W + (long long)c.Co * K + M * c.Co + (c.has_bias ? c.Co : 0));
         if (c.direct) snprintf(pl.name, sizeof(pl.name), "conv2d_direct_f32%s", c.wgrad ? "_wgrad" : (c.flip ? "_dgrad" : ""));
         else snprintf(pl.name, sizeof(pl.name), "conv2d_igemm_%s%s", c.mode == EB200_GEMM_TF32 ? "tf32" : "3xtf32", c.wgrad ? "_wgrad" : (c.flip ? "_dgrad" : ""));
+        return EB200_OK;
+    }
+    if (d->kclass == EB200_K_SOFTMAX_XENT) {
+        // structured descriptor: shape = {N, C}; logits and one-hot targets in, [64 + N*C] out
+        EB_REQUIRE(d->ndim == 2 && d->n_inputs == 2, EB200_ERR_INVALID, "softmax cross-entropy takes shape {N, C} and two inputs");
+        const long long N = d->shape[0], Cn = d->shape[1];
+        EB_REQUIRE(N >= 1 && Cn >= 1 && N < (1LL << 31) && Cn <= 65536, EB200_ERR_UNSUPPORTED, "softmax cross-entropy over [%lld, %lld]", N, Cn);
+        Plan& pl = *plan;
+        pl = Plan();
+        memset(&pl.p, 0, sizeof(pl.p));
+        for (int i = 0; i <= 2; ++i) {
+            const eb200_operand& o = i < 2 ? d->inputs[i] : d->output;
+            EB_REQUIRE(o.dtype == EB200_F32 && o.n_bounds == 0 && o.offset >= 0, EB200_ERR_UNSUPPORTED, "softmax cross-entropy operands are plain contiguous f32 buffers");
+            EB_REQUIRE(o.numel - o.offset >= N * Cn + (i == 2 ? 64 : 0), EB200_ERR_BOUNDS, "softmax cross-entropy operand %d too small", i);
+            (i < 2 ? pl.p.in[i] : pl.p.out).offset = o.offset;
+        }
+        pl.p.shape[0] = N; pl.p.shape[1] = Cn; pl.p.ndim = 2; pl.p.total = N * Cn; pl.p.n_in = 2;
+        pl.impl = IMPL_SOFTMAX_XENT;
+        pl.n_inputs = 2;
+        for (int i = 0; i < 2; ++i) { pl.in_dtype[i] = EB200_F32; pl.in_numel[i] = d->inputs[i].numel; pl.perm[i] = i; }
+        for (int j = 0; j < KMAX_CONSTS; ++j) pl.dyn_input[j] = -1;
+        pl.out_dtype = EB200_F32;
+        pl.out_numel = d->output.numel;
+        pl.scalar = d->scalar;
+        pl.scratch_bytes = 4096;          // per-CTA loss partials and the ticket word
+        pl.scratch_zero = true;
+        pl.algo_bytes = 4 * (3 * N * Cn + 1);
+        snprintf(pl.name, sizeof(pl.name), "softmax_xent_fwd_bwd");
         return EB200_OK;
     }
     EB_REQUIRE(d->ndim >= 0 && d->ndim <= EB200_MAX_DIMS, EB200_ERR_INVALID, "rank %d out of range", d->ndim);

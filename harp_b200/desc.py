@@ -34,9 +34,9 @@ DTYPE_SIZE = {F32: 4, BOOL: 1, I32: 4, I64: 8}
 DTYPE_NP = {F32: "float32", BOOL: "uint8", I32: "int32", I64: "int64"}
 
 # eb200_kclass
-K_ELEMENTWISE, K_REDUCE, K_COPY, K_SCATTER, K_SGD, K_CONV2D, K_SCAN, K_SGD_MOMENTUM, K_ADAM = 0, 1, 2, 3, 4, 5, 6, 7, 8
+K_ELEMENTWISE, K_REDUCE, K_COPY, K_SCATTER, K_SGD, K_CONV2D, K_SCAN, K_SGD_MOMENTUM, K_ADAM, K_SOFTMAX_XENT = 0, 1, 2, 3, 4, 5, 6, 7, 8, 9
 KCLASS_PREFIX = {K_ELEMENTWISE: "E", K_REDUCE: "R", K_COPY: "C", K_SCATTER: "S", K_SGD: "U", K_CONV2D: "CONV",
-                 K_SCAN: "P", K_SGD_MOMENTUM: "UM", K_ADAM: "UA"}
+                 K_SCAN: "P", K_SGD_MOMENTUM: "UM", K_ADAM: "UA", K_SOFTMAX_XENT: "XENT"}
 FLAG_RELU = 64
 FLAG_WFLIP = 128
 FLAG_WGRAD = 256
@@ -273,6 +273,41 @@ class KernelDesc:
         return d
 
 
+    # ---- serialised form (golden files, ahead-of-time descriptor programs) ----------------
+    def to_json(self) -> dict:
+        def op(o: Operand):
+            return {"dtype": o.dtype, "offset": int(o.offset), "strides": [int(x) for x in o.strides], "numel": int(o.numel),
+                    "pad_value": float(o.pad_value),
+                    "bounds": [{"coef": [int(c) for c in b.coef], "c": int(b.c), "lo": int(b.lo), "hi": int(b.hi)} for b in o.bounds]}
+        return {"name": self.name, "kclass": self.kclass, "shape": list(self.shape), "inputs": [op(o) for o in self.inputs],
+                "output": op(self.output), "reduce_op": self.reduce_op, "reduce_axis": self.reduce_axis,
+                "gemm_mode": self.gemm_mode, "flags": self.flags, "scalar": float(self.scalar), "hyper": [float(h) for h in self.hyper],
+                "prog": [[o, a, float32_hex(i)] for o, a, i in self.program()]}
+
+    @staticmethod
+    def from_json(j: dict) -> "KernelDesc":
+        import struct
+
+        def op(o):
+            return Operand(o["strides"], o["offset"], o["dtype"], o["numel"],
+                           [Bound(b["coef"], b["c"], b["lo"], b["hi"]) for b in o["bounds"]], o["pad_value"])
+        stack: List[Ast] = []
+        for opc, arg, imm in j["prog"]:
+            v = struct.unpack("<f", struct.pack("<I", int(imm, 16)))[0]
+            if opc == OP_LOAD:
+                stack.append(Ast.w(arg))
+            elif opc == OP_CONST:
+                stack.append(Ast.const(v))
+            else:
+                name = _OPNAME[opc]
+                n = _ARITY[name]
+                args = stack[len(stack) - n:]
+                del stack[len(stack) - n:]
+                stack.append(Ast(name, tuple(args), arg if name == "cast" else None))
+        return KernelDesc(j["kclass"], j["shape"], [op(o) for o in j["inputs"]], op(j["output"]), stack[0] if stack else None,
+                          j["reduce_op"], j["reduce_axis"], j["gemm_mode"], j["scalar"], j["name"], j["flags"], j["hyper"])
+
+
 def _fill_operand(c, o: Operand):
     c.dtype = o.dtype
     c.n_bounds = len(o.bounds)
@@ -381,6 +416,17 @@ def adam(n: int, lr: float, beta1: float = 0.9, beta2: float = 0.999, eps: float
     and the one-element I32 step counter (m, v, t updated in place), output p."""
     ins = [contiguous([n])] * 4 + [Operand([0], 0, I32, 1)]
     return KernelDesc(K_ADAM, [n], ins, contiguous([n]), scalar=lr, hyper=[beta1, beta2, eps])
+
+
+XENT_GRAD_OFFSET = 64     # where the gradient starts in a K_SOFTMAX_XENT output (element 0 is the loss)
+
+
+def softmax_xent(n: int, c: int, scale: float) -> KernelDesc:
+    """scale * sum(onehot * log_softmax(logits)) and its gradient with respect to the
+    logits as one kernel (crates/nn/src/functional/activation.rs:174-187, loss.rs:32-65)."""
+    z2 = [0, 0]
+    return KernelDesc(K_SOFTMAX_XENT, [n, c], [Operand(z2, 0, F32, n * c), Operand(z2, 0, F32, n * c)],
+                      Operand(z2, 0, F32, XENT_GRAD_OFFSET + n * c), None, scalar=scale)
 
 
 def copy(shape, src: Operand, out: Optional[Operand] = None) -> KernelDesc:

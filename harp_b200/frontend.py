@@ -639,6 +639,28 @@ class Tensor:
         z = self - m
         return z - z.exp().sum(axis, keepdim=True).expand(self.shape).ln()
 
+    def softmax_cross_entropy(self, onehot: "Tensor", scale: float) -> "Tensor":
+        """scale * sum(onehot * log_softmax(self, axis 1)) for [N, C] logits as ONE kernel that
+        also produces the gradient with respect to the logits (the reference composes both
+        directions from two dozen tiny kernels: crates/nn/src/functional/activation.rs:174-187,
+        loss.rs:32-65, and their VJPs).  Same arithmetic, classes summed in index order."""
+        n, c = self.shape
+        ops = [self.contiguous(), onehot.contiguous()]
+        node = Node("xent", (D.XENT_GRAD_OFFSET + n * c,), [(t.node, t.view) for t in ops], name="softmax_xent")
+        node.xent = (n, c, float(scale))
+        loss = Tensor(node, View((), (), 0))
+        if ops[0].requires_grad:
+            dlogits = Tensor(node, View((n, c), (c, 1), D.XENT_GRAD_OFFSET))
+
+            def back(g):
+                # the loss is normally the root: its upstream gradient is the constant 1
+                if g.node.kind == "input" and g.node.name == "scalar" and float(g.node.data.reshape(-1)[0]) == 1.0:
+                    return dlogits
+                return dlogits * g.reshape(1, 1).expand(n, c)
+            loss.requires_grad = True
+            loss._parents.append((ops[0], back))
+        return loss
+
     # ---- autograd ----
     def backward(self, params: Sequence["Tensor"]) -> List["Tensor"]:
         """Reverse-mode sweep from this scalar (the role of grad::backward,
@@ -697,6 +719,7 @@ class _K:
         self.out_view, self.out_numel, self.out_shape = n.out_view, n.out_numel, n.out_shape
         self.data = n.data
         self.conv = getattr(n, "conv", None)
+        self.xent = getattr(n, "xent", None)
 
 
 def _dim_map(view: View, prod_shape) -> Optional[List[Optional[int]]]:
@@ -817,6 +840,14 @@ def _lower(k: _K, loc) -> D.KernelDesc:
             op.strides = z8
         return D.KernelDesc(D.K_CONV2D, [n, c, h, wd, co, kh, kw, pad], ins, D.Operand(z8, out_off, D.F32, out_numel),
                             None, gemm_mode=mode, flags=(D.FLAG_RELU if relu else 0) | (D.FLAG_WFLIP if flip else 0) | (D.FLAG_WGRAD if wgrad else D.FLAG_NCHW) | (D.FLAG_G_NCHW if g_nchw else 0), name=k.name)
+    if k.kind == "xent":
+        n, c, scale = k.xent
+        d = D.softmax_xent(n, c, scale)
+        for op, src in zip(d.inputs, ins):
+            op.offset, op.numel = src.offset, src.numel
+        d.output.offset, d.output.numel = out_off, out_numel
+        d.name = k.name
+        return d
     if k.kind == "fold":
         assert out_off == 0, "a scatter output owns its buffer (it is zero-filled as a whole)"
         return D.KernelDesc(D.K_SCATTER, k.shape, ins, k.out_view.operand(k.out_numel, D.F32), None, name=k.name)

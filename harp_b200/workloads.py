@@ -129,7 +129,10 @@ def cnn_graph(n: int = 4096, seed: int = 4, label_seed: int = 40, weight_seed: i
         h = x.conv2d(ps[0], ps[1]).relu().max_pool2d_unfold(2)
         h = h.conv2d(ps[2], ps[3]).relu().max_pool2d_unfold(2)
     h = h.reshape(n, 1600).linear(ps[4], ps[5]).relu().linear(ps[6], ps[7])
-    loss = -(h.log_softmax(1) * onehot).sum() * (1.0 / n)
+    if fused_conv:      # log-softmax + cross-entropy, loss and logits gradient, as one kernel
+        loss = h.softmax_cross_entropy(onehot, -1.0 / n)
+    else:
+        loss = -(h.log_softmax(1) * onehot).sum() * (1.0 / n)
     return loss, ps, loss.backward(ps), (x, onehot)
 
 

@@ -85,6 +85,12 @@ typedef enum {
                               * cumulative op when the axis is innermost); the output has the iteration shape */
     EB200_K_SGD_MOMENTUM = 7,/* v <- momentum*v - lr*g; p <- p + v (crates/nn/src/optim/sgd.rs:84-89): inputs p, g, v;
                               * the output receives p, input 2 (v) is updated IN PLACE; scalar = lr, hyper[0] = momentum */
+    EB200_K_SOFTMAX_XENT = 9,/* log_softmax (crates/nn/src/functional/activation.rs:174-187) + cross_entropy_loss
+                              * (crates/nn/src/functional/loss.rs:32-65) forward AND backward as one kernel:
+                              * shape = {N, C}; inputs logits [N, C] and the one-hot targets [N, C], contiguous;
+                              * output [64 + N*C]: element 0 = scalar * sum(onehot * log_softmax(logits)), elements
+                              * 64.. = its gradient with respect to the logits, scalar * (onehot - softmax *
+                              * rowsum(onehot)); scalar = the loss scale (-1/N for the mean) */
     EB200_K_ADAM = 8         /* Adam::step (crates/nn/src/optim/adam.rs:104-147): inputs p, g, m, v and a one-element
                               * I32 step counter t; the output receives p; m, v and t are updated IN PLACE (t <- t + 1
                               * on the device, so a captured step can be replayed); scalar = lr, hyper[0..2] = beta1,

@@ -321,6 +321,35 @@ def emit_kernel_c(k: D.KernelDesc, fn_name: str = "kernel", openmp: bool = False
         line(f"out[{_affine(k.output.offset, k.output.strides)}] = acc;")
         for _ in range(nd):
             close_loop()
+    elif k.kclass == D.K_SOFTMAX_XENT:
+        # log_softmax (crates/nn/src/functional/activation.rs:174-187: x - max, exp, sum, ln, subtract)
+        # followed by cross_entropy_loss (loss.rs:32-65: multiply by the one-hot targets, sum over classes,
+        # sum over the batch, scale), each step a loop nest of its own with f32 temporaries as the
+        # reference's separate kernels have; then the gradient with respect to the logits
+        n, c = k.shape
+        sc = f32_literal(k.scalar)
+        L2E, IL2E = f32_literal(D.LOG2_E), f"(1.0f / {f32_literal(D.LOG2_E)})"
+        line("float total;")
+        line("total = 0.0f;")
+        open_loop(0, n)
+        line("float m;"); line("m = (-INFINITY);")
+        open_loop(1, c); line(f"m = fmaxf(m, buf0[((ridx0 * {c}) + ridx1)]);"); close_loop()
+        line("float s;"); line("s = 0.0f;")
+        line("float ts;"); line("ts = 0.0f;")
+        open_loop(1, c)
+        line(f"s = (s + exp2f(((buf0[((ridx0 * {c}) + ridx1)] + (m * -1.0f)) * {L2E})));")
+        line(f"ts = (ts + buf1[((ridx0 * {c}) + ridx1)]);")
+        close_loop()
+        line(f"float lse = (log2f(s) * {IL2E});")
+        line("float acc;"); line("acc = 0.0f;")
+        open_loop(1, c)
+        line(f"float z = (buf0[((ridx0 * {c}) + ridx1)] + (m * -1.0f));")
+        line(f"acc = (acc + (buf1[((ridx0 * {c}) + ridx1)] * (z + (lse * -1.0f))));")
+        line(f"out[{D.XENT_GRAD_OFFSET} + ((ridx0 * {c}) + ridx1)] = ({sc} * (buf1[((ridx0 * {c}) + ridx1)] + (((exp2f((z * {L2E})) * (1.0f / s)) * ts) * -1.0f)));")
+        close_loop()
+        line("total = (total + acc);")
+        close_loop()
+        line(f"out[0] = ({sc} * total);")
     elif k.kclass == D.K_SGD:
         # host loop of SGD::step (crates/nn/src/optim/sgd.rs:91-95): p - lr*g
         open_loop(0, k.shape[0])

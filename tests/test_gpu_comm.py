@@ -60,7 +60,7 @@ def test_single_rank_communicator_matches_the_plain_kernels(dev, registry):
     comm.attach(k2)
     k1.execute([bx], [z1]); k2.execute([bx], [z2])
     assert z1.read_vec().tobytes() == z2.read_vec().tobytes() == x.max(axis=0).tobytes()
-    assert comm.info()["calls_one_shot"] >= 4
+    assert comm.info()["calls_one_shot"] >= 3      # the two fused updates and the fused reduce finish
     comm.destroy()
 
 

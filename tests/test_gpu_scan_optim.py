@@ -134,3 +134,25 @@ def test_program_with_momentum_and_adam_tracks_the_oracle(dev, registry):
             runs.append(hist)
         assert runs[0][-1] < runs[0][0]
         np.testing.assert_allclose(runs[0], runs[1], rtol=2e-3)
+
+
+@pytest.mark.parametrize("n,c", [(4096, 10), (512, 10), (37, 5), (3, 1000), (1, 1), (70000, 3)])
+def test_softmax_cross_entropy_forward_and_backward_in_one_kernel(dev, n, c):
+    """Loss and logits gradient against the oracle's restatement of the reference's composition
+    (log_softmax, multiply by the one-hot targets, sums, scale) and against float64."""
+    rng = np.random.default_rng(n + c)
+    x = (rng.standard_normal((n, c)) * 3).astype(np.float32)
+    t = np.eye(c, dtype=np.float32)[rng.integers(0, c, n)]
+    k = D.softmax_xent(n, c, -1.0 / n)
+    got, kern = run_gpu(dev, k, [x, t])
+    ref = O.run(k, [x, t])
+    assert kern.impl == "softmax_xent_fwd_bwd" and kern.launches == 1
+    x64 = x.astype(np.float64)
+    z = x64 - x64.max(axis=1, keepdims=True)
+    logp = z - np.log(np.exp(z).sum(axis=1, keepdims=True))
+    loss64 = -(t * logp).sum() / n
+    grad64 = -(t - np.exp(logp) * t.sum(axis=1, keepdims=True)) / n
+    assert abs(got[0] - ref[0]) <= 1e-5 * abs(ref[0]) + 1e-7 and abs(got[0] - loss64) <= 1e-5 * abs(loss64) + 1e-7
+    g, r = got[D.XENT_GRAD_OFFSET:].reshape(n, c), ref[D.XENT_GRAD_OFFSET:].reshape(n, c)
+    scale = np.abs(grad64).max()
+    assert np.abs(g - r).max() <= 1e-5 * scale and np.abs(g - grad64).max() <= 1e-5 * scale
