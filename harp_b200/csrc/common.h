@@ -174,6 +174,7 @@ struct GemmShape {
     int splits = 1;            // split-K: partial products go to scratch and are summed by a second kernel
     long long k_chunk = 0;     // k extent per split (multiple of 32)
     long long partial_off = 0; // float offset of the partials inside the kernel's scratch
+    int convert = 0;           // 3xTF32: hi / lo split inside the kernel (1) or by a pre-pass into scratch copies (0); fixed at plan time
 };
 
 struct ConvShape {
@@ -239,7 +240,7 @@ int launch_gemm_simt(Device* dev, const Plan& plan, const float* a, const float*
 int launch_splitk_reduce(Device* dev, const GemmShape& g, const float* partials, float* c);
 bool gemm_tc_supported(const GemmShape& g);
 void gemm_tc_scratch(const GemmShape& g, long long* a_span, long long* b_span);
-bool gemm_tc_convert(const GemmShape& g);
+bool gemm_tc_convert(const GemmShape& g, int flags);
 int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b, float* c, void* scratch);
 bool gemm_tall_supported(const GemmShape& g);
 int launch_gemm_tall(Device* dev, const Plan& plan, const float* a, const float* b, float* c, void* scratch);

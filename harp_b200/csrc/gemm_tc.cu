@@ -500,8 +500,10 @@ static long long span_of(long long batch, long long sb, long long rows, long lon
 // 3xTF32 with the hi / lo split done inside the kernel (no scratch copies, no extra passes over the
 // operands): for contractions that are short on arithmetic per operand byte, where the two pre-split
 // passes cost more than the MMAs (an MLP layer [65536, 256] x [256, 256]: 64 flop per byte).
-bool gemm_tc_convert(const GemmShape& g) {
+bool gemm_tc_convert(const GemmShape& g, int flags) {
     if (g.mode != EB200_GEMM_3XTF32) return false;
+    if (flags & 4096) return false;      // descriptor flag bit 12: always split in a pre-pass
+    if (flags & 8192) return true;       // descriptor flag bit 13: always split inside the kernel
     const double flops = 2.0 * (double)g.batch * g.m * g.n * g.k;
     const double bytes = 4.0 * (double)g.batch * ((double)g.m * g.k + (double)g.k * g.n + (double)g.m * g.n);
     return flops / bytes < 200.0;
@@ -525,7 +527,7 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
     EB_REQUIRE((reinterpret_cast<uintptr_t>(a_src) & 15) == 0 && (reinterpret_cast<uintptr_t>(b_src) & 15) == 0,
                EB200_ERR_INVALID, "GEMM operands must be 16-byte aligned");
     const float *a_hi = a_src, *a_lo = a_src, *b_hi = b_src, *b_lo = b_src;
-    const bool convert = gemm_tc_convert(g);
+    const bool convert = g.convert != 0;
     if (three && !convert) {
         EB_REQUIRE(scratch, EB200_ERR_INVALID, "3xTF32 launched without scratch");
         long long a_span, b_span;

@@ -780,7 +780,8 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
                 if (tc) {
                     pl.impl = IMPL_GEMM_TC;
                     const bool three = g.mode == EB200_GEMM_3XTF32;
-                    if (three && !gemm_tc_convert(g)) {
+                    g.convert = gemm_tc_convert(g, d->flags) ? 1 : 0;
+                    if (three && !g.convert) {
                         long long a_span, b_span;
                         gemm_tc_scratch(g, &a_span, &b_span);
                         scratch_floats = 2 * a_span + 2 * b_span;

@@ -331,6 +331,7 @@ def emit_kernel_c(k: D.KernelDesc, fn_name: str = "kernel", openmp: bool = False
         L2E, IL2E = f32_literal(D.LOG2_E), f"(1.0f / {f32_literal(D.LOG2_E)})"
         line("float total;")
         line("total = 0.0f;")
+        pragma_done[0] = True           # one accumulator across the rows: sequential
         open_loop(0, n)
         line("float m;"); line("m = (-INFINITY);")
         open_loop(1, c); line(f"m = fmaxf(m, buf0[((ridx0 * {c}) + ridx1)]);"); close_loop()
@@ -451,19 +452,29 @@ def run(k: D.KernelDesc, inputs: Sequence[np.ndarray], openmp: bool = False,
 
 def eval_f64(k: D.KernelDesc, inputs: Sequence[np.ndarray]) -> np.ndarray:
     """Evaluate an ELEMENTWISE / REDUCE / COPY descriptor in float64 with numpy.
-    Only for unmasked operands; used to show that CPU and GPU both sit within
-    rounding of the exact result where sums cancel."""
+    Used to show that CPU and GPU both sit within rounding of the exact result
+    where sums cancel."""
     shape = tuple(k.shape)
 
-    def view(a, op):
-        a = np.asarray(a).reshape(-1)
-        idx = np.full(shape, op.offset, dtype=np.int64)
-        for d, s in enumerate(op.strides):
+    def affine(c, coef):
+        idx = np.full(shape, c, dtype=np.int64)
+        for d, s in enumerate(coef):
             if s:
                 sh = [1] * len(shape)
                 sh[d] = shape[d]
                 idx = idx + (np.arange(shape[d], dtype=np.int64) * s).reshape(sh)
-        return a[idx].astype(np.float64)
+        return idx
+
+    def view(a, op):
+        a = np.asarray(a).reshape(-1)
+        idx = affine(op.offset, op.strides)
+        if not op.bounds:
+            return a[idx].astype(np.float64)
+        ok = np.ones(shape, dtype=bool)
+        for b in op.bounds:           # a masked load reads the pad value where a bound fails
+            e = affine(b.c, b.coef)
+            ok &= (e >= b.lo) & (e < b.hi)
+        return np.where(ok, a[np.where(ok, idx, 0)].astype(np.float64), np.float64(np.float32(op.pad_value)))
 
     loads = [view(a, o) for a, o in zip(inputs, k.inputs)]
 

@@ -163,6 +163,12 @@ def _check_kernel_against_oracle(d, ins, got, what):
         mag = O.run(d, _abs_inputs(ins))
         assert (np.abs(got.astype(np.float64) - ref) <= 1e-5 * mag + 1e-30).all(), what
         return "1e-5 sum|terms|"
+    if d.kclass == D.K_SOFTMAX_XENT:
+        ref = _oracle(d, ins, got)
+        assert abs(float(got[0]) - float(ref[0])) <= 1e-5 * abs(float(ref[0])), what
+        g, r = got[D.XENT_GRAD_OFFSET:], ref[D.XENT_GRAD_OFFSET:]
+        assert np.abs(g - r).max() <= 1e-5 * np.abs(r).max(), what
+        return "1e-5"
     raise AssertionError(f"unexpected kernel class {d.kclass} in the CNN step")
 
 
@@ -183,7 +189,10 @@ def _check_conv(d, ins, got, what, n_sample=16):
         mag = _oracle(d, _abs_inputs(ins), np.zeros_like(got))
         assert (np.abs(got.astype(np.float64) - ref) <= 1e-5 * mag + 1e-30).all(), (what, float(np.abs(got - ref).max()))
         return
-    pick = np.sort(np.random.default_rng(n).choice(n, n_sample, replace=False))
+    pick = np.random.default_rng(n).choice(n, n_sample, replace=False)
+    pick[:2] = (0, n - 1)                              # always the first and the last image
+    pick = np.unique(pick)
+    n_sample = len(pick)
     x = ins[0].reshape(n, -1)[pick]
     small = D.KernelDesc(D.K_CONV2D, [n_sample, c, h, w_, co, kh, kw, pad],
                          [D.Operand([0] * 8, 0, D.F32, x.size)] + [D.Operand([0] * 8, 0, D.F32, a.size) for a in ins[1:]],
@@ -194,11 +203,12 @@ def _check_conv(d, ins, got, what, n_sample=16):
     assert (np.abs(sub.astype(np.float64) - ref) <= 1e-5 * mag + 1e-30).all(), (what, float(np.abs(sub - ref).max()))
 
 
-def test_cfg4_every_kernel_at_batch_4096(dev, registry):
-    """Forward and backward of the CNN at the full batch; then each kernel of the step is
-    re-checked in isolation: its device inputs go through the oracle's loop nest for the
-    same descriptor and must reproduce the device output."""
-    loss, ps, grads, _ = W.cnn_graph(4096, fused_conv=True)
+@pytest.mark.parametrize("batch", [4096, 512])
+def test_cfg4_every_kernel_at_batch_4096(dev, registry, batch):
+    """Forward and backward of the CNN at the full batch (and at the 8-GPU shard size); then
+    each kernel of the step is re-checked in isolation: its device inputs go through the
+    oracle's loop nest for the same descriptor and must reproduce the device output."""
+    loss, ps, grads, _ = W.cnn_graph(batch, fused_conv=True)
     prog = Program([loss] + grads, B200Executor(dev, registry), persistent=True)
     prog.run_forward()
     dev.synchronize()
@@ -209,7 +219,7 @@ def test_cfg4_every_kernel_at_batch_4096(dev, registry):
         got = prog.buf[prog.where[i][0]].read_vec()
         what = f"kernel {pos} {d.name} {kern.impl}"
         if d.kclass == D.K_CONV2D:
-            _check_conv(d, ins, got, what)
+            _check_conv(d, ins, got, what, n_sample=16 if batch > 512 else 64)
             seen[kern.impl] = "1e-5 sum|terms|"
         else:
             # the oracle addresses whole buffers: inputs and output as the descriptor sees them
@@ -219,21 +229,49 @@ def test_cfg4_every_kernel_at_batch_4096(dev, registry):
     assert np.isfinite(float(prog.fetch(loss)))
 
 
+def _cnn_f64(vals, X, onehot):
+    """Loss and the eight gradients of the config-4 network in float64 (torch on the CPU)."""
+    import torch
+    import torch.nn.functional as F
+    ps = [torch.tensor(v, dtype=torch.float64, requires_grad=True) for v in vals]
+    x, t = torch.tensor(X, dtype=torch.float64), torch.tensor(onehot, dtype=torch.float64)
+    n = x.shape[0]
+    h = F.max_pool2d(F.relu(F.conv2d(x, ps[0], ps[1])), 2)
+    h = F.max_pool2d(F.relu(F.conv2d(h, ps[2], ps[3])), 2)
+    h = F.linear(F.relu(F.linear(h.reshape(n, 1600), ps[4], ps[5])), ps[6], ps[7])
+    loss = -(F.log_softmax(h, 1) * t).sum() / n
+    loss.backward()
+    return float(loss.detach()), [p.grad.numpy() for p in ps]
+
+
 def test_cfg4_step_at_the_8_gpu_shard_size(dev, registry):
     """Loss and all eight gradients at 512 images (what one of 8 GPUs holds of the global
     batch 4096): this backend's one-kernel forms on the GPU against the reference's
-    spelling of the same graph on the OpenMP oracle."""
+    spelling of the same graph on the OpenMP oracle, with float64 as the arbiter.  The
+    reference adds the 346 112 terms of a first-layer weight gradient one after the other
+    in f32, so ITS distance to the exact result is the larger one; the bounds say so."""
     def run(fused, ex, fuse):
-        loss, ps, grads, _ = W.cnn_graph(512, fused_conv=fused)
+        loss, ps, grads, (x, onehot) = W.cnn_graph(512, fused_conv=fused)
         p = Program([loss] + grads, ex, fuse=fuse)
         p.run()
-        return [np.array(p.fetch(t), np.float64) for t in [loss] + grads]
-    g = run(True, B200Executor(dev, registry), "chains")
-    o = run(False, OracleExecutor(openmp=True), "reference")
-    assert abs(g[0] - o[0]) <= 1e-5 * abs(o[0])
-    for a, b in zip(g[1:], o[1:]):
-        scale = np.abs(b).max() + 1e-12
-        assert np.abs(a - b).max() <= 2e-4 * scale, (np.abs(a - b).max(), scale)
+        return [np.array(p.fetch(t), np.float64) for t in [loss] + grads], ([q.node.data for q in ps], x.node.data, onehot.node.data)
+    g, data = run(True, B200Executor(dev, registry), "chains")
+    o, _ = run(False, OracleExecutor(openmp=True), "reference")
+    loss64, grads64 = _cnn_f64(*data)
+    assert abs(g[0] - o[0]) <= 1e-5 * abs(o[0]) and abs(g[0] - loss64) <= 1e-5 * abs(loss64)
+    for j, (a, b, e) in enumerate(zip(g[1:], o[1:], grads64)):
+        scale = np.abs(e).max() + 1e-12
+        # The gradients of the convolutions pass backwards through a max-pool: of the 819 200 pooling
+        # windows of this batch a handful hold two candidates that differ by about one f32 rounding, and
+        # the 3xTF32 forward and the f32 / f64 forwards then pick different winners, which moves single
+        # (large) gradient entries to a neighbouring pixel.  Measured here: 3 windows, up to 4e-3 of the
+        # largest entry of a convolution's weight gradient.  Every kernel of this step on its own matches
+        # the oracle to 1e-5 on identical inputs (test_cfg4_every_kernel_at_batch_4096[512]); the layers
+        # after the last pool see no such discontinuity and get the tight bound.
+        tol = 2e-2 if j < 4 else 2e-4
+        assert np.abs(a.reshape(e.shape) - e).max() <= tol * scale, ("gpu", j, np.abs(a.reshape(e.shape) - e).max(), scale)
+        assert np.abs(b.reshape(e.shape) - e).max() <= tol * scale, ("oracle", j, np.abs(b.reshape(e.shape) - e).max(), scale)
+        assert np.abs(a - b).max() <= tol * scale, ("gpu vs oracle", j, np.abs(a - b).max(), scale)
 
 
 def test_models_as_the_reference_tensor_api_builds_them(dev, registry):

@@ -481,7 +481,7 @@ def test_gemm_tall_skinny_weight_gradient(dev, b_, o_, i_):
 
 
 @pytest.mark.parametrize("form", ["nn", "tn", "wgrad"])
-def test_gemm_3xtf32_split_in_the_kernel_equals_split_beforehand(dev, form, monkeypatch):
+def test_gemm_3xtf32_split_in_the_kernel_equals_split_beforehand(dev, form):
     """3xTF32 either splits the operands into hi / lo copies with two passes beforehand (large,
     compute-bound contractions) or inside the kernel after the TMA load (everything below 200
     flop per operand byte).  Same hi / lo values, same MMAs: the results are equal bit for bit."""
@@ -498,7 +498,7 @@ def test_gemm_3xtf32_split_in_the_kernel_equals_split_beforehand(dev, form, monk
         ins = [dy, x]
     outs = {}
     for mode in ("1", "0"):
-        monkeypatch.setenv("EB200_TC_CONVERT", mode)
+        kd.flags = 8192 if mode == "1" else 4096       # descriptor flags: split inside the kernel / by a pre-pass
         got, kern = run_gpu(dev, kd, ins)
         assert kern.impl.startswith("gemm_tcgen05_3xtf32"), kern.impl
         assert (kern.scratch_bytes == 0) == (mode == "1" and "splitk" not in kern.impl) or "splitk" in kern.impl
