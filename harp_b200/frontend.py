@@ -911,6 +911,16 @@ class Program:
         root_ids = {t.node.id for t in all_roots}
         _fuse(ks, order, root_ids, fuse)
         self.order = [i for i in order if i in ks]
+        # As-soon-as-possible order: a kernel runs right after the level of its last producer (ties keep
+        # the depth-first order).  The depth-first walk alone leaves, e.g., the weight gradients of the
+        # last layers at the very end of the backward pass although their inputs exist early; with them
+        # early, their share of a data-parallel step's gradient all-reduce overlaps the rest of the pass.
+        level: Dict[int, int] = {}
+        for i in self.order:
+            srcs = [s_ for s_, _ in ks[i].operands]
+            level[i] = 0 if ks[i].kind == "input" else 1 + max([level[s_] for s_ in srcs], default=0)
+        rank_of = {i: r for r, i in enumerate(self.order)}
+        self.order.sort(key=lambda i: (level[i], rank_of[i]))
         self.ks = ks
         self.numel = {i: ks[i].out_numel for i in self.order}
         self.inputs = {i: ks[i] for i in self.order if ks[i].kind == "input"}
@@ -920,7 +930,8 @@ class Program:
         pids, gids = [p_.node.id for p_, _ in self.sgd], [g_.node.id for _, g_ in self.sgd]
         self.flat = bool(flat and self.sgd and len(set(pids)) == len(pids) and len(set(gids)) == len(gids)
                          and all(ks[i].kind == "input" for i in pids)
-                         and all(ks[i].kind in ("map", "reduce") for i in gids))
+                         and all(ks[i].kind in ("map", "reduce", "conv") for i in gids))
+        assert comm is None or self.flat, "a data-parallel step needs every gradient to be a kernel output that can live in the flat buffer"
         if self.flat:
             off = 0
             for pid, gid in zip(pids, gids):
