@@ -283,12 +283,12 @@ def run_b200(args):
 
     def step(x=bx, oy=by, oz=bz, ot=bt):
         ky.execute([b0, x, b1], [oy])
+        if z_mode == "async":
+            comm.join()            # the previous step's all-reduce: it had that step's copy and this y to hide behind
         kz.execute([x], [oz])
         if z_mode == "async":
             comm.allreduce(oz, D.R_MAX, side_stream=True)
         kt.execute([x], [ot])
-        if z_mode == "async":
-            comm.join()
 
     sampler.start()
     for _ in range(max(args.warmup, 3)):
@@ -311,13 +311,15 @@ def run_b200(args):
             step()
             continue
         e[0].record(); ky.execute([b0, bx, b1], [by])
+        if z_mode == "async":
+            comm.join()
         e[1].record(); kz.execute([bx], [bz])
         if z_mode == "async":
             comm.allreduce(bz, D.R_MAX, side_stream=True)
         e[2].record(); kt.execute([bx], [bt])
         e[3].record()
-        if z_mode == "async":
-            comm.join()
+    if z_mode == "async":
+        comm.join()                # the last step's column maxima are complete inside the timed region
     e_end.record()
     ranks.barrier(dev)
     w1 = time.perf_counter()
@@ -354,6 +356,8 @@ def run_b200(args):
                 dev.wait_event(ev_down[sl])    # ... and for the previous results of this slot to have left
             oy, oz, ot = outs[sl]
             step(xs[sl], oy, oz, ot)
+            if z_mode == "async":
+                comm.join()                    # z leaves the device with this step's results
             ev_k[sl].record()
             dev.wait_event(ev_k[sl], down)     # download batch i's results
             oy.read_on(down, y_host.ptr, y_host.nbytes)
@@ -384,18 +388,19 @@ def run_b200(args):
 
         def step_other():
             ky.execute([b0, bx, b1], [by])
+            if other == "async":
+                comm.join()
             kz2.execute([bx], [bz])
             if other == "async":
                 comm.allreduce(bz, D.R_MAX, side_stream=True)
             kt.execute([bx], [bt])
-            if other == "async":
-                comm.join()
         for _ in range(3):
             step_other()
         ranks.barrier(dev)
         dev.timer_begin()
         for _ in range(K):
             step_other()
+        comm.join()
         ms_other = ranks.max([dev.timer_end() / K])[0]
         z_other = {"z_allreduce": other, "ms_per_step": ms_other, "value_gbs": BYTES_STEP * n / (ms_other * 1e-3) / 1e9}
         ranks.barrier(dev)
@@ -634,10 +639,10 @@ def extra_measurements(reg, dev, ranks, comm, quick=False):
 
         def strong_step():
             ky.execute([b0, bx, b1], [by])
+            comm.join()
             kz.execute([bx], [bz])
             comm.allreduce(bz, D.R_MAX, side_stream=True)
             kt.execute([bx], [bt])
-            comm.join()
         for _ in range(3):
             strong_step()
         ranks.barrier(dev)
@@ -645,6 +650,7 @@ def extra_measurements(reg, dev, ranks, comm, quick=False):
         dev.timer_begin()
         for _ in range(steps):
             strong_step()
+        comm.join()
         ms = ranks.max([dev.timer_end() / steps])[0]
         out["cfg2_strong"] = {"ms_per_step": ms, "value_gbs": BYTES_STEP / (ms * 1e-3) / 1e9, "rows_per_gpu": rl,
                               "sharding": "rows [r*8192/g, (r+1)*8192/g) of ONE [8192,8192] tensor; y and t stay sharded, z by a 32 KB MAX all-reduce",

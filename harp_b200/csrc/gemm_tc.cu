@@ -48,7 +48,9 @@ struct TcParams {
     int tiles_n;
     int ks;            // two-CTA kernel: 32-wide k blocks per pipeline stage (2 halves the barrier round trips per MMA)
     int convert;       // one-CTA kernel, 3xTF32: TMA brings the raw f32 tiles, the epilogue warps split them into hi / lo in shared memory
-    int nh;            // two-CTA kernel: 256-column halves per pair tile (2: a 256 x 512 tile, the whole tensor memory)
+    int nh;            // (unused by the persistent pair kernel; kept at 1)
+    int total_tiles;   // persistent pair kernel: pair tiles over all batches and splits, band padding included
+    int tiles_per_z;   // ... per batch x split slot
     int* error_flag;
 };
 
@@ -245,7 +247,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 1) tmem_dealloc(tmem_base, TC_BN);
 }
 
-// ---- two-CTA form ---------------------------------------------------------------------------
+// ---- two-CTA form: the pair tile -------------------------------------------------------------
 // A cluster of two CTAs computes a 256 x 256 tile with tcgen05.mma.cta_group::2:
 // CTA r stages rows [r*128, r*128+128) of A and columns [r*128, r*128+128) of B, the
 // tensor cores of both SMs read both halves of B, and each CTA's tensor memory holds
@@ -286,149 +288,206 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
                  ::"r"(smem_u32(bar)), "h"((unsigned short)3) : "memory");
 }
 
-__global__ void __launch_bounds__(TC_THREADS, 1)
-gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_alo,
-                const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_blo,
-                const __grid_constant__ TcParams q, float* __restrict__ C, int a_zmul, int b_zmul) {
-    constexpr int HALF = 128;                           // columns of one 256-wide MMA that each CTA stages
-    const int BN = 256 * q.nh;                          // pair tile columns: one or two 256-wide MMA halves
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    const int sub_bytes = (q.three_pass ? 2 : 1) * (1 + q.nh) * TC_TILE_BYTES;     // A tile and nh B tiles, all 128 x 32
-    const int stage_bytes = q.ks * sub_bytes;                          // a stage holds q.ks consecutive k blocks
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)q.stages * stage_bytes);
-    uint64_t* empty_bar = full_bar + q.stages;
-    uint64_t* acc_bar = empty_bar + q.stages;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+// ---- two-CTA form, persistent -------------------------------------------------------------
+// The same pair tile as gemm_tc2_kernel, but one CTA pair per SM pair walks a list of tiles
+// (tile t, t + P, t + 2P, ... for P pairs) and the accumulator is double buffered in tensor
+// memory (2 x 256 columns = all 512): while the epilogue warps drain tile i (tcgen05.ld ->
+// global stores), the MMA thread already accumulates tile i + 1 into the other half.  The
+// operand ring keeps running across tile boundaries, so there is no pipeline fill / drain
+// and no tensor-memory allocation per tile -- what cost the one-tile-per-CTA form a third of
+// its time on short-K tiles (64 x [1024^2]: 32 k blocks per tile).
+//   acc_full[a]   MMA -> epilogue, both CTAs (tcgen05.commit, multicast)
+//   acc_empty[a]  epilogue warps of both CTAs -> the MMA thread (8 arrivals on the even CTA's barrier)
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, unsigned parity, int* error_flag) {
+    for (unsigned i = 0; i < TC_SPIN_LIMIT; ++i) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if (i > 4096) __nanosleep(64);
+    }
+    atomicExch(error_flag, 1);
+    return false;
+}
 
-    const int warp = uniform_warp_idx(), lane = threadIdx.x & 31;
-    const uint32_t rank = __shfl_sync(0xffffffffu, cluster_ctarank(), 0);     // provably warp-uniform
-    const int pair = (int)blockIdx.x >> 1;
+struct PairTile {
+    bool idle;
+    long long m0, n0;     // first row of this CTA's half, first column of the pair tile
+    int bz, zslot;        // batch index; batch * splits + split (slot of split-K partials)
+    int kb_begin, num_kb;
+};
+
+__device__ __forceinline__ PairTile decode_pair_tile(const TcParams& q, int t, uint32_t rank) {
+    PairTile p;
+    const int z = t / q.tiles_per_z, r = t - z * q.tiles_per_z;
     const int tiles_m = (int)((q.m + 255) / 256);
     const int per_band = q.raster * q.tiles_n;
-    const int band = pair / per_band, within = pair % per_band;
+    const int band = r / per_band, within = r - band * per_band;
     const int band_rows = min(q.raster, tiles_m - band * q.raster);
     const int tile_m = band * q.raster + within % band_rows;
     const int tile_n = within / band_rows;
-    const bool idle = tile_n >= q.tiles_n;              // padding of the last band: same answer in both CTAs
-    const long long n0 = (long long)tile_n * BN, m0 = (long long)tile_m * 256 + rank * 128;
-    const int bz = (int)blockIdx.z / q.splits, split = (int)blockIdx.z % q.splits;
+    p.idle = tile_n >= q.tiles_n;
+    p.n0 = (long long)tile_n * 256;
+    p.m0 = (long long)tile_m * 256 + rank * 128;
+    p.bz = z / q.splits;
+    p.zslot = z;
+    const int split = z - p.bz * q.splits;
     const int total_kb = (int)((q.k + TC_BK - 1) / TC_BK);
-    const int kb_begin = split * q.kb_per_split;
-    const int num_kb32 = min(total_kb - kb_begin, q.kb_per_split);
-    const int num_kb = (num_kb32 + q.ks - 1) / q.ks;     // pipeline stages to walk; a k block past K arrives as zeros (TMA fill)
+    p.kb_begin = split * q.kb_per_split;
+    p.num_kb = min(total_kb - p.kb_begin, q.kb_per_split);
+    return p;
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc2p_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_alo,
+                 const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_blo,
+                 const __grid_constant__ TcParams q, float* __restrict__ C, int a_zmul, int b_zmul) {
+    constexpr int HALF = 128;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const int stage_bytes = (q.three_pass ? 2 : 1) * 2 * TC_TILE_BYTES;     // [A hi | (A lo) | B hi | (B lo)], all 128 x 32
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)q.stages * stage_bytes);
+    uint64_t* empty_bar = full_bar + q.stages;
+    uint64_t* acc_full = empty_bar + q.stages;      // [2]
+    uint64_t* acc_empty = acc_full + 2;             // [2], used in the even CTA
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+    const int warp = uniform_warp_idx(), lane = threadIdx.x & 31;
+    const uint32_t rank = __shfl_sync(0xffffffffu, cluster_ctarank(), 0);
+    const int pair = (int)blockIdx.x >> 1, num_pairs = (int)gridDim.x >> 1;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < q.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        mbar_init(acc_bar, 1);
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 8); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
-    cluster_sync_all();          // both CTAs' barriers exist before anything signals them
+    cluster_sync_all();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (!idle) {
-        if (warp == 0) {
-            int s = 0;
-            unsigned phase = 0;
-            for (int kb = 0; kb < num_kb; ++kb, s = (s + 1 == q.stages ? 0 : s + 1), phase ^= (s == 0)) {
-                if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], phase ^ 1u, q.error_flag))) break;
+    if (warp == 0) {
+        // ---- TMA producer: the ring runs on across tiles ----
+        int s = 0;
+        unsigned phase = 0;
+        bool ok = true;
+        for (int t = pair; t < q.total_tiles && ok; t += num_pairs) {
+            const PairTile p = decode_pair_tile(q, t, rank);
+            if (p.idle) continue;
+            const int nb = (int)p.n0 + (int)rank * HALF;
+            for (int kb = 0; kb < p.num_kb; ++kb, s = (s + 1 == q.stages ? 0 : s + 1), phase ^= (s == 0)) {
+                if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], phase ^ 1u, q.error_flag))) { ok = false; break; }
                 if (elect_one()) {
-                    // every load of the pair completes on the even CTA's barrier
                     const uint32_t lead = map_to_cta(smem_u32(&full_bar[s]), 0);
                     if (rank == 0) mbar_expect_tx(&full_bar[s], 2u * (unsigned)stage_bytes);
-                    const int nb = (int)n0 + (int)rank * HALF;    // this CTA's half of the columns
-                    for (int u = 0; u < q.ks; ++u) {
-                        unsigned char* st = smem + (size_t)s * stage_bytes + (size_t)u * sub_bytes;
-                        const int kx = (kb_begin + kb * q.ks + u) * TC_BK;
-                        unsigned char* a_hi = st;
-                        if (q.a_mmajor) {
+                    unsigned char* st = smem + (size_t)s * stage_bytes;
+                    const int kx = (p.kb_begin + kb) * TC_BK;
+                    unsigned char* b_hi = st + (q.three_pass ? 2 : 1) * TC_TILE_BYTES;
+                    if (q.a_mmajor) {
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                tma_load_3d_pair(a_hi + j * 4096, &map_a, lead, (int)m0 + j * 32, kx, bz * a_zmul);
-                                if (q.three_pass) tma_load_3d_pair(st + TC_TILE_BYTES + j * 4096, &map_alo, lead, (int)m0 + j * 32, kx, bz * a_zmul);
-                            }
-                        } else {
-                            tma_load_3d_pair(a_hi, &map_a, lead, kx, (int)m0, bz * a_zmul);
-                            if (q.three_pass) tma_load_3d_pair(st + TC_TILE_BYTES, &map_alo, lead, kx, (int)m0, bz * a_zmul);
+                        for (int j = 0; j < 4; ++j) {
+                            tma_load_3d_pair(st + j * 4096, &map_a, lead, (int)p.m0 + j * 32, kx, p.bz * a_zmul);
+                            if (q.three_pass) tma_load_3d_pair(st + TC_TILE_BYTES + j * 4096, &map_alo, lead, (int)p.m0 + j * 32, kx, p.bz * a_zmul);
                         }
-                        for (int h = 0; h < q.nh; ++h) {
-                            // layout of a k block: [A hi | (A lo) | B(h=0) hi | (lo) | B(h=1) hi | (lo)]
-                            unsigned char* b_hi = st + (q.three_pass ? 2 : 1) * (1 + h) * TC_TILE_BYTES;
-                            const int nbh = nb + h * 256;
-                            if (q.b_nmajor) {
+                    } else {
+                        tma_load_3d_pair(st, &map_a, lead, kx, (int)p.m0, p.bz * a_zmul);
+                        if (q.three_pass) tma_load_3d_pair(st + TC_TILE_BYTES, &map_alo, lead, kx, (int)p.m0, p.bz * a_zmul);
+                    }
+                    if (q.b_nmajor) {
 #pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    tma_load_3d_pair(b_hi + j * 4096, &map_b, lead, nbh + j * 32, kx, bz * b_zmul);
-                                    if (q.three_pass) tma_load_3d_pair(b_hi + TC_TILE_BYTES + j * 4096, &map_blo, lead, nbh + j * 32, kx, bz * b_zmul);
-                                }
-                            } else {
-                                tma_load_3d_pair(b_hi, &map_b, lead, kx, nbh, bz * b_zmul);
-                                if (q.three_pass) tma_load_3d_pair(b_hi + TC_TILE_BYTES, &map_blo, lead, kx, nbh, bz * b_zmul);
-                            }
+                        for (int j = 0; j < 4; ++j) {
+                            tma_load_3d_pair(b_hi + j * 4096, &map_b, lead, nb + j * 32, kx, p.bz * b_zmul);
+                            if (q.three_pass) tma_load_3d_pair(b_hi + TC_TILE_BYTES + j * 4096, &map_blo, lead, nb + j * 32, kx, p.bz * b_zmul);
                         }
+                    } else {
+                        tma_load_3d_pair(b_hi, &map_b, lead, kx, nb, p.bz * b_zmul);
+                        if (q.three_pass) tma_load_3d_pair(b_hi + TC_TILE_BYTES, &map_blo, lead, kx, nb, p.bz * b_zmul);
                     }
                 }
                 __syncwarp();
             }
-        } else if (warp == 1) {
-            if (rank == 0) {
-                const uint32_t idesc = umma_idesc_tf32(256, 256, q.a_mmajor, q.b_nmajor);
-                const uint32_t a_lbo = q.a_mmajor ? 4096 : 16, a_sbo = q.a_mmajor ? 512 : 1024, a_layout = q.a_mmajor ? 1 : 2;
-                const uint32_t b_lbo = q.b_nmajor ? 4096 : 16, b_sbo = q.b_nmajor ? 512 : 1024, b_layout = q.b_nmajor ? 1 : 2;
-                const uint64_t a_jstep = (q.a_mmajor ? 1024u : (unsigned)(TC_UK * 4)) >> 4;
-                const uint64_t b_jstep = (q.b_nmajor ? 1024u : (unsigned)(TC_UK * 4)) >> 4;
-                const uint32_t smem_base = smem_u32(smem);
-                const uint32_t b_off = (q.three_pass ? 2 : 1) * TC_TILE_BYTES;
-                int s = 0;
-                unsigned phase = 0;
-                for (int kb = 0; kb < num_kb; ++kb, s = (s + 1 == q.stages ? 0 : s + 1), phase ^= (s == 0)) {
-                    if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[s], phase, q.error_flag))) break;
+        }
+    } else if (warp == 1) {
+        if (rank == 0) {
+            // ---- MMA issuer (even CTA) ----
+            const uint32_t idesc = umma_idesc_tf32(256, 256, q.a_mmajor, q.b_nmajor);
+            const uint32_t a_lbo = q.a_mmajor ? 4096 : 16, a_sbo = q.a_mmajor ? 512 : 1024, a_layout = q.a_mmajor ? 1 : 2;
+            const uint32_t b_lbo = q.b_nmajor ? 4096 : 16, b_sbo = q.b_nmajor ? 512 : 1024, b_layout = q.b_nmajor ? 1 : 2;
+            const uint64_t a_jstep = (q.a_mmajor ? 1024u : (unsigned)(TC_UK * 4)) >> 4;
+            const uint64_t b_jstep = (q.b_nmajor ? 1024u : (unsigned)(TC_UK * 4)) >> 4;
+            const uint32_t smem_base = smem_u32(smem);
+            const uint32_t b_off = (q.three_pass ? 2 : 1) * TC_TILE_BYTES;
+            int s = 0, it = 0;
+            unsigned phase = 0;
+            bool ok = true;
+            for (int t = pair; t < q.total_tiles && ok; t += num_pairs) {
+                const PairTile p = decode_pair_tile(q, t, rank);
+                if (p.idle) continue;
+                const int a = it & 1;
+                const unsigned aphase = (unsigned)(it >> 1) & 1u;
+                // the epilogue of the tile that used this half two tiles ago must have drained it
+                if (!__all_sync(0xffffffffu, mbar_wait_cluster(&acc_empty[a], aphase ^ 1u, q.error_flag))) break;
+                tc_fence_after();
+                const uint32_t acc = tmem_base + (uint32_t)a * 256u;
+                for (int kb = 0; kb < p.num_kb; ++kb, s = (s + 1 == q.stages ? 0 : s + 1), phase ^= (s == 0)) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[s], phase, q.error_flag))) { ok = false; break; }
                     tc_fence_after();
                     if (elect_one()) {
-                        for (int u = 0; u < q.ks; ++u) {
-                            const uint32_t st = smem_base + (uint32_t)s * (uint32_t)stage_bytes + (uint32_t)u * (uint32_t)sub_bytes;
-                            const uint64_t da0 = umma_desc(st, a_lbo, a_sbo, a_layout), dal0 = umma_desc(st + TC_TILE_BYTES, a_lbo, a_sbo, a_layout);
-                            for (int h = 0; h < q.nh; ++h) {
-                                const uint32_t bh = st + b_off * (1 + h);
-                                const uint64_t db0 = umma_desc(bh, b_lbo, b_sbo, b_layout), dbl0 = umma_desc(bh + TC_TILE_BYTES, b_lbo, b_sbo, b_layout);
-                                const uint32_t acc = tmem_base + h * 256;          // columns of this half
+                        const uint32_t st = smem_base + (uint32_t)s * (uint32_t)stage_bytes;
+                        const uint64_t da0 = umma_desc(st, a_lbo, a_sbo, a_layout), dal0 = umma_desc(st + TC_TILE_BYTES, a_lbo, a_sbo, a_layout);
+                        const uint64_t db0 = umma_desc(st + b_off, b_lbo, b_sbo, b_layout), dbl0 = umma_desc(st + b_off + TC_TILE_BYTES, b_lbo, b_sbo, b_layout);
 #pragma unroll
-                                for (int j = 0; j < TC_BK / TC_UK; ++j) {
-                                    const uint64_t da = da0 + j * a_jstep, db = db0 + j * b_jstep;
-                                    umma_tf32_pair(acc, da, db, idesc, (kb > 0 || u > 0 || j > 0) ? 1u : 0u);
-                                    if (q.three_pass) {
-                                        umma_tf32_pair(acc, dal0 + j * a_jstep, db, idesc, 1u);
-                                        umma_tf32_pair(acc, da, dbl0 + j * b_jstep, idesc, 1u);
-                                    }
-                                }
+                        for (int j = 0; j < TC_BK / TC_UK; ++j) {
+                            const uint64_t da = da0 + j * a_jstep, db = db0 + j * b_jstep;
+                            umma_tf32_pair(acc, da, db, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                            if (q.three_pass) {
+                                umma_tf32_pair(acc, dal0 + j * a_jstep, db, idesc, 1u);
+                                umma_tf32_pair(acc, da, dbl0 + j * b_jstep, idesc, 1u);
                             }
                         }
                         umma_commit_pair(&empty_bar[s]);
                     }
                     __syncwarp();
                 }
-                if (elect_one()) umma_commit_pair(acc_bar);
+                if (!ok) break;
+                if (elect_one()) umma_commit_pair(&acc_full[a]);
                 __syncwarp();
+                ++it;
             }
-        } else {
-            const int quarter = warp & 3;
-            const bool ok = mbar_wait(acc_bar, 0, q.error_flag);
+        }
+    } else {
+        // ---- epilogue: warps 2..5 own tensor-memory lanes 32*(warp%4) .. +31 of this CTA ----
+        const int quarter = warp & 3;
+        int it = 0;
+        for (int t = pair; t < q.total_tiles; t += num_pairs) {
+            const PairTile p = decode_pair_tile(q, t, rank);
+            if (p.idle) continue;
+            const int a = it & 1;
+            const unsigned aphase = (unsigned)(it >> 1) & 1u;
+            if (!mbar_wait_warp(&acc_full[a], aphase, q.error_flag)) break;
             tc_fence_after();
-            const long long row = m0 + quarter * 32 + lane;
-            float* crow = C + q.c_off + (long long)(q.splits > 1 ? (int)blockIdx.z : bz) * q.c_sb + row * q.c_sm;
+            const long long row = p.m0 + quarter * 32 + lane;
+            float* crow = C + q.c_off + (long long)(q.splits > 1 ? p.zslot : p.bz) * q.c_sb + row * q.c_sm;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
+            for (int c = 0; c < 8; ++c) {
                 float v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), v);
-                const long long col0 = n0 + c * 32;
-                if (!ok || row >= q.m || col0 >= q.n) continue;
+                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(a * 256 + c * 32), v);
+                const long long col0 = p.n0 + c * 32;
+                if (row >= q.m || col0 >= q.n) continue;
                 float* dst = crow + col0 * q.c_sn;
                 if (q.c_sn == 1 && col0 + 32 <= q.n && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
@@ -440,13 +499,18 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         if (col0 + i < q.n) dst[i * q.c_sn] = v[i];
                 }
             }
+            // this warp has read its lanes of the half: hand it back to the MMA thread
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&acc_empty[a]), 0));
+            ++it;
         }
     }
     tc_fence_before();
     __syncthreads();
-    cluster_sync_all();          // neither CTA leaves (or frees tensor memory) while the other still works
+    cluster_sync_all();
     if (warp == 1)
-        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
 }
 
 // hi = x rounded to tf32 (low 13 mantissa bits zero), lo = x - hi (exact in f32).
@@ -593,7 +657,7 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
     if (!dev->tc_configured) {
         EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc2p_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         dev->tc_configured = true;
     }
     const int az = g.a_sb > 0 ? 1 : 0, bzm = g.b_sb > 0 ? 1 : 0;
@@ -603,23 +667,23 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
             if ((st = make_map(&mb, b_hi, g.k, g.n, b_b, g.b_sn, g.b_sb, 128))) return st;
             if ((st = make_map(&mbl, b_lo, g.k, g.n, b_b, g.b_sn, g.b_sb, 128))) return st;
         }
-        // plain TF32 with a long K: two k blocks per stage, half as many barrier round trips per MMA
-        // Two measured variants that are off by default because neither moved the 8192^3 TF32 time
-        // (1.57 ms either way, the kernel runs at the sustained tensor rate of the part, as cuBLAS does):
-        // EB200_TC_KS=2 puts two k blocks in a pipeline stage (half the barrier round trips per MMA),
-        // EB200_TC_NH=2 makes the pair tile 256 x 512 (the whole tensor memory; a third less operand
-        // traffic per flop).  Both pass the GEMM parity tests.
         q.ks = 1;
         q.nh = 1;
-        const int stage_bytes = q.ks * (three ? 2 : 1) * (1 + q.nh) * TC_TILE_BYTES;
+        const int stage_bytes = (three ? 2 : 1) * 2 * TC_TILE_BYTES;
         q.stages = std::min(8, (196 * 1024) / stage_bytes);
         EB_REQUIRE(q.stages >= 2, EB200_ERR_UNSUPPORTED, "GEMM stage does not fit shared memory twice");
         const size_t smem = (size_t)q.stages * stage_bytes + 1024 + 256;
-        const long long tm2 = (g.m + 255) / 256, tn2 = (g.n + 256 * q.nh - 1) / (256 * q.nh);
+        const long long tm2 = (g.m + 255) / 256, tn2 = (g.n + 255) / 256;
         const long long bands = (tm2 + q.raster - 1) / q.raster;
         q.tiles_n = (int)tn2;
+        const long long per_z = bands * q.raster * tn2, total = per_z * g.batch * g.splits;
+        EB_REQUIRE(total < (1LL << 31), EB200_ERR_UNSUPPORTED, "too many GEMM tiles");
+        q.tiles_per_z = (int)per_z;
+        q.total_tiles = (int)total;
+        // one CTA pair per SM pair, each walking tiles pair, pair + P, ...
+        const long long pairs = std::min<long long>(total, dev->prop.multiProcessorCount / 2);
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)(bands * q.raster * tn2 * 2), 1, (unsigned)(g.batch * g.splits));
+        cfg.gridDim = dim3((unsigned)(pairs * 2), 1, 1);
         cfg.blockDim = dim3(TC_THREADS, 1, 1);
         cfg.dynamicSmemBytes = smem;
         cfg.stream = dev->stream;
@@ -628,7 +692,7 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
         attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        EB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel, ma, mal, mb, mbl, q, c_out, az, bzm));
+        EB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc2p_kernel, ma, mal, mb, mbl, q, c_out, az, bzm));
     } else {
         const int stage_bytes = (three ? 2 : 1) * (TC_TILE_BYTES + bn * TC_BK * 4);
         q.stages = std::min(8, (196 * 1024) / stage_bytes);

@@ -722,51 +722,130 @@ class _K:
         self.xent = getattr(n, "xent", None)
 
 
-def _dim_map(view: View, prod_shape) -> Optional[List[Optional[int]]]:
-    """How a consumer's view walks a producer's contiguous output: for every
-    consumer dim the producer dim it follows, or None for a broadcast.  None
-    overall when the view is not a pure permute/broadcast of the whole output."""
-    if view.bounds or view.offset != 0:
+def _dim_map(view: View, prod_shape):
+    """How a consumer's view walks a producer's contiguous output, as an affine map onto the
+    producer's own multi-index: for every consumer dim (producer dim, multiplier) or None for a
+    broadcast, plus a base index per producer dim -- producer index[pd] = base[pd] + sum over
+    the consumer dims mapped to pd of multiplier * consumer index.  Permutes, broadcasts,
+    slices, strided taps (the 2 x 2 taps of a pooling window) and sliding windows all have this
+    form.  None when the view is masked or does not decompose without carries between dims."""
+    if view.bounds or view.offset < 0:
         return None
+    nd = len(prod_shape)
     cstr = D.contiguous_strides(prod_shape)
-    by_stride = {cstr[d]: d for d in range(len(prod_shape)) if prod_shape[d] > 1}
-    out, used = [], set()
-    for s, st in zip(view.shape, view.strides):
-        if s == 1 or st == 0:
+    base, rest = [0] * nd, view.offset
+    for d in range(nd):
+        base[d], rest = divmod(rest, cstr[d]) if prod_shape[d] > 1 else (0, rest)
+        if base[d] >= max(prod_shape[d], 1):
+            return None
+    if rest != 0:
+        return None
+    top = list(base)                       # largest index reached per producer dim so far
+    out = []
+    for s_, st in zip(view.shape, view.strides):
+        if s_ == 1 or st == 0:
             out.append(None)
             continue
-        pd = by_stride.get(st)
-        if pd is None or prod_shape[pd] != s or pd in used:
+        if st < 0:
             return None
-        used.add(pd)
-        out.append(pd)
-    if len(used) != len(by_stride):
-        return None
-    return out
+        choice = None
+        for pd in range(nd):               # outermost first: the largest producer stride that divides st and fits
+            if prod_shape[pd] > 1 and st % cstr[pd] == 0:
+                mult = st // cstr[pd]
+                if top[pd] + mult * (s_ - 1) < prod_shape[pd]:
+                    choice = (pd, mult)
+                    break
+        if choice is None:
+            return None
+        top[choice[0]] += choice[1] * (s_ - 1)
+        out.append(choice)
+    return out, base
 
 
 def _through(view: View, dmap, shape) -> View:
-    """A producer operand's view re-expressed over the consumer's dims."""
-    strides = [view.strides[pd] if pd is not None else 0 for pd in dmap]
-    bounds = tuple(Bound([b.coef[pd] if pd is not None else 0 for pd in dmap], b.c, b.lo, b.hi) for b in view.bounds)
-    return View(shape, strides, view.offset, bounds, view.pad_value)
+    """A producer operand's view re-expressed over the consumer's dims (composition of the two
+    affine maps)."""
+    dims, base = dmap
+    strides = [view.strides[pd] * mult if pd is not None else 0 for pd, mult in ((d if d is not None else (None, 0)) for d in dims)]
+    offset = view.offset + sum(st * b for st, b in zip(view.strides, base))
+    bounds = tuple(Bound([b.coef[d[0]] * d[1] if d is not None else 0 for d in dims],
+                         b.c + sum(k * o for k, o in zip(b.coef, base)), b.lo, b.hi) for b in view.bounds)
+    return View(shape, strides, offset, bounds, view.pad_value)
 
 
 def _view_key(v: View):
     return (v.shape, v.strides, v.offset, tuple((tuple(b.coef), b.c, b.lo, b.hi) for b in v.bounds), v.pad_value)
 
 
+def _absorb(c_ops, c_expr, c_shape, j, p: _K):
+    """Consumer (operands, expr, shape) with its operand `j` -- the output of the elementwise
+    producer `p` -- replaced by p's own expression over p's operands (Wildcard substitution,
+    src/ast/mod.rs:1196-1207).  Returns the new (operands, expr) or None when the view is not
+    a pure permute / broadcast of the producer or the result would not fit a descriptor."""
+    dmap = _dim_map(c_ops[j][1], p.shape)
+    if dmap is None:
+        return None
+    # merged operand list (deduplicated), wildcard renumbering
+    new_ops = [o for i, o in enumerate(c_ops) if i != j]
+    remap_c = {}
+    for i in range(len(c_ops)):
+        if i != j:
+            remap_c[i] = w(i if i < j else i - 1)
+    sub = {}
+    for i, (ps, pv) in enumerate(p.operands):
+        nv = _through(pv, dmap, c_shape)
+        key = (ps, _view_key(nv))
+        idx = next((t for t, (s2, v2) in enumerate(new_ops) if (s2, _view_key(v2)) == key), None)
+        if idx is None:
+            new_ops.append((ps, nv))
+            idx = len(new_ops) - 1
+        sub[i] = w(idx)
+    if len(new_ops) > D.MAX_INPUTS:
+        return None
+    remap_c[j] = p.expr.substitute(sub)
+    new_expr = c_expr.substitute(remap_c)
+    prog = new_expr.postfix()
+    if len(prog) > D.MAX_INSNS or sum(1 for o in prog if o[0] == D.OP_CONST) > 24 or _stack_depth(prog) > 14:
+        return None
+    return new_ops, new_expr
+
+
+def _stack_depth(prog) -> int:
+    pops = {D.OP_LOAD: 0, D.OP_CONST: 0, D.OP_SELECT: 3, D.OP_FMA: 3, D.OP_RECIP: 1, D.OP_SQRT: 1, D.OP_LOG2: 1, D.OP_EXP2: 1,
+            D.OP_SIN: 1, D.OP_FLOOR: 1, D.OP_NOT: 1, D.OP_CAST: 1}
+    depth = best = 0
+    for op, _, _ in prog:
+        depth += 1 - pops.get(op, 2)
+        best = max(best, depth)
+    return best
+
+
+def _is_contraction(k: _K) -> bool:
+    """sum over a product of two loads: what the planner serves as a GEMM.  Nothing is inlined
+    into its operands (the pattern must survive)."""
+    return (k.kind == "reduce" and k.reduce_op == D.R_SUM and k.expr is not None and k.expr.op == "mul"
+            and all(a.op == "w" for a in k.expr.args))
+
+
 def _fuse(ks: Dict[int, _K], order: List[int], roots: set, level: str):
+    """Graph-level fusion.  "reference": what eclat does (the last elementwise node folded
+    into the reduce that consumes it, src/lowerer/fusion.rs:28-128).  "chains": (1) an
+    elementwise node with ONE consumer is composed into it; (2) an elementwise node with
+    several elementwise / reduce consumers is RECOMPUTED inside each of them when that moves
+    fewer bytes than writing it once and reading it back k times (k consumers, m full-size
+    operands: k * m <= m + k) -- e.g. the exp and the reciprocal inside tanh, which the backward
+    pass needs again, or a ReLU read by the pool and by two gradient masks."""
     if level == "none":
         return
     changed = True
     while changed:
         changed = False
-        consumers: Dict[int, int] = {}
+        uses: Dict[int, List[Tuple[int, int]]] = {}
         for kid in order:
             if kid in ks:
-                for src, _ in ks[kid].operands:
-                    consumers[src] = consumers.get(src, 0) + 1
+                for j, (src, _) in enumerate(ks[kid].operands):
+                    uses.setdefault(src, []).append((kid, j))
+        # (1) single consumer
         for kid in order:
             c = ks.get(kid)
             if c is None or c.kind not in ("map", "reduce"):
@@ -775,41 +854,65 @@ def _fuse(ks: Dict[int, _K], order: List[int], roots: set, level: str):
                 continue       # eclat only folds an elementwise node into the reduce that consumes it
             for j, (src, v) in enumerate(c.operands):
                 p = ks.get(src)
-                if p is None or p.kind != "map" or src in roots or consumers.get(src, 0) != 1:
+                if p is None or p.kind != "map" or src in roots or len(uses.get(src, [])) != 1:
                     continue
                 if level == "reference" and getattr(c, "_absorbed", False):
                     continue
-                dmap = _dim_map(v, p.shape)
-                if dmap is None:
+                res = _absorb(c.operands, c.expr, c.shape, j, p)
+                if res is None:
                     continue
-                # merged operand list (deduplicated), wildcard renumbering
-                new_ops = [o for i, o in enumerate(c.operands) if i != j]
-                remap_c = {}
-                for i in range(len(c.operands)):
-                    if i != j:
-                        remap_c[i] = w(i if i < j else i - 1)
-                sub = {}
-                for i, (ps, pv) in enumerate(p.operands):
-                    nv = _through(pv, dmap, c.shape)
-                    key = (ps, _view_key(nv))
-                    idx = next((t for t, (s2, v2) in enumerate(new_ops) if (s2, _view_key(v2)) == key), None)
-                    if idx is None:
-                        new_ops.append((ps, nv))
-                        idx = len(new_ops) - 1
-                    sub[i] = w(idx)
-                if len(new_ops) > D.MAX_INPUTS:
-                    continue
-                remap_c[j] = p.expr.substitute(sub)
-                new_expr = c.expr.substitute(remap_c)
-                if len(new_expr.postfix()) > D.MAX_INSNS:
-                    continue
-                c.operands, c.expr = new_ops, new_expr
+                c.operands, c.expr = res
                 c._absorbed = True
                 del ks[src]
                 changed = True
                 break
             if changed:
                 break
+        if changed or level != "chains":
+            continue
+        # (2) several consumers: recompute instead of store + reload, all consumers or none
+        for pid in order:
+            p = ks.get(pid)
+            cons = uses.get(pid, [])
+            if p is None or p.kind != "map" or pid in roots or len(cons) < 2:
+                continue
+            if p.expr.op == "w" and len(p.operands) == 1:
+                continue               # a materialising copy (contiguous / unfold) exists to be read many times
+            # operands that are as large as the node itself (broadcast rows / scalars cost next to nothing to re-read)
+            p_numel = math.prod(p.shape) if p.shape else 1
+            m = sum(1 for _, v in p.operands
+                    if 2 * math.prod(ext for st, ext in zip(v.strides, v.shape) if st != 0) > p_numel)
+            k = len(cons)
+            if k * m > m + k:
+                continue
+            staged: Dict[int, Tuple[list, Ast]] = {}
+            ok = True
+            for cid in sorted({cid for cid, _ in cons}):
+                c = ks[cid]
+                if c.kind not in ("map", "reduce") or _is_contraction(c):
+                    ok = False
+                    break
+                ops_, expr_ = list(c.operands), c.expr
+                while ok:                       # a consumer may read the producer through more than one operand
+                    j = next((t for t, (s_, _) in enumerate(ops_) if s_ == pid), None)
+                    if j is None:
+                        break
+                    res = _absorb(ops_, expr_, c.shape, j, p)
+                    if res is None:
+                        ok = False
+                        break
+                    ops_, expr_ = res
+                if not ok:
+                    break
+                staged[cid] = (ops_, expr_)
+            if not ok:
+                continue
+            for cid, (ops_, expr_) in staged.items():
+                ks[cid].operands, ks[cid].expr = ops_, expr_
+                ks[cid]._absorbed = True
+            del ks[pid]
+            changed = True
+            break
 
 
 def _lower(k: _K, loc) -> D.KernelDesc:
