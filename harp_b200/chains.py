@@ -87,7 +87,7 @@ def _model_chains():
             sub = {}
             for j, op in enumerate(d.inputs):
                 if not op.bounds and all(st == 0 or ext == 1 for st, ext in zip(op.strides, d.shape)):
-                    sub[j] = Ast.const(1.0)
+                    sub[j] = Ast.const(1000003.0 + j)     # a distinct stand-in per operand (equal constants share a slot)
             out.append((f"{tag}_{i}", d.map.substitute(sub)))
     return out
 

@@ -22,8 +22,8 @@ int find_chain(const KInsn* prog, int n_insns) {
         if (e.n != n_insns) continue;
         bool same = true;
         for (int i = 0; i < n_insns && same; ++i) {
-            if (e.prog[i].op != prog[i].op) same = false;
-            else if (prog[i].op != EB200_OP_CONST && e.prog[i].arg != prog[i].arg) same = false;
+            // operator, operand number, and for constants the slot (equal constants share one)
+            if (e.prog[i].op != prog[i].op || e.prog[i].arg != prog[i].arg) same = false;
         }
         if (same) return c;
     }

@@ -611,11 +611,22 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
                 if (canon[i] < 0) { canon[i] = n_kin; pl.perm[n_kin] = i; p.in[n_kin] = old_in[i]; ++n_kin; }
                 ins.arg = (short)canon[i];
             } else if (nd.op == EB200_OP_CONST) {
-                if (nc >= KMAX_CONSTS) { too_many = true; break; }
-                ins.arg = (short)nc;
-                if (nd.dyn >= 0) { pl.dyn_input[nc] = nd.dyn; pl.dyn_offset[nc] = old_in[nd.dyn].offset; p.consts[nc] = 0.0f; ins.imm = 0.0f; }
-                else p.consts[nc] = nd.imm;
-                ++nc;
+                // equal constants share a slot (the same literal bits, or the same element of the same
+                // tensor), so repeated subexpressions -- tanh's exp inside its gradient, say -- are
+                // textually identical in the compiled functor and evaluated once
+                int slot = -1;
+                for (int j = 0; j < nc && slot < 0; ++j) {
+                    if (nd.dyn >= 0) { if (pl.dyn_input[j] == nd.dyn && pl.dyn_offset[j] == old_in[nd.dyn].offset) slot = j; }
+                    else if (pl.dyn_input[j] < 0 && memcmp(&p.consts[j], &nd.imm, sizeof(float)) == 0) slot = j;
+                }
+                if (slot < 0) {
+                    if (nc >= KMAX_CONSTS) { too_many = true; break; }
+                    slot = nc++;
+                    if (nd.dyn >= 0) { pl.dyn_input[slot] = nd.dyn; pl.dyn_offset[slot] = old_in[nd.dyn].offset; p.consts[slot] = 0.0f; }
+                    else p.consts[slot] = nd.imm;
+                }
+                ins.arg = (short)slot;
+                if (nd.dyn >= 0) ins.imm = 0.0f;
             }
             p.prog[n_out++] = ins;
         }
