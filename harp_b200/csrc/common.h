@@ -161,6 +161,7 @@ enum Impl {
     IMPL_SGD_MOMENTUM,    // v = momentum*v - lr*g; p += v
     IMPL_ADAM,            // Adam step with device-resident moments and step counter
     IMPL_SOFTMAX_XENT,    // log-softmax + cross-entropy, loss and logits gradient in one kernel
+    IMPL_SIBLINGS,        // row reduce + column max + transposing copy of one [R, C] tensor in one pass
 };
 
 struct GemmShape {
@@ -198,6 +199,7 @@ struct Plan {
     GemmShape gemm;
     ConvShape conv;
     bool narrow = false;          // outer reduce with few kept elements: column threads x row lanes
+    long long sib_rows = 0, sib_cols = 0;   // IMPL_SIBLINGS: the shared [R, C] operand
     TransposeShape tr;
     int64_t scratch_bytes = 0;
     bool scratch_zero = false;    // the scratch must start at zero (set once, at kernel creation)
@@ -235,6 +237,8 @@ int launch_adam(Device* dev, const Plan& plan, const float* p, const float* g, f
                 long long n, void* scratch);
 int launch_softmax_xent(Device* dev, const Plan& plan, const float* logits, const float* onehot, float* out, void* scratch);
 long long scan_scratch_floats(const KParams& p, int sms);
+long long siblings_scratch_floats(long long R, long long C);
+int launch_siblings(Device* dev, const Plan& plan, const KParams& p, const float* x, float* out, void* scratch);
 int launch_scan(Device* dev, const Plan& plan, const KParams& p, void* scratch);
 int launch_gemm_simt(Device* dev, const Plan& plan, const float* a, const float* b, float* c, void* scratch);
 int launch_splitk_reduce(Device* dev, const GemmShape& g, const float* partials, float* c);

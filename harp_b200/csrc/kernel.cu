@@ -153,6 +153,9 @@ int eb200_kernel_launch(eb200_kernel* k, eb200_buffer* const* inputs, int n_inpu
                                reinterpret_cast<int*>(p.in[4].ptr) + p.in[4].offset,
                                reinterpret_cast<float*>(p.out.ptr) + p.out.offset, p.total, scratch);
         case IMPL_SCAN: return launch_scan(dev, plan, p, scratch);
+        case IMPL_SIBLINGS:
+            return launch_siblings(dev, plan, p, reinterpret_cast<const float*>(p.in[0].ptr) + p.in[0].offset,
+                                   reinterpret_cast<float*>(p.out.ptr) + p.out.offset, scratch);
         case IMPL_SOFTMAX_XENT:
             return launch_softmax_xent(dev, plan, reinterpret_cast<const float*>(p.in[0].ptr) + p.in[0].offset,
                                        reinterpret_cast<const float*>(p.in[1].ptr) + p.in[1].offset,

@@ -818,12 +818,46 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
                 pl.scratch_bytes = scratch_floats * 4;
                 break;
             }
+            if ((d->flags & 16384) != 0) {
+                // sibling fusion (descriptor flag bit 14): besides this row reduce, the kernel also produces the column
+                // maximum and the transposed copy of the one full-size operand it reads
+                EB_REQUIRE(raxis == nk - 1 && nk == 2 && p.rop == EB200_R_SUM && p.n_in == 1, EB200_ERR_UNSUPPORTED,
+                           "sibling fusion wants a sum over the rows of one [R, C] operand (other operands one-element)");
+                const KOperand& x = p.in[0];
+                EB_REQUIRE(x.dtype == EB200_F32 && !x.n_bounds && x.strides[1] == 1 && x.strides[0] == shape[1] && x.offset % 4 == 0 &&
+                           shape[0] % 64 == 0 && shape[1] % 64 == 0, EB200_ERR_UNSUPPORTED,
+                           "sibling fusion wants a contiguous f32 operand with R and C multiples of 64");
+                const long long R = shape[0], Cc = shape[1];
+                EB_REQUIRE(d->output.numel - d->output.offset >= R + Cc + R * Cc && d->output.offset % 4 == 0, EB200_ERR_BOUNDS,
+                           "sibling fusion writes [y (R) | z (C) | t (C*R)] into its output");
+                pl.impl = IMPL_SIBLINGS;
+                pl.sib_rows = R; pl.sib_cols = Cc;
+                pl.scratch_bytes = siblings_scratch_floats(R, Cc) * 4;
+                pl.launches = 2;
+                pl.algo_bytes = 4 * (2 * R * Cc + R + Cc);
+                snprintf(pl.name, sizeof(pl.name), "siblings_rowsum_colmax_transpose");
+                pl.chain = find_chain(p.prog, p.n_insns);
+                return EB200_OK;
+            }
             if (raxis == nk - 1) {
                 pl.impl = IMPL_REDUCE_INNER;
                 bool v = p.rlen % 4 == 0 && p.rlen >= 4;
                 for (int i = 0; v && i < p.n_in; ++i) v = vec_ok(p.in[i], raxis, false);
                 p.vec = v ? 4 : 1;
                 pl.threads_per_row = p.rlen <= 64 ? 1 : (p.rlen <= 16384 ? 32 : 256);
+                if (v && p.rlen >= 2048 && p.rlen <= 16384) {
+                    // Few waves of CTAs: pick the row group whose CTA count fills whole waves.  A warp per row makes
+                    // kept / 8 CTAs; 8192 rows are 1024 CTAs = 1.73 waves of the 592 resident ones (4 per SM), so a
+                    // quarter of the second wave idles; 128 threads per row make 4096 CTAs = 6.92 waves.
+                    const long long resident = 4LL * sm_count;
+                    double best = 0.0;
+                    for (int T : {32, 128, 256}) {
+                        const long long units = (p.kept * T + 255) / 256;
+                        const long long waves = (units + resident - 1) / resident;
+                        const double eff = (double)units / (double)(waves * resident);
+                        if (eff > best + 0.02) { best = eff; pl.threads_per_row = T; }
+                    }
+                }
                 // tuning override (desc.flags bits 0-1): 1 -> thread, 2 -> warp, 3 -> CTA per row
                 if ((d->flags & 7) == 1) pl.threads_per_row = 1;
                 if ((d->flags & 7) == 2) pl.threads_per_row = 32;

@@ -309,7 +309,10 @@ __global__ void __launch_bounds__(RT_WARPS * 32, 1) reduce_inner_tma_kernel(cons
     }
 }
 
-constexpr int RO_U = 4;  // reduce steps in flight per thread
+#ifndef EB_RO_U
+#define EB_RO_U 4
+#endif
+constexpr int RO_U = EB_RO_U;  // reduce steps in flight per thread
 
 template <class F>
 __global__ void __launch_bounds__(256) reduce_outer_kernel(const __grid_constant__ KParams p, float* __restrict__ scratch) {

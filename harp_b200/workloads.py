@@ -45,6 +45,20 @@ def cfg2_t(rows: int = 8192, cols: int = 8192) -> D.KernelDesc:
     return D.elementwise([cols, rows], [src], w(0))
 
 
+FLAG_SIBLINGS = 16384
+
+
+def cfg2_siblings(rows: int = 8192, cols: int = 8192) -> D.KernelDesc:
+    """y, z and t of config 2 from ONE pass over x (sibling fusion, descriptor flag bit 14): the
+    row-sum descriptor of `cfg2_y` whose output buffer also receives z = max(x, axis 0) and
+    t = x transposed: [y (rows) | z (cols) | t (cols * rows)], y and z padded to multiples of 64."""
+    k = cfg2_y(rows, cols)
+    pad = lambda v: (v + 63) // 64 * 64
+    k.output = D.Operand([1, 0], 0, D.F32, pad(rows) + pad(cols) + rows * cols)
+    k.flags = FLAG_SIBLINGS
+    return k
+
+
 def cfg2_consts():
     return np.array([0.5], np.float32), np.array([1.0], np.float32)
 

@@ -156,3 +156,23 @@ def test_softmax_cross_entropy_forward_and_backward_in_one_kernel(dev, n, c):
     g, r = got[D.XENT_GRAD_OFFSET:].reshape(n, c), ref[D.XENT_GRAD_OFFSET:].reshape(n, c)
     scale = np.abs(grad64).max()
     assert np.abs(g - r).max() <= 1e-5 * scale and np.abs(g - grad64).max() <= 1e-5 * scale
+
+
+@pytest.mark.parametrize("rows,cols", [(64, 64), (256, 512), (1024, 192), (8192, 8192)])
+def test_sibling_fusion_reads_x_once_for_y_z_and_t(dev, rows, cols):
+    """Config 2's three roots from one pass over x: y against the oracle's row sum (and float64),
+    z and t bit-exact against the oracle's column max and transposing copy."""
+    from harp_b200 import workloads as W
+    x = W.cfg2_input(rows, cols)
+    c0, c1 = W.cfg2_consts()
+    k = W.cfg2_siblings(rows, cols)
+    got, kern = run_gpu(dev, k, [c0, x, c1])
+    assert kern.impl == "siblings_rowsum_colmax_transpose" and kern.specialised and kern.launches == 2
+    pad = lambda v: (v + 63) // 64 * 64
+    y, z, t = got[:rows], got[pad(rows):pad(rows) + cols], got[pad(rows) + pad(cols):]
+    y_ref = O.run(W.cfg2_y(rows, cols), [c0, x, c1])
+    terms = np.abs(np.exp(0.5 * x.astype(np.float64) + 1.0) * x).sum(axis=1)
+    exact = (np.exp(0.5 * x.astype(np.float64) + 1.0) * x).sum(axis=1)
+    assert (np.abs(y.astype(np.float64) - y_ref) <= 1e-5 * terms).all() and (np.abs(y - exact) <= 1e-5 * terms).all()
+    assert z.tobytes() == O.run(W.cfg2_z(rows, cols), [x]).tobytes()
+    assert t.tobytes() == np.ascontiguousarray(x.T).tobytes()
