@@ -738,6 +738,11 @@ def extra_measurements(reg, dev, ranks, comm, quick=False):
     return out
 
 
+def W_matmul(m, k, n):
+    from harp_b200 import workloads as W
+    return W.matmul_desc(m, k, n)
+
+
 def misc_kernel_measurements(reg, dev, rng, hbm, quick=False):
     """Kernel classes that no configuration's headline covers, each alone on inputs larger
     than L2: scans, optimizer updates, scatter-add, a plain elementwise add."""
@@ -774,12 +779,22 @@ def misc_kernel_measurements(reg, dev, rng, hbm, quick=False):
     dst = View.contiguous(dst_shape).unfold([2, 3], [3, 3], [1, 1], [1, 1])
     kd = D.KernelDesc(D.K_SCATTER, src_shape, [D.contiguous(src_shape)], dst.operand(int(np.prod(dst_shape)), D.F32), None)
     run("scatter_add_fold3x3", kd, [int(np.prod(src_shape))], int(np.prod(dst_shape)))
+    # a bias gradient: column sums of [2.77 M, 32] (few kept elements: column threads x row lanes)
+    rows = 4096 * 676
+    run("bias_grad_colsum_2768896x32", D.reduce([rows, 32], [D.contiguous([rows, 32])], w(0), D.R_SUM, 0), [rows * 32], 32)
+    # a first-layer weight gradient as a contraction: dW[32, 9] over 2.77 M positions (one output tile, long K)
+    a = D.Operand([32, 1, 0], 0, D.F32, rows * 32)
+    b = D.Operand([9, 0, 1], 0, D.F32, rows * 9)
+    run("tall_wgrad_32x9_over_2768896", D.reduce([rows, 32, 9], [a, b], w(0) * w(1), D.R_SUM, 0), [rows * 32, rows * 9], 32 * 9)
+    # a contraction on the f32 FFMA kernel (row stride not a multiple of 16 bytes: TMA cannot address it)
+    run("gemm_simt_2048x1022x2048", W_matmul(2048, 1022, 2048), [2048 * 1022, 1022 * 2048], 2048 * 2048)
     return res
 
 
 def run_only_small(args):
-    """`--only gemm`: the tensor-core contraction on a 2048^3 case; `--only kernels`: the kernel
-    classes of misc_kernel_measurements on 32 M-element inputs (profiler captures)."""
+    """`--only gemm`: the tensor-core contraction on a 4096 x 2048 x 4096 case; `--only cfg2`: the
+    config 2 kernels and the one-pass sibling form on a [4096, 8192] block; `--only kernels`: the
+    kernel classes of misc_kernel_measurements (small cases for profiler captures)."""
     from harp_b200 import desc as D
     from harp_b200 import workloads as W
     from harp_b200.backend import B200BackendRegistry
@@ -789,14 +804,31 @@ def run_only_small(args):
     hbm, _, _ = measured_peaks()
     if args.only == "gemm":
         res = {}
-        n = 2048
-        ba, bb, bo = (reg.allocate_buffer(dev, [n * n]) for _ in range(3))
-        ba.write_vec(rng.uniform(-1, 1, n * n).astype(np.float32)); bb.write_vec(rng.uniform(-1, 1, n * n).astype(np.float32))
+        m, k_, n = 4096, 2048, 4096          # 256 pair tiles: the persistent two-CTA kernel; 64 + 32 + 64 MiB
+        ba, bb, bo = reg.allocate_buffer(dev, [m * k_]), reg.allocate_buffer(dev, [k_ * n]), reg.allocate_buffer(dev, [m * n])
+        ba.write_vec(rng.uniform(-1, 1, m * k_).astype(np.float32)); bb.write_vec(rng.uniform(-1, 1, k_ * n).astype(np.float32))
         for mode, mname in ((D.GEMM_TF32, "tf32"), (D.GEMM_3XTF32, "3xtf32")):
-            kern = reg.compile_ast(dev, W.matmul_desc(n, n, n, mode=mode))
+            kern = reg.compile_ast(dev, W.matmul_desc(m, k_, n, mode=mode))
             ms = time_kernel(dev, kern, [ba, bb], [bo], reps=2, warm=1)
-            res[mname] = {"impl": kern.impl, "ms": ms, "tflops": 2.0 * n ** 3 / ms / 1e9}
-        print(json.dumps({"only": "gemm", "gemm_2048": res}))
+            res[mname] = {"impl": kern.impl, "ms": ms, "tflops": 2.0 * m * k_ * n / ms / 1e9}
+        print(json.dumps({"only": "gemm", "gemm_4096x2048x4096": res}))
+        return
+    if args.only == "cfg2":
+        # the config 2 kernels on a [4096, 8192] block (128 MiB, larger than L2), plus the one-pass sibling form
+        rows = 4096
+        c0, c1 = W.cfg2_consts()
+        bx = reg.allocate_buffer(dev, [rows * COLS]); bx.write_vec(W.cfg2_input(rows, COLS))
+        b0 = reg.allocate_buffer(dev, [1]); b0.write_vec(c0)
+        b1 = reg.allocate_buffer(dev, [1]); b1.write_vec(c1)
+        res = {}
+        for name, kd, ins in (("y", W.cfg2_y(rows, COLS), [b0, bx, b1]), ("z", W.cfg2_z(rows, COLS), [bx]),
+                              ("t", W.cfg2_t(rows, COLS), [bx]), ("siblings", W.cfg2_siblings(rows, COLS), [b0, bx, b1])):
+            kern = reg.compile_ast(dev, kd)
+            bo = reg.allocate_buffer(dev, [int(kd.output.numel)])
+            ms = time_kernel(dev, kern, ins, [bo], reps=3, warm=2)
+            res[name] = {"impl": kern.impl, "ms": ms, "gbs": kern.algo_bytes / ms / 1e6}
+            bo.release()
+        print(json.dumps({"only": "cfg2", "rows": rows, "kernels": res}))
         return
     print(json.dumps({"only": "kernels", "kernels": misc_kernel_measurements(reg, dev, rng, hbm, quick=True)}))
 
@@ -811,7 +843,7 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="only config 2 (skip matmul / MLP / CNN measurements)")
     ap.add_argument("--z-allreduce", default="async", choices=["async", "fused"],
                     help="multi-GPU: how the column-max partials are combined (side-stream all-reduce, or fused into the reduce's finish pass)")
-    ap.add_argument("--only", default="", choices=["", "conv2d", "conv2d_grad", "gemm", "kernels"],
+    ap.add_argument("--only", default="", choices=["", "conv2d", "conv2d_grad", "gemm", "kernels", "cfg2"],
                     help="run one small kernel case alone (profiler captures); prints no bench line")
     args = ap.parse_args()
     if args.only in ("conv2d", "conv2d_grad"):

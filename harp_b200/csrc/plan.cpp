@@ -845,19 +845,9 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
                 for (int i = 0; v && i < p.n_in; ++i) v = vec_ok(p.in[i], raxis, false);
                 p.vec = v ? 4 : 1;
                 pl.threads_per_row = p.rlen <= 64 ? 1 : (p.rlen <= 16384 ? 32 : 256);
-                if (v && p.rlen >= 2048 && p.rlen <= 16384) {
-                    // Few waves of CTAs: pick the row group whose CTA count fills whole waves.  A warp per row makes
-                    // kept / 8 CTAs; 8192 rows are 1024 CTAs = 1.73 waves of the 592 resident ones (4 per SM), so a
-                    // quarter of the second wave idles; 128 threads per row make 4096 CTAs = 6.92 waves.
-                    const long long resident = 4LL * sm_count;
-                    double best = 0.0;
-                    for (int T : {32, 128, 256}) {
-                        const long long units = (p.kept * T + 255) / 256;
-                        const long long waves = (units + resident - 1) / resident;
-                        const double eff = (double)units / (double)(waves * resident);
-                        if (eff > best + 0.02) { best = eff; pl.threads_per_row = T; }
-                    }
-                }
+                // (a row group that fills whole waves of CTAs -- 128 threads per row make 6.92 waves of config 2's
+                // 8192 rows where a warp per row makes 1.73 -- measured SLOWER: 51.8 us against 47.1 us; the warp
+                // form has no block barrier and keeps more rows in flight per SM)
                 // tuning override (desc.flags bits 0-1): 1 -> thread, 2 -> warp, 3 -> CTA per row
                 if ((d->flags & 7) == 1) pl.threads_per_row = 1;
                 if ((d->flags & 7) == 2) pl.threads_per_row = 32;

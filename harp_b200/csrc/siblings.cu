@@ -150,7 +150,11 @@ long long siblings_scratch_floats(long long R, long long C) { return (C / 64) * 
 
 template <class F>
 static int launch_siblings_one(Device* dev, const KParams& p, const SibParams& q, const float* x) {
-    const long long blocks = std::min<long long>(q.tiles, (long long)dev->prop.multiProcessorCount * 6);
+    // persistent CTAs: exactly as many as are resident at once (a second wave would start only when
+    // first-wave CTAs have finished their whole share of the tiles)
+    int per_sm = 0;
+    EB_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, siblings_kernel<F>, 256, 0));
+    const long long blocks = std::min<long long>(q.tiles, (long long)dev->prop.multiProcessorCount * std::max(1, per_sm));
     siblings_kernel<F><<<(unsigned)blocks, 256, 0, dev->stream>>>(p, q, x);
     count_launch();
     long long fb = std::min<long long>((q.R + q.C + 255) / 256, (long long)dev->prop.multiProcessorCount * 8);

@@ -19,9 +19,9 @@ def query(k: D.KernelDesc, sms: int = 148):
     return info
 
 
-def test_cfg2_row_sum_is_vectorised_and_compiled_with_a_row_group_that_fills_whole_waves():
+def test_cfg2_row_sum_is_vectorised_warp_per_row_and_compiled():
     i = query(W.cfg2_y())
-    assert i.impl.decode() == "reduce_inner_t128_v4"
+    assert i.impl.decode() == "reduce_inner_t32_v4"
     assert i.specialised == 1 and i.launches == 1 and i.scratch_bytes == 0
     assert i.algo_bytes == 4 * 8192 * 8192 + 4 * 8192 + 8   # x once, y once, two scalars
 
