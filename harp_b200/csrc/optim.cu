@@ -37,14 +37,43 @@ __device__ __forceinline__ float powi_f32(float a, int b) {
     return recip ? __fdiv_rn(1.0f, r) : r;
 }
 
+__device__ __forceinline__ float momentum_step(float p, float g, float& v, float lr, float momentum) {
+    v = __fsub_rn(__fmul_rn(momentum, v), __fmul_rn(lr, g));
+    return __fadd_rn(p, v);
+}
+
+// 128-bit accesses when every buffer is 16-byte aligned (flat parameter buffers are); `out` may be `p`.
 __global__ void __launch_bounds__(256) sgd_momentum_kernel(const float* p, const float* __restrict__ g, float* v, float* out,
                                                            long long n, float lr, float momentum) {
     const long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-        const float vn = __fsub_rn(__fmul_rn(momentum, v[i]), __fmul_rn(lr, g[i]));
-        v[i] = vn;
-        out[i] = __fadd_rn(p[i], vn);
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(v) |
+                           reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    const long long nvec = aligned ? (n >> 2) : 0;
+    for (long long i = tid; i < nvec; i += stride) {
+        const float4 pv = reinterpret_cast<const float4*>(p)[i];
+        const float4 gv = __ldg(reinterpret_cast<const float4*>(g) + i);
+        float4 vv = reinterpret_cast<float4*>(v)[i];
+        float4 r;
+        r.x = momentum_step(pv.x, gv.x, vv.x, lr, momentum); r.y = momentum_step(pv.y, gv.y, vv.y, lr, momentum);
+        r.z = momentum_step(pv.z, gv.z, vv.z, lr, momentum); r.w = momentum_step(pv.w, gv.w, vv.w, lr, momentum);
+        reinterpret_cast<float4*>(v)[i] = vv;
+        reinterpret_cast<float4*>(out)[i] = r;
     }
+    for (long long i = (nvec << 2) + tid; i < n; i += stride) {
+        float vi = v[i];
+        out[i] = momentum_step(p[i], g[i], vi, lr, momentum);
+        v[i] = vi;
+    }
+}
+
+struct AdamConsts { float lr, beta1, beta2, eps, omb1, omb2, bc1, bc2; };
+
+__device__ __forceinline__ float adam_step(float p, float g, float& m, float& v, const AdamConsts& c) {
+    m = __fadd_rn(__fmul_rn(c.beta1, m), __fmul_rn(c.omb1, g));
+    v = __fadd_rn(__fmul_rn(c.beta2, v), __fmul_rn(__fmul_rn(c.omb2, g), g));
+    const float m_hat = __fdiv_rn(m, c.bc1), v_hat = __fdiv_rn(v, c.bc2);
+    return __fsub_rn(p, __fdiv_rn(__fmul_rn(c.lr, m_hat), __fadd_rn(__fsqrt_rn(v_hat), c.eps)));
 }
 
 __global__ void __launch_bounds__(256) adam_kernel(const float* p, const float* __restrict__ g, float* m, float* v, int* t,
@@ -52,18 +81,31 @@ __global__ void __launch_bounds__(256) adam_kernel(const float* p, const float* 
                                                    unsigned* ticket) {
     // every CTA reads the old step count before the last CTA to finish replaces it
     const int step = *reinterpret_cast<volatile int*>(t) + 1;
-    const float bc1 = __fsub_rn(1.0f, powi_f32(beta1, step));
-    const float bc2 = __fsub_rn(1.0f, powi_f32(beta2, step));
-    const float omb1 = __fsub_rn(1.0f, beta1), omb2 = __fsub_rn(1.0f, beta2);
+    AdamConsts c;
+    c.lr = lr; c.beta1 = beta1; c.beta2 = beta2; c.eps = eps;
+    c.bc1 = __fsub_rn(1.0f, powi_f32(beta1, step));
+    c.bc2 = __fsub_rn(1.0f, powi_f32(beta2, step));
+    c.omb1 = __fsub_rn(1.0f, beta1); c.omb2 = __fsub_rn(1.0f, beta2);
     const long long stride = (long long)gridDim.x * blockDim.x;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-        const float gi = g[i];
-        const float mn = __fadd_rn(__fmul_rn(beta1, m[i]), __fmul_rn(omb1, gi));
-        const float vn = __fadd_rn(__fmul_rn(beta2, v[i]), __fmul_rn(__fmul_rn(omb2, gi), gi));
-        m[i] = mn;
-        v[i] = vn;
-        const float m_hat = __fdiv_rn(mn, bc1), v_hat = __fdiv_rn(vn, bc2);
-        out[i] = __fsub_rn(p[i], __fdiv_rn(__fmul_rn(lr, m_hat), __fadd_rn(__fsqrt_rn(v_hat), eps)));
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(m) |
+                           reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+    const long long nvec = aligned ? (n >> 2) : 0;
+    for (long long i = tid; i < nvec; i += stride) {
+        const float4 pv = reinterpret_cast<const float4*>(p)[i];
+        const float4 gv = __ldg(reinterpret_cast<const float4*>(g) + i);
+        float4 mv = reinterpret_cast<float4*>(m)[i], vv = reinterpret_cast<float4*>(v)[i];
+        float4 r;
+        r.x = adam_step(pv.x, gv.x, mv.x, vv.x, c); r.y = adam_step(pv.y, gv.y, mv.y, vv.y, c);
+        r.z = adam_step(pv.z, gv.z, mv.z, vv.z, c); r.w = adam_step(pv.w, gv.w, mv.w, vv.w, c);
+        reinterpret_cast<float4*>(m)[i] = mv;
+        reinterpret_cast<float4*>(v)[i] = vv;
+        reinterpret_cast<float4*>(out)[i] = r;
+    }
+    for (long long i = (nvec << 2) + tid; i < n; i += stride) {
+        float mi = m[i], vi = v[i];
+        out[i] = adam_step(p[i], g[i], mi, vi, c);
+        m[i] = mi; v[i] = vi;
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -77,7 +119,7 @@ __global__ void __launch_bounds__(256) adam_kernel(const float* p, const float* 
 }
 
 static unsigned optim_blocks(Device* dev, long long n) {
-    long long blocks = (n + 255) / 256;
+    long long blocks = (n / 4 + 255) / 256 + 1;
     const long long cap = (long long)dev->prop.multiProcessorCount * 16;
     return (unsigned)std::max(1LL, std::min(blocks, cap));
 }

@@ -34,6 +34,14 @@ namespace eb200 {
 
 constexpr int SCAN_TILE = 8192;     // elements per tile of the two-pass form
 
+// The scan op as a template parameter (ROP >= 0: the plain cumsum / cummax / cummin / cumprod of one
+// operand, the common case) or read from the parameters (ROP < 0: every fused-map chain).  With the op
+// known at compile time the shuffle scan is a third of the instructions: the kernels are issue bound.
+template <int ROP> __device__ __forceinline__ float scan_comb(int rop, float a, float b) { return Red<ROP>::combine(a, b); }
+template <> __device__ __forceinline__ float scan_comb<-1>(int rop, float a, float b) { return red_combine(rop, a, b); }
+template <int ROP> __device__ __forceinline__ float scan_ident(int rop) { return Red<ROP>::identity(); }
+template <> __device__ __forceinline__ float scan_ident<-1>(int rop) { return red_identity(rop); }
+
 // One element of the row: map over the loads at linear index e (through the
 // operands' views, masked loads included).
 template <class F>
@@ -80,13 +88,13 @@ __device__ __forceinline__ void scan_vec4(const KParams& p, const long long* rid
 // Scans positions [pos0, pos1) of `row` with a group of T threads (a warp or the
 // whole 256-thread CTA), starting from `carry`; returns the carry after pos1.
 // `store` false only accumulates (the tile-total pass).
-template <class F, int T, bool STORE>
+template <class F, int T, bool STORE, int ROP>
 __device__ __forceinline__ float scan_segment(const KParams& p, const float* cl, long long row, long long pos0, long long pos1,
                                               float carry, float* smem) {
     const int rop = p.rop;
     const int lane = threadIdx.x % T;
     const int wlane = threadIdx.x & 31;
-    const float ident = red_identity(rop);
+    const float ident = scan_ident<ROP>(rop);
     long long ridx[KMAX_DIMS];
     if (p.vec == 4) {
         decompose(p, row * p.rlen, ridx);          // index of the row's first element; the tail dim is 0
@@ -101,15 +109,15 @@ __device__ __forceinline__ float scan_segment(const KParams& p, const float* cl,
 #pragma unroll
             for (int j = 0; j < 4; ++j) x[j] = my + j < pos1 ? scan_elem<F>(p, row * p.rlen + my + j, cl) : ident;
         }
-        x[1] = red_combine(rop, x[0], x[1]);
-        x[2] = red_combine(rop, x[1], x[2]);
-        x[3] = red_combine(rop, x[2], x[3]);
+        x[1] = scan_comb<ROP>(rop, x[0], x[1]);
+        x[2] = scan_comb<ROP>(rop, x[1], x[2]);
+        x[3] = scan_comb<ROP>(rop, x[2], x[3]);
         // inclusive scan of the thread totals across the warp
         float incl = x[3];
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
             const float t = __shfl_up_sync(0xffffffffu, incl, o);
-            if (wlane >= o) incl = red_combine(rop, t, incl);
+            if (wlane >= o) incl = scan_comb<ROP>(rop, t, incl);
         }
         float excl = __shfl_up_sync(0xffffffffu, incl, 1);
         if (wlane == 0) excl = ident;
@@ -125,34 +133,34 @@ __device__ __forceinline__ float scan_segment(const KParams& p, const float* cl,
 #pragma unroll
             for (int w = 0; w < T / 32; ++w) {
                 const float t = smem[w];
-                if (w < warp) before = red_combine(rop, before, t);
-                total = red_combine(rop, total, t);
+                if (w < warp) before = scan_comb<ROP>(rop, before, t);
+                total = scan_comb<ROP>(rop, total, t);
             }
             __syncthreads();
-            excl = red_combine(rop, before, excl);
+            excl = scan_comb<ROP>(rop, before, excl);
         }
         if (STORE && my < pos1) {
-            const float base = red_combine(rop, carry, excl);
+            const float base = scan_comb<ROP>(rop, carry, excl);
             if (p.vec == 4) {
                 float* o = reinterpret_cast<float*>(p.out.ptr) + operand_index(p, p.out, ridx) + my;
-                *reinterpret_cast<float4*>(o) = make_float4(red_combine(rop, base, x[0]), red_combine(rop, base, x[1]),
-                                                            red_combine(rop, base, x[2]), red_combine(rop, base, x[3]));
+                *reinterpret_cast<float4*>(o) = make_float4(scan_comb<ROP>(rop, base, x[0]), scan_comb<ROP>(rop, base, x[1]),
+                                                            scan_comb<ROP>(rop, base, x[2]), scan_comb<ROP>(rop, base, x[3]));
             } else {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     if (my + j >= pos1) break;
                     long long idx[KMAX_DIMS];
                     decompose(p, row * p.rlen + my + j, idx);
-                    store_elem(p.out, operand_index(p, p.out, idx), red_combine(rop, base, x[j]));
+                    store_elem(p.out, operand_index(p, p.out, idx), scan_comb<ROP>(rop, base, x[j]));
                 }
             }
         }
-        carry = red_combine(rop, carry, total);
+        carry = scan_comb<ROP>(rop, carry, total);
     }
     return carry;
 }
 
-template <class F, int T>
+template <class F, int T, int ROP>
 __global__ void __launch_bounds__(256) scan_rows_kernel(const __grid_constant__ KParams p) {
     __shared__ float smem[8];
     float cl[F::kNconst];
@@ -163,12 +171,12 @@ __global__ void __launch_bounds__(256) scan_rows_kernel(const __grid_constant__ 
     for (long long blk = blockIdx.x; blk < nblk; blk += gridDim.x) {
         const long long row = blk * ROWS + sub;
         // T == 256: the whole CTA walks one row (barriers inside are uniform); T == 32: a warp per row
-        if (row < p.kept) scan_segment<F, T, true>(p, cl, row, 0, p.rlen, red_identity(p.rop), smem);
+        if (row < p.kept) scan_segment<F, T, true, ROP>(p, cl, row, 0, p.rlen, scan_ident<ROP>(p.rop), smem);
     }
 }
 
 // grid = (tiles, rows): total of every tile
-template <class F>
+template <class F, int ROP>
 __global__ void __launch_bounds__(256) scan_tile_total_kernel(const __grid_constant__ KParams p, float* __restrict__ totals, int tiles) {
     __shared__ float smem[8];
     float cl[F::kNconst];
@@ -176,13 +184,13 @@ __global__ void __launch_bounds__(256) scan_tile_total_kernel(const __grid_const
     const long long row = blockIdx.y;
     const long long pos0 = (long long)blockIdx.x * SCAN_TILE;
     const long long pos1 = min(pos0 + SCAN_TILE, p.rlen);
-    const float t = scan_segment<F, 256, false>(p, cl, row, pos0, pos1, red_identity(p.rop), smem);
+    const float t = scan_segment<F, 256, false, ROP>(p, cl, row, pos0, pos1, scan_ident<ROP>(p.rop), smem);
     if (threadIdx.x == 0) totals[row * tiles + blockIdx.x] = t;
 }
 
 // grid = (tiles, rows): fold the totals of the tiles before this one (in tile
 // order, so every CTA of a row sees the same prefixes), then scan the tile
-template <class F>
+template <class F, int ROP>
 __global__ void __launch_bounds__(256) scan_tile_apply_kernel(const __grid_constant__ KParams p, const float* __restrict__ totals, int tiles) {
     __shared__ float smem[8];
     __shared__ float prefix_s;
@@ -204,7 +212,7 @@ __global__ void __launch_bounds__(256) scan_tile_apply_kernel(const __grid_const
     __syncthreads();
     const long long pos0 = (long long)blockIdx.x * SCAN_TILE;
     const long long pos1 = min(pos0 + SCAN_TILE, p.rlen);
-    scan_segment<F, 256, true>(p, cl, row, pos0, pos1, prefix_s, smem);
+    scan_segment<F, 256, true, ROP>(p, cl, row, pos0, pos1, prefix_s, smem);
 }
 
 long long scan_scratch_floats(const KParams& p, int sms) {
@@ -213,7 +221,7 @@ long long scan_scratch_floats(const KParams& p, int sms) {
     return p.kept * ((p.rlen + SCAN_TILE - 1) / SCAN_TILE);
 }
 
-template <class F>
+template <class F, int ROP>
 static int launch_scan_one(Device* dev, const Plan& plan, const KParams& p, float* scratch) {
     const int sms = dev->prop.multiProcessorCount;
     if (p.kept <= 0 || p.rlen <= 0) return EB200_OK;
@@ -222,9 +230,9 @@ static int launch_scan_one(Device* dev, const Plan& plan, const KParams& p, floa
         const int tiles = (int)((p.rlen + SCAN_TILE - 1) / SCAN_TILE);
         EB_REQUIRE(p.kept <= 65535, EB200_ERR_UNSUPPORTED, "tiled scan over %lld rows", p.kept);
         dim3 grid((unsigned)tiles, (unsigned)p.kept);
-        scan_tile_total_kernel<F><<<grid, 256, 0, dev->stream>>>(p, scratch, tiles);
+        scan_tile_total_kernel<F, ROP><<<grid, 256, 0, dev->stream>>>(p, scratch, tiles);
         count_launch();
-        scan_tile_apply_kernel<F><<<grid, 256, 0, dev->stream>>>(p, scratch, tiles);
+        scan_tile_apply_kernel<F, ROP><<<grid, 256, 0, dev->stream>>>(p, scratch, tiles);
         count_launch();
         EB_CHECK_CUDA(cudaGetLastError());
         return EB200_OK;
@@ -233,8 +241,8 @@ static int launch_scan_one(Device* dev, const Plan& plan, const KParams& p, floa
     const long long rows_per = warp_rows ? 8 : 1;
     long long blocks = (p.kept + rows_per - 1) / rows_per;
     blocks = std::min<long long>(blocks, (long long)sms * 8);
-    if (warp_rows) scan_rows_kernel<F, 32><<<(unsigned)blocks, 256, 0, dev->stream>>>(p);
-    else scan_rows_kernel<F, 256><<<(unsigned)blocks, 256, 0, dev->stream>>>(p);
+    if (warp_rows) scan_rows_kernel<F, 32, ROP><<<(unsigned)blocks, 256, 0, dev->stream>>>(p);
+    else scan_rows_kernel<F, 256, ROP><<<(unsigned)blocks, 256, 0, dev->stream>>>(p);
     count_launch();
     EB_CHECK_CUDA(cudaGetLastError());
     return EB200_OK;
@@ -242,11 +250,19 @@ static int launch_scan_one(Device* dev, const Plan& plan, const KParams& p, floa
 
 int launch_scan(Device* dev, const Plan& plan, const KParams& p, void* scratch) {
     float* s = reinterpret_cast<float*>(scratch);
+    if (plan.chain == 0) {          // the identity map: the scan op is a template parameter
+        switch (p.rop) {
+            case EB200_R_SUM: return launch_scan_one<Compiled<Chain0>, EB200_R_SUM>(dev, plan, p, s);
+            case EB200_R_MAX: return launch_scan_one<Compiled<Chain0>, EB200_R_MAX>(dev, plan, p, s);
+            case EB200_R_MIN: return launch_scan_one<Compiled<Chain0>, EB200_R_MIN>(dev, plan, p, s);
+            default: return launch_scan_one<Compiled<Chain0>, EB200_R_PROD>(dev, plan, p, s);
+        }
+    }
     switch (plan.chain) {
-#define X(i) case i: return launch_scan_one<Compiled<Chain##i>>(dev, plan, p, s);
+#define X(i) case i: return launch_scan_one<Compiled<Chain##i>, -1>(dev, plan, p, s);
         EB_FOR_EACH_CHAIN(X)
 #undef X
-        default: return launch_scan_one<Interp>(dev, plan, p, s);
+        default: return launch_scan_one<Interp, -1>(dev, plan, p, s);
     }
 }
 
