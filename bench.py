@@ -620,7 +620,7 @@ def extra_measurements(reg, dev, ranks, comm, quick=False):
             flops = 2.0 * max(batch, 1) * m * k_ * n
             tf = flops / ms / 1e9
             gemm[f"{name}_{mname}"] = {"impl": kern.impl, "ms": ms, "tflops": tf,
-                                       "frac_of_tf32_peak": tf * (3 if mode == D.GEMM_3XTF32 else 1) / tf32_peak,
+                                       "frac_of_tf32_peak": tf * (3 if mode == D.GEMM_3XTF32 else 1) / (tf32_peak * (world if sharded else 1)),
                                        "per_gpu": f"A,C rows {ml} of {m}, B replicated" if not batch else f"batches {bs} of {batch}",
                                        "n_gpus": world if sharded else 1}
         for b_ in (ba, bb, bo):

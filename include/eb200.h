@@ -321,7 +321,10 @@ int eb200_kernel_release(eb200_kernel* k);
  * split needs more fails with EB200_ERR_UNSUPPORTED before anything launches.
  * The first call on a device looks up that array's device address; make that
  * first call outside any stream capture.  All calls share the array: two calls
- * whose kernels overlap on the GPU (different streams) race on it. */
+ * whose kernels overlap on the GPU (different streams) race on it.  The device
+ * that owns x, out and `stream` must be the calling thread's current device
+ * (cudaSetDevice): the scratch array is looked up, and the kernels are
+ * launched, on the current device. */
 int eb200_reduce_cols_static(const float* x, int64_t rows, int64_t cols, int reduce_op,
                              float* out, void* stream);
 /* ---- collectives.  No counterpart in the reference (it has no distributed code: no collective

@@ -39,7 +39,9 @@ def static_path(dev, bx, rows, cols, op, registry):
     return bo.read_vec()
 
 
-@pytest.mark.parametrize("rows,cols", [(4096, 512), (777, 130)])
+# besides a regular shape: a ragged one (cols not a multiple of 4: scalar path), one column of many
+# rows (every split holds one partial), and one row (nothing to reduce; the copy must still be exact)
+@pytest.mark.parametrize("rows,cols", [(4096, 512), (777, 130), (200000, 1), (1, 4096), (5000, 130)])
 def test_static_scratch_reduce_matches_regular_path_twice(dev, registry, rows, cols):
     rng = np.random.default_rng(99)
     for call in range(2):                                 # two calls in a row share the scratch
