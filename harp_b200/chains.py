@@ -78,7 +78,7 @@ def _model_chains():
         def compile(self, d): return None
 
     out = []
-    for tag, (loss, ps, grads, _) in (("mlp", W.mlp_graph(8, 8)), ("cnn", W.cnn_graph(2)), ("cnnf", W.cnn_graph(2, fused_conv=True))):
+    for tag, (loss, ps, grads, _) in (("mlp", W.mlp_graph(8, 8)), ("cnn", W.cnn_graph(2)), ("cnnf", W.cnn_graph(2, fused_conv=True, fused_pool=False)), ("cnnp", W.cnn_graph(2, fused_conv=True))):
         prog = Program([loss], _Null(), fuse="chains", sgd=list(zip(ps, grads)), lr=0.1)
         for i, d in enumerate(prog.kernel_descs()):
             if d.map is None or d.kclass not in (D.K_ELEMENTWISE, D.K_REDUCE):

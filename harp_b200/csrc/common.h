@@ -162,6 +162,7 @@ enum Impl {
     IMPL_ADAM,            // Adam step with device-resident moments and step counter
     IMPL_SOFTMAX_XENT,    // log-softmax + cross-entropy, loss and logits gradient in one kernel
     IMPL_SIBLINGS,        // row reduce + column max + transposing copy of one [R, C] tensor in one pass
+    IMPL_MAXPOOL,         // max_pool2d (stride = window) forward or gradient, optional fused ReLU
 };
 
 struct GemmShape {
@@ -175,7 +176,7 @@ struct GemmShape {
     int splits = 1;            // split-K: partial products go to scratch and are summed by a second kernel
     long long k_chunk = 0;     // k extent per split (multiple of 32)
     long long partial_off = 0; // float offset of the partials inside the kernel's scratch
-    int convert = 0;           // 3xTF32: hi / lo split inside the kernel (1) or by a pre-pass into scratch copies (0); fixed at plan time
+    int convert = 0;           // 3xTF32: bit 0 / bit 1 = A / B split into hi / lo inside the kernel; a clear bit = by a pre-pass into scratch copies; fixed at plan time
 };
 
 struct ConvShape {
@@ -200,6 +201,8 @@ struct Plan {
     ConvShape conv;
     bool narrow = false;          // outer reduce with few kept elements: column threads x row lanes
     long long sib_rows = 0, sib_cols = 0;   // IMPL_SIBLINGS: the shared [R, C] operand
+    long long pool[4] = {0, 0, 0, 0};       // IMPL_MAXPOOL: planes, H, W, window
+    int pool_flags = 0;                     // IMPL_MAXPOOL: 1 = ReLU on the taps, 2 = gradient
     TransposeShape tr;
     int64_t scratch_bytes = 0;
     bool scratch_zero = false;    // the scratch must start at zero (set once, at kernel creation)
@@ -238,13 +241,14 @@ int launch_adam(Device* dev, const Plan& plan, const float* p, const float* g, f
 int launch_softmax_xent(Device* dev, const Plan& plan, const float* logits, const float* onehot, float* out, void* scratch);
 long long scan_scratch_floats(const KParams& p, int sms);
 long long siblings_scratch_floats(long long R, long long C);
+int launch_maxpool(Device* dev, const Plan& plan, const float* a, const float* b, const float* c, float* out);
 int launch_siblings(Device* dev, const Plan& plan, const KParams& p, const float* x, float* out, void* scratch);
 int launch_scan(Device* dev, const Plan& plan, const KParams& p, void* scratch);
 int launch_gemm_simt(Device* dev, const Plan& plan, const float* a, const float* b, float* c, void* scratch);
 int launch_splitk_reduce(Device* dev, const GemmShape& g, const float* partials, float* c);
 bool gemm_tc_supported(const GemmShape& g);
 void gemm_tc_scratch(const GemmShape& g, long long* a_span, long long* b_span);
-bool gemm_tc_convert(const GemmShape& g, int flags);
+int gemm_tc_convert(const GemmShape& g, int flags);
 int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b, float* c, void* scratch);
 bool gemm_tall_supported(const GemmShape& g);
 int launch_gemm_tall(Device* dev, const Plan& plan, const float* a, const float* b, float* c, void* scratch);

@@ -47,7 +47,8 @@ struct TcParams {
     int raster;        // tile rows per band
     int tiles_n;
     int ks;            // two-CTA kernel: 32-wide k blocks per pipeline stage (2 halves the barrier round trips per MMA)
-    int convert;       // one-CTA kernel, 3xTF32: TMA brings the raw f32 tiles, the epilogue warps split them into hi / lo in shared memory
+    int convert;       // one-CTA kernel, 3xTF32: bit 0 / bit 1 = TMA brings the raw f32 tiles of A / of B and the epilogue warps
+                       // split them into hi / lo in shared memory (an operand without its bit comes pre-split from scratch copies)
     int nh;            // (unused by the persistent pair kernel; kept at 1)
     int total_tiles;   // persistent pair kernel: pair tiles over all batches and splits, band padding included
     int tiles_per_z;   // ... per batch x split slot
@@ -99,6 +100,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // which lo tiles TMA brings from pre-split copies (the others are made here from the raw tile)
+    const bool lo_a = q.three_pass && !(q.convert & 1), lo_b = q.three_pass && !(q.convert & 2);
 
     // The producer and the MMA warp run their loops as whole warps and elect one lane to
     // issue: TMA and tcgen05.mma take their descriptors and coordinates from uniform
@@ -112,7 +115,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], phase ^ 1u, q.error_flag))) break;
             if (elect_one()) {
                 unsigned char* st = smem + (size_t)s * stage_bytes;
-                mbar_expect_tx(&full_bar[s], q.convert ? (unsigned)(TC_TILE_BYTES + B_TILE_BYTES) : (unsigned)stage_bytes);
+                mbar_expect_tx(&full_bar[s], (unsigned)((lo_a ? 2 : 1) * TC_TILE_BYTES + (lo_b ? 2 : 1) * B_TILE_BYTES));
                 const int kx = (kb_begin + kb) * TC_BK;
                 unsigned char* a_hi = st;
                 unsigned char* b_hi = st + (q.three_pass ? 2 : 1) * TC_TILE_BYTES;   // [A hi | A lo | B hi | B lo]
@@ -121,22 +124,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                     for (int j = 0; j < TC_BM / 32; ++j) {
                         tma_load_3d(a_hi + j * 4096, &map_a, &full_bar[s], (int)m0 + j * 32, kx, bz * a_zmul);
-                        if (q.three_pass && !q.convert) tma_load_3d(st + TC_TILE_BYTES + j * 4096, &map_alo, &full_bar[s], (int)m0 + j * 32, kx, bz * a_zmul);
+                        if (lo_a) tma_load_3d(st + TC_TILE_BYTES + j * 4096, &map_alo, &full_bar[s], (int)m0 + j * 32, kx, bz * a_zmul);
                     }
                 } else {
                     tma_load_3d(a_hi, &map_a, &full_bar[s], kx, (int)m0, bz * a_zmul);
-                    if (q.three_pass && !q.convert) tma_load_3d(st + TC_TILE_BYTES, &map_alo, &full_bar[s], kx, (int)m0, bz * a_zmul);
+                    if (lo_a) tma_load_3d(st + TC_TILE_BYTES, &map_alo, &full_bar[s], kx, (int)m0, bz * a_zmul);
                 }
                 if (q.b_nmajor) {
                     // four [32 k][32 n] boxes side by side along n
 #pragma unroll
                     for (int j = 0; j < TC_BN / 32; ++j) {
                         tma_load_3d(b_hi + j * 4096, &map_b, &full_bar[s], (int)n0 + j * 32, kx, bz * b_zmul);
-                        if (q.three_pass && !q.convert) tma_load_3d(b_hi + B_TILE_BYTES + j * 4096, &map_blo, &full_bar[s], (int)n0 + j * 32, kx, bz * b_zmul);
+                        if (lo_b) tma_load_3d(b_hi + B_TILE_BYTES + j * 4096, &map_blo, &full_bar[s], (int)n0 + j * 32, kx, bz * b_zmul);
                     }
                 } else {
                     tma_load_3d(b_hi, &map_b, &full_bar[s], kx, (int)n0, bz * b_zmul);
-                    if (q.three_pass && !q.convert) tma_load_3d(b_hi + B_TILE_BYTES, &map_blo, &full_bar[s], kx, (int)n0, bz * b_zmul);
+                    if (lo_b) tma_load_3d(b_hi + B_TILE_BYTES, &map_blo, &full_bar[s], kx, (int)n0, bz * b_zmul);
                 }
             }
             __syncwarp();
@@ -193,6 +196,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 float4* al = reinterpret_cast<float4*>(st + TC_TILE_BYTES);
                 float4* bh = reinterpret_cast<float4*>(st + 2 * TC_TILE_BYTES);
                 float4* bl = reinterpret_cast<float4*>(st + 2 * TC_TILE_BYTES + B_TILE_BYTES);
+                if (q.convert & 1)
 #pragma unroll 4
                 for (int i = ct; i < TC_TILE_BYTES / 16; i += 128) {
                     const float4 t = ah[i];
@@ -204,6 +208,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     ah[i] = h;
                     al[i] = make_float4(t.x - h.x, t.y - h.y, t.z - h.z, t.w - h.w);
                 }
+                if (q.convert & 2)
 #pragma unroll 4
                 for (int i = ct; i < B_TILE_BYTES / 16; i += 128) {
                     const float4 t = bh[i];
@@ -564,13 +569,20 @@ static long long span_of(long long batch, long long sb, long long rows, long lon
 // 3xTF32 with the hi / lo split done inside the kernel (no scratch copies, no extra passes over the
 // operands): for contractions that are short on arithmetic per operand byte, where the two pre-split
 // passes cost more than the MMAs (an MLP layer [65536, 256] x [256, 256]: 64 flop per byte).
-bool gemm_tc_convert(const GemmShape& g, int flags) {
-    if (g.mode != EB200_GEMM_3XTF32) return false;
-    if (flags & 4096) return false;      // descriptor flag bit 12: always split in a pre-pass
-    if (flags & 8192) return true;       // descriptor flag bit 13: always split inside the kernel
+// Returns 0 (both operands pre-split), 3 (both split in the kernel) or 1 (A split in the kernel, B pre-split:
+// when B is a small matrix every row tile re-reads -- a layer's weights -- one tiny pre-pass over it removes two
+// thirds of the shared-memory traffic the in-kernel split costs per k block).
+int gemm_tc_convert(const GemmShape& g, int flags) {
+    if (g.mode != EB200_GEMM_3XTF32) return 0;
+    if (flags & 4096) return 0;          // descriptor flag bit 12: always split in a pre-pass
+    if (flags & 8192) return 3;          // descriptor flag bit 13: always split inside the kernel
     const double flops = 2.0 * (double)g.batch * g.m * g.n * g.k;
     const double bytes = 4.0 * (double)g.batch * ((double)g.m * g.k + (double)g.k * g.n + (double)g.m * g.n);
-    return flops / bytes < 200.0;
+    if (flops / bytes >= 200.0) return 0;
+    long long a_span, b_span;
+    gemm_tc_scratch(g, &a_span, &b_span);
+    if (g.splits == 1 && b_span <= (1LL << 20) && b_span * 16 <= a_span) return 1;
+    return 3;
 }
 
 void gemm_tc_scratch(const GemmShape& g, long long* a_span, long long* b_span) {
@@ -591,24 +603,31 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
     EB_REQUIRE((reinterpret_cast<uintptr_t>(a_src) & 15) == 0 && (reinterpret_cast<uintptr_t>(b_src) & 15) == 0,
                EB200_ERR_INVALID, "GEMM operands must be 16-byte aligned");
     const float *a_hi = a_src, *a_lo = a_src, *b_hi = b_src, *b_lo = b_src;
-    const bool convert = g.convert != 0;
-    if (three && !convert) {
+    const int convert = three ? g.convert : 0;       // bit 0 / 1: A / B split inside the kernel
+    if (three && convert != 3) {
         EB_REQUIRE(scratch, EB200_ERR_INVALID, "3xTF32 launched without scratch");
         long long a_span, b_span;
         gemm_tc_scratch(g, &a_span, &b_span);
         float* s = reinterpret_cast<float*>(scratch);
-        float *ah = s, *al = s + a_span, *bh = s + 2 * a_span, *bl = s + 2 * a_span + b_span;
         const long long cap = (long long)dev->prop.multiProcessorCount * 16;
-        long long blocks = std::min(cap, (a_span / 4 + 255) / 256 + 1);
-        const long long as = a_mmajor ? span_of(g.batch, g.a_sb, g.k, g.a_sk, g.m) : span_of(g.batch, g.a_sb, g.m, g.a_sm, g.k);
-        split_tf32_kernel<<<(unsigned)blocks, 256, 0, dev->stream>>>(a_src, ah, al, as);
-        count_launch();
-        blocks = std::min(cap, (b_span / 4 + 255) / 256 + 1);
-        const long long bs = b_nmajor ? span_of(g.batch, g.b_sb, g.k, g.b_sk, g.n) : span_of(g.batch, g.b_sb, g.n, g.b_sn, g.k);
-        split_tf32_kernel<<<(unsigned)blocks, 256, 0, dev->stream>>>(b_src, bh, bl, bs);
-        count_launch();
+        if (!(convert & 1)) {
+            float *ah = s, *al = s + a_span;
+            s += 2 * a_span;
+            const long long blocks = std::min(cap, (a_span / 4 + 255) / 256 + 1);
+            const long long as = a_mmajor ? span_of(g.batch, g.a_sb, g.k, g.a_sk, g.m) : span_of(g.batch, g.a_sb, g.m, g.a_sm, g.k);
+            split_tf32_kernel<<<(unsigned)blocks, 256, 0, dev->stream>>>(a_src, ah, al, as);
+            count_launch();
+            a_hi = ah; a_lo = al;
+        }
+        if (!(convert & 2)) {
+            float *bh = s, *bl = s + b_span;
+            const long long blocks = std::min(cap, (b_span / 4 + 255) / 256 + 1);
+            const long long bs = b_nmajor ? span_of(g.batch, g.b_sb, g.k, g.b_sk, g.n) : span_of(g.batch, g.b_sb, g.n, g.b_sn, g.k);
+            split_tf32_kernel<<<(unsigned)blocks, 256, 0, dev->stream>>>(b_src, bh, bl, bs);
+            count_launch();
+            b_hi = bh; b_lo = bl;
+        }
         EB_CHECK_CUDA(cudaGetLastError());
-        a_hi = ah; a_lo = al; b_hi = bh; b_lo = bl;
     }
     CUtensorMap ma, mal, mb, mbl;
     const long long a_b = g.a_sb > 0 ? g.batch : 1, b_b = g.b_sb > 0 ? g.batch : 1;
@@ -645,7 +664,7 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
         q.c_off = 0; q.c_sm = g.n; q.c_sn = 1; q.c_sb = g.m * g.n;
     }
     q.three_pass = three ? 1 : 0;
-    q.convert = convert ? 1 : 0;
+    q.convert = convert;
     q.ks = 1;
     q.nh = 1;
     // two-CTA pairs (256 x 256 per pair) when there are enough pair tiles to fill the machine

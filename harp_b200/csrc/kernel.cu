@@ -58,7 +58,7 @@ static void fill_info(const Plan& plan, eb200_kernel_info* info) {
     strncpy(info->impl, plan.name, sizeof(info->impl) - 1);
     info->launches = plan.launches;
     info->specialised = plan.chain >= 0 || plan.impl == IMPL_TRANSPOSE || plan.impl == IMPL_SCATTER ||
-                        plan.impl == IMPL_SGD || plan.impl == IMPL_SGD_MOMENTUM || plan.impl == IMPL_ADAM || plan.impl == IMPL_SOFTMAX_XENT || plan.impl == IMPL_GEMM_SIMT || plan.impl == IMPL_GEMM_TC || plan.impl == IMPL_CONV2D || plan.impl == IMPL_GEMM_TALL || plan.impl == IMPL_CONV2D_WGRAD || plan.impl == IMPL_CONV2D_DIRECT || plan.impl == IMPL_CONV2D_DIRECT_WGRAD;
+                        plan.impl == IMPL_SGD || plan.impl == IMPL_SGD_MOMENTUM || plan.impl == IMPL_ADAM || plan.impl == IMPL_SOFTMAX_XENT || plan.impl == IMPL_MAXPOOL || plan.impl == IMPL_GEMM_SIMT || plan.impl == IMPL_GEMM_TC || plan.impl == IMPL_CONV2D || plan.impl == IMPL_GEMM_TALL || plan.impl == IMPL_CONV2D_WGRAD || plan.impl == IMPL_CONV2D_DIRECT || plan.impl == IMPL_CONV2D_DIRECT_WGRAD;
     info->scratch_bytes = plan.scratch_bytes;
     info->algo_bytes = plan.algo_bytes;
     info->algo_flops = plan.algo_flops;
@@ -156,6 +156,11 @@ int eb200_kernel_launch(eb200_kernel* k, eb200_buffer* const* inputs, int n_inpu
         case IMPL_SIBLINGS:
             return launch_siblings(dev, plan, p, reinterpret_cast<const float*>(p.in[0].ptr) + p.in[0].offset,
                                    reinterpret_cast<float*>(p.out.ptr) + p.out.offset, scratch);
+        case IMPL_MAXPOOL:
+            return launch_maxpool(dev, plan, reinterpret_cast<const float*>(p.in[0].ptr) + p.in[0].offset,
+                                  p.n_in > 1 ? reinterpret_cast<const float*>(p.in[1].ptr) + p.in[1].offset : nullptr,
+                                  p.n_in > 2 ? reinterpret_cast<const float*>(p.in[2].ptr) + p.in[2].offset : nullptr,
+                                  reinterpret_cast<float*>(p.out.ptr) + p.out.offset);
         case IMPL_SOFTMAX_XENT:
             return launch_softmax_xent(dev, plan, reinterpret_cast<const float*>(p.in[0].ptr) + p.in[0].offset,
                                        reinterpret_cast<const float*>(p.in[1].ptr) + p.in[1].offset,

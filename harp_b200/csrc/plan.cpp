@@ -237,7 +237,7 @@ bool try_gemm(const KParams& p, Plan* plan, int mode) {
 
 int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
     EB_REQUIRE(d && plan, EB200_ERR_INVALID, "null argument");
-    EB_REQUIRE(d->kclass >= EB200_K_ELEMENTWISE && d->kclass <= EB200_K_SOFTMAX_XENT, EB200_ERR_INVALID, "unknown kernel class %d", d->kclass);
+    EB_REQUIRE(d->kclass >= EB200_K_ELEMENTWISE && d->kclass <= EB200_K_MAXPOOL2D, EB200_ERR_INVALID, "unknown kernel class %d", d->kclass);
     if (d->kclass == EB200_K_CONV2D) {
         // structured descriptor: shape = {N, C, H, W, Co, KH, KW, pad}
         EB_REQUIRE(d->ndim == 8, EB200_ERR_INVALID, "conv2d descriptor wants 8 shape entries, got %d", d->ndim);
@@ -294,6 +294,42 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
         pl.algo_bytes = 4 * ((long long)c.N * c.C * c.H * c.W + (long long)c.Co * K + M * c.Co + (c.has_bias ? c.Co : 0));
         if (c.direct) snprintf(pl.name, sizeof(pl.name), "conv2d_direct_f32%s", c.wgrad ? "_wgrad" : (c.flip ? "_dgrad" : ""));
         else snprintf(pl.name, sizeof(pl.name), "conv2d_igemm_%s%s", c.mode == EB200_GEMM_TF32 ? "tf32" : "3xtf32", c.wgrad ? "_wgrad" : (c.flip ? "_dgrad" : ""));
+        return EB200_OK;
+    }
+    if (d->kclass == EB200_K_MAXPOOL2D) {
+        // structured descriptor: shape = {P, H, W, k}; forward x -> y, gradient (g, x, y) -> gx
+        const bool grad = (d->flags & 128) != 0;
+        EB_REQUIRE(d->ndim == 4 && d->n_inputs == (grad ? 3 : 1), EB200_ERR_INVALID,
+                   "max_pool2d takes shape {P, H, W, k} and %d input(s)", grad ? 3 : 1);
+        const long long P = d->shape[0], H = d->shape[1], W = d->shape[2], K = d->shape[3];
+        EB_REQUIRE(P >= 1 && K >= 1 && K <= 4 && H >= K && W >= K && H < 65536 && W < 65536 && P * H * W < (1LL << 40) &&
+                   P * ((H + K - 1) / K) * ((W + K - 1) / K) < (1LL << 31), EB200_ERR_UNSUPPORTED,
+                   "max_pool2d over [%lld, %lld, %lld] with window %lld", P, H, W, K);
+        const long long full = P * H * W, pooled = P * (H / K) * (W / K);
+        Plan& pl = *plan;
+        pl = Plan();
+        memset(&pl.p, 0, sizeof(pl.p));
+        for (int i = 0; i <= d->n_inputs; ++i) {
+            const eb200_operand& o = i < d->n_inputs ? d->inputs[i] : d->output;
+            EB_REQUIRE(o.dtype == EB200_F32 && o.n_bounds == 0 && o.offset >= 0, EB200_ERR_UNSUPPORTED, "max_pool2d operands are plain contiguous f32 buffers");
+            const bool is_full = grad ? (i == 1 || i == d->n_inputs) : (i == 0);
+            EB_REQUIRE(o.numel - o.offset >= (is_full ? full : pooled), EB200_ERR_BOUNDS, "max_pool2d operand %d too small", i);
+            (i < d->n_inputs ? pl.p.in[i] : pl.p.out).offset = o.offset;
+        }
+        pl.p.shape[0] = P; pl.p.shape[1] = H; pl.p.shape[2] = W; pl.p.ndim = 3; pl.p.total = full; pl.p.n_in = d->n_inputs;
+        pl.impl = IMPL_MAXPOOL;
+        pl.pool[0] = P; pl.pool[1] = H; pl.pool[2] = W; pl.pool[3] = K;
+        pl.pool_flags = ((d->flags & 64) ? 1 : 0) | (grad ? 2 : 0);
+        pl.n_inputs = d->n_inputs;
+        for (int i = 0; i < d->n_inputs; ++i) { pl.in_dtype[i] = EB200_F32; pl.in_numel[i] = d->inputs[i].numel; pl.perm[i] = i; }
+        for (int j = 0; j < KMAX_CONSTS; ++j) pl.dyn_input[j] = -1;
+        pl.out_dtype = EB200_F32;
+        pl.out_numel = d->output.numel;
+        pl.launches = 1;
+        // forward: the covered part of x once, y once; gradient: g, y, the covered part of x in, gx out
+        const long long covered = P * (H / K) * K * (W / K) * K;
+        pl.algo_bytes = 4 * (grad ? 2 * pooled + covered + full : covered + pooled);
+        snprintf(pl.name, sizeof(pl.name), "maxpool2d_k%lld%s%s", K, (d->flags & 64) ? "_relu" : "", grad ? "_grad" : "");
         return EB200_OK;
     }
     if (d->kclass == EB200_K_SOFTMAX_XENT) {
@@ -791,12 +827,13 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
                 if (tc) {
                     pl.impl = IMPL_GEMM_TC;
                     const bool three = g.mode == EB200_GEMM_3XTF32;
-                    g.convert = gemm_tc_convert(g, d->flags) ? 1 : 0;
-                    if (three && !g.convert) {
+                    g.convert = gemm_tc_convert(g, d->flags);
+                    if (three && g.convert != 3) {
+                        // hi / lo copies of every operand that is not split inside the kernel, one pre-pass each
                         long long a_span, b_span;
                         gemm_tc_scratch(g, &a_span, &b_span);
-                        scratch_floats = 2 * a_span + 2 * b_span;
-                        pl.launches = 3;
+                        if (!(g.convert & 1)) { scratch_floats += 2 * a_span; pl.launches += 1; }
+                        if (!(g.convert & 2)) { scratch_floats += 2 * b_span; pl.launches += 1; }
                     }
                     // name: arithmetic mode, then which dim of A and of B is contiguous (k, m / k, n)
                     snprintf(pl.name, sizeof(pl.name), "gemm_tcgen05_%s_%c%c%s", three ? "3xtf32" : "tf32",

@@ -35,10 +35,12 @@ DTYPE_NP = {F32: "float32", BOOL: "uint8", I32: "int32", I64: "int64"}
 
 # eb200_kclass
 K_ELEMENTWISE, K_REDUCE, K_COPY, K_SCATTER, K_SGD, K_CONV2D, K_SCAN, K_SGD_MOMENTUM, K_ADAM, K_SOFTMAX_XENT = 0, 1, 2, 3, 4, 5, 6, 7, 8, 9
+K_MAXPOOL2D = 10
 KCLASS_PREFIX = {K_ELEMENTWISE: "E", K_REDUCE: "R", K_COPY: "C", K_SCATTER: "S", K_SGD: "U", K_CONV2D: "CONV",
-                 K_SCAN: "P", K_SGD_MOMENTUM: "UM", K_ADAM: "UA", K_SOFTMAX_XENT: "XENT"}
+                 K_SCAN: "P", K_SGD_MOMENTUM: "UM", K_ADAM: "UA", K_SOFTMAX_XENT: "XENT", K_MAXPOOL2D: "POOL"}
 FLAG_RELU = 64
 FLAG_WFLIP = 128
+FLAG_POOL_GRAD = 128       # K_MAXPOOL2D: the gradient kernel
 FLAG_WGRAD = 256
 FLAG_NCHW = 512
 FLAG_G_NCHW = 1024
@@ -427,6 +429,18 @@ def softmax_xent(n: int, c: int, scale: float) -> KernelDesc:
     z2 = [0, 0]
     return KernelDesc(K_SOFTMAX_XENT, [n, c], [Operand(z2, 0, F32, n * c), Operand(z2, 0, F32, n * c)],
                       Operand(z2, 0, F32, XENT_GRAD_OFFSET + n * c), None, scalar=scale)
+
+
+def maxpool2d(p: int, h: int, w: int, k: int, relu: bool = False, grad: bool = False) -> KernelDesc:
+    """functional::max_pool2d with stride = window (crates/nn/src/functional/pool.rs:117-160)
+    over P = N*C planes as one kernel: x [P, H, W] -> y [P, H//k, W//k]; `relu`: the taps are
+    max(x, 0); `grad`: inputs g, x, y -> gx [P, H, W] (with `relu` the activation's gradient
+    mask is applied too)."""
+    z4 = [0] * 4
+    full, pooled = p * h * w, p * (h // k) * (w // k)
+    ins = [Operand(z4, 0, F32, pooled), Operand(z4, 0, F32, full), Operand(z4, 0, F32, pooled)] if grad else [Operand(z4, 0, F32, full)]
+    return KernelDesc(K_MAXPOOL2D, [p, h, w, k], ins, Operand(z4, 0, F32, full if grad else pooled), None,
+                      flags=(FLAG_RELU if relu else 0) | (FLAG_POOL_GRAD if grad else 0))
 
 
 def copy(shape, src: Operand, out: Optional[Operand] = None) -> KernelDesc:

@@ -632,6 +632,33 @@ class Tensor:
             y._parents.append((self, back))
         return y
 
+    def max_pool2d_fused(self, k: int, relu: bool = False) -> "Tensor":
+        """``max_pool2d`` (of ``relu(self)`` when `relu`) as ONE kernel, and its gradient --
+        through the ReLU as well -- as ONE kernel (EB200_K_MAXPOOL2D).  Values and gradients
+        equal ``self.relu().max_pool2d(k)`` and its autograd bit for bit (only comparisons and
+        selections are involved); what changes is the traffic: the strided-view spelling reads
+        its taps through four operands and needs a second full-size pass for the activation's
+        mask (and a third to zero-pad odd planes)."""
+        n, c, h, wd = self.shape
+        if k > 4 or h < k or wd < k:
+            return (self.relu() if relu else self).max_pool2d(k)
+        ho, wo = h // k, wd // k
+        xc = self.contiguous()
+        node = Node("pool", (n, c, ho, wo), [(xc.node, xc.view)], name="maxpool2d")
+        node.pool = (n * c, h, wd, k, bool(relu), False)
+        y = Tensor(node)
+        if self.requires_grad:
+            x_, y_ = Tensor(xc.node, xc.view), Tensor(node)
+
+            def back(g):
+                gc = g.contiguous()
+                gnode = Node("pool", (n, c, h, wd), [(gc.node, gc.view), (x_.node, x_.view), (y_.node, y_.view)], name="maxpool2d_grad")
+                gnode.pool = (n * c, h, wd, k, bool(relu), True)
+                return Tensor(gnode)
+            y.requires_grad = True
+            y._parents.append((self, back))
+        return y
+
     def log_softmax(self, axis=-1) -> "Tensor":
         """crates/nn/src/functional/activation.rs:174-187."""
         axis = axis % self.ndim
@@ -720,6 +747,7 @@ class _K:
         self.data = n.data
         self.conv = getattr(n, "conv", None)
         self.xent = getattr(n, "xent", None)
+        self.pool = getattr(n, "pool", None)
 
 
 def _dim_map(view: View, prod_shape):
@@ -943,6 +971,14 @@ def _lower(k: _K, loc) -> D.KernelDesc:
             op.strides = z8
         return D.KernelDesc(D.K_CONV2D, [n, c, h, wd, co, kh, kw, pad], ins, D.Operand(z8, out_off, D.F32, out_numel),
                             None, gemm_mode=mode, flags=(D.FLAG_RELU if relu else 0) | (D.FLAG_WFLIP if flip else 0) | (D.FLAG_WGRAD if wgrad else D.FLAG_NCHW) | (D.FLAG_G_NCHW if g_nchw else 0), name=k.name)
+    if k.kind == "pool":
+        planes, h, wd, win, relu, grad = k.pool
+        d = D.maxpool2d(planes, h, wd, win, relu, grad)
+        for op, src in zip(d.inputs, ins):
+            op.offset, op.numel = src.offset, src.numel
+        d.output.offset, d.output.numel = out_off, out_numel
+        d.name = k.name
+        return d
     if k.kind == "xent":
         n, c, scale = k.xent
         d = D.softmax_xent(n, c, scale)

@@ -114,12 +114,14 @@ def mlp_graph(batch: int = 65536, hidden: int = 256, seed: int = 3, weight_seed:
     return loss, ps, loss.backward(ps), (x, t)
 
 
-def cnn_graph(n: int = 4096, seed: int = 4, label_seed: int = 40, weight_seed: int = 41, fused_conv: bool = False):
+def cnn_graph(n: int = 4096, seed: int = 4, label_seed: int = 40, weight_seed: int = 41, fused_conv: bool = False,
+              fused_pool=None):
     """Config 4: MNIST-shaped CNN (conv 1->32 3x3, ReLU, maxpool 2, conv 32->64 3x3,
     ReLU, maxpool 2, flatten 1600, linear 128, ReLU, linear 10, softmax
     cross-entropy) on synthetic images uniform[0,1] and uniform labels; `fused_conv`
     selects this backend's forms of the same functions (one implicit-GEMM kernel per
-    convolution and per input gradient, pools over strided views) instead of the
+    convolution and per input gradient; ReLU + max-pool as one kernel each way, or with
+    ``fused_pool=False`` as elementwise kernels over strided views) instead of the
     reference's spelling; Kaiming
     normal weights from `weight_seed` (the reference's deterministic sin() init is
     not used), zero biases."""
@@ -136,7 +138,12 @@ def cnn_graph(n: int = 4096, seed: int = 4, label_seed: int = 40, weight_seed: i
     ps = [Tensor.input(v, requires_grad=True) for v in vals]
     x = Tensor.input(X)
     onehot = Tensor.input(np.eye(10, dtype=np.float32)[lab])       # built on the host, as loss.rs:43-51 does
-    if fused_conv:      # each convolution (and its input gradient) as one implicit-GEMM kernel
+    if fused_pool is None:
+        fused_pool = fused_conv
+    if fused_conv and fused_pool:   # each convolution (and its input gradient) as one implicit-GEMM kernel, ReLU + pool as one
+        h = x.conv2d_fused(ps[0], ps[1]).max_pool2d_fused(2, relu=True)
+        h = h.conv2d_fused(ps[2], ps[3]).max_pool2d_fused(2, relu=True)
+    elif fused_conv:
         h = x.conv2d_fused(ps[0], ps[1]).relu().max_pool2d(2)
         h = h.conv2d_fused(ps[2], ps[3]).relu().max_pool2d(2)
     else:               # the reference's spelling: pad, unfold, permute, contiguous, GEMM, bias; pools through unfold/fold

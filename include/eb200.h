@@ -91,6 +91,16 @@ typedef enum {
                               * output [64 + N*C]: element 0 = scalar * sum(onehot * log_softmax(logits)), elements
                               * 64.. = its gradient with respect to the logits, scalar * (onehot - softmax *
                               * rowsum(onehot)); scalar = the loss scale (-1/N for the mean) */
+    EB200_K_MAXPOOL2D = 10,  /* functional::max_pool2d with stride = window (crates/nn/src/functional/pool.rs:117-160: unfold,
+                              * max over the window) as one kernel, and its VJP as one kernel: shape = {P, H, W, k} with
+                              * P = N*C planes; forward: input x [P, H, W], output y [P, H/k, W/k] (floor: rows / columns
+                              * no window covers are not read), the window folded as max(max(t0, t1), ...) in row-major
+                              * tap order; flags bit 6 = the taps are max(x, 0) (a ReLU the function was applied to);
+                              * flags bit 7 = gradient: inputs g [P, H/k, W/k], x [P, H, W], y [P, H/k, W/k] (the forward
+                              * result), output gx [P, H, W] = (tap < y ? 0 : g) on covered elements (every element that
+                              * equals its window's maximum receives the gradient, the mask-times-gradient of
+                              * src/grad/rules.rs:379-399 folded back), 0 elsewhere; with bit 6 also the ReLU's own
+                              * gradient mask, gx = x < 0 ? 0 : gx.  All operands contiguous f32 */
     EB200_K_ADAM = 8         /* Adam::step (crates/nn/src/optim/adam.rs:104-147): inputs p, g, m, v and a one-element
                               * I32 step counter t; the output receives p; m, v and t are updated IN PLACE (t <- t + 1
                               * on the device, so a captured step can be replayed); scalar = lr, hyper[0..2] = beta1,

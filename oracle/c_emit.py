@@ -304,6 +304,45 @@ def emit_kernel_c(k: D.KernelDesc, fn_name: str = "kernel", openmp: bool = False
             line(f"out[{k.output.offset} + ((((ridx0 * {ho}) + ridx1) * {wo} + ridx2) * {co} + ridx3)] = {val};")
         for _ in range(4):
             close_loop()
+    elif k.kclass == D.K_MAXPOOL2D:
+        # max_pool2d with stride = window (crates/nn/src/functional/pool.rs:117-160): the window tensor
+        # unfold would materialise is read in place; the reduce over it is the R_ loop nest (acc = -inf,
+        # acc = fmaxf(acc, tap) in row-major window order, src/lowerer/loop_gen.rs:87-151).  Gradient:
+        # mask-times-gradient of the max reduce (src/grad/rules.rs:379-399) written where unfold's VJP
+        # (src/grad/rules.rs:40-53) would scatter it -- every element lies in at most one window --
+        # zero where no window covers the element, then the ReLU's mask when the taps were max(x, 0)
+        planes, h, w_, win = k.shape
+        ho, wo = h // win, w_ // win
+        relu = bool(k.flags & D.FLAG_RELU)
+        o = [op.offset for op in k.inputs]
+        if not (k.flags & D.FLAG_POOL_GRAD):
+            for d, e in enumerate((planes, ho, wo)):
+                open_loop(d, e)
+            line("float acc;")
+            line("acc = (-INFINITY);")
+            pragma_done[0] = True
+            open_loop(3, win); open_loop(4, win)
+            tap = f"buf0[{o[0]} + (((ridx0 * {h}) + ((ridx1 * {win}) + ridx3)) * {w_} + ((ridx2 * {win}) + ridx4))]"
+            if relu:
+                tap = f"fmaxf({tap}, 0.0f)"
+            line(f"acc = fmaxf(acc, {tap});")
+            close_loop(); close_loop()
+            line(f"out[{k.output.offset} + (((ridx0 * {ho}) + ridx1) * {wo} + ridx2)] = acc;")
+            for _ in range(3):
+                close_loop()
+        else:
+            for d, e in enumerate((planes, h, w_)):
+                open_loop(d, e)
+            xv = f"buf1[{o[1]} + (((ridx0 * {h}) + ridx1) * {w_} + ridx2)]"
+            win_i = f"(((ridx0 * {ho}) + (ridx1 / {win})) * {wo} + (ridx2 / {win}))"
+            tap = f"fmaxf({xv}, 0.0f)" if relu else xv
+            val = f"((({tap} < buf2[{o[2]} + {win_i}]) ? 0.0f : buf0[{o[0]} + {win_i}]))"
+            val = f"(((ridx1 < {ho * win}) && (ridx2 < {wo * win})) ? {val} : 0.0f)"
+            if relu:
+                val = f"(({xv} < 0.0f) ? 0.0f : {val})"
+            line(f"out[{k.output.offset} + (((ridx0 * {h}) + ridx1) * {w_} + ridx2)] = {val};")
+            for _ in range(3):
+                close_loop()
     elif k.kclass == D.K_SCAN:
         # generate_scan (src/lowerer/loop_gen.rs:237-327): loops before the axis outside, then
         # `acc = identity`, then the scan loop with the loops of the later dims INSIDE it; the body

@@ -163,6 +163,9 @@ def _check_kernel_against_oracle(d, ins, got, what):
         mag = O.run(d, _abs_inputs(ins))
         assert (np.abs(got.astype(np.float64) - ref) <= 1e-5 * mag + 1e-30).all(), what
         return "1e-5 sum|terms|"
+    if d.kclass == D.K_MAXPOOL2D:
+        assert got.tobytes() == _oracle(d, ins, got).tobytes(), what
+        return "bit-exact"
     if d.kclass == D.K_SOFTMAX_XENT:
         ref = _oracle(d, ins, got)
         assert abs(float(got[0]) - float(ref[0])) <= 1e-5 * abs(float(ref[0])), what
