@@ -27,6 +27,24 @@ __device__ __forceinline__ void load_vec4(const KParams& p, long long e, float (
         if (i >= n) break;
         const KOperand& o = p.in[i];
         const long long a = ND == 1 ? o.offset + e * o.strides[0] : operand_index<ND>(p, o, idx);
+        if (o.dtype != EB200_F32) {
+            // f16 / bf16 storage: four elements are one 64-bit load, widened to f32 here
+            if (o.strides[inner] == 1) {
+                const uint2 t = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const unsigned short*>(o.ptr) + a));
+                if (o.dtype == EB200_F16) {
+                    const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&t.x));
+                    const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&t.y));
+                    in[i][0] = lo.x; in[i][1] = lo.y; in[i][2] = hi.x; in[i][3] = hi.y;
+                } else {
+                    in[i][0] = __uint_as_float(t.x << 16); in[i][1] = __uint_as_float(t.x & 0xffff0000u);
+                    in[i][2] = __uint_as_float(t.y << 16); in[i][3] = __uint_as_float(t.y & 0xffff0000u);
+                }
+            } else {
+                const float t = load_elem(o, a);
+                in[i][0] = t; in[i][1] = t; in[i][2] = t; in[i][3] = t;
+            }
+            continue;
+        }
         const float* src = reinterpret_cast<const float*>(o.ptr) + a;
         if (o.strides[inner] == 1) {
             const float4 t = __ldg(reinterpret_cast<const float4*>(src));
@@ -48,7 +66,19 @@ __device__ __forceinline__ void store_vec4(const KParams& p, long long e, const 
         decompose<ND>(p, e, idx);
         a = operand_index<ND>(p, p.out, idx);
     }
-    *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out.ptr) + a) = make_float4(v[0], v[1], v[2], v[3]);
+    if (p.out.dtype == EB200_F32) {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out.ptr) + a) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+        uint2 t;
+        if (p.out.dtype == EB200_F16) {
+            *reinterpret_cast<__half2*>(&t.x) = __floats2half2_rn(v[0], v[1]);
+            *reinterpret_cast<__half2*>(&t.y) = __floats2half2_rn(v[2], v[3]);
+        } else {
+            *reinterpret_cast<__nv_bfloat162*>(&t.x) = __floats2bfloat162_rn(v[0], v[1]);
+            *reinterpret_cast<__nv_bfloat162*>(&t.y) = __floats2bfloat162_rn(v[2], v[3]);
+        }
+        *reinterpret_cast<uint2*>(reinterpret_cast<unsigned short*>(p.out.ptr) + a) = t;
+    }
 }
 
 template <class F, int ND>

@@ -14,6 +14,9 @@
 // yield 1 or 0; Select tests its condition against zero.
 #pragma once
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
 #include "common.h"
 
 namespace eb200 {
@@ -49,6 +52,8 @@ __device__ __forceinline__ float op_idiv(float a, float b) {
 __device__ __forceinline__ float op_cast(float a, int dtype) {
     if (dtype == EB200_F32) return a;
     if (dtype == EB200_BOOL) return a != 0.0f ? 1.0f : 0.0f;
+    if (dtype == EB200_F16) return __half2float(__float2half_rn(a));
+    if (dtype == EB200_BF16) return __bfloat162float(__float2bfloat16_rn(a));
     return truncf(a);
 }
 
@@ -58,6 +63,8 @@ __device__ __forceinline__ float load_elem(const KOperand& o, long long idx) {
         case EB200_F32: return reinterpret_cast<const float*>(o.ptr)[idx];
         case EB200_BOOL: return (float)reinterpret_cast<const unsigned char*>(o.ptr)[idx];
         case EB200_I32: return (float)reinterpret_cast<const int*>(o.ptr)[idx];
+        case EB200_F16: return __half2float(reinterpret_cast<const __half*>(o.ptr)[idx]);
+        case EB200_BF16: return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(o.ptr)[idx]);
         default: return 0.0f;
     }
 }
@@ -67,6 +74,8 @@ __device__ __forceinline__ void store_elem(const KOperand& o, long long idx, flo
         case EB200_F32: reinterpret_cast<float*>(o.ptr)[idx] = v; break;
         case EB200_BOOL: reinterpret_cast<unsigned char*>(o.ptr)[idx] = (unsigned char)(v != 0.0f); break;
         case EB200_I32: reinterpret_cast<int*>(o.ptr)[idx] = (int)v; break;
+        case EB200_F16: reinterpret_cast<__half*>(o.ptr)[idx] = __float2half_rn(v); break;
+        case EB200_BF16: reinterpret_cast<__nv_bfloat16*>(o.ptr)[idx] = __float2bfloat16_rn(v); break;
         default: break;
     }
 }

@@ -38,6 +38,8 @@ int dtype_size(int dt) {
         case EB200_F32: return 4;
         case EB200_BOOL: return 1;
         case EB200_I32: return 4;
+        case EB200_F16: return 2;
+        case EB200_BF16: return 2;
         case EB200_I64: return 8;
     }
     return 0;
@@ -573,8 +575,10 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
     }
 
     // ---- 128-bit legality along the innermost collapsed dim
-    auto vec_ok = [&](const KOperand& ko, int inner, bool is_store) -> bool {
-        if (ko.dtype != EB200_F32 || ko.n_bounds) return false;
+    // (`half_ok`: the elementwise kernel also moves f16 / bf16 operands four at a time, with 64-bit accesses)
+    auto vec_ok = [&](const KOperand& ko, int inner, bool is_store, bool half_ok = false) -> bool {
+        const bool dt_ok = ko.dtype == EB200_F32 || (half_ok && (ko.dtype == EB200_F16 || ko.dtype == EB200_BF16));
+        if (!dt_ok || ko.n_bounds) return false;
         long long s = ko.strides[inner];
         if (s == 0) return !is_store;
         if (s != 1) return false;
@@ -753,8 +757,8 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
                 snprintf(pl.name, sizeof(pl.name), "transpose_copy");
             } else {
                 int inner = nk - 1;
-                bool v = nk >= 1 && shape[inner] % 4 == 0 && vec_ok(p.out, inner, true);
-                for (int i = 0; v && i < p.n_in; ++i) v = vec_ok(p.in[i], inner, false);
+                bool v = nk >= 1 && shape[inner] % 4 == 0 && vec_ok(p.out, inner, true, true);
+                for (int i = 0; v && i < p.n_in; ++i) v = vec_ok(p.in[i], inner, false, true);
                 p.vec = v ? 4 : 1;
                 snprintf(pl.name, sizeof(pl.name), "ew_chain_v%d", p.vec);
                 if (!v && nk >= 2 && total % 4 == 0 && total >= 1024) {

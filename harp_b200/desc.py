@@ -20,6 +20,8 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+
+import numpy as np
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence, Tuple
 
@@ -29,9 +31,20 @@ MAX_BOUNDS = 4
 MAX_INSNS = 96
 
 # eb200_dtype
-F32, BOOL, I32, I64 = 0, 1, 2, 3
+F32, BOOL, I32, I64, F16, BF16 = 0, 1, 2, 3, 4, 5
 DTYPE_SIZE = {F32: 4, BOOL: 1, I32: 4, I64: 8}
-DTYPE_NP = {F32: "float32", BOOL: "uint8", I32: "int32", I64: "int64"}
+DTYPE_NP = {F32: "float32", BOOL: "uint8", I32: "int32", I64: "int64", F16: "float16", BF16: "uint16"}   # bf16 travels as its bits
+
+
+def bf16_bits(a) -> "np.ndarray":
+    """float32 -> bfloat16 bit patterns (uint16), round to nearest even (finite values)."""
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def bf16_value(bits) -> "np.ndarray":
+    """bfloat16 bit patterns (uint16) -> float32."""
+    return (np.ascontiguousarray(bits, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
 
 # eb200_kclass
 K_ELEMENTWISE, K_REDUCE, K_COPY, K_SCATTER, K_SGD, K_CONV2D, K_SCAN, K_SGD_MOMENTUM, K_ADAM, K_SOFTMAX_XENT = 0, 1, 2, 3, 4, 5, 6, 7, 8, 9

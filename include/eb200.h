@@ -52,8 +52,12 @@ typedef enum {
     EB200_F32 = 0,
     EB200_BOOL = 1,
     EB200_I32 = 2,
-    EB200_I64 = 3
+    EB200_I64 = 3,
+    EB200_F16 = 4,    /* IEEE binary16, the reference's `_Float16` (crates/backend-c/src/renderer.rs:129) */
+    EB200_BF16 = 5    /* bfloat16, the reference's `__bf16` (crates/backend-c/src/renderer.rs:130) */
 } eb200_dtype;
+/* 16-bit types are STORAGE types: elements are widened to f32 when loaded, all arithmetic and every
+ * accumulator is f32, results are rounded to nearest even when stored. */
 
 /* Kernel classes the lowerer emits (src/lowerer/lower.rs:335-388). */
 typedef enum {

@@ -55,7 +55,8 @@ from harp_b200 import desc as D
 _CACHE_DIR = os.environ.get(
     "EB200_ORACLE_CACHE", os.path.join(os.path.dirname(os.path.abspath(__file__)), "_build"))
 
-C_TYPE = {D.F32: "float", D.BOOL: "unsigned char", D.I32: "int", D.I64: "long long"}
+C_TYPE = {D.F32: "float", D.BOOL: "unsigned char", D.I32: "int", D.I64: "long long",
+          D.F16: "_Float16", D.BF16: "__bf16"}      # crates/backend-c/src/renderer.rs:129-130
 
 HEADER = """/* Generated C code by Harp */
 /* This code is pure C99 without parallelization */

@@ -1,0 +1,88 @@
+"""f16 / bf16 storage on the GPU against the oracle's `_Float16` / `__bf16` kernels.
+
+Tolerance: one unit in the last place of the STORED type for an elementwise result (the reference's
+C computes the chain in the 16-bit type's promoted arithmetic, this library in f32 with one rounding
+at the store), 1e-5 of the sum of magnitudes for f32-accumulated sums; comparisons, selections,
+maxima and plain casts are exact."""
+import numpy as np
+import pytest
+
+from harp_b200 import desc as D
+from harp_b200.desc import Ast
+from oracle import c_emit as O
+from test_half import as_f32, half_inputs, ulp
+from util import run_gpu
+
+pytestmark = pytest.mark.gpu
+w = Ast.w
+
+
+def close(got, ref, dt, what):
+    g, r = as_f32(got, dt).astype(np.float64), as_f32(ref, dt).astype(np.float64)
+    assert (np.abs(g - r) <= ulp(dt) * np.abs(r) + 1e-30).all(), what
+
+
+@pytest.mark.parametrize("shape", [(512, 1024), (37, 1023), (4, 6, 260), (2048, 4096)])
+@pytest.mark.parametrize("dts", [(D.F16, D.F16, D.F16), (D.BF16, D.BF16, D.BF16), (D.BF16, D.F32, D.F16), (D.F16, D.BF16, D.F32)])
+def test_elementwise_over_16_bit_storage(dev, shape, dts):
+    da, db, do = dts
+    a, b = half_inputs(shape, da, 1), half_inputs(shape, db, 2)
+    shape = list(shape)
+    for name, m in (("add", w(0) + w(1)), ("fused", (w(0) * w(1) + 0.5).maximum(w(0))), ("select", Ast.select(w(0).lt(w(1)), w(0), w(1)))):
+        k = D.KernelDesc(D.K_ELEMENTWISE, shape, [D.contiguous(shape, da), D.contiguous(shape, db)], D.contiguous(shape, do), m)
+        got, kern = run_gpu(dev, k, [a, b])
+        assert kern.impl == ("ew_chain_v4" if int(np.prod(shape)) % 4 == 0 else "ew_chain_v1")     # contiguous operands collapse to one dim
+        ref = O.run(k, [a, b])
+        if name == "select":
+            assert got.tobytes() == ref.tobytes(), (name, dts)
+        else:
+            close(got, ref, do, (name, dts))
+
+
+@pytest.mark.parametrize("dt", [D.F16, D.BF16])
+def test_broadcast_strided_and_masked_16_bit_operands(dev, dt):
+    x, bias = half_inputs((96, 200), dt, 3), half_inputs((200,), dt, 4)
+    # bias broadcast along rows, x read transposed, output f32
+    k = D.KernelDesc(D.K_ELEMENTWISE, [200, 96], [D.Operand([1, 200], 0, dt, 96 * 200), D.Operand([1, 0], 0, dt, 200)],
+                     D.contiguous([200, 96]), w(0) + w(1))
+    got, _ = run_gpu(dev, k, [x, bias])
+    ref = (as_f32(x, dt).reshape(96, 200).T + as_f32(bias, dt)[:, None]).astype(np.float32)
+    assert got.tobytes() == O.run(k, [x, bias]).tobytes() == ref.reshape(-1).tobytes()     # one f32 addition of exactly widened values
+    # padded view: zeros around a [96, 200] block
+    src = D.Operand([200, 1], -(2 * 200 + 3), dt, 96 * 200,
+                    bounds=[D.Bound([1, 0], -2, 0, 96), D.Bound([0, 1], -3, 0, 200)])
+    k = D.KernelDesc(D.K_ELEMENTWISE, [100, 208], [src], D.contiguous([100, 208], dt), w(0) * 2.0)
+    got, _ = run_gpu(dev, k, [x])
+    assert got.tobytes() == O.run(k, [x]).tobytes()          # doubling is exact
+
+
+@pytest.mark.parametrize("dt", [D.F16, D.BF16])
+def test_reductions_accumulate_in_f32(dev, dt):
+    x = half_inputs((300, 1000), dt, 5)
+    xf = as_f32(x, dt).reshape(300, 1000).astype(np.float64)
+    for axis in (0, 1):
+        k = D.reduce([300, 1000], [D.contiguous([300, 1000], dt)], w(0) * w(0), D.R_SUM, axis)
+        got, kern = run_gpu(dev, k, [x])
+        ref = O.run(k, [x])
+        bound = 1e-5 * (xf * xf).sum(axis)
+        assert (np.abs(got - ref) <= bound).all() and (np.abs(got - (xf * xf).sum(axis)) <= bound).all(), kern.impl
+        # max keeps the storage type and is exact
+        kept = [1 if d == axis else e for d, e in enumerate([300, 1000])]
+        st = D.contiguous_strides(kept)
+        st[axis] = 0
+        k = D.reduce([300, 1000], [D.contiguous([300, 1000], dt)], w(0), D.R_MAX, axis, out=D.Operand(st, 0, dt, 1000 if axis == 0 else 300))
+        got, _ = run_gpu(dev, k, [x])
+        assert (as_f32(got, dt) == as_f32(x, dt).reshape(300, 1000).max(axis)).all()
+
+
+def test_cast_rounds_like_the_storage_type(dev):
+    x = np.random.default_rng(6).standard_normal(4096).astype(np.float32) * 100
+    for dt in (D.F16, D.BF16):
+        k = D.KernelDesc(D.K_ELEMENTWISE, [4096], [D.contiguous([4096])], D.contiguous([4096]), w(0).cast(dt))
+        got, _ = run_gpu(dev, k, [x])
+        ref = x.astype(np.float16).astype(np.float32) if dt == D.F16 else D.bf16_value(D.bf16_bits(x))
+        assert got.tobytes() == ref.tobytes()
+        # and storing through a 16-bit output is the same rounding
+        k = D.KernelDesc(D.K_ELEMENTWISE, [4096], [D.contiguous([4096])], D.contiguous([4096], dt), w(0) * 1.0)
+        got, _ = run_gpu(dev, k, [x])
+        assert as_f32(got, dt).tobytes() == ref.tobytes()
