@@ -794,7 +794,8 @@ def misc_kernel_measurements(reg, dev, rng, hbm, quick=False):
 def run_only_small(args):
     """`--only gemm`: the tensor-core contraction on a 4096 x 2048 x 4096 case; `--only cfg2`: the
     config 2 kernels and the one-pass sibling form on a [4096, 8192] block; `--only kernels`: the
-    kernel classes of misc_kernel_measurements (small cases for profiler captures)."""
+    kernel classes of misc_kernel_measurements; `--only mlp` / `--only cnn`: the kernels of one training
+    step of config 3 / of config 4's 512-image shard (small cases for profiler captures)."""
     from harp_b200 import desc as D
     from harp_b200 import workloads as W
     from harp_b200.backend import B200BackendRegistry
@@ -830,6 +831,19 @@ def run_only_small(args):
             bo.release()
         print(json.dumps({"only": "cfg2", "rows": rows, "kernels": res}))
         return
+    if args.only in ("mlp", "cnn"):
+        # one training step of config 3 (batch 65536) / config 4 (batch 512), kernel by kernel, no graph:
+        # every buffer is at most 67 MB, so a profiler capture of a few launches stays small
+        from harp_b200.frontend import B200Executor, Program
+        ex = B200Executor(dev, reg)
+        loss, ps, grads, _ = W.mlp_graph(65536, 256) if args.only == "mlp" else W.cnn_graph(512, fused_conv=True)
+        prog = Program([loss], ex, sgd=list(zip(ps, grads)), lr=1e-3, persistent=True, flat=True)
+        for _ in range(2):
+            prog.run()
+        dev.synchronize()
+        print(json.dumps({"only": args.only, "kernels": [k.impl for _, _, k, _ in prog.kernels], "table_us": kernel_table(dev, prog, reps=3),
+                          "loss": float(prog.fetch(loss))}))
+        return
     print(json.dumps({"only": "kernels", "kernels": misc_kernel_measurements(reg, dev, rng, hbm, quick=True)}))
 
 
@@ -843,7 +857,7 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="only config 2 (skip matmul / MLP / CNN measurements)")
     ap.add_argument("--z-allreduce", default="async", choices=["async", "fused"],
                     help="multi-GPU: how the column-max partials are combined (side-stream all-reduce, or fused into the reduce's finish pass)")
-    ap.add_argument("--only", default="", choices=["", "conv2d", "conv2d_grad", "gemm", "kernels", "cfg2"],
+    ap.add_argument("--only", default="", choices=["", "conv2d", "conv2d_grad", "gemm", "kernels", "cfg2", "mlp", "cnn"],
                     help="run one small kernel case alone (profiler captures); prints no bench line")
     args = ap.parse_args()
     if args.only in ("conv2d", "conv2d_grad"):

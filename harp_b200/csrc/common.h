@@ -176,6 +176,8 @@ struct GemmShape {
     int splits = 1;            // split-K: partial products go to scratch and are summed by a second kernel
     long long k_chunk = 0;     // k extent per split (multiple of 32)
     long long partial_off = 0; // float offset of the partials inside the kernel's scratch
+    int half = 0;              // 0: f32 operands; EB200_F16 / EB200_BF16: 16-bit operands (tcgen05 kind::f16, f32 accumulate)
+    int c_dtype = EB200_F32;   // storage type of C (f32, or the operands' 16-bit type)
     int convert = 0;           // 3xTF32: bit 0 / bit 1 = A / B split into hi / lo inside the kernel; a clear bit = by a pre-pass into scratch copies; fixed at plan time
 };
 

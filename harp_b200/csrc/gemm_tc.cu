@@ -30,6 +30,9 @@
 
 #include <algorithm>
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
 #include "tc_ptx.cuh"
 
 namespace eb200 {
@@ -50,6 +53,9 @@ struct TcParams {
     int convert;       // one-CTA kernel, 3xTF32: bit 0 / bit 1 = TMA brings the raw f32 tiles of A / of B and the epilogue warps
                        // split them into hi / lo in shared memory (an operand without its bit comes pre-split from scratch copies)
     int nh;            // (unused by the persistent pair kernel; kept at 1)
+    int half;          // 0: f32 operands (kind::tf32); EB200_F16 / EB200_BF16: 16-bit operands (kind::f16), pair kernel only
+    int bke;           // elements of k per 128-byte block: 32 (f32) or 64 (16-bit)
+    int c_dtype;       // storage type of C
     int total_tiles;   // persistent pair kernel: pair tiles over all batches and splits, band padding included
     int tiles_per_z;   // ... per batch x split slot
     int* error_flag;
@@ -288,6 +294,18 @@ __device__ __forceinline__ void umma_tf32_pair(uint32_t d_tmem, uint64_t a_desc,
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 // arrives on the mbarrier at this offset in both CTAs of the pair once the MMAs so far are done
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// instruction descriptor for kind::f16: f32 accumulator, A and B both f16 (0) or both bf16 (1), K-major
+__device__ __forceinline__ uint32_t umma_idesc_f16(int M, int N, bool bf16) {
+    const uint32_t fmt = bf16 ? 1u : 0u;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
 __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
                  ::"r"(smem_u32(bar)), "h"((unsigned short)3) : "memory");
@@ -346,7 +364,7 @@ __device__ __forceinline__ PairTile decode_pair_tile(const TcParams& q, int t, u
     p.bz = z / q.splits;
     p.zslot = z;
     const int split = z - p.bz * q.splits;
-    const int total_kb = (int)((q.k + TC_BK - 1) / TC_BK);
+    const int total_kb = (int)((q.k + q.bke - 1) / q.bke);
     p.kb_begin = split * q.kb_per_split;
     p.num_kb = min(total_kb - p.kb_begin, q.kb_per_split);
     return p;
@@ -400,7 +418,7 @@ gemm_tc2p_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     const uint32_t lead = map_to_cta(smem_u32(&full_bar[s]), 0);
                     if (rank == 0) mbar_expect_tx(&full_bar[s], 2u * (unsigned)stage_bytes);
                     unsigned char* st = smem + (size_t)s * stage_bytes;
-                    const int kx = (p.kb_begin + kb) * TC_BK;
+                    const int kx = (p.kb_begin + kb) * q.bke;
                     unsigned char* b_hi = st + (q.three_pass ? 2 : 1) * TC_TILE_BYTES;
                     if (q.a_mmajor) {
 #pragma unroll
@@ -429,7 +447,7 @@ gemm_tc2p_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     } else if (warp == 1) {
         if (rank == 0) {
             // ---- MMA issuer (even CTA) ----
-            const uint32_t idesc = umma_idesc_tf32(256, 256, q.a_mmajor, q.b_nmajor);
+            const uint32_t idesc = q.half ? umma_idesc_f16(256, 256, q.half == EB200_BF16) : umma_idesc_tf32(256, 256, q.a_mmajor, q.b_nmajor);
             const uint32_t a_lbo = q.a_mmajor ? 4096 : 16, a_sbo = q.a_mmajor ? 512 : 1024, a_layout = q.a_mmajor ? 1 : 2;
             const uint32_t b_lbo = q.b_nmajor ? 4096 : 16, b_sbo = q.b_nmajor ? 512 : 1024, b_layout = q.b_nmajor ? 1 : 2;
             const uint64_t a_jstep = (q.a_mmajor ? 1024u : (unsigned)(TC_UK * 4)) >> 4;
@@ -458,7 +476,9 @@ gemm_tc2p_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
                         for (int j = 0; j < TC_BK / TC_UK; ++j) {
                             const uint64_t da = da0 + j * a_jstep, db = db0 + j * b_jstep;
-                            umma_tf32_pair(acc, da, db, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                            // (a 128-byte row holds four K = 8 steps of f32 or four K = 16 steps of f16 / bf16: same descriptors)
+                            if (q.half) umma_f16_pair(acc, da, db, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                            else umma_tf32_pair(acc, da, db, idesc, (kb > 0 || j > 0) ? 1u : 0u);
                             if (q.three_pass) {
                                 umma_tf32_pair(acc, dal0 + j * a_jstep, db, idesc, 1u);
                                 umma_tf32_pair(acc, da, dbl0 + j * b_jstep, idesc, 1u);
@@ -486,13 +506,43 @@ gemm_tc2p_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if (!mbar_wait_warp(&acc_full[a], aphase, q.error_flag)) break;
             tc_fence_after();
             const long long row = p.m0 + quarter * 32 + lane;
-            float* crow = C + q.c_off + (long long)(q.splits > 1 ? p.zslot : p.bz) * q.c_sb + row * q.c_sm;
+            const long long crow_off = q.c_off + (long long)(q.splits > 1 ? p.zslot : p.bz) * q.c_sb + row * q.c_sm;
+            float* crow = C + crow_off;
 #pragma unroll 1
             for (int c = 0; c < 8; ++c) {
                 float v[32];
                 tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(a * 256 + c * 32), v);
                 const long long col0 = p.n0 + c * 32;
                 if (row >= q.m || col0 >= q.n) continue;
+                if (q.c_dtype != EB200_F32) {
+                    // C stored in the operands' 16-bit type: round to nearest even at the store
+                    unsigned short* d16 = reinterpret_cast<unsigned short*>(C) + crow_off + col0 * q.c_sn;
+                    if (q.c_sn == 1 && col0 + 32 <= q.n && (reinterpret_cast<uintptr_t>(d16) & 15) == 0) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 w;
+                            if (q.c_dtype == EB200_F16) {
+                                *reinterpret_cast<__half2*>(&w.x) = __floats2half2_rn(v[i], v[i + 1]);
+                                *reinterpret_cast<__half2*>(&w.y) = __floats2half2_rn(v[i + 2], v[i + 3]);
+                                *reinterpret_cast<__half2*>(&w.z) = __floats2half2_rn(v[i + 4], v[i + 5]);
+                                *reinterpret_cast<__half2*>(&w.w) = __floats2half2_rn(v[i + 6], v[i + 7]);
+                            } else {
+                                *reinterpret_cast<__nv_bfloat162*>(&w.x) = __floats2bfloat162_rn(v[i], v[i + 1]);
+                                *reinterpret_cast<__nv_bfloat162*>(&w.y) = __floats2bfloat162_rn(v[i + 2], v[i + 3]);
+                                *reinterpret_cast<__nv_bfloat162*>(&w.z) = __floats2bfloat162_rn(v[i + 4], v[i + 5]);
+                                *reinterpret_cast<__nv_bfloat162*>(&w.w) = __floats2bfloat162_rn(v[i + 6], v[i + 7]);
+                            }
+                            *reinterpret_cast<uint4*>(d16 + i) = w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (col0 + i < q.n)
+                                d16[i * q.c_sn] = q.c_dtype == EB200_F16 ? __half_as_ushort(__float2half_rn(v[i]))
+                                                                         : __bfloat16_as_ushort(__float2bfloat16_rn(v[i]));
+                    }
+                    continue;
+                }
                 float* dst = crow + col0 * q.c_sn;
                 if (q.c_sn == 1 && col0 + 32 <= q.n && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
@@ -545,6 +595,15 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const float* __restrict
 
 // Whether the tensor-core kernel can take this contraction (plan.cpp asks).
 bool gemm_tc_supported(const GemmShape& g) {
+    if (g.half) {
+        // 16-bit operands: both contiguous along k; TMA wants 16-byte aligned rows (8 elements)
+        auto mult8 = [](long long v) { return (v & 7) == 0; };
+        if (g.a_sk != 1 || g.b_sk != 1 || g.a_sm <= 0 || g.b_sn <= 0) return false;
+        if (!mult8(g.a_sm) || !mult8(g.a_sb) || !mult8(g.a_off) || !mult8(g.b_sn) || !mult8(g.b_sb) || !mult8(g.b_off)) return false;
+        if (g.batch < 1 || g.batch > 65535 || (g.batch > 1 && (g.a_sb < 0 || g.b_sb < 0))) return false;
+        if (g.m < 1 || g.n < 1 || g.k < 1 || g.m >= (1LL << 31) || g.n >= (1LL << 31) || g.k >= (1LL << 31)) return false;
+        return true;
+    }
     const bool a_kmajor = g.a_sk == 1, a_mmajor = g.a_sm == 1;
     if (!a_kmajor && !a_mmajor) return false;
     const bool b_kmajor = g.b_sk == 1, b_nmajor = g.b_sn == 1;
@@ -573,7 +632,7 @@ static long long span_of(long long batch, long long sb, long long rows, long lon
 // when B is a small matrix every row tile re-reads -- a layer's weights -- one tiny pre-pass over it removes two
 // thirds of the shared-memory traffic the in-kernel split costs per k block).
 int gemm_tc_convert(const GemmShape& g, int flags) {
-    if (g.mode != EB200_GEMM_3XTF32) return 0;
+    if (g.mode != EB200_GEMM_3XTF32 || g.half) return 0;
     if (flags & 4096) return 0;          // descriptor flag bit 12: always split in a pre-pass
     if (flags & 8192) return 3;          // descriptor flag bit 13: always split inside the kernel
     const double flops = 2.0 * (double)g.batch * g.m * g.n * g.k;
@@ -593,8 +652,67 @@ void gemm_tc_scratch(const GemmShape& g, long long* a_span, long long* b_span) {
     *b_span = (b + 63) / 64 * 64;
 }
 
+// 16-bit operands (f16 / bf16), both contiguous along k, f32 accumulation in tensor memory: the persistent pair
+// kernel with tcgen05.mma.kind::f16.  A 128-byte swizzled row holds 64 elements of k, so a k block is 64 deep and
+// every stage feeds four K = 16 MMAs; everything else (ring, double-buffered accumulator, epilogue) is shared
+// with the f32 path.  C is f32 or the operands' type.
+static int launch_gemm_tc_half(Device* dev, const GemmShape& g, const float* a, const float* b, float* c) {
+    const unsigned short* a_src = reinterpret_cast<const unsigned short*>(a) + g.a_off;
+    const unsigned short* b_src = reinterpret_cast<const unsigned short*>(b) + g.b_off;
+    EB_REQUIRE((reinterpret_cast<uintptr_t>(a_src) & 15) == 0 && (reinterpret_cast<uintptr_t>(b_src) & 15) == 0,
+               EB200_ERR_INVALID, "GEMM operands must be 16-byte aligned");
+    const CUtensorMapDataType dt = g.half == EB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUtensorMap ma, mb;
+    const long long a_b = g.a_sb > 0 ? g.batch : 1, b_b = g.b_sb > 0 ? g.batch : 1;
+    int st;
+    if ((st = make_map16(&ma, a_src, dt, g.k, g.m, a_b, g.a_sm, g.a_sb, 128))) return st;
+    if ((st = make_map16(&mb, b_src, dt, g.k, g.n, b_b, g.b_sn, g.b_sb, 128))) return st;
+    TcParams q{};
+    q.m = g.m; q.n = g.n; q.k = g.k;
+    q.c_sm = g.c_sm; q.c_sn = g.c_sn; q.c_sb = g.c_sb; q.c_off = g.c_off;
+    q.splits = 1;
+    q.half = g.half; q.bke = 64; q.c_dtype = g.c_dtype;
+    q.kb_per_split = (int)((g.k + 63) / 64);
+    q.ks = 1; q.nh = 1;
+    q.error_flag = dev->error_flag_dev;
+    q.raster = 8;
+    if (!dev->tc_configured) {
+        EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc2p_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        dev->tc_configured = true;
+    }
+    const int stage_bytes = 2 * TC_TILE_BYTES;
+    q.stages = std::min(8, (196 * 1024) / stage_bytes);
+    const size_t smem = (size_t)q.stages * stage_bytes + 1024 + 256;
+    const long long tm2 = (g.m + 255) / 256, tn2 = (g.n + 255) / 256;
+    const long long bands = (tm2 + q.raster - 1) / q.raster;
+    q.tiles_n = (int)tn2;
+    const long long per_z = bands * q.raster * tn2, total = per_z * g.batch;
+    EB_REQUIRE(total < (1LL << 31), EB200_ERR_UNSUPPORTED, "too many GEMM tiles");
+    q.tiles_per_z = (int)per_z;
+    q.total_tiles = (int)total;
+    const long long pairs = std::min<long long>(total, dev->prop.multiProcessorCount / 2);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(pairs * 2), 1, 1);
+    cfg.blockDim = dim3(TC_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = dev->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const int az = g.a_sb > 0 ? 1 : 0, bzm = g.b_sb > 0 ? 1 : 0;
+    EB_CHECK_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc2p_kernel, ma, ma, mb, mb, q, c, az, bzm));
+    count_launch();
+    EB_CHECK_CUDA(cudaGetLastError());
+    return EB200_OK;
+}
+
 int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b, float* c, void* scratch) {
     const GemmShape& g = plan.gemm;
+    if (g.half) return launch_gemm_tc_half(dev, g, a, b, c);
     const bool three = g.mode == EB200_GEMM_3XTF32;
     const bool b_nmajor = !(g.b_sk == 1);
     const bool a_mmajor = !(g.a_sk == 1);
@@ -664,6 +782,7 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
         q.c_off = 0; q.c_sm = g.n; q.c_sn = 1; q.c_sb = g.m * g.n;
     }
     q.three_pass = three ? 1 : 0;
+    q.half = 0; q.bke = TC_BK; q.c_dtype = EB200_F32;
     q.convert = convert;
     q.ks = 1;
     q.nh = 1;

@@ -198,7 +198,11 @@ bool try_gemm(const KParams& p, Plan* plan, int mode) {
     if (ia == ib) return false;
     const KOperand* A = &p.in[ia];
     const KOperand* B = &p.in[ib];
-    if (A->dtype != EB200_F32 || B->dtype != EB200_F32 || p.out.dtype != EB200_F32) return false;
+    // f32 x f32 -> f32, or f16 x f16 / bf16 x bf16 -> f32 or the operands' own type (the reference's F16 MatMul node,
+    // src/lowerer/lower.rs:745-1000, accumulating in f32)
+    const bool half = A->dtype == EB200_F16 || A->dtype == EB200_BF16;
+    if (A->dtype != B->dtype || (!half && A->dtype != EB200_F32)) return false;
+    if (p.out.dtype != EB200_F32 && !(half && p.out.dtype == A->dtype)) return false;
     if (A->n_bounds || B->n_bounds) return false;
     if (A->strides[p.raxis] == 0 || B->strides[p.raxis] == 0) return false;
     int dm = -1, dn = -1, db = -1;
@@ -214,6 +218,8 @@ bool try_gemm(const KParams& p, Plan* plan, int mode) {
     GemmShape g;
     g.mode = mode == EB200_GEMM_DEFAULT ? EB200_GEMM_3XTF32 : mode;
     g.a_input = ia; g.b_input = ib;
+    g.half = half ? A->dtype : 0;
+    g.c_dtype = p.out.dtype;
     g.m = p.shape[dm]; g.n = p.shape[dn]; g.k = p.shape[p.raxis];
     g.batch = db >= 0 ? p.shape[db] : 1;
     g.a_sm = A->strides[dm]; g.a_sk = A->strides[p.raxis]; g.a_sb = db >= 0 ? A->strides[db] : 0; g.a_off = A->offset;
@@ -231,6 +237,8 @@ bool try_gemm(const KParams& p, Plan* plan, int mode) {
         t.c_sm = g.c_sn; t.c_sn = g.c_sm;
         g = t;
     }
+    // 16-bit operands are served by the tensor-core kernel only, and only with both operands contiguous along k
+    if (g.half && !gemm_tc_supported(g)) return false;
     plan->gemm = g;
     return true;
 }
@@ -809,14 +817,14 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
                 // is more than a few tiles of work; f32 FFMA tiles otherwise
                 const bool force_simt = (d->flags & 8) != 0;
                 GemmShape& g = pl.gemm;
-                const bool tc = !force_simt && gemm_tc_supported(g) && pl.algo_flops >= (1LL << 22);
+                const bool tc = g.half || (!force_simt && gemm_tc_supported(g) && pl.algo_flops >= (1LL << 22));
                 // split-K when the output has too few tiles to fill the machine
                 // (weight gradients: small M x N, K = batch)
                 {
                     const long long tm = tc ? 128 : 64, tn = tc ? 128 : 64;
                     const long long tiles = ((g.m + tm - 1) / tm) * ((g.n + tn - 1) / tn) * g.batch;
                     const long long kblocks = (g.k + 31) / 32;
-                    if (tiles < sm_count && kblocks >= 16 && (d->flags & 16) == 0) {
+                    if (tiles < sm_count && kblocks >= 16 && (d->flags & 16) == 0 && !g.half) {
                         long long s = std::min<long long>((2LL * sm_count + tiles - 1) / tiles, kblocks / 8);
                         s = std::min<long long>(s, 65535 / std::max<long long>(1, g.batch));
                         if (s > 1) {
@@ -830,7 +838,7 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
                 long long scratch_floats = 0;
                 if (tc) {
                     pl.impl = IMPL_GEMM_TC;
-                    const bool three = g.mode == EB200_GEMM_3XTF32;
+                    const bool three = g.mode == EB200_GEMM_3XTF32 && !g.half;
                     g.convert = gemm_tc_convert(g, d->flags);
                     if (three && g.convert != 3) {
                         // hi / lo copies of every operand that is not split inside the kernel, one pre-pass each
@@ -840,7 +848,8 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
                         if (!(g.convert & 2)) { scratch_floats += 2 * b_span; pl.launches += 1; }
                     }
                     // name: arithmetic mode, then which dim of A and of B is contiguous (k, m / k, n)
-                    snprintf(pl.name, sizeof(pl.name), "gemm_tcgen05_%s_%c%c%s", three ? "3xtf32" : "tf32",
+                    snprintf(pl.name, sizeof(pl.name), "gemm_tcgen05_%s_%c%c%s",
+                             g.half == EB200_F16 ? "f16" : g.half == EB200_BF16 ? "bf16" : three ? "3xtf32" : "tf32",
                              g.a_sk == 1 ? 'k' : 'm', g.b_sk == 1 ? 'k' : 'n', g.splits > 1 ? "_splitk" : "");
                 } else if (!force_simt && gemm_tall_supported(g) && (d->flags & 16) == 0) {
                     pl.impl = IMPL_GEMM_TALL;

@@ -176,6 +176,22 @@ static inline int make_map(CUtensorMap* map, const float* base, long long inner,
     return EB200_OK;
 }
 
+// 16-bit elements (f16 / bf16), K-major: boxes of 64 elements (one 128-byte swizzled row) x box_rows rows.
+static inline int make_map16(CUtensorMap* map, const void* base, CUtensorMapDataType dt, long long inner, long long rows, long long batch,
+                             long long row_stride, long long batch_stride, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    EB_REQUIRE(fn, EB200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)(batch > 0 ? batch : 1)};
+    cuuint64_t strides[2] = {(cuuint64_t)row_stride * 2, (cuuint64_t)(batch_stride > 0 ? batch_stride : row_stride * rows) * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    EB_REQUIRE(r == CUDA_SUCCESS, EB200_ERR_CUDA, "cuTensorMapEncodeTiled (16-bit) failed with %d (inner %lld rows %lld stride %lld)",
+               (int)r, inner, rows, row_stride);
+    return EB200_OK;
+}
+
 // General 3-D f32 tensor map without swizzle: dims/box innermost first, byte strides of dims 1 and 2.
 static inline int make_map_plain(CUtensorMap* map, const float* base, const cuuint64_t dims[3], const cuuint64_t strides[2],
                                  const cuuint32_t box[3]) {

@@ -32,7 +32,7 @@ MAX_INSNS = 96
 
 # eb200_dtype
 F32, BOOL, I32, I64, F16, BF16 = 0, 1, 2, 3, 4, 5
-DTYPE_SIZE = {F32: 4, BOOL: 1, I32: 4, I64: 8}
+DTYPE_SIZE = {F32: 4, BOOL: 1, I32: 4, I64: 8, F16: 2, BF16: 2}
 DTYPE_NP = {F32: "float32", BOOL: "uint8", I32: "int32", I64: "int64", F16: "float16", BF16: "uint16"}   # bf16 travels as its bits
 
 

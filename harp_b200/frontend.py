@@ -848,6 +848,39 @@ def _stack_depth(prog) -> int:
     return best
 
 
+def _fold_constants(e: Ast) -> Ast:
+    """Products and sums with several literal operands keep ONE: x*2*(-1)*log2(e) -> x*(-2 log2 e)
+    (eclat's AST optimiser folds constants the same way, src/opt/ast/rules.rs; under the reference's
+    `-ffast-math` the C compiler may reassociate them too).  Chains of `mul` / `add` are flattened,
+    their literals combined in f32, the other operands kept in order."""
+    if not e.args:
+        return e
+    if e.op not in ("mul", "add"):
+        return Ast(e.op, tuple(_fold_constants(a) for a in e.args), e.value)
+    terms, stack = [], [e]
+    while stack:
+        t = stack.pop()
+        if t.op == e.op:
+            stack.extend(reversed(t.args))
+        else:
+            terms.append(t)
+    ident = np.float32(1.0 if e.op == "mul" else 0.0)
+    c, rest = ident, []
+    for t in terms:
+        if t.op == "const":
+            c = np.float32(c * np.float32(t.value)) if e.op == "mul" else np.float32(c + np.float32(t.value))
+        else:
+            rest.append(_fold_constants(t))
+    if not rest:
+        return Ast.const(float(c))
+    out = rest[0]
+    for t in rest[1:]:
+        out = Ast(e.op, (out, t))
+    if c != ident or not np.isfinite(c):
+        out = Ast(e.op, (out, Ast.const(float(c))))
+    return out
+
+
 def _is_contraction(k: _K) -> bool:
     """sum over a product of two loads: what the planner serves as a GEMM.  Nothing is inlined
     into its operands (the pattern must survive)."""
@@ -941,6 +974,10 @@ def _fuse(ks: Dict[int, _K], order: List[int], roots: set, level: str):
             del ks[pid]
             changed = True
             break
+    if level == "chains":
+        for k in ks.values():
+            if k.kind in ("map", "reduce") and k.expr is not None and not _is_contraction(k):
+                k.expr = _fold_constants(k.expr)
 
 
 def _lower(k: _K, loc) -> D.KernelDesc:

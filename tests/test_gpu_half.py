@@ -86,3 +86,28 @@ def test_cast_rounds_like_the_storage_type(dev):
         k = D.KernelDesc(D.K_ELEMENTWISE, [4096], [D.contiguous([4096])], D.contiguous([4096], dt), w(0) * 1.0)
         got, _ = run_gpu(dev, k, [x])
         assert as_f32(got, dt).tobytes() == ref.tobytes()
+
+
+@pytest.mark.parametrize("m,n,k,batch", [(256, 256, 128, 1), (300, 200, 72, 1), (1024, 512, 4096, 1), (128, 256, 64, 4), (1, 8, 8, 1),
+                                         (2048, 2048, 2048, 1)])
+@pytest.mark.parametrize("dt", [D.F16, D.BF16])
+def test_16_bit_contraction_on_the_tensor_cores(dev, m, n, k, batch, dt):
+    """tcgen05 kind::f16: exact products of the 16-bit operands, f32 accumulation.  Against float64: within
+    1e-5 of the sum of magnitudes (plus one rounding of the stored type when C is 16-bit).  The oracle's loop
+    (the reference's 3-loop MatMul fallback, src/lowerer/lower.rs:834-984) rounds every product to the 16-bit
+    type before adding it, so it is held to the looser 2^-9 of the same sum."""
+    from test_half import half_matmul_desc
+    a, b = half_inputs((batch, m, k), dt, 11), half_inputs((batch, n, k), dt, 12)
+    af, bf = as_f32(a, dt).reshape(batch, m, k).astype(np.float64), as_f32(b, dt).reshape(batch, n, k).astype(np.float64)
+    exact = np.einsum("bmk,bnk->bmn", af, bf).reshape(-1)
+    mag = np.einsum("bmk,bnk->bmn", np.abs(af), np.abs(bf)).reshape(-1)
+    for out_dt in (D.F32, dt):
+        kd = half_matmul_desc(m, n, k, dt, out_dt, batch)
+        got, kern = run_gpu(dev, kd, [a, b])
+        assert kern.impl == ("gemm_tcgen05_f16_kk" if dt == D.F16 else "gemm_tcgen05_bf16_kk"), kern.impl
+        g = as_f32(got, out_dt).astype(np.float64)
+        tol = 1e-5 * mag + (ulp(out_dt) * np.abs(exact) if out_dt != D.F32 else 0.0)
+        assert (np.abs(g - exact) <= tol + 1e-30).all(), (out_dt, float(np.abs(g - exact).max()))
+        if m * n * k * batch <= 1 << 24:
+            ref = as_f32(O.run(kd, [a, b], openmp=True), out_dt).astype(np.float64)
+            assert (np.abs(ref - exact) <= 2.0 ** -9 * mag + ulp(out_dt) * np.abs(exact) + 1e-30).all()

@@ -65,3 +65,39 @@ def test_planner_moves_16_bit_operands_four_at_a_time():
     assert query(k).impl.decode() == "ew_chain_v1"
     k = D.reduce([300, 1000], [D.contiguous([300, 1000], D.BF16)], w(0), D.R_SUM, 1)
     assert query(k).impl.decode().startswith("reduce_inner")
+
+
+def half_matmul_desc(m, n, k, dt, out_dt=D.F32, batch=1):
+    """C[b][m][n] = sum_k A[b][m][k] * B[b][n][k] with 16-bit A and B, both contiguous along k (x @ W^T)."""
+    if batch > 1:
+        shape = [batch, m, n, k]
+        a = D.Operand([m * k, k, 0, 1], 0, dt, batch * m * k)
+        b = D.Operand([n * k, 0, k, 1], 0, dt, batch * n * k)
+        out = D.Operand([m * n, n, 1, 0], 0, out_dt, batch * m * n)
+        return D.reduce(shape, [a, b], w(0) * w(1), D.R_SUM, 3, out=out)
+    a = D.Operand([k, 0, 1], 0, dt, m * k)
+    b = D.Operand([0, k, 1], 0, dt, n * k)
+    return D.reduce([m, n, k], [a, b], w(0) * w(1), D.R_SUM, 2, out=D.Operand([n, 1, 0], 0, out_dt, m * n))
+
+
+def test_planner_sends_16_bit_contractions_to_the_tensor_cores():
+    def query(k):
+        info = D.CKernelInfo()
+        cd = k.to_c()
+        capi.call("eb200_kernel_query", C.byref(cd), 148, C.byref(info))
+        return info
+    i = query(half_matmul_desc(1024, 512, 4096, D.BF16))
+    assert i.impl.decode() == "gemm_tcgen05_bf16_kk" and i.launches == 1 and i.scratch_bytes == 0
+    assert i.algo_flops == 2 * 1024 * 512 * 4096
+    assert query(half_matmul_desc(300, 200, 72, D.F16, D.F16, batch=3)).impl.decode() == "gemm_tcgen05_f16_kk"
+    # rows that are not 16-byte aligned (k = 100 elements of 2 bytes is fine, k = 99 is not) stay a plain reduce
+    assert query(half_matmul_desc(256, 256, 99, D.F16)).impl.decode().startswith("reduce_")
+    # B contiguous along n (the matmul_demo form) is not staged for 16-bit operands: plain reduce
+    a = D.Operand([64, 0, 1], 0, D.F16, 128 * 64)
+    b = D.Operand([0, 1, 256], 0, D.F16, 64 * 256)
+    k = D.reduce([128, 256, 64], [a, b], w(0) * w(1), D.R_SUM, 2, out=D.Operand([256, 1, 0], 0, D.F32, 128 * 256))
+    assert query(k).impl.decode().startswith("reduce_")
+    # mixed operand types are not a GEMM
+    k = half_matmul_desc(256, 256, 128, D.F16)
+    k.inputs[1].dtype = D.BF16
+    assert query(k).impl.decode().startswith("reduce_")
