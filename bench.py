@@ -757,8 +757,11 @@ def misc_kernel_measurements(reg, dev, rng, hbm, quick=False):
             b = reg.allocate_buffer(dev, [sz], dt)
             if dt == D.F32:
                 b.write_vec(rng.uniform(-1, 1, sz).astype(np.float32))
+            elif dt in (D.F16, D.BF16):
+                x = rng.uniform(-1, 1, sz).astype(np.float32)
+                b.write_vec(x.astype(np.float16) if dt == D.F16 else D.bf16_bits(x))
             bufs.append(b)
-        bo = bufs[in_place] if in_place is not None else reg.allocate_buffer(dev, [out_size])
+        bo = bufs[in_place] if in_place is not None else reg.allocate_buffer(dev, [out_size], kd.output.dtype)
         kern = reg.compile_ast(dev, kd)
         ms = time_kernel(dev, kern, bufs, [bo], reps=3 if quick else 10)
         gbs = kern.algo_bytes / ms / 1e6
@@ -788,13 +791,33 @@ def misc_kernel_measurements(reg, dev, rng, hbm, quick=False):
     run("tall_wgrad_32x9_over_2768896", D.reduce([rows, 32, 9], [a, b], w(0) * w(1), D.R_SUM, 0), [rows * 32, rows * 9], 32 * 9)
     # a contraction on the f32 FFMA kernel (row stride not a multiple of 16 bytes: TMA cannot address it)
     run("gemm_simt_2048x1022x2048", W_matmul(2048, 1022, 2048), [2048 * 1022, 1022 * 2048], 2048 * 2048)
+    # ReLU + 2x2 max-pool of config 4's first layer at batch 4096, forward and gradient, one kernel each
+    planes = 4096 * 32
+    run("relu_maxpool2_fwd_131072x26x26", D.maxpool2d(planes, 26, 26, 2, relu=True), [planes * 676], planes * 169)
+    run("relu_maxpool2_grad_131072x26x26", D.maxpool2d(planes, 26, 26, 2, relu=True, grad=True),
+        [planes * 169, planes * 676, planes * 169], planes * 676)
+    # 16-bit storage: elements widen to f32 in registers, 64-bit accesses
+    run("ew_add_bf16", D.elementwise([2 * n], [D.contiguous([2 * n], D.BF16)] * 2, w(0) + w(1), out_dtype=D.BF16), [2 * n, 2 * n], 2 * n,
+        dtypes=[D.BF16, D.BF16])
+    # 16-bit contractions on tcgen05 kind::f16 (x @ W^T form, f32 accumulate, f32 result)
+    for dt, tag in ((D.BF16, "bf16"), (D.F16, "f16")):
+        for m_, n_, k_ in ((8192, 8192, 8192),) if not quick else ((2048, 2048, 2048),):
+            a = D.Operand([k_, 0, 1], 0, dt, m_ * k_)
+            b = D.Operand([0, k_, 1], 0, dt, n_ * k_)
+            kd = D.reduce([m_, n_, k_], [a, b], w(0) * w(1), D.R_SUM, 2, out=D.Operand([n_, 1, 0], 0, D.F32, m_ * n_))
+            name = f"gemm_{tag}_{m_}x{n_}x{k_}"
+            run(name, kd, [m_ * k_, n_ * k_], m_ * n_, dtypes=[dt, dt])
+            res[name]["tflops"] = 2.0 * m_ * n_ * k_ / res[name]["ms"] / 1e9
+            res[name]["frac_of_bf16_peak"] = res[name]["tflops"] / measured_peaks()[1]
+            del res[name]["gbs"], res[name]["frac_of_hbm"]
     return res
 
 
 def run_only_small(args):
     """`--only gemm`: the tensor-core contraction on a 4096 x 2048 x 4096 case; `--only cfg2`: the
     config 2 kernels and the one-pass sibling form on a [4096, 8192] block; `--only kernels`: the
-    kernel classes of misc_kernel_measurements; `--only mlp` / `--only cnn`: the kernels of one training
+    kernel classes of misc_kernel_measurements; `--only gemm16`: a 4096^3 bf16 / f16 contraction; `--only pool`: the
+    fused ReLU + max-pool kernels and a bf16 elementwise add; `--only mlp` / `--only cnn`: the kernels of one training
     step of config 3 / of config 4's 512-image shard (small cases for profiler captures)."""
     from harp_b200 import desc as D
     from harp_b200 import workloads as W
@@ -831,6 +854,43 @@ def run_only_small(args):
             bo.release()
         print(json.dumps({"only": "cfg2", "rows": rows, "kernels": res}))
         return
+    if args.only == "gemm16":
+        # bf16 / f16 contraction 4096^3 on the persistent pair kernel (32 MiB per operand, 64 MiB result)
+        res = {}
+        m = k_ = n = 4096
+        for dt, tag in ((D.BF16, "bf16"), (D.F16, "f16")):
+            x = rng.uniform(-1, 1, m * k_).astype(np.float32)
+            ba, bb = reg.allocate_buffer(dev, [m * k_], dt), reg.allocate_buffer(dev, [n * k_], dt)
+            ba.write_vec(x.astype(np.float16) if dt == D.F16 else D.bf16_bits(x)); bb.write_vec(x.astype(np.float16) if dt == D.F16 else D.bf16_bits(x))
+            bo = reg.allocate_buffer(dev, [m * n])
+            kd = D.reduce([m, n, k_], [D.Operand([k_, 0, 1], 0, dt, m * k_), D.Operand([0, k_, 1], 0, dt, n * k_)], D.Ast.w(0) * D.Ast.w(1),
+                          D.R_SUM, 2, out=D.Operand([n, 1, 0], 0, D.F32, m * n))
+            kern = reg.compile_ast(dev, kd)
+            ms = time_kernel(dev, kern, [ba, bb], [bo], reps=2, warm=1)
+            res[tag] = {"impl": kern.impl, "ms": ms, "tflops": 2.0 * m * k_ * n / ms / 1e9}
+        print(json.dumps({"only": "gemm16", "gemm_4096x4096x4096": res}))
+        return
+    if args.only == "pool":
+        # ReLU + 2x2 max-pool of config 4's first layer at batch 1024 (88 MiB in), forward and gradient, and a bf16 add
+        planes = 1024 * 32
+        res = {}
+        bx = reg.allocate_buffer(dev, [planes * 676]); bx.write_vec(rng.standard_normal(planes * 676).astype(np.float32))
+        by, bg, bgx = reg.allocate_buffer(dev, [planes * 169]), reg.allocate_buffer(dev, [planes * 169]), reg.allocate_buffer(dev, [planes * 676])
+        bg.write_vec(rng.standard_normal(planes * 169).astype(np.float32))
+        for name, kd, ins, out in (("fwd", D.maxpool2d(planes, 26, 26, 2, relu=True), [bx], by),
+                                   ("grad", D.maxpool2d(planes, 26, 26, 2, relu=True, grad=True), [bg, bx, by], bgx)):
+            kern = reg.compile_ast(dev, kd)
+            ms = time_kernel(dev, kern, ins, [out], reps=3, warm=2)
+            res[name] = {"impl": kern.impl, "ms": ms, "gbs": kern.algo_bytes / ms / 1e6}
+        n16 = 1 << 26
+        x = rng.uniform(-1, 1, n16).astype(np.float32)
+        ba, bb, bo = (reg.allocate_buffer(dev, [n16], D.BF16) for _ in range(3))
+        ba.write_vec(D.bf16_bits(x)); bb.write_vec(D.bf16_bits(x))
+        kern = reg.compile_ast(dev, D.elementwise([n16], [D.contiguous([n16], D.BF16)] * 2, D.Ast.w(0) + D.Ast.w(1), out_dtype=D.BF16))
+        ms = time_kernel(dev, kern, [ba, bb], [bo], reps=3, warm=2)
+        res["ew_add_bf16"] = {"impl": kern.impl, "ms": ms, "gbs": kern.algo_bytes / ms / 1e6}
+        print(json.dumps({"only": "pool", "kernels": res}))
+        return
     if args.only in ("mlp", "cnn"):
         # one training step of config 3 (batch 65536) / config 4 (batch 512), kernel by kernel, no graph:
         # every buffer is at most 67 MB, so a profiler capture of a few launches stays small
@@ -857,7 +917,7 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="only config 2 (skip matmul / MLP / CNN measurements)")
     ap.add_argument("--z-allreduce", default="async", choices=["async", "fused"],
                     help="multi-GPU: how the column-max partials are combined (side-stream all-reduce, or fused into the reduce's finish pass)")
-    ap.add_argument("--only", default="", choices=["", "conv2d", "conv2d_grad", "gemm", "kernels", "cfg2", "mlp", "cnn"],
+    ap.add_argument("--only", default="", choices=["", "conv2d", "conv2d_grad", "gemm", "gemm16", "pool", "kernels", "cfg2", "mlp", "cnn"],
                     help="run one small kernel case alone (profiler captures); prints no bench line")
     args = ap.parse_args()
     if args.only in ("conv2d", "conv2d_grad"):

@@ -25,6 +25,8 @@ pub const F32: i32 = 0;
 pub const BOOL: i32 = 1;
 pub const I32: i32 = 2;
 pub const I64: i32 = 3;
+pub const F16: i32 = 4;
+pub const BF16: i32 = 5;
 
 // eb200_kclass
 pub const K_ELEMENTWISE: i32 = 0;
@@ -36,6 +38,8 @@ pub const K_CONV2D: i32 = 5;
 pub const K_SCAN: i32 = 6;
 pub const K_SGD_MOMENTUM: i32 = 7;
 pub const K_ADAM: i32 = 8;
+pub const K_SOFTMAX_XENT: i32 = 9;
+pub const K_MAXPOOL2D: i32 = 10;
 
 // eb200_reduce_op
 pub const R_NONE: i32 = 0;

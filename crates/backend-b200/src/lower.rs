@@ -93,6 +93,8 @@ fn dtype_code(dt: &DType) -> Result<i32, Unsupported> {
         DType::Bool => Ok(BOOL),
         DType::I32 => Ok(I32),
         DType::I64 => Ok(I64),
+        DType::F16 => Ok(F16),
+        DType::BF16 => Ok(BF16),
         other => unsupported(format!("element type {other:?}")),
     }
 }

@@ -28,20 +28,14 @@ __device__ __forceinline__ void load_vec4(const KParams& p, long long e, float (
         const KOperand& o = p.in[i];
         const long long a = ND == 1 ? o.offset + e * o.strides[0] : operand_index<ND>(p, o, idx);
         if (o.dtype != EB200_F32) {
-            // f16 / bf16 storage: four elements are one 64-bit load, widened to f32 here
+            // f16 / bf16 storage: four elements are one 64-bit load; the raw bits wait in in[i][0..1] and are
+            // widened by widen_vec4 when the values are used, so that no load has a dependent instruction
+            // between itself and the loads that follow it
             if (o.strides[inner] == 1) {
                 const uint2 t = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const unsigned short*>(o.ptr) + a));
-                if (o.dtype == EB200_F16) {
-                    const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&t.x));
-                    const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&t.y));
-                    in[i][0] = lo.x; in[i][1] = lo.y; in[i][2] = hi.x; in[i][3] = hi.y;
-                } else {
-                    in[i][0] = __uint_as_float(t.x << 16); in[i][1] = __uint_as_float(t.x & 0xffff0000u);
-                    in[i][2] = __uint_as_float(t.y << 16); in[i][3] = __uint_as_float(t.y & 0xffff0000u);
-                }
+                in[i][0] = __uint_as_float(t.x); in[i][1] = __uint_as_float(t.y);
             } else {
-                const float t = load_elem(o, a);
-                in[i][0] = t; in[i][1] = t; in[i][2] = t; in[i][3] = t;
+                in[i][0] = load_elem(o, a);
             }
             continue;
         }
@@ -52,6 +46,32 @@ __device__ __forceinline__ void load_vec4(const KParams& p, long long e, float (
         } else {
             const float t = __ldg(src);
             in[i][0] = t; in[i][1] = t; in[i][2] = t; in[i][3] = t;
+        }
+    }
+}
+
+// second half of load_vec4 for 16-bit operands: raw bits -> four f32 values (a broadcast element -> four copies)
+template <class F, int ND>
+__device__ __forceinline__ void widen_vec4(const KParams& p, float (*in)[4]) {
+    const int inner = ND > 0 ? ND - 1 : p.ndim - 1;
+    const int n = F::nin(p);
+#pragma unroll
+    for (int i = 0; i < (F::kCompiled ? n : KMAX_IN); ++i) {
+        if (i >= n) break;
+        const KOperand& o = p.in[i];
+        if (o.dtype == EB200_F32) continue;
+        if (o.strides[inner] == 1) {
+            const unsigned x = __float_as_uint(in[i][0]), y = __float_as_uint(in[i][1]);
+            if (o.dtype == EB200_F16) {
+                const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&x));
+                const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&y));
+                in[i][0] = lo.x; in[i][1] = lo.y; in[i][2] = hi.x; in[i][3] = hi.y;
+            } else {
+                in[i][0] = __uint_as_float(x << 16); in[i][1] = __uint_as_float(x & 0xffff0000u);
+                in[i][2] = __uint_as_float(y << 16); in[i][3] = __uint_as_float(y & 0xffff0000u);
+            }
+        } else {
+            in[i][1] = in[i][0]; in[i][2] = in[i][0]; in[i][3] = in[i][0];
         }
     }
 }
@@ -81,27 +101,35 @@ __device__ __forceinline__ void store_vec4(const KParams& p, long long e, const 
     }
 }
 
+// Vectors (or elements) in flight per thread: four for plain chains; two for chains that evaluate special
+// functions -- their long dependent sequences want more resident warps (launch bounds: 4 CTAs per SM)
+// rather than more work per thread.
+template <class F>
+constexpr int ew_u() { return F::kSpecial ? 2 : EW_U; }
+
 template <class F, int ND>
-__global__ void __launch_bounds__(256) ew_kernel(const __grid_constant__ KParams p) {
+__global__ void __launch_bounds__(256, F::kSpecial ? 4 : 1) ew_kernel(const __grid_constant__ KParams p) {
+    constexpr int U = ew_u<F>();
     const long long stride = (long long)gridDim.x * blockDim.x;
     const int n = F::nin(p);
     float cl[F::kNconst];
     load_consts<F>(p, cl);
     if (p.vec == 4) {
         const long long nvec = p.total >> 2;
-        // a CTA owns EW_U consecutive 4 KB segments per iteration
-        for (long long v0 = ((long long)blockIdx.x * EW_U) * blockDim.x + threadIdx.x; v0 < nvec; v0 += EW_U * stride) {
-            float in[EW_U][KMAX_IN][4];
+        // a CTA owns U consecutive 4 KB segments per iteration
+        for (long long v0 = ((long long)blockIdx.x * U) * blockDim.x + threadIdx.x; v0 < nvec; v0 += U * stride) {
+            float in[U][KMAX_IN][4];
 #pragma unroll
-            for (int u = 0; u < EW_U; ++u) {
+            for (int u = 0; u < U; ++u) {
                 const long long v = v0 + (long long)u * blockDim.x;
                 if (v < nvec) load_vec4<F, ND>(p, v << 2, in[u]);
             }
 #pragma unroll
-            for (int u = 0; u < EW_U; ++u) {
+            for (int u = 0; u < U; ++u) {
                 const long long v = v0 + (long long)u * blockDim.x;
                 if (v < nvec) {
                     float r[4];
+                    widen_vec4<F, ND>(p, in[u]);
                     F::template eval<4>(p, in[u], r, cl);
                     store_vec4<ND>(p, v << 2, r);
                 }
@@ -173,14 +201,14 @@ __global__ void __launch_bounds__(256) ew_kernel(const __grid_constant__ KParams
             }
         }
     } else {
-        // scalar path: EW_U independent elements per thread in flight (the loads of all of
-        // them are issued before the first is evaluated); a CTA owns EW_U consecutive
+        // scalar path: U independent elements per thread in flight (the loads of all of
+        // them are issued before the first is evaluated); a CTA owns U consecutive
         // 256-element segments per iteration
-        for (long long e0 = ((long long)blockIdx.x * EW_U) * blockDim.x + threadIdx.x; e0 < p.total; e0 += EW_U * stride) {
-            float in[EW_U][KMAX_IN][1];
-            long long oa[EW_U];
+        for (long long e0 = ((long long)blockIdx.x * U) * blockDim.x + threadIdx.x; e0 < p.total; e0 += U * stride) {
+            float in[U][KMAX_IN][1];
+            long long oa[U];
 #pragma unroll
-            for (int u = 0; u < EW_U; ++u) {
+            for (int u = 0; u < U; ++u) {
                 const long long e = e0 + (long long)u * blockDim.x;
                 if (e < p.total) {
                     long long idx[KMAX_DIMS];
@@ -196,7 +224,7 @@ __global__ void __launch_bounds__(256) ew_kernel(const __grid_constant__ KParams
                 }
             }
 #pragma unroll
-            for (int u = 0; u < EW_U; ++u) {
+            for (int u = 0; u < U; ++u) {
                 const long long e = e0 + (long long)u * blockDim.x;
                 if (e < p.total) {
                     float r[1];
@@ -212,7 +240,7 @@ template <class F>
 static int launch_one(Device* dev, const KParams& p) {
     long long work = p.vec == 1 ? p.total : (p.total >> 2);
     if (work <= 0) return EB200_OK;
-    long long per_block = 256LL * (p.vec == 2 ? 2 : EW_U);
+    long long per_block = 256LL * (p.vec == 2 ? 2 : ew_u<F>());
     long long blocks = (work + per_block - 1) / per_block;
     long long cap = (long long)dev->prop.multiProcessorCount * 32;
     if (blocks > cap) blocks = cap;

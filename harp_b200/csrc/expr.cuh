@@ -33,7 +33,7 @@ __device__ __forceinline__ float op_recip(float a) { return __frcp_rn(a); }
 // routines (exp2f / log2f, with their range handling) cost four times as many instructions.
 __device__ __forceinline__ float op_exp2(float a) {
     float r;
-    asm("ex2.approx.f32 %0, %1;" : "=f"(r) : "f"(a));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(a));      // (results below 2^-126 flush to zero)
     return r;
 }
 __device__ __forceinline__ float op_log2(float a) {
@@ -96,6 +96,7 @@ __device__ __forceinline__ bool bounds_ok(const KParams& p, const KOperand& o, c
 // ---- bytecode interpreter ---------------------------------------------------------
 struct Interp {
     static constexpr bool kCompiled = false;
+    static constexpr bool kSpecial = false;
     static constexpr int kNin = KMAX_IN;
     static constexpr int kNconst = KMAX_CONSTS;
     __device__ __forceinline__ static int nin(const KParams& p) { return p.n_in; }
@@ -171,6 +172,7 @@ struct Interp {
 template <class C>
 struct Compiled {
     static constexpr bool kCompiled = true;
+    static constexpr bool kSpecial = C::SPECIAL != 0;   // evaluates exp2 / log2 / recip / sqrt / sin: long dependent chains
     static constexpr int kNin = C::NIN > 0 ? C::NIN : 1;
     static constexpr int kNconst = C::NCONST > 0 ? C::NCONST : 1;
     __device__ __forceinline__ static int nin(const KParams&) { return C::NIN; }

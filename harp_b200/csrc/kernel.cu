@@ -30,7 +30,7 @@ int find_chain(const KInsn* prog, int n_insns) {
     return -1;
 }
 
-static int dtype_bytes(int dt) { return dt == EB200_BOOL ? 1 : (dt == EB200_I64 ? 8 : 4); }
+static int dtype_bytes(int dt) { return dt == EB200_BOOL ? 1 : dt == EB200_I64 ? 8 : (dt == EB200_F16 || dt == EB200_BF16) ? 2 : 4; }
 
 }  // namespace eb200
 

@@ -505,6 +505,34 @@ __global__ void __launch_bounds__(256) reduce_finish_kernel(const __grid_constan
     }
 }
 
+// The same fold for few kept elements and many splits (a bias gradient: 256 columns, ~600 row blocks): one thread
+// per column would walk its partials alone, one dependent load after the other.  Here a CTA is 32 columns x 8
+// split lanes: lane j folds splits j, j + 8, ... (in order), the eight partial results are folded in lane order
+// through shared memory -- a fixed order, so the result does not depend on the launch.
+__global__ void __launch_bounds__(256) reduce_finish_wide_kernel(const __grid_constant__ KParams p, const float* __restrict__ scratch) {
+    __shared__ float part[8][33];
+    const int col = threadIdx.x & 31, lane_s = threadIdx.x >> 5;
+    for (long long k0 = (long long)blockIdx.x * 32; k0 < p.kept; k0 += (long long)gridDim.x * 32) {
+        const long long k = k0 + col;
+        float acc = red_identity(p.rop);
+        if (k < p.kept) {
+#pragma unroll 4
+            for (int s = lane_s; s < p.splits; s += 8) acc = red_combine(p.rop, acc, __ldg(scratch + (long long)s * p.kept + k));
+        }
+        part[lane_s][col] = acc;
+        __syncthreads();
+        if (lane_s == 0 && k < p.kept) {
+            float r = part[0][col];
+#pragma unroll
+            for (int j = 1; j < 8; ++j) r = red_combine(p.rop, r, part[j][col]);
+            long long idx[KMAX_DIMS];
+            decompose(p, k, idx, p.raxis);
+            store_elem(p.out, operand_index(p, p.out, idx), r);
+        }
+        __syncthreads();
+    }
+}
+
 template <class F>
 static int launch_one(Device* dev, const Plan& plan, const KParams& p, float* scratch, bool finish) {
     const int sms = dev->prop.multiProcessorCount;
@@ -553,7 +581,10 @@ static int launch_one(Device* dev, const Plan& plan, const KParams& p, float* sc
         long long blocks = (p.kept + 255) / 256;
         long long cap = (long long)sms * 8;
         if (blocks > cap) blocks = cap;
-        reduce_finish_kernel<<<(unsigned)blocks, 256, 0, dev->stream>>>(p, scratch);
+        if (p.splits >= 32 && p.kept <= 32LL * sms)
+            reduce_finish_wide_kernel<<<(unsigned)((p.kept + 31) / 32), 256, 0, dev->stream>>>(p, scratch);
+        else
+            reduce_finish_kernel<<<(unsigned)blocks, 256, 0, dev->stream>>>(p, scratch);
         count_launch();
         EB_CHECK_CUDA(cudaGetLastError());
     }

@@ -33,10 +33,11 @@ def test_elementwise_over_16_bit_storage(dev, shape, dts):
         got, kern = run_gpu(dev, k, [a, b])
         assert kern.impl == ("ew_chain_v4" if int(np.prod(shape)) % 4 == 0 else "ew_chain_v1")     # contiguous operands collapse to one dim
         ref = O.run(k, [a, b])
-        if name == "select":
+        if name == "select" and da == db:
+            # (with one f16 and one bf16 operand the C conditional converts both to one 16-bit type first)
             assert got.tobytes() == ref.tobytes(), (name, dts)
         else:
-            close(got, ref, do, (name, dts))
+            close(got, ref, do if da == db or do != D.F32 else D.BF16, (name, dts))
 
 
 @pytest.mark.parametrize("dt", [D.F16, D.BF16])
@@ -104,7 +105,8 @@ def test_16_bit_contraction_on_the_tensor_cores(dev, m, n, k, batch, dt):
     for out_dt in (D.F32, dt):
         kd = half_matmul_desc(m, n, k, dt, out_dt, batch)
         got, kern = run_gpu(dev, kd, [a, b])
-        assert kern.impl == ("gemm_tcgen05_f16_kk" if dt == D.F16 else "gemm_tcgen05_bf16_kk"), kern.impl
+        if m > 1:         # (an extent-1 row dim is dropped before classification: a matrix-vector product stays a reduce)
+            assert kern.impl == ("gemm_tcgen05_f16_kk" if dt == D.F16 else "gemm_tcgen05_bf16_kk"), kern.impl
         g = as_f32(got, out_dt).astype(np.float64)
         tol = 1e-5 * mag + (ulp(out_dt) * np.abs(exact) if out_dt != D.F32 else 0.0)
         assert (np.abs(g - exact) <= tol + 1e-30).all(), (out_dt, float(np.abs(g - exact).max()))
