@@ -731,7 +731,7 @@ def extra_measurements(reg, dev, ranks, comm, quick=False):
         res["img_per_s"] = 512 / res["ms_per_step"] * 1e3
         out["cnn_cfg4_shard_512"] = res
         del prog
-        res, prog = train_step(lambda nl: W.cnn_graph(nl, seed=4, fused_conv=False), 4096, 1e-2, 3 if quick else 10)
+        res, prog = train_step(lambda nl: W.cnn_graph(nl, seed=4, fused_conv=False), 4096, 1e-2, 3 if quick else 10, tables=True)
         res["img_per_s"] = 4096 / res["ms_per_step"] * 1e3
         out["cnn_cfg4_reference_spelling"] = res
         del prog

@@ -16,7 +16,8 @@ namespace eb200 {
 
 constexpr int EW_U = 4;  // independent 128-bit vectors in flight per thread
 
-template <class F, int ND>
+// H16: some operand is stored as f16 / bf16 (kernels without such operands carry none of the type handling)
+template <class F, int ND, bool H16>
 __device__ __forceinline__ void load_vec4(const KParams& p, long long e, float (*in)[4]) {
     long long idx[KMAX_DIMS];
     if (ND != 1) decompose<ND>(p, e, idx);
@@ -27,7 +28,7 @@ __device__ __forceinline__ void load_vec4(const KParams& p, long long e, float (
         if (i >= n) break;
         const KOperand& o = p.in[i];
         const long long a = ND == 1 ? o.offset + e * o.strides[0] : operand_index<ND>(p, o, idx);
-        if (o.dtype != EB200_F32) {
+        if (H16 && o.dtype != EB200_F32) {
             // f16 / bf16 storage: four elements are one 64-bit load; the raw bits wait in in[i][0..1] and are
             // widened by widen_vec4 when the values are used, so that no load has a dependent instruction
             // between itself and the loads that follow it
@@ -76,7 +77,7 @@ __device__ __forceinline__ void widen_vec4(const KParams& p, float (*in)[4]) {
     }
 }
 
-template <int ND>
+template <int ND, bool H16>
 __device__ __forceinline__ void store_vec4(const KParams& p, long long e, const float* v) {
     long long a;
     if (ND == 1) {
@@ -86,7 +87,7 @@ __device__ __forceinline__ void store_vec4(const KParams& p, long long e, const 
         decompose<ND>(p, e, idx);
         a = operand_index<ND>(p, p.out, idx);
     }
-    if (p.out.dtype == EB200_F32) {
+    if (!H16 || p.out.dtype == EB200_F32) {
         *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out.ptr) + a) = make_float4(v[0], v[1], v[2], v[3]);
     } else {
         uint2 t;
@@ -104,12 +105,14 @@ __device__ __forceinline__ void store_vec4(const KParams& p, long long e, const 
 // Vectors (or elements) in flight per thread: four for plain chains; two for chains that evaluate special
 // functions -- their long dependent sequences want more resident warps (launch bounds: 4 CTAs per SM)
 // rather than more work per thread.
-template <class F>
+// (16-bit operands move half the bytes per vector; their kernels are built for four CTAs per SM as well, so that
+// twice the threads keep the same bytes in flight.)
+template <class F, bool H16>
 constexpr int ew_u() { return F::kSpecial ? 2 : EW_U; }
 
-template <class F, int ND>
-__global__ void __launch_bounds__(256, F::kSpecial ? 4 : 1) ew_kernel(const __grid_constant__ KParams p) {
-    constexpr int U = ew_u<F>();
+template <class F, int ND, bool H16>
+__global__ void __launch_bounds__(256, (F::kSpecial || H16) ? 4 : 1) ew_kernel(const __grid_constant__ KParams p) {
+    constexpr int U = ew_u<F, H16>();
     const long long stride = (long long)gridDim.x * blockDim.x;
     const int n = F::nin(p);
     float cl[F::kNconst];
@@ -122,16 +125,16 @@ __global__ void __launch_bounds__(256, F::kSpecial ? 4 : 1) ew_kernel(const __gr
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const long long v = v0 + (long long)u * blockDim.x;
-                if (v < nvec) load_vec4<F, ND>(p, v << 2, in[u]);
+                if (v < nvec) load_vec4<F, ND, H16>(p, v << 2, in[u]);
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const long long v = v0 + (long long)u * blockDim.x;
                 if (v < nvec) {
                     float r[4];
-                    widen_vec4<F, ND>(p, in[u]);
+                    if (H16) widen_vec4<F, ND>(p, in[u]);
                     F::template eval<4>(p, in[u], r, cl);
-                    store_vec4<ND>(p, v << 2, r);
+                    store_vec4<ND, H16>(p, v << 2, r);
                 }
             }
         }
@@ -240,7 +243,13 @@ template <class F>
 static int launch_one(Device* dev, const KParams& p) {
     long long work = p.vec == 1 ? p.total : (p.total >> 2);
     if (work <= 0) return EB200_OK;
-    long long per_block = 256LL * (p.vec == 2 ? 2 : ew_u<F>());
+    // 16-bit operands on the vector path: instantiated for rank 1 and for any rank only
+    bool h16 = false;
+    if (p.vec == 4) {
+        for (int i = 0; i < p.n_in; ++i) h16 = h16 || p.in[i].dtype == EB200_F16 || p.in[i].dtype == EB200_BF16;
+        h16 = h16 || p.out.dtype == EB200_F16 || p.out.dtype == EB200_BF16;
+    }
+    long long per_block = 256LL * (p.vec == 2 ? 2 : (h16 ? ew_u<F, true>() : ew_u<F, false>()));
     long long blocks = (work + per_block - 1) / per_block;
     long long cap = (long long)dev->prop.multiProcessorCount * 32;
     if (blocks > cap) blocks = cap;
@@ -250,13 +259,17 @@ static int launch_one(Device* dev, const KParams& p) {
     if (p.total < (1LL << 31)) nd = p.ndim <= 4 ? p.ndim : (p.ndim <= 6 && p.vec != 4 ? 6 : 0);
     if (p.vec == 2 && nd == 1) nd = 0;      // (rank 1 never plans groups of four; keep the switch total)
     const unsigned g = (unsigned)blocks;
+    if (h16) {
+        if (nd == 1) ew_kernel<F, 1, true><<<g, 256, 0, dev->stream>>>(p);
+        else ew_kernel<F, 0, true><<<g, 256, 0, dev->stream>>>(p);
+    } else
     switch (nd) {
-        case 1: ew_kernel<F, 1><<<g, 256, 0, dev->stream>>>(p); break;
-        case 2: ew_kernel<F, 2><<<g, 256, 0, dev->stream>>>(p); break;
-        case 3: ew_kernel<F, 3><<<g, 256, 0, dev->stream>>>(p); break;
-        case 4: ew_kernel<F, 4><<<g, 256, 0, dev->stream>>>(p); break;
-        case 6: ew_kernel<F, 6><<<g, 256, 0, dev->stream>>>(p); break;
-        default: ew_kernel<F, 0><<<g, 256, 0, dev->stream>>>(p); break;
+        case 1: ew_kernel<F, 1, false><<<g, 256, 0, dev->stream>>>(p); break;
+        case 2: ew_kernel<F, 2, false><<<g, 256, 0, dev->stream>>>(p); break;
+        case 3: ew_kernel<F, 3, false><<<g, 256, 0, dev->stream>>>(p); break;
+        case 4: ew_kernel<F, 4, false><<<g, 256, 0, dev->stream>>>(p); break;
+        case 6: ew_kernel<F, 6, false><<<g, 256, 0, dev->stream>>>(p); break;
+        default: ew_kernel<F, 0, false><<<g, 256, 0, dev->stream>>>(p); break;
     }
     count_launch();
     EB_CHECK_CUDA(cudaGetLastError());
