@@ -258,6 +258,249 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 1) tmem_dealloc(tmem_base, TC_BN);
 }
 
+// ---- one-CTA form, persistent (the in-kernel hi / lo split lives here) --------------------------
+// One CTA per SM walks tiles t, t + G, t + 2G, ... (G CTAs); the accumulator is double buffered in tensor
+// memory (2 x BN columns), the operand ring runs on across tiles.  Ten warps: 0 TMA, 1 MMA, 2-5 epilogue
+// (tensor-memory lanes 32 * (warp % 4) ..), 6-9 split the raw f32 tiles into hi / lo while the previous tile's
+// accumulator is drained -- in the one-tile-per-CTA form the same four warps did both, one after the other,
+// and every tile paid its own pipeline fill, tensor-memory allocation and epilogue (an MLP layer
+// [65536, 256] x [256, 256]: 8 k blocks per tile, a third of the time outside the main loop).
+//   full[s]      TMA -> split warps (or -> MMA when nothing is split in the kernel)
+//   conv[s]      split warps -> MMA (128 arrivals)
+//   empty[s]     MMA -> TMA (tcgen05.commit)
+//   acc_full[a]  MMA -> epilogue (tcgen05.commit);  acc_empty[a]  epilogue -> MMA (4 arrivals)
+constexpr int TC1P_THREADS = 320;
+
+struct OneTile {
+    bool idle;
+    long long m0, n0;
+    int bz, zslot, kb_begin, num_kb;
+};
+
+template <int TC_BN>
+__device__ __forceinline__ OneTile decode_one_tile(const TcParams& q, int t) {
+    OneTile p;
+    const int z = t / q.tiles_per_z, r = t - z * q.tiles_per_z;
+    const int tiles_m = (int)((q.m + TC_BM - 1) / TC_BM);
+    const int per_band = q.raster * q.tiles_n;
+    const int band = r / per_band, within = r - band * per_band;
+    const int band_rows = min(q.raster, tiles_m - band * q.raster);
+    const int tile_m = band * q.raster + within % band_rows;
+    const int tile_n = within / band_rows;
+    p.idle = tile_n >= q.tiles_n;
+    p.n0 = (long long)tile_n * TC_BN;
+    p.m0 = (long long)tile_m * TC_BM;
+    p.bz = z / q.splits;
+    p.zslot = z;
+    const int split = z - p.bz * q.splits;
+    const int total_kb = (int)((q.k + TC_BK - 1) / TC_BK);
+    p.kb_begin = split * q.kb_per_split;
+    p.num_kb = min(total_kb - p.kb_begin, q.kb_per_split);
+    return p;
+}
+
+template <int TC_BN>
+__global__ void __launch_bounds__(TC1P_THREADS, 1)
+gemm_tc1p_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_alo,
+                 const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_blo,
+                 const __grid_constant__ TcParams q, float* __restrict__ C, int a_zmul, int b_zmul) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr int B_TILE_BYTES = TC_BN * TC_BK * 4;
+    const int stage_bytes = (q.three_pass ? 2 : 1) * (TC_TILE_BYTES + B_TILE_BYTES);
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)q.stages * stage_bytes);
+    uint64_t* empty_bar = full_bar + q.stages;
+    uint64_t* conv_bar = empty_bar + q.stages;
+    uint64_t* acc_full = conv_bar + q.stages;       // [2]
+    uint64_t* acc_empty = acc_full + 2;             // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+    const int warp = uniform_warp_idx(), lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < q.stages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); mbar_init(&conv_bar[s], 128); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, 2 * TC_BN);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const bool lo_a = q.three_pass && !(q.convert & 1), lo_b = q.three_pass && !(q.convert & 2);
+    const int first = (int)blockIdx.x, step = (int)gridDim.x;
+
+    if (warp == 0) {
+        // ---- TMA producer ----
+        int s = 0;
+        unsigned phase = 0;
+        bool ok = true;
+        for (int t = first; t < q.total_tiles && ok; t += step) {
+            const OneTile p = decode_one_tile<TC_BN>(q, t);
+            if (p.idle) continue;
+            for (int kb = 0; kb < p.num_kb; ++kb, s = (s + 1 == q.stages ? 0 : s + 1), phase ^= (s == 0)) {
+                if (!__all_sync(0xffffffffu, mbar_wait(&empty_bar[s], phase ^ 1u, q.error_flag))) { ok = false; break; }
+                if (elect_one()) {
+                    unsigned char* st = smem + (size_t)s * stage_bytes;
+                    mbar_expect_tx(&full_bar[s], (unsigned)((lo_a ? 2 : 1) * TC_TILE_BYTES + (lo_b ? 2 : 1) * B_TILE_BYTES));
+                    const int kx = (p.kb_begin + kb) * TC_BK;
+                    unsigned char* b_hi = st + (q.three_pass ? 2 : 1) * TC_TILE_BYTES;
+                    if (q.a_mmajor) {
+#pragma unroll
+                        for (int j = 0; j < TC_BM / 32; ++j) {
+                            tma_load_3d(st + j * 4096, &map_a, &full_bar[s], (int)p.m0 + j * 32, kx, p.bz * a_zmul);
+                            if (lo_a) tma_load_3d(st + TC_TILE_BYTES + j * 4096, &map_alo, &full_bar[s], (int)p.m0 + j * 32, kx, p.bz * a_zmul);
+                        }
+                    } else {
+                        tma_load_3d(st, &map_a, &full_bar[s], kx, (int)p.m0, p.bz * a_zmul);
+                        if (lo_a) tma_load_3d(st + TC_TILE_BYTES, &map_alo, &full_bar[s], kx, (int)p.m0, p.bz * a_zmul);
+                    }
+                    if (q.b_nmajor) {
+#pragma unroll
+                        for (int j = 0; j < TC_BN / 32; ++j) {
+                            tma_load_3d(b_hi + j * 4096, &map_b, &full_bar[s], (int)p.n0 + j * 32, kx, p.bz * b_zmul);
+                            if (lo_b) tma_load_3d(b_hi + B_TILE_BYTES + j * 4096, &map_blo, &full_bar[s], (int)p.n0 + j * 32, kx, p.bz * b_zmul);
+                        }
+                    } else {
+                        tma_load_3d(b_hi, &map_b, &full_bar[s], kx, (int)p.n0, p.bz * b_zmul);
+                        if (lo_b) tma_load_3d(b_hi + B_TILE_BYTES, &map_blo, &full_bar[s], kx, (int)p.n0, p.bz * b_zmul);
+                    }
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer ----
+        const uint32_t idesc = umma_idesc_tf32(TC_BM, TC_BN, q.a_mmajor, q.b_nmajor);
+        const uint32_t a_lbo = q.a_mmajor ? 4096 : 16, a_sbo = q.a_mmajor ? 512 : 1024, a_layout = q.a_mmajor ? 1 : 2;
+        const uint32_t b_lbo = q.b_nmajor ? 4096 : 16, b_sbo = q.b_nmajor ? 512 : 1024, b_layout = q.b_nmajor ? 1 : 2;
+        const uint64_t a_jstep = (q.a_mmajor ? 1024u : (unsigned)(TC_UK * 4)) >> 4;
+        const uint64_t b_jstep = (q.b_nmajor ? 1024u : (unsigned)(TC_UK * 4)) >> 4;
+        const uint32_t smem_base = smem_u32(smem);
+        const uint32_t b_off = (q.three_pass ? 2 : 1) * TC_TILE_BYTES;
+        int s = 0, it = 0;
+        unsigned phase = 0;
+        bool ok = true;
+        for (int t = first; t < q.total_tiles && ok; t += step) {
+            const OneTile p = decode_one_tile<TC_BN>(q, t);
+            if (p.idle) continue;
+            const int a = it & 1;
+            const unsigned aphase = (unsigned)(it >> 1) & 1u;
+            // the epilogue of the tile that used this half two tiles ago must have drained it
+            if (!__all_sync(0xffffffffu, mbar_wait(&acc_empty[a], aphase ^ 1u, q.error_flag))) break;
+            tc_fence_after();
+            const uint32_t acc = tmem_base + (uint32_t)(a * TC_BN);
+            for (int kb = 0; kb < p.num_kb; ++kb, s = (s + 1 == q.stages ? 0 : s + 1), phase ^= (s == 0)) {
+                if (!__all_sync(0xffffffffu, mbar_wait(q.convert ? &conv_bar[s] : &full_bar[s], phase, q.error_flag))) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t st = smem_base + (uint32_t)s * (uint32_t)stage_bytes;
+                const uint64_t da0 = umma_desc(st, a_lbo, a_sbo, a_layout), dal0 = umma_desc(st + TC_TILE_BYTES, a_lbo, a_sbo, a_layout);
+                const uint64_t db0 = umma_desc(st + b_off, b_lbo, b_sbo, b_layout), dbl0 = umma_desc(st + b_off + B_TILE_BYTES, b_lbo, b_sbo, b_layout);
+                if (elect_one()) {
+#pragma unroll
+                    for (int j = 0; j < TC_BK / TC_UK; ++j) {
+                        const uint64_t da = da0 + j * a_jstep, db = db0 + j * b_jstep;
+                        umma_tf32(acc, da, db, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+                        if (q.three_pass) {
+                            umma_tf32(acc, dal0 + j * a_jstep, db, idesc, 1u);
+                            umma_tf32(acc, da, dbl0 + j * b_jstep, idesc, 1u);
+                        }
+                    }
+                    umma_commit(&empty_bar[s]);
+                }
+                __syncwarp();
+            }
+            if (!ok) break;
+            if (elect_one()) umma_commit(&acc_full[a]);
+            __syncwarp();
+            ++it;
+        }
+    } else if (warp >= 6) {
+        // ---- hi / lo split of the raw f32 tiles (3xTF32 without pre-split copies) ----
+        if (q.convert) {
+            const int ct = threadIdx.x - 192;                // 0..127
+            int s = 0;
+            unsigned phase = 0;
+            bool ok = true;
+            for (int t = first; t < q.total_tiles && ok; t += step) {
+                const OneTile p = decode_one_tile<TC_BN>(q, t);
+                if (p.idle) continue;
+                for (int kb = 0; kb < p.num_kb; ++kb, s = (s + 1 == q.stages ? 0 : s + 1), phase ^= (s == 0)) {
+                    if (!mbar_wait(&full_bar[s], phase, q.error_flag)) { ok = false; break; }
+                    unsigned char* st = smem + (size_t)s * stage_bytes;
+                    float4* ah = reinterpret_cast<float4*>(st);
+                    float4* al = reinterpret_cast<float4*>(st + TC_TILE_BYTES);
+                    float4* bh = reinterpret_cast<float4*>(st + 2 * TC_TILE_BYTES);
+                    float4* bl = reinterpret_cast<float4*>(st + 2 * TC_TILE_BYTES + B_TILE_BYTES);
+                    if (q.convert & 1)
+#pragma unroll 4
+                    for (int i = ct; i < TC_TILE_BYTES / 16; i += 128) {
+                        const float4 v = ah[i];
+                        float4 h;
+                        h.x = __uint_as_float((__float_as_uint(v.x) + 0x1000u) & 0xffffe000u);
+                        h.y = __uint_as_float((__float_as_uint(v.y) + 0x1000u) & 0xffffe000u);
+                        h.z = __uint_as_float((__float_as_uint(v.z) + 0x1000u) & 0xffffe000u);
+                        h.w = __uint_as_float((__float_as_uint(v.w) + 0x1000u) & 0xffffe000u);
+                        ah[i] = h;
+                        al[i] = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
+                    }
+                    if (q.convert & 2)
+#pragma unroll 4
+                    for (int i = ct; i < B_TILE_BYTES / 16; i += 128) {
+                        const float4 v = bh[i];
+                        float4 h;
+                        h.x = __uint_as_float((__float_as_uint(v.x) + 0x1000u) & 0xffffe000u);
+                        h.y = __uint_as_float((__float_as_uint(v.y) + 0x1000u) & 0xffffe000u);
+                        h.z = __uint_as_float((__float_as_uint(v.z) + 0x1000u) & 0xffffe000u);
+                        h.w = __uint_as_float((__float_as_uint(v.w) + 0x1000u) & 0xffffe000u);
+                        bh[i] = h;
+                        bl[i] = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&conv_bar[s])) : "memory");
+                }
+            }
+        }
+    } else {
+        // ---- epilogue: warps 2..5 own tensor-memory lanes 32 * (warp % 4) .. + 31 ----
+        const int quarter = warp & 3;
+        int it = 0;
+        for (int t = first; t < q.total_tiles; t += step) {
+            const OneTile p = decode_one_tile<TC_BN>(q, t);
+            if (p.idle) continue;
+            const int a = it & 1;
+            const unsigned aphase = (unsigned)(it >> 1) & 1u;
+            if (!mbar_wait_warp(&acc_full[a], aphase, q.error_flag)) break;
+            tc_fence_after();
+            const long long row = p.m0 + quarter * 32 + lane;
+            float* crow = C + q.c_off + (long long)(q.splits > 1 ? p.zslot : p.bz) * q.c_sb + row * q.c_sm;
+#pragma unroll 1
+            for (int c = 0; c < TC_BN / 32; ++c) {
+                float v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(a * TC_BN + c * 32), v);
+                const long long col0 = p.n0 + c * 32;
+                if (row >= q.m || col0 >= q.n) continue;
+                float* dst = crow + col0 * q.c_sn;
+                if (q.c_sn == 1 && col0 + 32 <= q.n && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4)
+                        *reinterpret_cast<float4*>(dst + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (col0 + i < q.n) dst[i * q.c_sn] = v[i];
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[a])) : "memory");
+            ++it;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, 2 * TC_BN);
+}
+
 // ---- two-CTA form: the pair tile -------------------------------------------------------------
 // A cluster of two CTAs computes a 256 x 256 tile with tcgen05.mma.cta_group::2:
 // CTA r stages rows [r*128, r*128+128) of A and columns [r*128, r*128+128) of B, the
@@ -652,6 +895,18 @@ void gemm_tc_scratch(const GemmShape& g, long long* a_span, long long* b_span) {
     *b_span = (b + 63) / 64 * 64;
 }
 
+// Every tensor-core GEMM kernel needs more dynamic shared memory than the default limit (set once per device).
+static int configure_tc(Device* dev) {
+    if (dev->tc_configured) return EB200_OK;
+    EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc2p_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc1p_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc1p_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    dev->tc_configured = true;
+    return EB200_OK;
+}
+
 // 16-bit operands (f16 / bf16), both contiguous along k, f32 accumulation in tensor memory: the persistent pair
 // kernel with tcgen05.mma.kind::f16.  A 128-byte swizzled row holds 64 elements of k, so a k block is 64 deep and
 // every stage feeds four K = 16 MMAs; everything else (ring, double-buffered accumulator, epilogue) is shared
@@ -676,12 +931,7 @@ static int launch_gemm_tc_half(Device* dev, const GemmShape& g, const float* a, 
     q.ks = 1; q.nh = 1;
     q.error_flag = dev->error_flag_dev;
     q.raster = 8;
-    if (!dev->tc_configured) {
-        EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc2p_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        dev->tc_configured = true;
-    }
+    { const int st_cfg = configure_tc(dev); if (st_cfg) return st_cfg; }
     const int stage_bytes = 2 * TC_TILE_BYTES;
     q.stages = std::min(8, (196 * 1024) / stage_bytes);
     const size_t smem = (size_t)q.stages * stage_bytes + 1024 + 256;
@@ -792,12 +1042,7 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
     if (convert) two_cta = false;      // the in-kernel split lives in the one-CTA kernel
     q.error_flag = dev->error_flag_dev;
     q.raster = 8;
-    if (!dev->tc_configured) {
-        EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        EB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tc2p_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        dev->tc_configured = true;
-    }
+    { const int st_cfg = configure_tc(dev); if (st_cfg) return st_cfg; }
     const int az = g.a_sb > 0 ? 1 : 0, bzm = g.b_sb > 0 ? 1 : 0;
     if (two_cta) {
         // B maps were built for `bn`-row boxes when B is K-major; each CTA stages 128 columns
@@ -839,9 +1084,19 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
         const long long bands = (tiles_m + q.raster - 1) / q.raster;
         q.tiles_n = (int)tiles_n;
         // grid.x walks bands x (raster x tiles_n) slots; the last band may be padded
-        dim3 grid((unsigned)(bands * q.raster * tiles_n), 1, (unsigned)(g.batch * g.splits));
-        if (bn == 256) gemm_tc_kernel<256><<<grid, TC_THREADS, smem, dev->stream>>>(ma, mal, mb, mbl, q, c_out, az, bzm);
-        else gemm_tc_kernel<128><<<grid, TC_THREADS, smem, dev->stream>>>(ma, mal, mb, mbl, q, c_out, az, bzm);
+        const long long per_z = bands * q.raster * tiles_n, total = per_z * g.batch * g.splits;
+        if (convert && total < (1LL << 31)) {
+            // split inside the kernel: the persistent form (split warps work ahead while the epilogue drains)
+            q.tiles_per_z = (int)per_z;
+            q.total_tiles = (int)total;
+            const unsigned ctas = (unsigned)std::min<long long>(total, dev->prop.multiProcessorCount);
+            if (bn == 256) gemm_tc1p_kernel<256><<<ctas, TC1P_THREADS, smem, dev->stream>>>(ma, mal, mb, mbl, q, c_out, az, bzm);
+            else gemm_tc1p_kernel<128><<<ctas, TC1P_THREADS, smem, dev->stream>>>(ma, mal, mb, mbl, q, c_out, az, bzm);
+        } else {
+            dim3 grid((unsigned)(bands * q.raster * tiles_n), 1, (unsigned)(g.batch * g.splits));
+            if (bn == 256) gemm_tc_kernel<256><<<grid, TC_THREADS, smem, dev->stream>>>(ma, mal, mb, mbl, q, c_out, az, bzm);
+            else gemm_tc_kernel<128><<<grid, TC_THREADS, smem, dev->stream>>>(ma, mal, mb, mbl, q, c_out, az, bzm);
+        }
     }
     count_launch();
     EB_CHECK_CUDA(cudaGetLastError());

@@ -895,6 +895,9 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
                 for (int i = 0; v && i < p.n_in; ++i) v = vec_ok(p.in[i], raxis, false);
                 p.vec = v ? 4 : 1;
                 pl.threads_per_row = p.rlen <= 64 ? 1 : (p.rlen <= 16384 ? 32 : 256);
+                // short vectorised rows (an MLP's [65536, 256] . w): eight lanes per row, four rows per warp -- a warp per
+                // row would leave every lane two dependent loads and nothing else in flight
+                if (p.vec == 4 && p.rlen > 64 && p.rlen < 512 && p.kept >= 4096) pl.threads_per_row = 8;
                 // (a row group that fills whole waves of CTAs -- 128 threads per row make 6.92 waves of config 2's
                 // 8192 rows where a warp per row makes 1.73 -- measured SLOWER: 51.8 us against 47.1 us; the warp
                 // form has no block barrier and keeps more rows in flight per SM)
@@ -903,6 +906,7 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
                 if ((d->flags & 7) == 2) pl.threads_per_row = 32;
                 if ((d->flags & 7) == 3) pl.threads_per_row = 256;
                 if ((d->flags & 7) == 4) pl.threads_per_row = 128;
+                if ((d->flags & 7) == 5) pl.threads_per_row = 8;
                 // few long rows: split each row over several CTAs, finish in a second pass
                 long long ctas = pl.threads_per_row == 256 ? p.kept : 0;
                 if (pl.threads_per_row == 256 && ctas < 2LL * sm_count && p.rlen >= 65536) {

@@ -45,9 +45,10 @@ __device__ __forceinline__ void set_idx(long long* idx, int d, long long v) {
 template <int T>
 __device__ __forceinline__ float group_reduce(float v, int rop, float* smem) {
     if (T == 1) return v;
+    // T < 32: several row groups share a warp, the exchange stays inside each group of T lanes
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = red_combine(rop, v, __shfl_xor_sync(0xffffffffu, v, o));
-    if (T == 32) return v;
+    for (int o = (T < 32 ? T : 32) / 2; o > 0; o >>= 1) v = red_combine(rop, v, __shfl_xor_sync(0xffffffffu, v, o));
+    if (T <= 32) return v;
     // T is 128 or 256: the 256-thread CTA holds 256/T row groups of T/32 warps
     constexpr int WPG = T >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -563,6 +564,7 @@ static int launch_one(Device* dev, const Plan& plan, const KParams& p, float* sc
             reduce_inner_tma_kernel<F><<<(unsigned)g, RT_WARPS * 32, smem, dev->stream>>>(p);
         } else
         if (T == 1) reduce_inner_kernel<F, 1><<<(unsigned)blocks, 256, 0, dev->stream>>>(p, scratch);
+        else if (T == 8) reduce_inner_kernel<F, 8><<<(unsigned)blocks, 256, 0, dev->stream>>>(p, scratch);
         else if (T == 32) reduce_inner_kernel<F, 32><<<(unsigned)blocks, 256, 0, dev->stream>>>(p, scratch);
         else if (T == 128) reduce_inner_kernel<F, 128><<<(unsigned)blocks, 256, 0, dev->stream>>>(p, scratch);
         else reduce_inner_kernel<F, 256><<<(unsigned)blocks, 256, 0, dev->stream>>>(p, scratch);

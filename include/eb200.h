@@ -193,7 +193,7 @@ typedef struct {
     int32_t reduce_axis;  /* iteration dim that is reduced */
     int32_t n_insns;      /* 0 = identity map of input 0 (COPY / SCATTER) */
     int32_t gemm_mode;    /* eb200_gemm_mode */
-    int32_t flags;        /* tuning hints, 0 = automatic; bits 0-2 force the row-reduce group (1 thread, 2 warp, 3 CTA, 4 half CTA per row); bit 3 keeps a contraction on the f32 FFMA kernel; bit 4 disables split-K (and keeps a narrow column reduce on the thread-per-vector kernel); bit 5 stages long reduce rows through shared memory with bulk async copies; bits 6-11: see EB200_K_CONV2D; 3xTF32 contractions split their operands into hi / lo either inside the kernel or by a pre-pass into scratch copies, chosen from the arithmetic intensity: bit 12 forces the pre-pass, bit 13 the in-kernel split (same results bit for bit); bit 14 (REDUCE, sum over axis 1 of [R, C], one full-size contiguous f32 operand x, R and C multiples of 64): sibling fusion -- the kernel reads x once and writes, into an output of R + C + R*C elements (y and z padded to multiples of 64), y = this reduce, z = max(x, axis 0) and t = x transposed, the three roots a graph like config 2 realizes together */
+    int32_t flags;        /* tuning hints, 0 = automatic; bits 0-2 force the row-reduce group (1 thread, 2 warp, 3 CTA, 4 half CTA, 5 eight lanes per row); bit 3 keeps a contraction on the f32 FFMA kernel; bit 4 disables split-K (and keeps a narrow column reduce on the thread-per-vector kernel); bit 5 stages long reduce rows through shared memory with bulk async copies; bits 6-11: see EB200_K_CONV2D; 3xTF32 contractions split their operands into hi / lo either inside the kernel or by a pre-pass into scratch copies, chosen from the arithmetic intensity: bit 12 forces the pre-pass, bit 13 the in-kernel split (same results bit for bit); bit 14 (REDUCE, sum over axis 1 of [R, C], one full-size contiguous f32 operand x, R and C multiples of 64): sibling fusion -- the kernel reads x once and writes, into an output of R + C + R*C elements (y and z padded to multiples of 64), y = this reduce, z = max(x, axis 0) and t = x transposed, the three roots a graph like config 2 realizes together */
     float   scalar;       /* optimizer kernels: learning rate */
     float   hyper[7];     /* optimizer kernels: further hyper-parameters (see eb200_kclass) */
     eb200_operand inputs[EB200_MAX_INPUTS];

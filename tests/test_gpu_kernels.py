@@ -217,6 +217,23 @@ def test_reduce_inner_axis(dev, rows, cols, op):
         assert_close(got, ref, rel=1e-4)
 
 
+@pytest.mark.parametrize("rows,cols", [(4096, 256), (5000, 68), (4100, 508), (8192, 128)])
+def test_reduce_inner_short_rows_eight_lanes_per_row(dev, rows, cols):
+    """Many short rows: eight lanes per row, four rows per warp; with a second operand that repeats for
+    every row (a layer's weight vector) and one value per row (a broadcast column)."""
+    x, wv, col = rnd([rows, cols], rows + cols), rnd([cols], 5), rnd([rows], 6)
+    ins = [D.contiguous([rows, cols]), D.Operand([0, 1], 0, D.F32, cols), D.Operand([1, 0], 0, D.F32, rows)]
+    for op, m in ((D.R_SUM, w(0) * w(1) + w(2)), (D.R_MAX, w(0) * w(2))):
+        k = D.reduce([rows, cols], ins, m, op, 1)
+        got, kern = run_gpu(dev, k, [x, wv, col])
+        assert kern.impl == "reduce_inner_t8_v4"
+        ref = O.run(k, [x, wv, col])
+        if op == D.R_MAX:
+            assert (got == ref).all()
+        else:
+            assert (np.abs(got.astype(np.float64) - ref) <= sum_tolerance(k, [x, wv, col]) + 1e-30).all()
+
+
 @pytest.mark.parametrize("rows,cols", [(1, 1), (10, 7), (64, 4), (1000, 12), (4096, 64), (513, 130), (70, 1024)])
 @pytest.mark.parametrize("op", [D.R_SUM, D.R_MAX])
 def test_reduce_outer_axis(dev, rows, cols, op):

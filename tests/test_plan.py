@@ -96,6 +96,11 @@ def test_small_rows_use_thread_or_warp_per_row():
     assert query(k).impl.decode() == "reduce_inner_t1_v1"
     k = D.reduce([1000, 1024], [D.contiguous([1000, 1024])], w(0), D.R_SUM, 1)
     assert query(k).impl.decode() == "reduce_inner_t32_v4"
+    # many short rows: eight lanes per row (few such rows stay on a warp per row)
+    k = D.reduce([65536, 256], [D.contiguous([65536, 256])], w(0), D.R_SUM, 1)
+    assert query(k).impl.decode() == "reduce_inner_t8_v4"
+    k = D.reduce([1000, 256], [D.contiguous([1000, 256])], w(0), D.R_SUM, 1)
+    assert query(k).impl.decode() == "reduce_inner_t32_v4"
 
 
 def test_long_single_row_is_split():
