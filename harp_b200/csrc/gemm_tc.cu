@@ -19,9 +19,13 @@
 // representable in tf32) and lo = x - hi and accumulates hi.hi + lo.hi + hi.lo,
 // which restores f32-level accuracy at three times the MMA work.
 //
-// B may be K-major ([N][K], the `linear` form) or N-major ([K][N], the
-// matmul_demo form); A must be K-major.  Anything else (odd strides, unaligned
-// offsets, M-major A) stays on the f32 SIMT kernel.
+// Layouts: A K-major or M-major, B K-major ([N][K], the `linear` form) or N-major ([K][N], the matmul_demo
+// form); odd strides and unaligned offsets stay on the f32 SIMT kernel.
+//
+// Kernels: gemm_tc_kernel<BN> (one tile per CTA), gemm_tc1p_kernel<BN> (persistent, the hi / lo split done
+// inside by dedicated warps, accumulator double buffered), gemm_tc2p_kernel (persistent CTA pairs,
+// cta_group::2, 256 x 256 tiles, accumulator double buffered; also serves f16 / bf16 operands with
+// tcgen05.mma kind::f16).
 //
 // Every wait on an mbarrier is bounded: when the bound is hit the kernel raises
 // a flag in global memory, leaves its loops, frees its tensor memory and
@@ -49,10 +53,8 @@ struct TcParams {
     int stages;
     int raster;        // tile rows per band
     int tiles_n;
-    int ks;            // two-CTA kernel: 32-wide k blocks per pipeline stage (2 halves the barrier round trips per MMA)
     int convert;       // one-CTA kernel, 3xTF32: bit 0 / bit 1 = TMA brings the raw f32 tiles of A / of B and the epilogue warps
                        // split them into hi / lo in shared memory (an operand without its bit comes pre-split from scratch copies)
-    int nh;            // (unused by the persistent pair kernel; kept at 1)
     int half;          // 0: f32 operands (kind::tf32); EB200_F16 / EB200_BF16: 16-bit operands (kind::f16), pair kernel only
     int bke;           // elements of k per 128-byte block: 32 (f32) or 64 (16-bit)
     int c_dtype;       // storage type of C
@@ -928,7 +930,6 @@ static int launch_gemm_tc_half(Device* dev, const GemmShape& g, const float* a, 
     q.splits = 1;
     q.half = g.half; q.bke = 64; q.c_dtype = g.c_dtype;
     q.kb_per_split = (int)((g.k + 63) / 64);
-    q.ks = 1; q.nh = 1;
     q.error_flag = dev->error_flag_dev;
     q.raster = 8;
     { const int st_cfg = configure_tc(dev); if (st_cfg) return st_cfg; }
@@ -1034,8 +1035,6 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
     q.three_pass = three ? 1 : 0;
     q.half = 0; q.bke = TC_BK; q.c_dtype = EB200_F32;
     q.convert = convert;
-    q.ks = 1;
-    q.nh = 1;
     // two-CTA pairs (256 x 256 per pair) when there are enough pair tiles to fill the machine
     const long long pair_tiles = ((g.m + 255) / 256) * ((g.n + 255) / 256) * g.batch * g.splits;
     bool two_cta = g.m > 128 && pair_tiles * 2 >= dev->prop.multiProcessorCount;
@@ -1050,8 +1049,6 @@ int launch_gemm_tc(Device* dev, const Plan& plan, const float* a, const float* b
             if ((st = make_map(&mb, b_hi, g.k, g.n, b_b, g.b_sn, g.b_sb, 128))) return st;
             if ((st = make_map(&mbl, b_lo, g.k, g.n, b_b, g.b_sn, g.b_sb, 128))) return st;
         }
-        q.ks = 1;
-        q.nh = 1;
         const int stage_bytes = (three ? 2 : 1) * 2 * TC_TILE_BYTES;
         q.stages = std::min(8, (196 * 1024) / stage_bytes);
         EB_REQUIRE(q.stages >= 2, EB200_ERR_UNSUPPORTED, "GEMM stage does not fit shared memory twice");
