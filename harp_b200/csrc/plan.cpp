@@ -825,7 +825,9 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
                     const long long tiles = ((g.m + tm - 1) / tm) * ((g.n + tn - 1) / tn) * g.batch;
                     const long long kblocks = (g.k + 31) / 32;
                     if (tiles < sm_count && kblocks >= 16 && (d->flags & 16) == 0 && !g.half) {
-                        long long s = std::min<long long>((2LL * sm_count + tiles - 1) / tiles, kblocks / 8);
+                        // (a handful of output tiles -- a [10, 128] weight gradient over a batch of 512 -- may cut k down to two
+                        // blocks per CTA: otherwise two or four CTAs walk the whole of k one block after the other)
+                        long long s = std::min<long long>((2LL * sm_count + tiles - 1) / tiles, kblocks / (tiles <= 4 && !tc ? 2 : 8));
                         s = std::min<long long>(s, 65535 / std::max<long long>(1, g.batch));
                         if (s > 1) {
                             long long per = (kblocks + s - 1) / s;

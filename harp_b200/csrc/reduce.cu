@@ -413,9 +413,10 @@ __global__ void __launch_bounds__(256) reduce_outer_kernel(const __grid_constant
 // would work.  Here the CTA's 256 threads are (kept / 4) column threads x row lanes;
 // a warp reads whole consecutive rows (coalesced), every lane folds the rows
 // lane, lane + L, ... of the CTA's row chunk, and the lanes are combined through
-// shared memory in lane order (deterministic).
+// shared memory in lane order (deterministic).  Built for four CTAs per SM: the planner sizes the row split as
+// one wave of 4 x SMs CTAs.
 template <class F>
-__global__ void __launch_bounds__(256) reduce_outer_narrow_kernel(const __grid_constant__ KParams p, float* __restrict__ scratch) {
+__global__ void __launch_bounds__(256, 4) reduce_outer_narrow_kernel(const __grid_constant__ KParams p, float* __restrict__ scratch) {
     constexpr int NI = F::kCompiled ? F::kNin : KMAX_IN;
     const int ra = p.raxis;
     const int n = F::nin(p);
