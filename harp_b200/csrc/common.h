@@ -149,6 +149,7 @@ enum Impl {
     IMPL_REDUCE_OUTER,    // reduce over a strided dim (column reduce) + generic fallback
     IMPL_TRANSPOSE,       // batched 2-D transpose through shared memory
     IMPL_SCATTER,         // zero fill + red.global.add
+    IMPL_FOLD_GATHER,     // scatter-add of sliding windows (fold) as a gather over the output: deterministic, no atomics
     IMPL_SGD,             // p - lr*g
     IMPL_GEMM_SIMT,       // dense contraction, fp32 FFMA tiles (exact-f32 fallback)
     IMPL_GEMM_TC,         // dense contraction, tcgen05 TF32 / 3xTF32
@@ -204,6 +205,9 @@ struct Plan {
     bool narrow = false;          // outer reduce with few kept elements: column threads x row lanes
     long long sib_rows = 0, sib_cols = 0;   // IMPL_SIBLINGS: the shared [R, C] operand
     long long pool[4] = {0, 0, 0, 0};       // IMPL_MAXPOOL: planes, H, W, window
+    // IMPL_FOLD_GATHER: the last four iteration dims are (Ho, Wo, KH, KW); output row pitch, window strides / dilations
+    long long fold_pitch = 0;
+    int fold_sh = 0, fold_sw = 0, fold_dh = 0, fold_dw = 0, fold_hout = 0, fold_wout = 0;
     int pool_flags = 0;                     // IMPL_MAXPOOL: 1 = ReLU on the taps, 2 = gradient
     TransposeShape tr;
     int64_t scratch_bytes = 0;
@@ -236,6 +240,7 @@ int launch_ew(Device* dev, const Plan& plan, const KParams& p);
 int launch_reduce(Device* dev, const Plan& plan, const KParams& p, void* scratch, bool finish = true);
 int launch_transpose(Device* dev, const Plan& plan, const void* in, void* out);
 int launch_scatter(Device* dev, const Plan& plan, const KParams& p);
+int launch_fold_gather(Device* dev, const Plan& plan, const KParams& p);
 int launch_sgd(Device* dev, const Plan& plan, const float* p, const float* g, float* out, long long n);
 int launch_sgd_momentum(Device* dev, const Plan& plan, const float* p, const float* g, float* v, float* out, long long n);
 int launch_adam(Device* dev, const Plan& plan, const float* p, const float* g, float* m, float* v, int* t, float* out,

@@ -285,6 +285,91 @@ int launch_scatter(Device* dev, const Plan& plan, const KParams& p) {
     return EB200_OK;
 }
 
+// ---- fold as a gather ---------------------------------------------------------------------
+// The scatter-add above serialises on atomics (a 3x3 fold adds nine terms into every element, from nine different
+// threads).  When the scatter is a fold -- iteration dims (..., Ho, Wo, KH, KW), output element (h, w) =
+// (ho*sh + kh*dh, wo*sw + kw*dw) of a dense plane -- each output element can collect its own terms instead: a thread
+// per output element walks the windows that cover it, largest (kh, kw) first, which is the order of increasing
+// (ho, wo) in which the reference's sequential loop nest adds them (src/lowerer/lower.rs:580-683): the result is
+// bit-identical to that loop, independent of the launch.  Elements of the planes no window reaches (and the rest of
+// the output buffer) keep the zero fill.
+struct FoldParams {
+    int n_outer;
+    unsigned oshape[KMAX_DIMS];
+    long long o_in[KMAX_DIMS], o_out[KMAX_DIMS];
+    unsigned Ho, Wo, KH, KW, sh, sw, dh, dw, hout, wout, total;
+    long long pitch, in_ho, in_wo, in_kh, in_kw, in_off, out_off;
+};
+
+__global__ void __launch_bounds__(256) fold_gather_kernel(const __grid_constant__ FoldParams q, const float* __restrict__ in,
+                                                          float* __restrict__ out) {
+    const unsigned stride = gridDim.x * blockDim.x;
+    for (unsigned e = blockIdx.x * blockDim.x + threadIdx.x; e < q.total; e += stride) {
+        const unsigned t = e / q.wout, w = e - t * q.wout;
+        unsigned o = t / q.hout;
+        const unsigned h = t - o * q.hout;
+        long long ib = q.in_off, ob = q.out_off + (long long)h * q.pitch + w;
+#pragma unroll 1
+        for (int j = q.n_outer - 1; j >= 0; --j) {
+            const unsigned nx = o / q.oshape[j], ix = o - nx * q.oshape[j];
+            ib += (long long)ix * q.o_in[j];
+            ob += (long long)ix * q.o_out[j];
+            o = nx;
+        }
+        float acc = 0.0f;
+        for (int kh = (int)q.KH - 1; kh >= 0; --kh) {
+            const int hh = (int)h - kh * (int)q.dh;
+            if (hh < 0) continue;
+            const unsigned ho = (unsigned)hh / q.sh;
+            if (ho * q.sh != (unsigned)hh || ho >= q.Ho) continue;
+            for (int kw = (int)q.KW - 1; kw >= 0; --kw) {
+                const int ww = (int)w - kw * (int)q.dw;
+                if (ww < 0) continue;
+                const unsigned wo = (unsigned)ww / q.sw;
+                if (wo * q.sw != (unsigned)ww || wo >= q.Wo) continue;
+                acc += __ldg(in + ib + (long long)ho * q.in_ho + (long long)wo * q.in_wo + (long long)kh * q.in_kh + (long long)kw * q.in_kw);
+            }
+        }
+        out[ob] = acc;
+    }
+}
+
+int launch_fold_gather(Device* dev, const Plan& plan, const KParams& p) {
+    const long long cap = (long long)dev->prop.multiProcessorCount * 16;
+    if (plan.out_numel > 0) {
+        long long blocks = (plan.out_numel + 255) / 256;
+        if (blocks > cap) blocks = cap;
+        fill_zero_kernel<<<(unsigned)blocks, 256, 0, dev->stream>>>(reinterpret_cast<float*>(p.out.ptr), plan.out_numel);
+        count_launch();
+        EB_CHECK_CUDA(cudaGetLastError());
+    }
+    if (p.total <= 0) return EB200_OK;
+    const int nk = p.ndim;
+    FoldParams q{};
+    q.n_outer = nk - 4;
+    long long outer = 1;
+    for (int j = 0; j < nk - 4; ++j) {
+        q.oshape[j] = (unsigned)p.shape[j];
+        q.o_in[j] = p.in[0].strides[j];
+        q.o_out[j] = p.out.strides[j];
+        outer *= p.shape[j];
+    }
+    q.Ho = (unsigned)p.shape[nk - 4]; q.Wo = (unsigned)p.shape[nk - 3]; q.KH = (unsigned)p.shape[nk - 2]; q.KW = (unsigned)p.shape[nk - 1];
+    q.in_ho = p.in[0].strides[nk - 4]; q.in_wo = p.in[0].strides[nk - 3]; q.in_kh = p.in[0].strides[nk - 2]; q.in_kw = p.in[0].strides[nk - 1];
+    q.sh = (unsigned)plan.fold_sh; q.sw = (unsigned)plan.fold_sw; q.dh = (unsigned)plan.fold_dh; q.dw = (unsigned)plan.fold_dw;
+    q.hout = (unsigned)plan.fold_hout; q.wout = (unsigned)plan.fold_wout;
+    q.pitch = plan.fold_pitch;
+    q.in_off = p.in[0].offset; q.out_off = p.out.offset;
+    q.total = (unsigned)(outer * q.hout * q.wout);
+    long long blocks = ((long long)q.total + 255) / 256;
+    const long long cap2 = (long long)dev->prop.multiProcessorCount * 32;
+    if (blocks > cap2) blocks = cap2;
+    fold_gather_kernel<<<(unsigned)blocks, 256, 0, dev->stream>>>(q, reinterpret_cast<const float*>(p.in[0].ptr), reinterpret_cast<float*>(p.out.ptr));
+    count_launch();
+    EB_CHECK_CUDA(cudaGetLastError());
+    return EB200_OK;
+}
+
 // ---- SGD ------------------------------------------------------------------------------
 // `out` may be `p` itself (the update runs in place), so neither is __restrict__
 // and p is read with plain loads.

@@ -57,7 +57,7 @@ static void fill_info(const Plan& plan, eb200_kernel_info* info) {
     memset(info, 0, sizeof(*info));
     strncpy(info->impl, plan.name, sizeof(info->impl) - 1);
     info->launches = plan.launches;
-    info->specialised = plan.chain >= 0 || plan.impl == IMPL_TRANSPOSE || plan.impl == IMPL_SCATTER ||
+    info->specialised = plan.chain >= 0 || plan.impl == IMPL_TRANSPOSE || plan.impl == IMPL_SCATTER || plan.impl == IMPL_FOLD_GATHER ||
                         plan.impl == IMPL_SGD || plan.impl == IMPL_SGD_MOMENTUM || plan.impl == IMPL_ADAM || plan.impl == IMPL_SOFTMAX_XENT || plan.impl == IMPL_MAXPOOL || plan.impl == IMPL_GEMM_SIMT || plan.impl == IMPL_GEMM_TC || plan.impl == IMPL_CONV2D || plan.impl == IMPL_GEMM_TALL || plan.impl == IMPL_CONV2D_WGRAD || plan.impl == IMPL_CONV2D_DIRECT || plan.impl == IMPL_CONV2D_DIRECT_WGRAD;
     info->scratch_bytes = plan.scratch_bytes;
     info->algo_bytes = plan.algo_bytes;
@@ -136,6 +136,7 @@ int eb200_kernel_launch(eb200_kernel* k, eb200_buffer* const* inputs, int n_inpu
         }
         case IMPL_TRANSPOSE: return launch_transpose(dev, plan, p.in[0].ptr, p.out.ptr);
         case IMPL_SCATTER: return launch_scatter(dev, plan, p);
+        case IMPL_FOLD_GATHER: return launch_fold_gather(dev, plan, p);
         case IMPL_SGD:
             return launch_sgd(dev, plan, reinterpret_cast<const float*>(p.in[0].ptr) + p.in[0].offset,
                               reinterpret_cast<const float*>(p.in[1].ptr) + p.in[1].offset,

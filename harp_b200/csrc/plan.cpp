@@ -738,6 +738,47 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
             pl.impl = IMPL_SCATTER;
             pl.launches = 2;
             snprintf(pl.name, sizeof(pl.name), "scatter_add");
+            // A fold -- the scatter-add unfold's gradient lowers to (src/grad/rules.rs:40-53): iteration dims
+            // (..., Ho, Wo, KH, KW), the output addressed as h = ho*sh + kh*dh, w = wo*sw + kw*dw inside dense planes --
+            // can be turned around: every output element sums the few windows that cover it.  No atomics, and the
+            // terms are added in the order the reference's sequential loop adds them.
+            if (nk >= 4 && !p.in[0].n_bounds && total < (1LL << 31)) {
+                const long long a = p.out.strides[nk - 4], b = p.out.strides[nk - 3], c = p.out.strides[nk - 2], e = p.out.strides[nk - 1];
+                const long long Ho = shape[nk - 4], Wo = shape[nk - 3], KH = shape[nk - 2], KW = shape[nk - 1];
+                bool ok = a > 0 && b > 0 && c > 0 && e > 0 && KH <= 16 && KW <= 16;
+                long long pitch = 0, sh = 0, dh = 0, wout = 0, hout = 0;
+                if (ok) {
+                    long long x = a, y = c;
+                    while (y) { const long long t = x % y; x = y; y = t; }
+                    pitch = x;                                   // gcd(a, c): the row pitch of the output planes
+                    sh = a / pitch; dh = c / pitch;
+                    wout = b * (Wo - 1) + e * (KW - 1) + 1;
+                    hout = sh * (Ho - 1) + dh * (KH - 1) + 1;
+                    ok = wout <= pitch && hout < (1LL << 20) && wout < (1LL << 20) && b < (1LL << 20) && e < (1LL << 20) &&
+                         sh < (1LL << 20) && dh < (1LL << 20);
+                }
+                // the dims in front of the windows address disjoint planes
+                if (ok) {
+                    int order[KMAX_DIMS], m = 0;
+                    for (int j = 0; j < nk - 4; ++j) if (shape[j] > 1) order[m++] = j;
+                    std::sort(order, order + m, [&](int u, int v) { return p.out.strides[u] < p.out.strides[v]; });
+                    long long span = hout * pitch;
+                    for (int j = 0; j < m && ok; ++j) {
+                        ok = p.out.strides[order[j]] >= span;
+                        span = p.out.strides[order[j]] * shape[order[j]];
+                    }
+                    long long outer = 1;
+                    for (int j = 0; j < nk - 4; ++j) outer *= shape[j];
+                    ok = ok && outer * hout * wout < (1LL << 31);
+                }
+                if (ok) {
+                    pl.impl = IMPL_FOLD_GATHER;
+                    pl.fold_pitch = pitch;
+                    pl.fold_sh = (int)sh; pl.fold_dh = (int)dh; pl.fold_sw = (int)b; pl.fold_dw = (int)e;
+                    pl.fold_hout = (int)hout; pl.fold_wout = (int)wout;
+                    snprintf(pl.name, sizeof(pl.name), "scatter_add_as_gather");
+                }
+            }
             break;
         }
         case EB200_K_COPY:

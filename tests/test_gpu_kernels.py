@@ -536,14 +536,50 @@ def test_gemm_misaligned_layout_stays_on_f32_kernel(dev):
 # ---- scatter / sgd ---------------------------------------------------------------------------------
 
 def test_scatter_add_overlapping_windows(dev):
-    # fold of 3x3 stride-1 windows over [2,4,9,9] -> overlapping accumulation
+    # fold of 3x3 stride-1 windows over [2,4,9,9] -> overlapping accumulation; served as a gather over the output,
+    # which adds the terms in the order of the reference's sequential loop nest: bit-identical to the plain C oracle
     n, c, h = 2, 4, 9
     oh = h - 2
     cols = rnd([n, c, oh, oh, 3, 3], 26)
     out = D.Operand([c * h * h, h * h, h, 1, h, 1], 0, D.F32, n * c * h * h)
     k = D.KernelDesc(D.K_SCATTER, list(cols.shape), [D.contiguous(cols.shape)], out)
-    got, _ = run_gpu(dev, k, [cols])
-    assert_close(got, O.run(k, [cols]), rel=1e-5, abs_tol=1e-5)
+    got, kern = run_gpu(dev, k, [cols])
+    assert kern.impl == "scatter_add_as_gather"
+    assert got.tobytes() == O.run(k, [cols]).tobytes()
+
+
+@pytest.mark.parametrize("case", ["pool_odd_plane", "permuted_input", "strided_dilated", "one_plane"])
+def test_fold_as_gather_matches_the_sequential_loop_bit_for_bit(dev, case):
+    from harp_b200.frontend import View
+    if case == "pool_odd_plane":        # 2x2 windows, stride 2, over 11x11 planes: row and column 10 stay zero
+        src_shape, dst_shape, uf = [3, 5, 5, 5, 2, 2], [3, 5, 11, 11], ([2, 3], [2, 2], [2, 2], [1, 1])
+        src = D.contiguous(src_shape)
+    elif case == "permuted_input":      # the [n, ho, wo, c, kh, kw] rows a convolution-as-GEMM produces
+        src_shape, dst_shape, uf = [4, 6, 11, 11, 3, 3], [4, 6, 13, 13], ([2, 3], [3, 3], [1, 1], [1, 1])
+        src = D.Operand([11 * 11 * 6 * 9, 9, 11 * 6 * 9, 6 * 9, 3, 1], 0, D.F32, int(np.prod(src_shape)))
+    elif case == "strided_dilated":     # stride 3, dilation 2: gaps no window reaches
+        src_shape, dst_shape, uf = [2, 3, 4, 5, 2, 3], [2, 3, 12, 17], ([2, 3], [2, 3], [3, 3], [2, 2])
+        src = D.contiguous(src_shape)
+    else:
+        src_shape, dst_shape, uf = [1, 1, 30, 30, 3, 3], [1, 1, 32, 32], ([2, 3], [3, 3], [1, 1], [1, 1])
+        src = D.contiguous(src_shape)
+    x = rnd([int(np.prod(src_shape))], 77)
+    dst = View.contiguous(dst_shape).unfold(*uf)
+    assert list(dst.shape) == src_shape
+    k = D.KernelDesc(D.K_SCATTER, src_shape, [src], dst.operand(int(np.prod(dst_shape)), D.F32), None)
+    got, kern = run_gpu(dev, k, [x])
+    assert kern.impl == "scatter_add_as_gather" and kern.launches == 2
+    assert got.tobytes() == O.run(k, [x]).tobytes()
+
+
+def test_scatter_that_is_not_a_fold_keeps_the_atomic_kernel(dev):
+    # planes that overlap each other (stride 5 between planes of 9 elements): no output element owns its terms
+    x = rnd([6, 2, 2, 2, 2], 78)
+    out = D.Operand([5, 3, 1, 3, 1], 0, D.F32, 40)
+    k = D.KernelDesc(D.K_SCATTER, [6, 2, 2, 2, 2], [D.contiguous([6, 2, 2, 2, 2])], out)
+    got, kern = run_gpu(dev, k, [x])
+    assert kern.impl == "scatter_add"
+    assert_close(got, O.run(k, [x]), rel=1e-5, abs_tol=1e-5)
 
 
 @pytest.mark.parametrize("n", [1, 5, 4096, 225034])

@@ -123,7 +123,7 @@ def test_cfg4_cnn_step_matches_oracle(dev, registry):
         return [loss] + grads, None
     g, o, pg, po = both(build, dev, registry)
     impls = {k.impl.split("_v")[0] for _, _, k, _ in pg.kernels}
-    assert "scatter_add" in impls and any(i.startswith("gemm") for i in impls)
+    assert "scatter_add_as_gather" in impls and any(i.startswith("gemm") for i in impls)
     assert abs(float(g[0]) - float(o[0])) <= 1e-5 * abs(float(o[0]))
     for a, b in zip(g[1:], o[1:]):
         scale = np.abs(b).max() + 1e-12
