@@ -293,11 +293,26 @@ int launch_scatter(Device* dev, const Plan& plan, const KParams& p) {
 // (ho, wo) in which the reference's sequential loop nest adds them (src/lowerer/lower.rs:580-683): the result is
 // bit-identical to that loop, independent of the launch.  Elements of the planes no window reaches (and the rest of
 // the output buffer) keep the zero fill.
+struct FastDiv {                 // exact n / d for n < 2^31: (n * mul) >> shr, with mul = ceil(2^(31+l) / d), l = ceil(log2 d)
+    unsigned d, mul, shr;
+};
+static FastDiv make_fastdiv(unsigned d) {
+    FastDiv f;
+    f.d = d ? d : 1;
+    int l = 0;
+    while ((1ULL << l) < f.d) ++l;
+    f.mul = (unsigned)((((1ULL << (31 + l)) + f.d - 1) / f.d));
+    f.shr = (unsigned)(31 + l);
+    return f;
+}
+__device__ __forceinline__ unsigned fdiv(unsigned n, const FastDiv& f) { return (unsigned)(((unsigned long long)n * f.mul) >> f.shr); }
+
 struct FoldParams {
     int n_outer;
-    unsigned oshape[KMAX_DIMS];
+    FastDiv oshape[KMAX_DIMS];
     long long o_in[KMAX_DIMS], o_out[KMAX_DIMS];
-    unsigned Ho, Wo, KH, KW, sh, sw, dh, dw, hout, wout, total;
+    FastDiv hout, wout, sh, sw;
+    unsigned Ho, Wo, KH, KW, dh, dw, total;
     long long pitch, in_ho, in_wo, in_kh, in_kw, in_off, out_off;
 };
 
@@ -305,13 +320,13 @@ __global__ void __launch_bounds__(256) fold_gather_kernel(const __grid_constant_
                                                           float* __restrict__ out) {
     const unsigned stride = gridDim.x * blockDim.x;
     for (unsigned e = blockIdx.x * blockDim.x + threadIdx.x; e < q.total; e += stride) {
-        const unsigned t = e / q.wout, w = e - t * q.wout;
-        unsigned o = t / q.hout;
-        const unsigned h = t - o * q.hout;
+        const unsigned t = fdiv(e, q.wout), w = e - t * q.wout.d;
+        unsigned o = fdiv(t, q.hout);
+        const unsigned h = t - o * q.hout.d;
         long long ib = q.in_off, ob = q.out_off + (long long)h * q.pitch + w;
 #pragma unroll 1
         for (int j = q.n_outer - 1; j >= 0; --j) {
-            const unsigned nx = o / q.oshape[j], ix = o - nx * q.oshape[j];
+            const unsigned nx = fdiv(o, q.oshape[j]), ix = o - nx * q.oshape[j].d;
             ib += (long long)ix * q.o_in[j];
             ob += (long long)ix * q.o_out[j];
             o = nx;
@@ -320,14 +335,15 @@ __global__ void __launch_bounds__(256) fold_gather_kernel(const __grid_constant_
         for (int kh = (int)q.KH - 1; kh >= 0; --kh) {
             const int hh = (int)h - kh * (int)q.dh;
             if (hh < 0) continue;
-            const unsigned ho = (unsigned)hh / q.sh;
-            if (ho * q.sh != (unsigned)hh || ho >= q.Ho) continue;
+            const unsigned ho = fdiv((unsigned)hh, q.sh);
+            if (ho * q.sh.d != (unsigned)hh || ho >= q.Ho) continue;
+            const long long rb = ib + (long long)ho * q.in_ho + (long long)kh * q.in_kh;
             for (int kw = (int)q.KW - 1; kw >= 0; --kw) {
                 const int ww = (int)w - kw * (int)q.dw;
                 if (ww < 0) continue;
-                const unsigned wo = (unsigned)ww / q.sw;
-                if (wo * q.sw != (unsigned)ww || wo >= q.Wo) continue;
-                acc += __ldg(in + ib + (long long)ho * q.in_ho + (long long)wo * q.in_wo + (long long)kh * q.in_kh + (long long)kw * q.in_kw);
+                const unsigned wo = fdiv((unsigned)ww, q.sw);
+                if (wo * q.sw.d != (unsigned)ww || wo >= q.Wo) continue;
+                acc += __ldg(in + rb + (long long)wo * q.in_wo + (long long)kw * q.in_kw);
             }
         }
         out[ob] = acc;
@@ -349,18 +365,18 @@ int launch_fold_gather(Device* dev, const Plan& plan, const KParams& p) {
     q.n_outer = nk - 4;
     long long outer = 1;
     for (int j = 0; j < nk - 4; ++j) {
-        q.oshape[j] = (unsigned)p.shape[j];
+        q.oshape[j] = make_fastdiv((unsigned)p.shape[j]);
         q.o_in[j] = p.in[0].strides[j];
         q.o_out[j] = p.out.strides[j];
         outer *= p.shape[j];
     }
     q.Ho = (unsigned)p.shape[nk - 4]; q.Wo = (unsigned)p.shape[nk - 3]; q.KH = (unsigned)p.shape[nk - 2]; q.KW = (unsigned)p.shape[nk - 1];
     q.in_ho = p.in[0].strides[nk - 4]; q.in_wo = p.in[0].strides[nk - 3]; q.in_kh = p.in[0].strides[nk - 2]; q.in_kw = p.in[0].strides[nk - 1];
-    q.sh = (unsigned)plan.fold_sh; q.sw = (unsigned)plan.fold_sw; q.dh = (unsigned)plan.fold_dh; q.dw = (unsigned)plan.fold_dw;
-    q.hout = (unsigned)plan.fold_hout; q.wout = (unsigned)plan.fold_wout;
+    q.sh = make_fastdiv((unsigned)plan.fold_sh); q.sw = make_fastdiv((unsigned)plan.fold_sw); q.dh = (unsigned)plan.fold_dh; q.dw = (unsigned)plan.fold_dw;
+    q.hout = make_fastdiv((unsigned)plan.fold_hout); q.wout = make_fastdiv((unsigned)plan.fold_wout);
     q.pitch = plan.fold_pitch;
     q.in_off = p.in[0].offset; q.out_off = p.out.offset;
-    q.total = (unsigned)(outer * q.hout * q.wout);
+    q.total = (unsigned)(outer * plan.fold_hout * plan.fold_wout);
     long long blocks = ((long long)q.total + 255) / 256;
     const long long cap2 = (long long)dev->prop.multiProcessorCount * 32;
     if (blocks > cap2) blocks = cap2;

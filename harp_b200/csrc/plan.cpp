@@ -754,7 +754,7 @@ int build_plan(const eb200_kernel_desc* d, int sm_count, Plan* plan) {
                     sh = a / pitch; dh = c / pitch;
                     wout = b * (Wo - 1) + e * (KW - 1) + 1;
                     hout = sh * (Ho - 1) + dh * (KH - 1) + 1;
-                    ok = wout <= pitch && hout < (1LL << 20) && wout < (1LL << 20) && b < (1LL << 20) && e < (1LL << 20) &&
+                    ok = wout <= pitch && hout < (1LL << 30) && wout < (1LL << 30) && b < (1LL << 20) && e < (1LL << 20) &&
                          sh < (1LL << 20) && dh < (1LL << 20);
                 }
                 // the dims in front of the windows address disjoint planes

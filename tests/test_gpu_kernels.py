@@ -548,7 +548,7 @@ def test_scatter_add_overlapping_windows(dev):
     assert got.tobytes() == O.run(k, [cols]).tobytes()
 
 
-@pytest.mark.parametrize("case", ["pool_odd_plane", "permuted_input", "strided_dilated", "one_plane"])
+@pytest.mark.parametrize("case", ["pool_odd_plane", "permuted_input", "strided_dilated", "one_plane", "many_planes_merged"])
 def test_fold_as_gather_matches_the_sequential_loop_bit_for_bit(dev, case):
     from harp_b200.frontend import View
     if case == "pool_odd_plane":        # 2x2 windows, stride 2, over 11x11 planes: row and column 10 stay zero
@@ -559,6 +559,9 @@ def test_fold_as_gather_matches_the_sequential_loop_bit_for_bit(dev, case):
         src = D.Operand([11 * 11 * 6 * 9, 9, 11 * 6 * 9, 6 * 9, 3, 1], 0, D.F32, int(np.prod(src_shape)))
     elif case == "strided_dilated":     # stride 3, dilation 2: gaps no window reaches
         src_shape, dst_shape, uf = [2, 3, 4, 5, 2, 3], [2, 3, 12, 17], ([2, 3], [2, 3], [3, 3], [2, 2])
+        src = D.contiguous(src_shape)
+    elif case == "many_planes_merged":  # even planes of non-overlapping windows collapse into ONE plane of 1 M rows
+        src_shape, dst_shape, uf = [262200, 1, 2, 2, 2, 2], [262200, 1, 4, 4], ([2, 3], [2, 2], [2, 2], [1, 1])
         src = D.contiguous(src_shape)
     else:
         src_shape, dst_shape, uf = [1, 1, 30, 30, 3, 3], [1, 1, 32, 32], ([2, 3], [3, 3], [1, 1], [1, 1])
