@@ -548,20 +548,20 @@ def test_scatter_add_overlapping_windows(dev):
     assert got.tobytes() == O.run(k, [cols]).tobytes()
 
 
-@pytest.mark.parametrize("case", ["pool_odd_plane", "permuted_input", "strided_dilated", "one_plane", "many_planes_merged"])
+@pytest.mark.parametrize("case", ["overlap_rows_only", "permuted_input", "strided_dilated", "one_plane", "many_planes_merged"])
 def test_fold_as_gather_matches_the_sequential_loop_bit_for_bit(dev, case):
     from harp_b200.frontend import View
-    if case == "pool_odd_plane":        # 2x2 windows, stride 2, over 11x11 planes: row and column 10 stay zero
-        src_shape, dst_shape, uf = [3, 5, 5, 5, 2, 2], [3, 5, 11, 11], ([2, 3], [2, 2], [2, 2], [1, 1])
+    if case == "overlap_rows_only":     # 3x2 windows, stride 2: rows overlap, columns do not; row 11 / column 10 stay zero
+        src_shape, dst_shape, uf = [3, 5, 5, 5, 3, 2], [3, 5, 12, 11], ([2, 3], [3, 2], [2, 2], [1, 1])
         src = D.contiguous(src_shape)
     elif case == "permuted_input":      # the [n, ho, wo, c, kh, kw] rows a convolution-as-GEMM produces
         src_shape, dst_shape, uf = [4, 6, 11, 11, 3, 3], [4, 6, 13, 13], ([2, 3], [3, 3], [1, 1], [1, 1])
         src = D.Operand([11 * 11 * 6 * 9, 9, 11 * 6 * 9, 6 * 9, 3, 1], 0, D.F32, int(np.prod(src_shape)))
-    elif case == "strided_dilated":     # stride 3, dilation 2: gaps no window reaches
+    elif case == "strided_dilated":     # stride 3, dilation 2 (columns overlap, some rows no window reaches)
         src_shape, dst_shape, uf = [2, 3, 4, 5, 2, 3], [2, 3, 12, 17], ([2, 3], [2, 3], [3, 3], [2, 2])
         src = D.contiguous(src_shape)
-    elif case == "many_planes_merged":  # even planes of non-overlapping windows collapse into ONE plane of 1 M rows
-        src_shape, dst_shape, uf = [262200, 1, 2, 2, 2, 2], [262200, 1, 4, 4], ([2, 3], [2, 2], [2, 2], [1, 1])
+    elif case == "many_planes_merged":  # row-disjoint windows over planes that collapse into ONE plane of 1 M rows
+        src_shape, dst_shape, uf = [262200, 1, 2, 2, 2, 3], [262200, 1, 4, 5], ([2, 3], [2, 3], [2, 2], [1, 1])
         src = D.contiguous(src_shape)
     else:
         src_shape, dst_shape, uf = [1, 1, 30, 30, 3, 3], [1, 1, 32, 32], ([2, 3], [3, 3], [1, 1], [1, 1])
@@ -572,6 +572,18 @@ def test_fold_as_gather_matches_the_sequential_loop_bit_for_bit(dev, case):
     k = D.KernelDesc(D.K_SCATTER, src_shape, [src], dst.operand(int(np.prod(dst_shape)), D.F32), None)
     got, kern = run_gpu(dev, k, [x])
     assert kern.impl == "scatter_add_as_gather" and kern.launches == 2
+    assert got.tobytes() == O.run(k, [x]).tobytes()
+
+
+def test_fold_of_disjoint_windows_keeps_the_atomic_kernel(dev):
+    # a pooling gradient: 2x2 windows, stride 2, over 11x11 planes -- at most one term per element, exact in any order
+    from harp_b200.frontend import View
+    src_shape, dst_shape = [3, 5, 5, 5, 2, 2], [3, 5, 11, 11]
+    x = rnd([int(np.prod(src_shape))], 79)
+    dst = View.contiguous(dst_shape).unfold([2, 3], [2, 2], [2, 2], [1, 1])
+    k = D.KernelDesc(D.K_SCATTER, src_shape, [D.contiguous(src_shape)], dst.operand(int(np.prod(dst_shape)), D.F32), None)
+    got, kern = run_gpu(dev, k, [x])
+    assert kern.impl == "scatter_add"
     assert got.tobytes() == O.run(k, [x]).tobytes()
 
 
