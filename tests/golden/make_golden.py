@@ -62,6 +62,18 @@ def cases():
     prog = Program([loss] + loss.backward([x, wt, b]), _Null(), fuse="reference")
     for i, d in enumerate(prog.kernel_descs()):
         out.append((f"conv2d_pad1_step_{i:02d}_{d.name}", "crates/nn/src/functional/conv.rs:113-184 + src/grad/rules.rs", d))
+    # 16-bit storage types as the C backend declares them (crates/backend-c/src/renderer.rs:129-130)
+    h8, b8 = D.contiguous([8], D.F16), D.contiguous([8], D.BF16)
+    out.append(("add_f16", "crates/backend-c/src/renderer.rs:129 (_Float16)", D.KernelDesc(D.K_ELEMENTWISE, [8], [h8, h8], D.contiguous([8], D.F16), w(0) + w(1))))
+    out.append(("sum_bf16_into_f32", "crates/backend-c/src/renderer.rs:130 (__bf16), src/lowerer/loop_gen.rs:87-151",
+                D.reduce([4, 8], [D.contiguous([4, 8], D.BF16)], w(0), D.R_SUM, 1)))
+    # max_pool2d as functional::max_pool2d composes it (crates/nn/src/functional/pool.rs:117-160) and its gradient
+    xp = Tensor.input([[[[float((i * 7 + j * 3) % 5) for j in range(4)] for i in range(4)]]], requires_grad=True)
+    yp = xp.max_pool2d_unfold(2)
+    lp = (yp * yp).sum()
+    prog = Program([lp] + lp.backward([xp]), _Null(), fuse="reference")
+    for i, d in enumerate(prog.kernel_descs()):
+        out.append((f"max_pool2d_step_{i:02d}_{d.name}", "crates/nn/src/functional/pool.rs:117-160 + src/grad/rules.rs", d))
     # config 2 as three realizes at the reference's fusion level
     rows, cols = 8, 16
     xt = Tensor.input([[float(i * cols + j) * 0.01 for j in range(cols)] for i in range(rows)])

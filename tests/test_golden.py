@@ -68,9 +68,14 @@ def test_golden_kernels_on_the_gpu(dev):
     for it in _items():
         d = D.KernelDesc.from_json(it["desc"])
         ins = [rng.uniform(0.5, 1.5, int(o.numel)).astype(np.float32) for o in d.inputs]
+        ins = [D.bf16_bits(a) if o.dtype == D.BF16 else a.astype(np.float16) if o.dtype == D.F16 else a for a, o in zip(ins, d.inputs)]
         got, kern = run_gpu(dev, d, ins)
         ref = O.run(d, ins)
         if d.kclass == D.K_COPY or d.reduce_op in (D.R_MAX, D.R_MIN):
             assert got.tobytes() == ref.tobytes(), it["name"]
+        elif d.output.dtype in (D.F16, D.BF16):      # one unit in the last place of the stored type
+            g = (D.bf16_value(got) if d.output.dtype == D.BF16 else got).astype(np.float64)
+            r = (D.bf16_value(ref) if d.output.dtype == D.BF16 else ref).astype(np.float64)
+            assert (np.abs(g - r) <= 2.0 ** (-7 if d.output.dtype == D.BF16 else -10) * np.abs(r)).all(), it["name"]
         else:
             assert np.allclose(got, ref, rtol=2e-5, atol=1e-6), (it["name"], kern.impl, float(np.abs(got - ref).max()))
