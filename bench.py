@@ -329,6 +329,12 @@ def run_b200(args):
     t_y = sum(e[0].elapsed_ms(e[1]) for e in evs.values()) / ns
     t_z = sum(e[1].elapsed_ms(e[2]) for e in evs.values()) / ns
     t_t = sum(e[2].elapsed_ms(e[3]) for e in evs.values()) / ns
+    # the same three kernels each on its own (20 launches back to back, outside the timed region): inside the
+    # step a kernel also pays for the dirty L2 lines its predecessor left behind
+    alone_ms = {}
+    if n == 1:                # (with several ranks the column reduce may carry its collective: never launched by one rank alone)
+        for name, kern_, ins_, out_ in (("y_fused_row_sum", ky, [b0, bx, b1], by), ("z_col_max", kz, [bx], bz), ("t_transpose", kt, [bx], bt)):
+            alone_ms[name] = time_kernel(dev, kern_, ins_, [out_], reps=20, warm=3)
 
     # ---- end-to-end: host buffers in, host buffers out, every step --------------------
     # Double-buffered: the upload of batch i+1, the kernels of batch i and the
@@ -431,6 +437,9 @@ def run_b200(args):
                               ("t_transpose", kt.impl, BYTES_T, t_t)):
         gbs = b / (ms * 1e-3) / 1e9
         kernels[name] = {"impl": impl, "ms": ms, "algo_bytes": b, "achieved_gbs": gbs, "frac_of_" + peak_kind: gbs / peak}
+        if name in alone_ms:
+            kernels[name]["alone_ms"] = alone_ms[name]
+            kernels[name]["alone_frac_of_" + peak_kind] = b / (alone_ms[name] * 1e-3) / 1e9 / peak
     top = max(kernels.items(), key=lambda kv: kv[1]["ms"])
     traffic = NCU_TRAFFIC.get("transpose_copy" if top[0] == "t_transpose" else
                               ("reduce_outer" if top[0] == "z_col_max" else "reduce_inner"))
