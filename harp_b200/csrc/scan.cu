@@ -12,7 +12,7 @@
 // sequence semantics is what is served here:
 //
 //  scan_rows    many rows: a warp (rows up to 1024 elements) or a 256-thread CTA
-//               per row walks it in chunks of 4 elements per thread: thread-local
+//               per row walks it in chunks of 16 elements per thread: thread-local
 //               scan, warp shuffle scan, cross-warp offsets through shared
 //               memory, a running carry between chunks.  8 B per element
 //               (one read, one write): HBM-bound.
@@ -99,21 +99,27 @@ __device__ __forceinline__ float scan_segment(const KParams& p, const float* cl,
     if (p.vec == 4) {
         decompose(p, row * p.rlen, ridx);          // index of the row's first element; the tail dim is 0
     }
-    for (long long chunk = pos0; chunk < pos1; chunk += (long long)T * 4) {
-        const long long my = chunk + (long long)lane * 4;
-        float x[4];
+    // SV vectors of four consecutive elements per thread and chunk: one thread-local scan of 4 * SV elements, ONE
+    // shuffle scan and one pair of block barriers per chunk (the kernels are bound by their instruction stream),
+    // SV independent 128-bit loads in flight
+    constexpr int SV = 4, PER = 4 * SV;
+    for (long long chunk = pos0; chunk < pos1; chunk += (long long)T * PER) {
+        const long long my = chunk + (long long)lane * PER;
+        float x[PER];
         if (p.vec == 4) {
-            if (my < pos1) scan_vec4<F>(p, ridx, my, cl, x);          // rlen and tile bounds are multiples of 4
-            else { x[0] = ident; x[1] = ident; x[2] = ident; x[3] = ident; }
+#pragma unroll
+            for (int v = 0; v < SV; ++v) {
+                if (my + 4 * v < pos1) scan_vec4<F>(p, ridx, my + 4 * v, cl, x + 4 * v);          // rlen and tile bounds are multiples of 4
+                else { x[4 * v] = ident; x[4 * v + 1] = ident; x[4 * v + 2] = ident; x[4 * v + 3] = ident; }
+            }
         } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) x[j] = my + j < pos1 ? scan_elem<F>(p, row * p.rlen + my + j, cl) : ident;
+            for (int j = 0; j < PER; ++j) x[j] = my + j < pos1 ? scan_elem<F>(p, row * p.rlen + my + j, cl) : ident;
         }
-        x[1] = scan_comb<ROP>(rop, x[0], x[1]);
-        x[2] = scan_comb<ROP>(rop, x[1], x[2]);
-        x[3] = scan_comb<ROP>(rop, x[2], x[3]);
+#pragma unroll
+        for (int j = 1; j < PER; ++j) x[j] = scan_comb<ROP>(rop, x[j - 1], x[j]);
         // inclusive scan of the thread totals across the warp
-        float incl = x[3];
+        float incl = x[PER - 1];
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
             const float t = __shfl_up_sync(0xffffffffu, incl, o);
@@ -143,11 +149,16 @@ __device__ __forceinline__ float scan_segment(const KParams& p, const float* cl,
             const float base = scan_comb<ROP>(rop, carry, excl);
             if (p.vec == 4) {
                 float* o = reinterpret_cast<float*>(p.out.ptr) + operand_index(p, p.out, ridx) + my;
-                *reinterpret_cast<float4*>(o) = make_float4(scan_comb<ROP>(rop, base, x[0]), scan_comb<ROP>(rop, base, x[1]),
-                                                            scan_comb<ROP>(rop, base, x[2]), scan_comb<ROP>(rop, base, x[3]));
+#pragma unroll
+                for (int v = 0; v < SV; ++v) {
+                    if (my + 4 * v < pos1)
+                        *reinterpret_cast<float4*>(o + 4 * v) =
+                            make_float4(scan_comb<ROP>(rop, base, x[4 * v]), scan_comb<ROP>(rop, base, x[4 * v + 1]),
+                                        scan_comb<ROP>(rop, base, x[4 * v + 2]), scan_comb<ROP>(rop, base, x[4 * v + 3]));
+                }
             } else {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < PER; ++j) {
                     if (my + j >= pos1) break;
                     long long idx[KMAX_DIMS];
                     decompose(p, row * p.rlen + my + j, idx);
