@@ -239,6 +239,97 @@ __global__ void __launch_bounds__(256, (F::kSpecial || H16) ? 4 : 1) ew_kernel(c
     }
 }
 
+// ---- flat kernels over 16-bit storage: eight elements per thread ---------------------------------------
+// With f16 / bf16 operands a vector of four elements is 8 bytes: the four-wide kernel above runs out of issue
+// slots (index arithmetic and loop control per vector) at 0.66 of the copy bandwidth.  For the flat case (one
+// collapsed dim, every operand unit-stride or broadcast, 16-byte aligned) a thread takes eight elements: one
+// 128-bit load per 16-bit operand, two per f32 operand, one 128-bit store of eight 16-bit results.
+template <class F>
+__global__ void __launch_bounds__(256, 4) ew16x8_kernel(const __grid_constant__ KParams p) {
+    constexpr int U = F::kSpecial ? 1 : 2;
+    constexpr int NI = F::kCompiled ? F::kNin : KMAX_IN;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const int n = F::nin(p);
+    float cl[F::kNconst];
+    load_consts<F>(p, cl);
+    const long long nvec = p.total >> 3;
+    for (long long v0 = ((long long)blockIdx.x * U) * blockDim.x + threadIdx.x; v0 < nvec; v0 += U * stride) {
+        float lo[U][NI][4], hi[U][NI][4];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long long v = v0 + (long long)u * blockDim.x;
+            if (v >= nvec) break;
+            const long long e = v << 3;
+#pragma unroll
+            for (int i = 0; i < NI; ++i) {
+                if (i >= n) break;
+                const KOperand& o = p.in[i];
+                if (o.strides[0] == 0) {
+                    lo[u][i][0] = load_elem(o, o.offset);
+                } else if (o.dtype == EB200_F32) {
+                    const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(o.ptr) + o.offset + e);
+                    const float4 a = __ldg(src), b = __ldg(src + 1);
+                    lo[u][i][0] = a.x; lo[u][i][1] = a.y; lo[u][i][2] = a.z; lo[u][i][3] = a.w;
+                    hi[u][i][0] = b.x; hi[u][i][1] = b.y; hi[u][i][2] = b.z; hi[u][i][3] = b.w;
+                } else {        // raw bits now, widened below (no dependent instruction between the loads)
+                    const uint4 t = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(o.ptr) + o.offset + e));
+                    lo[u][i][0] = __uint_as_float(t.x); lo[u][i][1] = __uint_as_float(t.y);
+                    lo[u][i][2] = __uint_as_float(t.z); lo[u][i][3] = __uint_as_float(t.w);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long long v = v0 + (long long)u * blockDim.x;
+            if (v >= nvec) break;
+#pragma unroll
+            for (int i = 0; i < NI; ++i) {
+                if (i >= n) break;
+                const KOperand& o = p.in[i];
+                if (o.strides[0] == 0) {
+                    const float t = lo[u][i][0];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) { lo[u][i][j] = t; hi[u][i][j] = t; }
+                } else if (o.dtype != EB200_F32) {
+                    unsigned w4[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) w4[j] = __float_as_uint(lo[u][i][j]);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float a, b;
+                        if (o.dtype == EB200_F16) {
+                            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w4[j]));
+                            a = f.x; b = f.y;
+                        } else {
+                            a = __uint_as_float(w4[j] << 16); b = __uint_as_float(w4[j] & 0xffff0000u);
+                        }
+                        if (j < 2) { lo[u][i][2 * j] = a; lo[u][i][2 * j + 1] = b; }
+                        else { hi[u][i][2 * (j - 2)] = a; hi[u][i][2 * (j - 2) + 1] = b; }
+                    }
+                }
+            }
+            float r[8];
+            F::template eval<4>(p, lo[u], r, cl);
+            F::template eval<4>(p, hi[u], r + 4, cl);
+            const long long e = v << 3;
+            if (p.out.dtype == EB200_F32) {
+                float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out.ptr) + p.out.offset + e);
+                dst[0] = make_float4(r[0], r[1], r[2], r[3]);
+                dst[1] = make_float4(r[4], r[5], r[6], r[7]);
+            } else {
+                uint4 t;
+                unsigned* tw = reinterpret_cast<unsigned*>(&t);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (p.out.dtype == EB200_F16) *reinterpret_cast<__half2*>(&tw[j]) = __floats2half2_rn(r[2 * j], r[2 * j + 1]);
+                    else *reinterpret_cast<__nv_bfloat162*>(&tw[j]) = __floats2bfloat162_rn(r[2 * j], r[2 * j + 1]);
+                }
+                *reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(p.out.ptr) + p.out.offset + e) = t;
+            }
+        }
+    }
+}
+
 template <class F>
 static int launch_one(Device* dev, const KParams& p) {
     long long work = p.vec == 1 ? p.total : (p.total >> 2);
@@ -260,7 +351,20 @@ static int launch_one(Device* dev, const KParams& p) {
     if (p.vec == 2 && nd == 1) nd = 0;      // (rank 1 never plans groups of four; keep the switch total)
     const unsigned g = (unsigned)blocks;
     if (h16) {
-        if (nd == 1) ew_kernel<F, 1, true><<<g, 256, 0, dev->stream>>>(p);
+        // flat, a multiple of eight elements, every operand 16-byte aligned: eight elements per thread
+        bool wide = nd == 1 && (p.total & 7) == 0;
+        for (int i = 0; wide && i <= p.n_in; ++i) {
+            const KOperand& o = i < p.n_in ? p.in[i] : p.out;
+            if (o.strides[0] == 0 && i < p.n_in) continue;
+            const int esz = o.dtype == EB200_F32 ? 4 : 2;
+            wide = (o.dtype == EB200_F32 || o.dtype == EB200_F16 || o.dtype == EB200_BF16) && o.strides[0] == 1 &&
+                   ((reinterpret_cast<uintptr_t>(o.ptr) + (uintptr_t)o.offset * esz) & 15) == 0;
+        }
+        if (wide) {
+            const long long nv8 = p.total >> 3, per8 = 256LL * (F::kSpecial ? 1 : 2);
+            const long long b8 = std::min<long long>((nv8 + per8 - 1) / per8, cap);
+            ew16x8_kernel<F><<<(unsigned)b8, 256, 0, dev->stream>>>(p);
+        } else if (nd == 1) ew_kernel<F, 1, true><<<g, 256, 0, dev->stream>>>(p);
         else ew_kernel<F, 0, true><<<g, 256, 0, dev->stream>>>(p);
     } else
     switch (nd) {
