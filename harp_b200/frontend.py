@@ -407,8 +407,15 @@ class Tensor:
 
     def tanh(self):
         # 2*sigmoid(2x) - 1, the mathematically intended form of
-        # crates/nn/src/functional/activation.rs:70-76 (whose scale() is a no-op)
-        return (self * 2.0).sigmoid() * 2.0 - 1.0
+        # crates/nn/src/functional/activation.rs:70-76 (whose scale() is a no-op).
+        # Gradient from the OUTPUT, d tanh = 1 - tanh^2 (as recip and exp above use theirs): differentiating
+        # through the composite would recompute exp and the reciprocal in every backward kernel, which are
+        # bound by those special functions, not by memory; the output is materialised anyway (the next
+        # layer's contraction reads it).
+        x = Tensor(self.node, self.view)                       # detached: one gradient rule for the whole function
+        out = (x * 2.0).sigmoid() * 2.0 - 1.0
+        o = Tensor(out.node, out.view)
+        return self._track(out, (self, lambda g: g * ((o * o) * -1.0 + 1.0)))
 
     # ---- the reference's own spellings, quirks included ----
     # What eclat's Tensor API really builds for these functions (graph-level
