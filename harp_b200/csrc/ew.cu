@@ -107,12 +107,15 @@ __device__ __forceinline__ void store_vec4(const KParams& p, long long e, const 
 // rather than more work per thread.
 // (16-bit operands move half the bytes per vector; their kernels are built for four CTAs per SM as well, so that
 // twice the threads keep the same bytes in flight.)
-template <class F, bool H16>
-constexpr int ew_u() { return F::kSpecial ? 2 : EW_U; }
+// Kernels of rank 2 and more spend most of their instructions on index arithmetic per vector (broadcast rows and
+// columns, strided operands): they, too, do better with more resident warps than with more vectors per thread
+// (a [65536, 256] kernel with two broadcast operands: 42.8 us with four vectors and 2-3 CTAs per SM).
+template <class F, bool H16, int ND = 1>
+constexpr int ew_u() { return (F::kSpecial || ND != 1) ? 2 : EW_U; }
 
 template <class F, int ND, bool H16>
-__global__ void __launch_bounds__(256, (F::kSpecial || H16) ? 4 : 1) ew_kernel(const __grid_constant__ KParams p) {
-    constexpr int U = ew_u<F, H16>();
+__global__ void __launch_bounds__(256, (F::kSpecial || H16 || ND != 1) ? 4 : 1) ew_kernel(const __grid_constant__ KParams p) {
+    constexpr int U = ew_u<F, H16, ND>();
     const long long stride = (long long)gridDim.x * blockDim.x;
     const int n = F::nin(p);
     float cl[F::kNconst];
@@ -340,15 +343,17 @@ static int launch_one(Device* dev, const KParams& p) {
         for (int i = 0; i < p.n_in; ++i) h16 = h16 || p.in[i].dtype == EB200_F16 || p.in[i].dtype == EB200_BF16;
         h16 = h16 || p.out.dtype == EB200_F16 || p.out.dtype == EB200_BF16;
     }
-    long long per_block = 256LL * (p.vec == 2 ? 2 : (h16 ? ew_u<F, true>() : ew_u<F, false>()));
-    long long blocks = (work + per_block - 1) / per_block;
-    long long cap = (long long)dev->prop.multiProcessorCount * 32;
-    if (blocks > cap) blocks = cap;
     // ranks 1-4 have their own instantiation; scalar kernels of rank 5 and 6 share the rank-6 one
     // (dims past the rank have extent 1 and stride 0); everything else takes the any-rank form
     int nd = 0;
     if (p.total < (1LL << 31)) nd = p.ndim <= 4 ? p.ndim : (p.ndim <= 6 && p.vec != 4 ? 6 : 0);
     if (p.vec == 2 && nd == 1) nd = 0;      // (rank 1 never plans groups of four; keep the switch total)
+    if (h16 && nd != 1) nd = 0;
+    const int u = (F::kSpecial || nd != 1) ? 2 : EW_U;      // ew_u<F, H16, ND>() of the instantiation that will run
+    long long per_block = 256LL * (p.vec == 2 ? 2 : u);
+    long long blocks = (work + per_block - 1) / per_block;
+    long long cap = (long long)dev->prop.multiProcessorCount * 32;
+    if (blocks > cap) blocks = cap;
     const unsigned g = (unsigned)blocks;
     if (h16) {
         // flat, a multiple of eight elements, every operand 16-byte aligned: eight elements per thread
