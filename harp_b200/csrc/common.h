@@ -206,6 +206,7 @@ struct Plan {
     long long sib_rows = 0, sib_cols = 0;   // IMPL_SIBLINGS: the shared [R, C] operand
     long long pool[4] = {0, 0, 0, 0};       // IMPL_MAXPOOL: planes, H, W, window
     // IMPL_FOLD_GATHER: the last four iteration dims are (Ho, Wo, KH, KW); output row pitch, window strides / dilations
+    int scatter_plain = 0;                  // IMPL_SCATTER: the windows are disjoint, stores instead of atomic adds
     long long fold_pitch = 0;
     int fold_sh = 0, fold_sw = 0, fold_dh = 0, fold_dw = 0, fold_hout = 0, fold_wout = 0;
     int pool_flags = 0;                     // IMPL_MAXPOOL: 1 = ReLU on the taps, 2 = gradient

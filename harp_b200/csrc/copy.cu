@@ -252,7 +252,10 @@ __global__ void __launch_bounds__(256) fill_zero_kernel(float* __restrict__ out,
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) out[i] = 0.0f;
 }
 
-__global__ void __launch_bounds__(256) scatter_add_kernel(const __grid_constant__ KParams p) {
+// PLAIN: the planner has shown that no two iteration points address the same output element (a fold of disjoint
+// windows): the zero fill plus one add is a store of v + 0 (the + 0 keeps the sign of a zero term as the add would).
+template <bool PLAIN>
+__global__ void __launch_bounds__(256, 4) scatter_add_kernel(const __grid_constant__ KParams p) {
     const long long stride = (long long)gridDim.x * blockDim.x;
     float* out = reinterpret_cast<float*>(p.out.ptr);
     for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < p.total; e += stride) {
@@ -262,7 +265,8 @@ __global__ void __launch_bounds__(256) scatter_add_kernel(const __grid_constant_
         float v;
         if (o.n_bounds && !bounds_ok(p, o, idx)) v = o.pad;
         else v = load_elem(o, operand_index(p, o, idx));
-        atomicAdd(out + operand_index(p, p.out, idx), v);
+        if (PLAIN) out[operand_index(p, p.out, idx)] = v + 0.0f;
+        else atomicAdd(out + operand_index(p, p.out, idx), v);
     }
 }
 
@@ -278,7 +282,8 @@ int launch_scatter(Device* dev, const Plan& plan, const KParams& p) {
     if (p.total > 0) {
         long long blocks = (p.total + 255) / 256;
         if (blocks > cap) blocks = cap;
-        scatter_add_kernel<<<(unsigned)blocks, 256, 0, dev->stream>>>(p);
+        if (plan.scatter_plain) scatter_add_kernel<true><<<(unsigned)blocks, 256, 0, dev->stream>>>(p);
+        else scatter_add_kernel<false><<<(unsigned)blocks, 256, 0, dev->stream>>>(p);
         count_launch();
         EB_CHECK_CUDA(cudaGetLastError());
     }
